@@ -1,0 +1,358 @@
+"""ctypes bindings for the CPU oracle.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke()`` and by the CPU
+baseline / reference arm of ``bench.py``. The product package (``flexllm_b200``) never imports it.
+
+Two libraries:
+
+* ``liboracle.so`` (``oracle/flexllm_oracle.cpp``) -- plain-C++ restatement of the reference's
+  operator templates; functions ``orc_*``; exposed here as module-level functions.
+* ``_ref/libflexllm_ref.so`` (``oracle/ref_wrap.cpp``) -- the reference's own templates compiled
+  through the header shim; functions ``ref_*``; exposed through :data:`ref` when the file exists.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "liboracle.so")
+_REF = os.path.join(_HERE, "_ref", "libflexllm_ref.so")
+
+
+def build(verbose=False):
+    """Compile the oracle libraries with the Makefile beside this file."""
+    r = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("oracle build failed:\n" + r.stdout + r.stderr)
+    if verbose:
+        print(r.stdout)
+
+
+def _load(path):
+    if not os.path.exists(path):
+        return None
+    return C.CDLL(path)
+
+
+if not os.path.exists(_LIB):
+    build()
+_lib = _load(_LIB)
+_ref = _load(_REF)
+
+
+def _p(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i8(a):
+    return np.ascontiguousarray(a, dtype=np.int8)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+# ------------------------------------------------------------------ Tier B (restatement)
+def quant_per_token(x):
+    x = _f32(x); M, K = x.shape
+    q = np.empty((M, K), np.int8); s = np.empty(M, np.float32)
+    _lib.orc_quant_per_token(_p(x), C.c_int(M), C.c_int(K), _p(q), _p(s))
+    return q, s
+
+
+def gemm_s8s8(a, w):
+    a = _i8(a); w = _i8(w); M, K = a.shape; N = w.shape[0]
+    acc = np.empty((M, N), np.int32)
+    _lib.orc_gemm_s8s8(_p(a), _p(w), C.c_int(M), C.c_int(N), C.c_int(K), _p(acc))
+    return acc
+
+
+def gemm_u8s8(a, w):
+    a = np.ascontiguousarray(a, dtype=np.uint8); w = _i8(w); M, K = a.shape; N = w.shape[0]
+    acc = np.empty((M, N), np.int32)
+    _lib.orc_gemm_u8s8(_p(a), _p(w), C.c_int(M), C.c_int(N), C.c_int(K), _p(acc))
+    return acc
+
+
+def dequant(acc, s_tok, s_ch):
+    acc = _i32(acc); M, N = acc.shape
+    y = np.empty((M, N), np.float32)
+    _lib.orc_dequant(_p(acc), _p(_f32(s_tok)), _p(_f32(s_ch)), C.c_int(M), C.c_int(N), _p(y))
+    return y
+
+
+def fht(x, scale):
+    x = _f32(x); N = x.shape[-1]; rows = x.size // N
+    y = np.empty_like(x)
+    _lib.orc_fht(_p(x), C.c_long(rows), C.c_int(N), C.c_float(scale), _p(y))
+    return y
+
+
+def rope_table(P):
+    c = np.empty((P, 32), np.float32); s = np.empty((P, 32), np.float32)
+    _lib.orc_rope_table(C.c_int(P), _p(c), _p(s))
+    return c, s
+
+
+def rope(x, pos, cos_t, sin_t):
+    """x [T,H,64] fp32, pos [T] int32."""
+    x = _f32(x); T, H, D = x.shape; assert D == 64
+    pos = _i32(pos)
+    y = np.empty_like(x)
+    _lib.orc_rope(_p(x), _p(pos), _p(_f32(cos_t)), _p(_f32(sin_t)), C.c_long(T), C.c_int(H), _p(y))
+    return y
+
+
+def softmax(x, valid=None):
+    x = _f32(x); L = x.shape[-1]; rows = x.size // L
+    p = np.empty_like(x)
+    v = None if valid is None else _i32(valid)
+    _lib.orc_softmax(_p(x), C.c_long(rows), C.c_int(L), _p(v), _p(p))
+    return p
+
+
+def rmsnorm(x, gamma, eps=1e-5, lanes=0):
+    x = _f32(x); M, D = x.shape
+    y = np.empty_like(x)
+    _lib.orc_rmsnorm(_p(x), _p(_f32(gamma)), C.c_int(M), C.c_int(D), C.c_float(eps), C.c_int(lanes), _p(y))
+    return y
+
+
+def silu(g):
+    g = _f32(g); y = np.empty_like(g)
+    _lib.orc_silu(_p(g), C.c_long(g.size), _p(y))
+    return y
+
+
+def silu_mul(g, u):
+    g = _f32(g); u = _f32(u); y = np.empty_like(g)
+    _lib.orc_silu_mul(_p(g), _p(u), C.c_long(g.size), _p(y))
+    return y
+
+
+def residual(a, b):
+    a = _f32(a); b = _f32(b); y = np.empty_like(a)
+    _lib.orc_residual(_p(a), _p(b), C.c_long(a.size), _p(y))
+    return y
+
+
+def static_quant(x, s, f=1.0, signed=True):
+    """x [rows,n]; s scalar or [rows]. Returns int8 (signed) or uint8."""
+    x = _f32(x); rows, n = x.shape
+    s = _f32(np.atleast_1d(s)); stride = 0 if s.size == 1 else 1
+    q = np.empty((rows, n), np.uint8)
+    _lib.orc_static_quant(_p(x), C.c_long(rows), C.c_int(n), _p(s), C.c_int(stride), C.c_float(f),
+                          C.c_int(1 if signed else 0), _p(q))
+    return q.view(np.int8) if signed else q
+
+
+def argmax(logits):
+    logits = _f32(logits); B, V = logits.shape
+    idx = np.empty(B, np.int32)
+    _lib.orc_argmax(_p(logits), C.c_int(B), C.c_long(V), _p(idx))
+    return idx
+
+
+def linear_i8(a, s_tok, w, s_ch):
+    a = _i8(a); w = _i8(w); M, K = a.shape; N = w.shape[0]
+    acc = np.empty((M, N), np.int32); y = np.empty((M, N), np.float32)
+    _lib.orc_linear_i8(_p(a), _p(_f32(s_tok)), _p(w), _p(_f32(s_ch)), C.c_int(M), C.c_int(N), C.c_int(K),
+                       _p(acc), _p(y))
+    return acc, y
+
+
+def mlp_block(h, gamma, wg, sg, wu, su, wd, sd, eps=1e-5, lanes=0, fht_scale=90.50966799):
+    """Returns dict(out, xq, xs, act, hq, hs, down_acc)."""
+    h = _f32(h); M, D = h.shape; F = wg.shape[0]
+    r = dict(out=np.empty((M, D), np.float32), xq=np.empty((M, D), np.int8), xs=np.empty(M, np.float32),
+             act=np.empty((M, F), np.float32), hq=np.empty((M, F), np.int8), hs=np.empty(M, np.float32),
+             down_acc=np.empty((M, D), np.int32))
+    _lib.orc_mlp_block(_p(h), _p(_f32(gamma)), _p(_i8(wg)), _p(_f32(sg)), _p(_i8(wu)), _p(_f32(su)),
+                       _p(_i8(wd)), _p(_f32(sd)), C.c_int(M), C.c_int(D), C.c_int(F), C.c_float(eps),
+                       C.c_int(lanes), C.c_float(fht_scale), _p(r["out"]), _p(r["xq"]), _p(r["xs"]),
+                       _p(r["act"]), _p(r["hq"]), _p(r["hs"]), _p(r["down_acc"]))
+    return r
+
+
+def qk_prepare(q, s, pos, cos_t, sin_t):
+    """q [T,H,64] int8, s [T,H]; returns (q2 int8, s2, rotated fp32)."""
+    q = _i8(q); T, H, D = q.shape; assert D == 64
+    q2 = np.empty_like(q); s2 = np.empty((T, H), np.float32); rot = np.empty((T, H, 64), np.float32)
+    _lib.orc_qk_prepare(_p(q), _p(_f32(s)), _p(_i32(pos)), _p(_f32(cos_t)), _p(_f32(sin_t)),
+                        C.c_long(T), C.c_int(H), _p(q2), _p(s2), _p(rot))
+    return q2, s2, rot
+
+
+def mha_prefill(q, qs, k, ks, v, vs, cos_t, sin_t, a_s):
+    """q [B,S,HQ,64] s8, qs [B,S,HQ]; k,v [B,S,HKV,64]; returns dict(out, q2, qs2, k2, ks2, oacc)."""
+    q = _i8(q); k = _i8(k); v = _i8(v)
+    B, S, HQ, _ = q.shape; HKV = k.shape[2]
+    r = dict(out=np.empty((B, S, HQ * 64), np.float32), q2=np.empty_like(q), qs2=np.empty((B, S, HQ), np.float32),
+             k2=np.empty_like(k), ks2=np.empty((B, S, HKV), np.float32), oacc=np.empty((B, S, HQ * 64), np.int32))
+    _lib.orc_mha_prefill(_p(q), _p(_f32(qs)), _p(k), _p(_f32(ks)), _p(v), _p(_f32(vs)), _p(_f32(cos_t)),
+                         _p(_f32(sin_t)), _p(_f32(a_s)), C.c_int(B), C.c_int(S), C.c_int(HQ), C.c_int(HKV),
+                         _p(r["out"]), _p(r["q2"]), _p(r["qs2"]), _p(r["k2"]), _p(r["ks2"]), _p(r["oacc"]))
+    return r
+
+
+def mha_decode(q, qs, k, ks, v, vs, cos_t, sin_t, a_s, k_pool, ks_pool, v_pool, vs_pool, page_table, ctx):
+    """One decode step; pools are modified in place (append). Returns (out [B,HQ*64], oacc)."""
+    q = _i8(q); B, HQ, _ = q.shape; HKV = k.shape[1]
+    n_pages, HKV2, PAGE, _ = k_pool.shape; assert HKV2 == HKV
+    for a in (k_pool, ks_pool, v_pool, vs_pool):
+        assert a.flags["C_CONTIGUOUS"]
+    page_table = _i32(page_table); ctx = _i32(ctx)
+    out = np.empty((B, HQ * 64), np.float32); oacc = np.empty((B, HQ * 64), np.int32)
+    _lib.orc_mha_decode(_p(q), _p(_f32(qs)), _p(_i8(k)), _p(_f32(ks)), _p(_i8(v)), _p(_f32(vs)),
+                        _p(_f32(cos_t)), _p(_f32(sin_t)), _p(_f32(a_s)), _p(k_pool), _p(ks_pool), _p(v_pool),
+                        _p(vs_pool), _p(page_table), C.c_int(page_table.shape[1]), _p(ctx), C.c_int(B),
+                        C.c_int(HQ), C.c_int(HKV), C.c_int(PAGE), _p(out), _p(oacc))
+    return out, oacc
+
+
+def attn_row(q, qs, k, ks, v, vs, a_s):
+    """One attention row; returns dict(out[64], oacc[64], p[nk] u8, score[nk])."""
+    k = _i8(k); nk = k.shape[0]
+    r = dict(out=np.empty(64, np.float32), oacc=np.empty(64, np.int32), p=np.empty(nk, np.uint8),
+             score=np.empty(nk, np.float32))
+    _lib.orc_attn_row(_p(_i8(q)), C.c_float(qs), _p(k), _p(_f32(ks)), _p(_i8(v)), _p(_f32(vs)), C.c_int(nk),
+                      C.c_float(a_s), _p(r["out"]), _p(r["oacc"]), _p(r["p"]), _p(r["score"]))
+    return r
+
+
+# ------------------------------------------------------------------ Tier A (reference templates)
+class _Ref:
+    """The reference's own operator templates (available only where oracle/_ref was built)."""
+
+    def __init__(self, lib):
+        self.lib = lib
+
+    def quant_per_token(self, x, decode=False):
+        x = _f32(x); M, K = x.shape
+        q = np.empty((M, K), np.int8); s = np.empty(M, np.float32)
+        fn = self.lib.ref_dec_quant_per_token if decode else self.lib.ref_quant_per_token
+        fn(_p(x), C.c_int(M), C.c_int(K), _p(q), _p(s))
+        return q, s
+
+    def dequant(self, acc, s_tok, s_ch):
+        acc = _i32(acc); M, N = acc.shape; y = np.empty((M, N), np.float32)
+        self.lib.ref_dequant(_p(acc), _p(_f32(s_tok)), _p(_f32(s_ch)), C.c_int(M), C.c_int(N), _p(y))
+        return y
+
+    def gemm_s8s8(self, a, w):
+        a = _i8(a); w = _i8(w); M, K = a.shape; N = w.shape[0]; acc = np.empty((M, N), np.int32)
+        self.lib.ref_gemm_s8s8(_p(a), _p(w), C.c_int(M), C.c_int(N), C.c_int(K), _p(acc))
+        return acc
+
+    def gemm_u8s8(self, a, w):
+        a = np.ascontiguousarray(a, dtype=np.uint8); w = _i8(w); M, K = a.shape; N = w.shape[0]
+        acc = np.empty((M, N), np.int32)
+        self.lib.ref_gemm_u8s8(_p(a), _p(w), C.c_int(M), C.c_int(N), C.c_int(K), _p(acc))
+        return acc
+
+    def fht(self, x, scale, decode=False):
+        x = _f32(x); N = x.shape[-1]; rows = x.size // N; y = np.empty_like(x)
+        fn = self.lib.ref_dec_fht if decode else self.lib.ref_fht
+        rc = fn(_p(x), C.c_long(rows), C.c_int(N), C.c_float(scale), _p(y))
+        assert rc == 0
+        return y
+
+    def rope_prefill(self, x, cos_t, sin_t):
+        x = _f32(x); S, H, _ = x.shape; y = np.empty_like(x)
+        rc = self.lib.ref_rope_prefill(_p(x), _p(_f32(cos_t)), _p(_f32(sin_t)), C.c_int(S), C.c_int(H), _p(y))
+        assert rc == 0
+        return y
+
+    def rope_decode(self, x, cos_t, sin_t, pos):
+        x = _f32(x); H, _ = x.shape; y = np.empty_like(x); cos_t = _f32(cos_t)
+        rc = self.lib.ref_rope_decode(_p(x), _p(cos_t), _p(_f32(sin_t)), C.c_int(cos_t.shape[0]), C.c_int(pos),
+                                      C.c_int(H), _p(y))
+        assert rc == 0
+        return y
+
+    def softmax_prefill(self, x, causal):
+        x = _f32(x); S, L = x.shape; p = np.empty_like(x)
+        rc = self.lib.ref_softmax_prefill(_p(x), C.c_int(S), C.c_int(L), C.c_int(1 if causal else 0), _p(p))
+        assert rc == 0
+        return p
+
+    def softmax_decode(self, x):
+        x = _f32(x); p = np.empty_like(x)
+        rc = self.lib.ref_softmax_decode(_p(x), C.c_int(x.size), _p(p))
+        assert rc == 0
+        return p
+
+    def rmsnorm(self, x, gamma, lanes=0):
+        x = _f32(x); M, D = x.shape; y = np.empty_like(x)
+        if lanes == 0:
+            self.lib.ref_rmsnorm_prefill(_p(x), _p(_f32(gamma)), C.c_int(M), C.c_int(D), _p(y))
+        else:
+            rc = self.lib.ref_rmsnorm_decode(_p(x), _p(_f32(gamma)), C.c_int(M), C.c_int(D), C.c_int(lanes), _p(y))
+            assert rc == 0
+        return y
+
+    def silu(self, g):
+        g = _f32(g); y = np.empty_like(g)
+        self.lib.ref_silu(_p(g), C.c_long(g.size), _p(y))
+        return y
+
+    def gate_mul(self, a, b):
+        a = _f32(a); b = _f32(b); y = np.empty_like(a)
+        self.lib.ref_gate_mul(_p(a), _p(b), C.c_long(a.size), _p(y))
+        return y
+
+    def residual(self, a, b):
+        a = _f32(a); b = _f32(b); y = np.empty_like(a)
+        self.lib.ref_residual(_p(a), _p(b), C.c_long(a.size), _p(y))
+        return y
+
+    def static_quant(self, x, s, f=1.0, signed=True):
+        x = _f32(x); rows, n = x.shape; q = np.empty((rows, n), np.uint8)
+        self.lib.ref_static_quant(_p(x), C.c_long(rows), C.c_int(n), C.c_float(s), C.c_float(f),
+                                  C.c_int(1 if signed else 0), _p(q))
+        return q.view(np.int8) if signed else q
+
+    def scale_stream_quant(self, x, s, signed=True):
+        x = _f32(x); rows, n = x.shape; q = np.empty((rows, n), np.uint8)
+        self.lib.ref_scale_stream_quant(_p(x), C.c_long(rows), C.c_int(n), _p(_f32(s)), C.c_int(1 if signed else 0), _p(q))
+        return q.view(np.int8) if signed else q
+
+    def scale_stream_dequant(self, acc, s_row, s_col):
+        acc = _i32(acc); M, N = acc.shape; y = np.empty((M, N), np.float32)
+        self.lib.ref_scale_stream_dequant(_p(acc), _p(_f32(s_row)), _p(_f32(s_col)), C.c_int(M), C.c_int(N), _p(y))
+        return y
+
+    def head_quant(self, x):
+        x = _f32(x); H, _ = x.shape; q = np.empty((H, 64), np.int8); s = np.empty(H, np.float32)
+        self.lib.ref_head_quant(_p(x), C.c_int(H), _p(q), _p(s))
+        return q, s
+
+    def mha_qxk(self, q, k):
+        q = _i8(q); k = _i8(k); S, G, _ = q.shape; acc = np.empty((S, G, S), np.int32)
+        rc = self.lib.ref_mha_qxk(_p(q), _p(k), C.c_int(S), C.c_int(G), _p(acc))
+        assert rc == 0
+        return acc
+
+    def mha_axv(self, p, v):
+        p = np.ascontiguousarray(p, dtype=np.uint8); v = _i8(v); S, G, _ = p.shape
+        acc = np.empty((S, G, 64), np.int32)
+        rc = self.lib.ref_mha_axv(_p(p), _p(v), C.c_int(S), C.c_int(G), _p(acc))
+        assert rc == 0
+        return acc
+
+    def argmax(self, logits):
+        logits = _f32(logits); B, V = logits.shape; idx = np.empty(B, np.int32)
+        self.lib.ref_argmax(_p(logits), C.c_int(B), C.c_long(V), _p(idx))
+        return idx
+
+
+ref = _Ref(_ref) if _ref is not None else None
