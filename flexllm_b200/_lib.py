@@ -1,0 +1,47 @@
+"""Loads libflexllm_b200.so and declares the C ABI of include/flexllm_b200.h for ctypes."""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libflexllm_b200.so")
+
+OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM = 0, -1, -2, -3, -4, -5
+
+# name -> argument types, in the order of include/flexllm_b200.h (return type is int unless noted)
+_P, _I, _L, _F, _SZ = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_size_t
+SIGNATURES = {
+    "flexllm_version": [],
+    "flexllm_last_cuda_error": [],
+    "flexllm_linear_prefill_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_linear_decode_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_quant_per_token": [_P, _I, _I, _P, _P, _P],
+    "flexllm_dequant": [_P, _P, _P, _I, _I, _P, _P],
+    "flexllm_static_quant": [_P, _L, _I, _P, _I, _F, _I, _P, _P],
+    "flexllm_fht": [_P, _L, _I, _F, _P, _P],
+    "flexllm_rope": [_P, _P, _P, _P, _L, _I, _P, _P],
+    "flexllm_softmax": [_P, _L, _I, _P, _P, _P],
+    "flexllm_rmsnorm_quant": [_P, _P, _I, _I, _F, _I, _P, _P, _P, _P],
+    "flexllm_swish": [_P, _L, _P, _P],
+    "flexllm_gate": [_P, _P, _L, _P, _P],
+    "flexllm_residual": [_P, _P, _L, _P, _P],
+    "flexllm_swiglu_fht_quant": [_P, _P, _I, _I, _F, _P, _P, _P, _P],
+    "flexllm_logits_argmax": [_P, _I, _L, _P, _P],
+    "flexllm_qk_prepare": [_P, _P, _P, _P, _P, _L, _I, _P, _P, _P],
+}
+RESTYPES = {"flexllm_status_string": C.c_char_p}
+
+
+def load():
+    """Returns the ctypes handle. Raises if the library has not been built: there is no fallback."""
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m flexllm_b200.build` "
+            "(flexllm_b200 has no CPU or PyTorch fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = RESTYPES.get(name, C.c_int)
+    lib.flexllm_status_string.argtypes = [C.c_int]
+    lib.flexllm_status_string.restype = C.c_char_p
+    return lib

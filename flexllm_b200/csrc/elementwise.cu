@@ -1,0 +1,383 @@
+// Row-wise and elementwise operators of the quantized Llama path: per-token quantisation, dequant,
+// static quantisation, RMSNorm(+quant), SiLU, gate, residual, RoPE, softmax, greedy argmax.
+// All are HBM-bound: one pass over the data with 128-bit accesses where the layout allows.
+#include "common.cuh"
+
+namespace flexllm {
+
+thread_local int g_last_cuda_error = 0;
+
+// ---------------------------------------------------------------------------------------------
+// Per-token symmetric int8 quantisation (Modules/quant.h:6-112, symmetric branch).
+// One CTA per row; the row stays in registers between the max/min pass and the rounding pass.
+// ---------------------------------------------------------------------------------------------
+template <int VPT>  // float4 vectors per thread
+__global__ void __launch_bounds__(256) quant_per_token_kernel(const float* __restrict__ x, int K,
+                                                              int8_t* __restrict__ q, float* __restrict__ s) {
+    __shared__ float red[64];
+    const long row = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * K);
+    const int nv = K >> 2;
+    float4 v[VPT];
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        int c = threadIdx.x + i * 256;
+        if (c < nv) {
+            v[i] = xr[c];
+            mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            mn = fminf(mn, fminf(fminf(v[i].x, v[i].y), fminf(v[i].z, v[i].w)));
+        }
+    }
+    block_max_min(mx, mn, red);
+    const float sc = sym_scale_from(mx, mn);
+    if (threadIdx.x == 0) s[row] = sc;
+    char4* qr = reinterpret_cast<char4*>(q + row * K);
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        int c = threadIdx.x + i * 256;
+        if (c < nv) {
+            char4 o;
+            o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc);
+            o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+            qr[c] = o;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Dequant (Modules/quant.h:151): y = ((float)acc * s_tok[m]) * s_ch[n]
+// ---------------------------------------------------------------------------------------------
+__global__ void dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ s_tok,
+                               const float* __restrict__ s_ch, int M, int N, float* __restrict__ y) {
+    const long nv = (long)M * (N >> 2);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+        int m = (int)(i / (N >> 2)), c = (int)(i % (N >> 2));
+        int4 a = reinterpret_cast<const int4*>(acc)[i];
+        float4 w = reinterpret_cast<const float4*>(s_ch)[c];
+        float st = s_tok[m];
+        float4 o;
+        o.x = ((float)a.x * st) * w.x; o.y = ((float)a.y * st) * w.y;
+        o.z = ((float)a.z * st) * w.z; o.w = ((float)a.w * st) * w.w;
+        reinterpret_cast<float4*>(y)[i] = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Static symmetric quantisation (Modules/quant.h:252-295, :166-211)
+// ---------------------------------------------------------------------------------------------
+__global__ void static_quant_kernel(const float* __restrict__ x, long rows, int n, const float* __restrict__ s,
+                                    int s_stride, float f, int is_signed, uint8_t* __restrict__ q) {
+    const long total = rows * n;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        long r = i / n;
+        float d = f * s[r * s_stride];
+        int v = (int)roundf(x[i] / d);
+        if (is_signed) v = v > 127 ? 127 : (v < -128 ? -128 : v);
+        else v = v > 255 ? 255 : v;
+        q[i] = (uint8_t)v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm (+ optional per-token int8 quant). One warp per row.
+// Sum of squares follows the reference order exactly:
+//   prefill (LayerNorm.h:82-114): 4 chains j = k mod 4 over the whole row, (p0+p1)+(p2+p3);
+//   decode  (LayerNorm.h:263-300): `lanes` contiguous chunks, 4 chains inside each, chunk totals
+//                                  added from 0 in chunk order.
+// Chains are strictly sequential fp32 additions, so each chain is owned by one thread.
+// ---------------------------------------------------------------------------------------------
+template <int MAXV>  // float4 per lane kept in registers for the output pass (D <= MAXV*128)
+__global__ void __launch_bounds__(128) rmsnorm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                            int M, int D, float eps, int lanes, float* __restrict__ y,
+                                                            int8_t* __restrict__ q, float* __restrict__ s) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    const float* xr = x + (long)warp * D;
+    float tot;
+    if (lanes == 0) {
+        float ss = 0.0f;
+        if (lane < 4) {
+            const int n = D >> 2;
+#pragma unroll 8
+            for (int k = 0; k < n; k++) { float v = xr[4 * k + lane]; ss += v * v; }
+        }
+        float p0 = __shfl_sync(0xffffffffu, ss, 0), p1 = __shfl_sync(0xffffffffu, ss, 1);
+        float p2 = __shfl_sync(0xffffffffu, ss, 2), p3 = __shfl_sync(0xffffffffu, ss, 3);
+        tot = (p0 + p1) + (p2 + p3);
+    } else {
+        // lanes*4 <= 32 chains: lane = chunk*4 + j
+        const int C = D / lanes;
+        float ss = 0.0f;
+        const int chunk = lane >> 2, j = lane & 3;
+        if (chunk < lanes) {
+            const float* xc = xr + chunk * C;
+            const int n = C >> 2;
+#pragma unroll 8
+            for (int k = 0; k < n; k++) { float v = xc[4 * k + j]; ss += v * v; }
+        }
+        tot = 0.0f;
+        for (int c = 0; c < lanes; c++) {
+            float p0 = __shfl_sync(0xffffffffu, ss, c * 4 + 0), p1 = __shfl_sync(0xffffffffu, ss, c * 4 + 1);
+            float p2 = __shfl_sync(0xffffffffu, ss, c * 4 + 2), p3 = __shfl_sync(0xffffffffu, ss, c * 4 + 3);
+            tot += (p0 + p1) + (p2 + p3);
+        }
+    }
+    const float r = 1.0f / sqrtf(tot / (float)D + eps);
+
+    const int nv = D >> 2;
+    float4 o[MAXV];
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+        int c = lane + i * 32;
+        if (c < nv) {
+            float4 v = reinterpret_cast<const float4*>(xr)[c];
+            float4 g = reinterpret_cast<const float4*>(gamma)[c];
+            o[i].x = (v.x * r) * g.x; o[i].y = (v.y * r) * g.y; o[i].z = (v.z * r) * g.z; o[i].w = (v.w * r) * g.w;
+            if (y) reinterpret_cast<float4*>(y + (long)warp * D)[c] = o[i];
+            mx = fmaxf(mx, fmaxf(fmaxf(o[i].x, o[i].y), fmaxf(o[i].z, o[i].w)));
+            mn = fminf(mn, fminf(fminf(o[i].x, o[i].y), fminf(o[i].z, o[i].w)));
+        }
+    }
+    if (q) {
+        mx = warp_max(mx); mn = warp_min(mn);
+        const float sc = sym_scale_from(mx, mn);
+        if (lane == 0) s[warp] = sc;
+        char4* qr = reinterpret_cast<char4*>(q + (long)warp * D);
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            int c = lane + i * 32;
+            if (c < nv) {
+                char4 w;
+                w.x = quant_s8(o[i].x, sc); w.y = quant_s8(o[i].y, sc); w.z = quant_s8(o[i].z, sc); w.w = quant_s8(o[i].w, sc);
+                qr[c] = w;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SiLU / gate / residual (Swish.h:19, Linear_Layer.h:626, Residual_Layer.h:61)
+// ---------------------------------------------------------------------------------------------
+template <int OP>  // 0 silu, 1 mul, 2 add
+__global__ void eltwise_kernel(const float* __restrict__ a, const float* __restrict__ b, long n, float* __restrict__ y) {
+    const long nv = n >> 2;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+        float4 u = reinterpret_cast<const float4*>(a)[i];
+        float4 o;
+        if (OP == 0) { o.x = silu_f(u.x); o.y = silu_f(u.y); o.z = silu_f(u.z); o.w = silu_f(u.w); }
+        else {
+            float4 v = reinterpret_cast<const float4*>(b)[i];
+            if (OP == 1) { o.x = u.x * v.x; o.y = u.y * v.y; o.z = u.z * v.z; o.w = u.w * v.w; }
+            else { o.x = u.x + v.x; o.y = u.y + v.y; o.z = u.z + v.z; o.w = u.w + v.w; }
+        }
+        reinterpret_cast<float4*>(y)[i] = o;
+    }
+    // tail
+    for (long i = (nv << 2) + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        if (OP == 0) y[i] = silu_f(a[i]);
+        else if (OP == 1) y[i] = a[i] * b[i];
+        else y[i] = a[i] + b[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE by table (RoPE.h:61-90): one warp per (token, head); lane k holds x[k] and x[k+32].
+// ---------------------------------------------------------------------------------------------
+__global__ void rope_kernel(const float* __restrict__ x, const int32_t* __restrict__ pos, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, long T, int H, float* __restrict__ y) {
+    const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= T * H) return;
+    const long t = w / H;
+    const int p = pos[t];
+    const float c = cos_t[(long)p * 32 + lane], sn = sin_t[(long)p * 32 + lane];
+    const float x0 = x[w * 64 + lane], x1 = x[w * 64 + 32 + lane];
+    y[w * 64 + lane] = x0 * c - x1 * sn;
+    y[w * 64 + 32 + lane] = x0 * sn + x1 * c;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Softmax (Softmax.h:25-161 / :474-634): one warp per row. exp values are written to p first,
+// then lanes 0..3 run the four sequential chains k = j mod 4, then every lane scales.
+// ---------------------------------------------------------------------------------------------
+__global__ void softmax_kernel(const float* __restrict__ x, long rows, int len, const int32_t* __restrict__ valid,
+                               float* __restrict__ p) {
+    const long row = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* xr = x + row * len;
+    float* pr = p + row * len;
+    const int nvld = valid ? valid[row] : len;
+    float mx = -1e32f;
+    for (int k = lane; k < len; k += 32) {
+        float v = k < nvld ? xr[k] : -1e32f;
+        mx = v > mx ? v : mx;
+    }
+    mx = warp_max(mx);
+    for (int k = lane; k < len; k += 32) {
+        float v = k < nvld ? xr[k] : -1e32f;
+        pr[k] = ref_expf(v - mx);
+    }
+    __syncwarp();
+    float ps = 0.0f;
+    if (lane < 4) {
+#pragma unroll 8
+        for (int k = lane; k < len; k += 4) ps += pr[k];
+    }
+    float p0 = __shfl_sync(0xffffffffu, ps, 0), p1 = __shfl_sync(0xffffffffu, ps, 1);
+    float p2 = __shfl_sync(0xffffffffu, ps, 2), p3 = __shfl_sync(0xffffffffu, ps, 3);
+    const float r = 1.0f / ((p0 + p1) + (p2 + p3));
+    for (int k = lane; k < len; k += 32) pr[k] = pr[k] * r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Greedy argmax, ties to the lowest index (Logits.h:13-17 strict '>'). One CTA per row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, long V, int32_t* __restrict__ idx) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* l = logits + (long)blockIdx.x * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (long v = threadIdx.x; v < V; v += blockDim.x) {
+        float t = l[v];
+        if (t > best || bi == 0x7fffffff) { best = t; bi = (int)v; }   // strided scan visits increasing v
+    }
+    auto better = [](float a, int ai, float b, int bi2) { return a > b || (a == b && ai < bi2); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ob, oi, best, bi)) { best = ob; bi = oi; }
+    }
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ob, oi, best, bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) idx[blockIdx.x] = bi;
+    }
+}
+
+static inline int grid_for(long n, int block, int cap = 148 * 16) {
+    long g = (n + block - 1) / block;
+    if (g < 1) g = 1;
+    return (int)(g > cap ? cap : g);
+}
+
+}  // namespace flexllm
+
+using namespace flexllm;
+
+extern "C" int flexllm_version(void) { return 100; }
+
+extern "C" const char* flexllm_status_string(int st) {
+    switch (st) {
+        case FLEXLLM_OK: return "ok";
+        case FLEXLLM_EINVAL: return "invalid argument";
+        case FLEXLLM_ECUDA: return "CUDA error";
+        case FLEXLLM_ETIMEDOUT: return "device wait timed out";
+        case FLEXLLM_ENOTSUP: return "unsupported shape";
+        case FLEXLLM_ENOMEM: return "out of memory";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int flexllm_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, float* s, void* stream) {
+    FLEXLLM_REQUIRE(x && q && s && M >= 0 && K > 0 && (K % 4) == 0 && K <= 8192);
+    FLEXLLM_REQUIRE(aligned(x, 16) && aligned(q, 4));
+    if (M == 0) return FLEXLLM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nv = K / 4;
+    if (nv <= 256) quant_per_token_kernel<1><<<M, 256, 0, st>>>(x, K, q, s);
+    else if (nv <= 512) quant_per_token_kernel<2><<<M, 256, 0, st>>>(x, K, q, s);
+    else if (nv <= 1024) quant_per_token_kernel<4><<<M, 256, 0, st>>>(x, K, q, s);
+    else quant_per_token_kernel<8><<<M, 256, 0, st>>>(x, K, q, s);
+    return launch_status();
+}
+
+extern "C" int flexllm_dequant(const int32_t* acc, const float* s_tok, const float* s_ch, int M, int N, float* y,
+                               void* stream) {
+    FLEXLLM_REQUIRE(acc && s_tok && s_ch && y && M >= 0 && N > 0 && (N % 4) == 0);
+    FLEXLLM_REQUIRE(aligned(acc, 16) && aligned(s_ch, 16) && aligned(y, 16));
+    if (M == 0) return FLEXLLM_OK;
+    dequant_kernel<<<grid_for((long)M * N / 4, 256), 256, 0, (cudaStream_t)stream>>>(acc, s_tok, s_ch, M, N, y);
+    return launch_status();
+}
+
+extern "C" int flexllm_static_quant(const float* x, long rows, int n, const float* s, int s_stride, float f,
+                                    int is_signed, uint8_t* q, void* stream) {
+    FLEXLLM_REQUIRE(x && s && q && rows >= 0 && n > 0 && (s_stride == 0 || s_stride == 1));
+    if (rows == 0) return FLEXLLM_OK;
+    static_quant_kernel<<<grid_for(rows * n, 256), 256, 0, (cudaStream_t)stream>>>(x, rows, n, s, s_stride, f, is_signed, q);
+    return launch_status();
+}
+
+extern "C" int flexllm_rmsnorm_quant(const float* x, const float* gamma, int M, int D, float eps, int order,
+                                     float* y, int8_t* q, float* s, void* stream) {
+    FLEXLLM_REQUIRE(x && gamma && (y || q) && (!q || s) && M >= 0 && D > 0);
+    FLEXLLM_REQUIRE((D % 4) == 0 && D <= 4096 && (order == 0 || order == 4 || order == 8));
+    FLEXLLM_REQUIRE(order == 0 || (D % (order * 4)) == 0);
+    FLEXLLM_REQUIRE(aligned(x, 16) && aligned(gamma, 16) && (!y || aligned(y, 16)) && (!q || aligned(q, 4)));
+    if (M == 0) return FLEXLLM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid = (M + 3) / 4;
+    if (D <= 2048) rmsnorm_quant_kernel<16><<<grid, 128, 0, st>>>(x, gamma, M, D, eps, order, y, q, s);
+    else rmsnorm_quant_kernel<32><<<grid, 128, 0, st>>>(x, gamma, M, D, eps, order, y, q, s);
+    return launch_status();
+}
+
+extern "C" int flexllm_swish(const float* g, long n, float* y, void* stream) {
+    FLEXLLM_REQUIRE(g && y && n >= 0 && aligned(g, 16) && aligned(y, 16));
+    if (n == 0) return FLEXLLM_OK;
+    eltwise_kernel<0><<<grid_for((n + 3) / 4, 256), 256, 0, (cudaStream_t)stream>>>(g, nullptr, n, y);
+    return launch_status();
+}
+extern "C" int flexllm_gate(const float* a, const float* b, long n, float* y, void* stream) {
+    FLEXLLM_REQUIRE(a && b && y && n >= 0 && aligned(a, 16) && aligned(b, 16) && aligned(y, 16));
+    if (n == 0) return FLEXLLM_OK;
+    eltwise_kernel<1><<<grid_for((n + 3) / 4, 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, y);
+    return launch_status();
+}
+extern "C" int flexllm_residual(const float* a, const float* b, long n, float* y, void* stream) {
+    FLEXLLM_REQUIRE(a && b && y && n >= 0 && aligned(a, 16) && aligned(b, 16) && aligned(y, 16));
+    if (n == 0) return FLEXLLM_OK;
+    eltwise_kernel<2><<<grid_for((n + 3) / 4, 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, y);
+    return launch_status();
+}
+
+extern "C" int flexllm_rope(const float* x, const int32_t* pos, const float* cos_t, const float* sin_t, long T,
+                            int H, float* y, void* stream) {
+    FLEXLLM_REQUIRE(x && pos && cos_t && sin_t && y && T >= 0 && H > 0);
+    if (T == 0) return FLEXLLM_OK;
+    const long warps = T * H;
+    rope_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(x, pos, cos_t, sin_t, T, H, y);
+    return launch_status();
+}
+
+extern "C" int flexllm_softmax(const float* x, long rows, int len, const int32_t* valid, float* p, void* stream) {
+    FLEXLLM_REQUIRE(x && p && rows >= 0 && len > 0);
+    if (rows == 0) return FLEXLLM_OK;
+    softmax_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(x, rows, len, valid, p);
+    return launch_status();
+}
+
+extern "C" int flexllm_logits_argmax(const float* logits, int B, long V, int32_t* idx, void* stream) {
+    FLEXLLM_REQUIRE(logits && idx && B >= 0 && V > 0);
+    if (B == 0) return FLEXLLM_OK;
+    argmax_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(logits, V, idx);
+    return launch_status();
+}

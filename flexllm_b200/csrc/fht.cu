@@ -1,0 +1,201 @@
+// Walsh-Hadamard transforms of the SpinQuant online rotations.
+//
+// The reference computes the transform with an Omega network (Modules/FHT.h:31-53). Its fp32
+// result is bit-identical to in-place butterflies (lo,hi) <- (lo+hi, lo-hi) applied on index
+// bits in the order 1, 2, ..., log2(N)-1, 0; every kernel here keeps exactly that stage order.
+//
+//  * fht8192_kernel  : R4, the 8192-point transform on the down_proj input. One CTA per token,
+//                      the row lives in shared memory, three register passes of 5+5+3 stages.
+//                      Optionally fused with silu(gate)*up on the way in and with the per-token
+//                      int8 quantiser on the way out.
+//  * fht_generic     : any power of two <= 8192, one stage per barrier (API completeness).
+//  * qk_prepare      : R3, the 64-point transform on Q/K heads, in registers with warp shuffles,
+//                      fused with dequant, RoPE and the per-head int8 quantiser.
+#include "common.cuh"
+
+namespace flexllm {
+
+__device__ __forceinline__ int pad32(int i) { return i + (i >> 5); }
+
+template <int B>
+__device__ __forceinline__ void reg_butterfly(float (&r)[32]) {
+#pragma unroll
+    for (int v = 0; v < 32; v++) {
+        if (!(v & (1 << B))) {
+            float lo = r[v], hi = r[v | (1 << B)];
+            r[v] = lo + hi;
+            r[v | (1 << B)] = lo - hi;
+        }
+    }
+}
+
+// FUSED: 0 = y = FHT(x)/scale (fp32 out); 1 = h = silu(g)*u, FHT, /scale, per-token int8 quant.
+template <int FUSED>
+__global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ x, const float* __restrict__ u,
+                                                      float scale, float* __restrict__ y, int8_t* __restrict__ q,
+                                                      float* __restrict__ s, float* __restrict__ act) {
+    constexpr int N = 8192;
+    __shared__ float buf[N + N / 32];
+    __shared__ float red[64];
+    const int tid = threadIdx.x;
+    const long row = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * N);
+    const float4* ur = FUSED ? reinterpret_cast<const float4*>(u + row * N) : nullptr;
+#pragma unroll
+    for (int it = 0; it < N / 1024; it++) {
+        const int c = it * 256 + tid;
+        float4 v = xr[c];
+        if (FUSED) {
+            float4 w = ur[c];
+            v.x = silu_f(v.x) * w.x; v.y = silu_f(v.y) * w.y; v.z = silu_f(v.z) * w.z; v.w = silu_f(v.w) * w.w;
+            if (act) reinterpret_cast<float4*>(act + row * N)[c] = v;
+        }
+        const int p = pad32(c * 4);
+        buf[p] = v.x; buf[p + 1] = v.y; buf[p + 2] = v.z; buf[p + 3] = v.w;
+    }
+    __syncthreads();
+    float r[32];
+    // pass 1: index bits 1..5 in registers
+    {
+        const int base = (tid & 1) | ((tid >> 1) << 6);
+#pragma unroll
+        for (int v = 0; v < 32; v++) r[v] = buf[pad32(base | (v << 1))];
+        reg_butterfly<0>(r); reg_butterfly<1>(r); reg_butterfly<2>(r); reg_butterfly<3>(r); reg_butterfly<4>(r);
+#pragma unroll
+        for (int v = 0; v < 32; v++) buf[pad32(base | (v << 1))] = r[v];
+    }
+    __syncthreads();
+    // pass 2: index bits 6..10
+    {
+        const int base = (tid & 63) | ((tid >> 6) << 11);
+#pragma unroll
+        for (int v = 0; v < 32; v++) r[v] = buf[pad32(base | (v << 6))];
+        reg_butterfly<0>(r); reg_butterfly<1>(r); reg_butterfly<2>(r); reg_butterfly<3>(r); reg_butterfly<4>(r);
+#pragma unroll
+        for (int v = 0; v < 32; v++) buf[pad32(base | (v << 6))] = r[v];
+    }
+    __syncthreads();
+    // pass 3: index bits 11, 12, then 0. Register v: bits 0..2 -> index bits 0..2, bits 3,4 -> 11,12
+    {
+        const int base = tid << 3;
+#pragma unroll
+        for (int v = 0; v < 32; v++) r[v] = buf[pad32(base | (v & 7) | ((v >> 3) << 11))];
+        reg_butterfly<3>(r); reg_butterfly<4>(r); reg_butterfly<0>(r);
+    }
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int v = 0; v < 32; v++) {
+        r[v] = r[v] / scale;
+        mx = fmaxf(mx, r[v]);
+        mn = fminf(mn, r[v]);
+    }
+    if (!FUSED) {
+#pragma unroll
+        for (int hi = 0; hi < 4; hi++) {
+            float4* yo = reinterpret_cast<float4*>(y + row * N + hi * 2048 + tid * 8);
+            yo[0] = make_float4(r[hi * 8 + 0], r[hi * 8 + 1], r[hi * 8 + 2], r[hi * 8 + 3]);
+            yo[1] = make_float4(r[hi * 8 + 4], r[hi * 8 + 5], r[hi * 8 + 6], r[hi * 8 + 7]);
+        }
+    } else {
+        block_max_min(mx, mn, red);
+        const float sc = sym_scale_from(mx, mn);
+        if (tid == 0) s[row] = sc;
+#pragma unroll
+        for (int hi = 0; hi < 4; hi++) {
+            union { int8_t b[8]; int2 v; } o;
+#pragma unroll
+            for (int c = 0; c < 8; c++) o.b[c] = quant_s8(r[hi * 8 + c], sc);
+            *reinterpret_cast<int2*>(q + row * N + hi * 2048 + tid * 8) = o.v;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) fht_generic_kernel(const float* __restrict__ x, int N, float scale,
+                                                          float* __restrict__ y) {
+    extern __shared__ float sb[];
+    const long row = blockIdx.x;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) sb[i] = x[row * N + i];
+    __syncthreads();
+    auto stage = [&](int h) {
+        for (int p = threadIdx.x; p < N / 2; p += blockDim.x) {
+            int i = (p / h) * 2 * h + (p % h);
+            float a = sb[i], b = sb[i + h];
+            sb[i] = a + b;
+            sb[i + h] = a - b;
+        }
+        __syncthreads();
+    };
+    for (int h = 2; h < N; h <<= 1) stage(h);
+    stage(1);
+    for (int i = threadIdx.x; i < N; i += blockDim.x) y[row * N + i] = sb[i] / scale;
+}
+
+// One warp per (token, head): lane L holds elements L and L+32 of the 64-wide head.
+__global__ void __launch_bounds__(256) qk_prepare_kernel(const int8_t* __restrict__ q, const float* __restrict__ s,
+                                                         const int32_t* __restrict__ pos, const float* __restrict__ cos_t,
+                                                         const float* __restrict__ sin_t, long T, int H,
+                                                         int8_t* __restrict__ q_out, float* __restrict__ s_out) {
+    const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= T * H) return;
+    const long t = w / H;
+    const int p = pos[t];
+    const float sc_in = s[w];
+    const float x0 = (float)q[w * 64 + lane] * sc_in;
+    const float x1 = (float)q[w * 64 + 32 + lane] * sc_in;
+    const float c = cos_t[(long)p * 32 + lane], sn = sin_t[(long)p * 32 + lane];
+    float a = x0 * c - x1 * sn;   // element lane
+    float b = x0 * sn + x1 * c;   // element lane + 32
+    auto lane_stage = [&](int bit) {
+        float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
+        float pb = __shfl_xor_sync(0xffffffffu, b, 1 << bit);
+        if (lane & (1 << bit)) { a = pa - a; b = pb - b; }
+        else { a = a + pa; b = b + pb; }
+    };
+    lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
+    { float lo = a, hi = b; a = lo + hi; b = lo - hi; }   // index bit 5
+    lane_stage(0);
+    a = a / 8.0f;
+    b = b / 8.0f;
+    float mx = warp_max(fmaxf(a, b)), mn = warp_min(fminf(a, b));
+    const float sc = sym_scale_from(mx, mn);
+    if (lane == 0) s_out[w] = sc;
+    q_out[w * 64 + lane] = quant_s8(a, sc);
+    q_out[w * 64 + 32 + lane] = quant_s8(b, sc);
+}
+
+}  // namespace flexllm
+
+using namespace flexllm;
+
+extern "C" int flexllm_fht(const float* x, long rows, int N, float scale, float* y, void* stream) {
+    FLEXLLM_REQUIRE(x && y && rows >= 0 && N >= 2 && N <= 8192 && (N & (N - 1)) == 0);
+    if (rows == 0) return FLEXLLM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (N == 8192 && aligned(x, 16) && aligned(y, 16)) {
+        fht8192_kernel<0><<<(unsigned)rows, 256, 0, st>>>(x, nullptr, scale, y, nullptr, nullptr, nullptr);
+    } else {
+        int threads = N / 2 < 256 ? (N / 2 < 32 ? 32 : N / 2) : 256;
+        fht_generic_kernel<<<(unsigned)rows, threads, N * sizeof(float), st>>>(x, N, scale, y);
+    }
+    return launch_status();
+}
+
+extern "C" int flexllm_swiglu_fht_quant(const float* g, const float* u, int M, int N, float scale, int8_t* q,
+                                        float* s, float* act, void* stream) {
+    FLEXLLM_REQUIRE(g && u && q && s && M >= 0);
+    if (N != 8192) return FLEXLLM_ENOTSUP;
+    FLEXLLM_REQUIRE(aligned(g, 16) && aligned(u, 16) && aligned(q, 8) && (!act || aligned(act, 16)));
+    if (M == 0) return FLEXLLM_OK;
+    fht8192_kernel<1><<<M, 256, 0, (cudaStream_t)stream>>>(g, u, scale, nullptr, q, s, act);
+    return launch_status();
+}
+
+extern "C" int flexllm_qk_prepare(const int8_t* q, const float* s, const int32_t* pos, const float* cos_t,
+                                  const float* sin_t, long T, int H, int8_t* q_out, float* s_out, void* stream) {
+    FLEXLLM_REQUIRE(q && s && pos && cos_t && sin_t && q_out && s_out && T >= 0 && H > 0);
+    if (T == 0) return FLEXLLM_OK;
+    const long warps = T * H;
+    qk_prepare_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(q, s, pos, cos_t, sin_t, T, H, q_out, s_out);
+    return launch_status();
+}

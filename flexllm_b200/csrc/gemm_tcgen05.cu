@@ -1,0 +1,371 @@
+// int8 x int8 -> int32 linear layer on the 5th-generation tensor cores (tcgen05, kind::i8).
+//
+//   acc[m][n] = sum_k a[m][k] * w[n][k]                    exact
+//   y[m][n]   = ((float)acc * s_tok[m]) * s_ch[n]          fused epilogue
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of both operands, STAGES-deep ring
+//   warp 1      MMA issuer (one thread): 4 x (128 x BN x 32) UMMAs per 128-byte K block into one of
+//               two TMEM accumulators; also owns TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one TMEM lane = one output row per
+//               thread), dequantise, store; runs while the MMA warp fills the other accumulator
+//
+// The "A side" is the UMMA M operand (128 rows per tile), the "B side" the N operand (BN rows).
+//   prefill : A = activations [M][K], B = weights [N][K]            out[rowA][rowB]
+//   decode  : A = weights [N][K],     B = activations [M<=64][K]     out[rowB][rowA]   (SWAP)
+// so that a handful of tokens still fills the 128-row dimension of the tensor core with weight
+// rows and the weight matrix is streamed exactly once. With split-K (decode) partial sums are added
+// into a zeroed int32 buffer with red.global.add (integer addition is exact and order-free).
+//
+// Replaces pref_Linear_Layer_i4xi4 / dec_Linear_Layer_i4xi4 + the dequant layers
+// (Modules/Linear_Layer.h:293-341, :862-923; Modules/quant.h:115-164, :434-524) at 8-bit precision.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace flexllm {
+
+using namespace tc;
+
+// ------------------------------------------------------------------ tensor-map encoding (host)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return FLEXLLM_ECUDA;
+    if (!aligned(base, 16) || (row_bytes % 16) != 0 || box_rows == 0 || box_rows > 256) return FLEXLLM_EINVAL;
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return FLEXLLM_ECUDA; }
+    return FLEXLLM_OK;
+}
+
+// ------------------------------------------------------------------ kernel
+struct GemmArgs {
+    int rowsA, rowsB, K;     // A side (128-row tiles), B side (BN-row tiles), reduction length
+    int tilesA, tilesB, ksplit;
+    int ldo;                 // leading dimension of the outputs
+    int32_t* acc;            // optional int32 output (required when ksplit > 1: added atomically)
+    float* y;                // optional fp32 output (ignored when ksplit > 1)
+    const float* sA;         // per-row scale of the A side
+    const float* sB;         // per-row scale of the B side
+    int* error_flag;         // set to 1 if a device-side wait ran out
+};
+
+template <int BN> struct GemmCfg {
+    static constexpr int A_BYTES = 128 * 128;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : BN == 32 ? 8 : 10;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmapA,
+                                                                 const __grid_constant__ CUtensorMap tmapB,
+                                                                 const GemmArgs args) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte aligned operand ring, then barriers
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;
+    uint8_t* ring_ptr = smem_raw + (ring - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + STAGES * Cfg::STAGE_BYTES);
+    // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem base word, abort flag
+    const uint32_t bar_full = smem_u32(bars);
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (args.K + 127) >> 7;
+    const int total_tiles = args.tilesA * args.tilesB * args.ksplit;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(bar_tfull + 8 * s, 1); mbar_init(bar_tempty + 8 * s, 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_base_slot), Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmapA);
+            tma_prefetch_desc(&tmapB);
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const int split = t % args.ksplit;
+                const int tb = (t / args.ksplit) % args.tilesB;
+                const int ta = t / (args.ksplit * args.tilesB);
+                const int kb0 = (int)((long)split * num_kb / args.ksplit);
+                const int kb1 = (int)((long)(split + 1) * num_kb / args.ksplit);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t full = bar_full + 8 * stage;
+                    mbar_expect_tx(full, Cfg::STAGE_BYTES);
+                    const uint32_t dstA = ring + stage * Cfg::STAGE_BYTES;
+                    tma_load_2d(dstA, &tmapA, full, kb * 128, ta * 128);
+                    tma_load_2d(dstA + Cfg::A_BYTES, &tmapB, full, kb * 128, tb * BN);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_i8(128, BN, 1, 1);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, it++) {
+                const int split = t % args.ksplit;
+                const int kb0 = (int)((long)split * num_kb / args.ksplit);
+                const int kb1 = (int)((long)(split + 1) * num_kb / args.ksplit);
+                const int as = it & 1;
+                const uint32_t aphase = (it >> 1) & 1;
+                if (!mbar_wait(bar_tempty + 8 * as, aphase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + as * BN;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = ring + stage * Cfg::STAGE_BYTES;
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; k++)   // 32 int8 = 32 bytes = 2 descriptor address units per step
+                        umma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar_empty + 8 * stage);   // slot is free once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(bar_tfull + 8 * as);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, it++) {
+            const int tb = (t / args.ksplit) % args.tilesB;
+            const int ta = t / (args.ksplit * args.tilesB);
+            const int as = it & 1;
+            const uint32_t aphase = (it >> 1) & 1;
+            // lane 0 polls; the verdict is broadcast so that the warp stays converged for the
+            // warp-collective TMEM loads below
+            int got = (lane == 0) ? (mbar_wait(bar_tfull + 8 * as, aphase, abort_flag) ? 1 : 0) : 1;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) { ok = false; break; }
+            tc_fence_after();
+            const int rowA = ta * 128 + q * 32 + lane;
+            const bool rowA_ok = rowA < args.rowsA;
+            const float sa = (rowA_ok && args.sA) ? args.sA[rowA] : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; c++) {
+                uint32_t v[16];
+                tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + c * 16, v);
+                tmem_ld_wait();
+                const int colB0 = tb * BN + c * 16;
+                if (!SWAP) {
+                    // out[rowA][colB0 + j]: token = rowA, channel = colB
+                    if (rowA_ok) {
+                        const long o = (long)rowA * args.ldo + colB0;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            if (colB0 + j < args.rowsB) {
+                                if (args.acc) {
+                                    *reinterpret_cast<int4*>(args.acc + o + j) =
+                                        make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
+                                }
+                                if (args.y) {
+                                    const float4 sb = *reinterpret_cast<const float4*>(args.sB + colB0 + j);
+                                    float4 r;
+                                    r.x = ((float)(int)v[j] * sa) * sb.x;
+                                    r.y = ((float)(int)v[j + 1] * sa) * sb.y;
+                                    r.z = ((float)(int)v[j + 2] * sa) * sb.z;
+                                    r.w = ((float)(int)v[j + 3] * sa) * sb.w;
+                                    *reinterpret_cast<float4*>(args.y + o + j) = r;
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    // out[colB0 + j][rowA]: token = colB, channel = rowA; a warp store covers 32 channels
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int tok = colB0 + j;
+                        if (rowA_ok && tok < args.rowsB) {
+                            const long o = (long)tok * args.ldo + rowA;
+                            if (args.ksplit > 1) {
+                                atomicAdd(args.acc + o, (int)v[j]);
+                            } else {
+                                if (args.acc) args.acc[o] = (int)v[j];
+                                if (args.y) args.y[o] = ((float)(int)v[j] * args.sB[tok]) * sa;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * as);
+        }
+    }
+
+    // ---------------------------------------------------------------- tear-down
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: give copies still in flight time to land before shared memory is released
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+        if (threadIdx.x == 0 && args.error_flag) atomicExch(args.error_flag, 1);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host launcher
+struct TmapKey {
+    const void* base; uint64_t rows, row_bytes; uint32_t box_rows;
+    bool operator==(const TmapKey& o) const { return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows; }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        h ^= std::hash<uint64_t>()(k.rows * 1000003ull + k.row_bytes * 31ull + k.box_rows) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+// Encoding a tensor map costs a few microseconds of host time; the same weights and activation
+// buffers come back every layer call, so maps are cached by (pointer, shape, box).
+static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    static std::mutex mu;
+    static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+    TmapKey key{base, rows, row_bytes, box_rows};
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return FLEXLLM_OK; }
+    int st = make_tmap_2d_u8(out, base, rows, row_bytes, box_rows);
+    if (st != FLEXLLM_OK) return st;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return FLEXLLM_OK;
+}
+
+static int* device_error_flag() {
+    static thread_local int* flag[16] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+    if (!flag[dev]) {
+        if (cudaMalloc(&flag[dev], sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(flag[dev], 0, sizeof(int));
+    }
+    return flag[dev];
+}
+
+static int sm_count() {
+    static int n[16] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) return 148;
+    if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+    return n[dev] > 0 ? n[dev] : 148;
+}
+
+template <int BN, bool SWAP>
+static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, int K, int ksplit, int ldo,
+                       int32_t* acc, float* y, const float* sA, const float* sB, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    CUtensorMap ta, tb;
+    int rc = cached_tmap(&ta, A, (uint64_t)rowsA, (uint64_t)K, 128);
+    if (rc != FLEXLLM_OK) return rc;
+    rc = cached_tmap(&tb, B, (uint64_t)rowsB, (uint64_t)K, BN);
+    if (rc != FLEXLLM_OK) return rc;
+    GemmArgs g;
+    g.rowsA = rowsA; g.rowsB = rowsB; g.K = K;
+    g.tilesA = (rowsA + 127) / 128; g.tilesB = (rowsB + BN - 1) / BN; g.ksplit = ksplit;
+    g.ldo = ldo; g.acc = acc; g.y = y; g.sA = sA; g.sB = sB; g.error_flag = device_error_flag();
+    auto kern = gemm_i8_tcgen05_kernel<BN, SWAP>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    const int total = g.tilesA * g.tilesB * g.ksplit;
+    const int grid = total < sm_count() ? total : sm_count();
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, g);
+    return launch_status();
+}
+
+// Prefill orientation: activations on the 128-row side.
+int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                    int32_t* acc, float* y, cudaStream_t st) {
+    if (N > 128) return launch_gemm<256, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
+    if (N > 64) return launch_gemm<128, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
+    if (N > 32) return launch_gemm<64, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
+    if (N > 16) return launch_gemm<32, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
+    return launch_gemm<16, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
+}
+
+// Decode orientation: weights on the 128-row side, M <= 64 tokens on the N side, optional split-K.
+// With ksplit > 1 the caller passes a ZEROED int32 buffer in `acc` and dequantises afterwards.
+int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                   int ksplit, int32_t* acc, float* y, cudaStream_t st) {
+    if (M > 64) return FLEXLLM_ENOTSUP;
+    if (M > 32) return launch_gemm<64, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st);
+    if (M > 16) return launch_gemm<32, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st);
+    return launch_gemm<16, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st);
+}
+
+int gemm_check_error_flag() {
+    int* f = device_error_flag();
+    if (!f) return FLEXLLM_ECUDA;
+    int h = 0;
+    FLEXLLM_CHECK_CUDA(cudaMemcpy(&h, f, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h) { cudaMemset(f, 0, sizeof(int)); return FLEXLLM_ETIMEDOUT; }
+    return FLEXLLM_OK;
+}
+
+int gemm_sm_count() { return sm_count(); }
+
+}  // namespace flexllm

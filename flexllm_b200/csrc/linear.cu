@@ -1,0 +1,86 @@
+// C-ABI entry points of the W8A8 linear layers: shape checks, choice between the weight-streaming
+// GEMV and the tcgen05 GEMM, split-K bookkeeping for decode.
+#include "common.cuh"
+
+namespace flexllm {
+int gemv_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+            int32_t* acc, float* y, cudaStream_t st);
+int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                    int32_t* acc, float* y, cudaStream_t st);
+int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                   int ksplit, int32_t* acc, float* y, cudaStream_t st);
+int gemm_sm_count();
+
+// Library-owned int32 scratch for split-K partial sums, one per device, grown on demand.
+struct Scratch { void* p = nullptr; size_t bytes = 0; };
+static Scratch g_scratch[16];
+
+int scratch_get(size_t bytes, void** out) {
+    int dev = 0;
+    FLEXLLM_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return FLEXLLM_EINVAL;
+    Scratch& s = g_scratch[dev];
+    if (s.bytes < bytes) {
+        if (s.p) { FLEXLLM_CHECK_CUDA(cudaDeviceSynchronize()); FLEXLLM_CHECK_CUDA(cudaFree(s.p)); s.p = nullptr; s.bytes = 0; }
+        size_t want = bytes < (size_t)(8 << 20) ? (size_t)(8 << 20) : bytes;
+        FLEXLLM_CHECK_CUDA(cudaMalloc(&s.p, want));
+        s.bytes = want;
+    }
+    *out = s.p;
+    return FLEXLLM_OK;
+}
+
+
+int decode_ksplit(int N, int K) {
+    const int tiles = (N + 127) / 128;
+    const int num_kb = (K + 127) / 128;
+    int ks = gemm_sm_count() / tiles;
+    if (ks > num_kb / 2) ks = num_kb / 2;
+    if (ks < 1) ks = 1;
+    return ks;
+}
+}  // namespace flexllm
+
+using namespace flexllm;
+
+static int check_linear(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                        int32_t* acc, float* y) {
+    FLEXLLM_REQUIRE(a && w && (acc || y) && M >= 0 && N > 0 && K > 0);
+    FLEXLLM_REQUIRE(!y || (s_tok && s_ch));
+    FLEXLLM_REQUIRE((K % 16) == 0 && (N % 8) == 0);
+    FLEXLLM_REQUIRE(aligned(a, 16) && aligned(w, 16) && (!acc || aligned(acc, 16)) && (!y || aligned(y, 16)) &&
+                    (!s_ch || aligned(s_ch, 16)));
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                         int M, int N, int K, int32_t* acc, float* y, void* stream) {
+    int rc = check_linear(a, s_tok, w, s_ch, M, N, K, acc, y);
+    if (rc != FLEXLLM_OK) return rc;
+    if (M == 0) return FLEXLLM_OK;
+    return gemm_i8_prefill(a, s_tok, w, s_ch, M, N, K, acc, y, (cudaStream_t)stream);
+}
+
+extern "C" int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                        int M, int N, int K, int32_t* acc, float* y, void* stream) {
+    int rc = check_linear(a, s_tok, w, s_ch, M, N, K, acc, y);
+    if (rc != FLEXLLM_OK) return rc;
+    if (M == 0) return FLEXLLM_OK;
+    if (M > 64) return FLEXLLM_ENOTSUP;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M <= 8) return gemv_i8(a, s_tok, w, s_ch, M, N, K, acc, y, st);
+    const int ks = decode_ksplit(N, K);
+    if (ks == 1) return gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, 1, acc, y, st);
+    int32_t* part = acc;
+    if (!part) {
+        void* p = nullptr;
+        rc = scratch_get((size_t)M * N * sizeof(int32_t), &p);
+        if (rc != FLEXLLM_OK) return rc;
+        part = (int32_t*)p;
+    }
+    FLEXLLM_CHECK_CUDA(cudaMemsetAsync(part, 0, (size_t)M * N * sizeof(int32_t), st));
+    rc = gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, ks, part, nullptr, st);
+    if (rc != FLEXLLM_OK) return rc;
+    if (y) return flexllm_dequant(part, s_tok, s_ch, M, N, y, stream);
+    return FLEXLLM_OK;
+}

@@ -1,0 +1,129 @@
+/* flexllm_b200 -- C ABI of the B200 (sm_100a) implementation of FlexLLM's quantized
+ * Llama-3.2-1B operator path.
+ *
+ * FlexLLM's operators are C++ function templates over TAPA streams (Modules/ *.h); a host
+ * program reaches them through tapa::invoke(top_fn, bitstream, mmaps..., scalars...)
+ * (SpinQuant_Llama_32_1B/Linear_Layer_Prefilling_tb.cpp:106-113). There is no FFI in the
+ * reference, so each entry point below names the operator template(s) it replaces. The C++ host
+ * API in include/flexllm/ keeps the Modules/ names and calls these functions.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless the parameter name ends in _host;
+ *  - tensors are row-major and dense; weights are [N][K] with K contiguous (the layout of the
+ *    reference's parameter files, Linear_Layer_Prefilling_tb.cpp:318-351);
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls are asynchronous;
+ *  - return value: FLEXLLM_OK or a negative FLEXLLM_E* code; nothing aborts or throws;
+ *  - the caller owns all buffers; the library owns only the opaque handles it creates;
+ *  - there is no CPU fallback: without a CUDA device every compute call returns FLEXLLM_ECUDA.
+ */
+#ifndef FLEXLLM_B200_H
+#define FLEXLLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FLEXLLM_API __attribute__((visibility("default")))
+#else
+#define FLEXLLM_API
+#endif
+
+#define FLEXLLM_OK 0
+#define FLEXLLM_EINVAL (-1)    /* bad dimension, alignment or null pointer */
+#define FLEXLLM_ECUDA (-2)     /* CUDA runtime error (see flexllm_last_cuda_error) */
+#define FLEXLLM_ETIMEDOUT (-3) /* a bounded device-side wait gave up */
+#define FLEXLLM_ENOTSUP (-4)   /* shape outside what the kernels were built for */
+#define FLEXLLM_ENOMEM (-5)
+
+/* RMSNorm summation orders (Modules/LayerNorm.h:82-130 prefill, :263-321 decode). */
+#define FLEXLLM_NORM_PREFILL 0 /* 4 interleaved partial sums over the whole row          */
+#define FLEXLLM_NORM_DECODE8 8 /* 8 contiguous chunks, 4 interleaved partial sums in each */
+#define FLEXLLM_NORM_DECODE4 4
+
+FLEXLLM_API int flexllm_version(void);
+FLEXLLM_API const char* flexllm_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+FLEXLLM_API int flexllm_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Linear layers.   acc[m][n] = sum_k a[m][k]*w[n][k]  (exact int32);
+ *                  y[m][n]   = ((float)acc * s_tok[m]) * s_ch[n]
+ * Replaces pref_Linear_Layer_i4xi4 (Modules/Linear_Layer.h:293-341) + pref_dequant_layer_qint_fp32
+ * (Modules/quant.h:115-164) at 8-bit symmetric precision, and dec_Linear_Layer_i4xi4
+ * (Linear_Layer.h:862-923) + dec_dequant_layer_qint_fp32 (quant.h:434-524) for decode.
+ * acc and y may each be NULL (not both). K % 16 == 0.
+ * prefill: tcgen05 tensor-core GEMM, any M >= 1, N % 8 == 0.
+ * decode : M <= 64 tokens; weight-streaming GEMV (M <= 8) or tensor-core skinny GEMM.
+ * ------------------------------------------------------------------------------------------- */
+FLEXLLM_API int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                              int M, int N, int K, int32_t* acc, float* y, void* stream);
+FLEXLLM_API int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                             int M, int N, int K, int32_t* acc, float* y, void* stream);
+
+/* Dynamic per-token symmetric int8 quantisation: s = max|x|/127 (0 -> 1), q = round(x/s).
+ * Replaces pref_quant_layer_fp32_qint / dec_quant_layer_fp32_qint (quant.h:6-112, :332-431). */
+FLEXLLM_API int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, float* s, void* stream);
+
+/* y = ((float)acc * s_tok[m]) * s_ch[n].  Replaces pref_dequant_layer_qint_fp32 (quant.h:115-164)
+ * and pref_static_sym_dequant_layer_qint_fp32 (quant.h:214-249). */
+FLEXLLM_API int flexllm_dequant(const int32_t* acc, const float* s_tok, const float* s_ch, int M, int N, float* y,
+                    void* stream);
+
+/* Static symmetric quantisation q = clamp(round(x / (f * s[row]))): signed -> [-128,127],
+ * unsigned -> upper clamp 255 only. s_stride 0 = one scale for all rows, 1 = one per row.
+ * Replaces pref_static_sym_per_tensor_quant_layer_fp32_qint (quant.h:252-295) and
+ * pref_static_sym_quant_layer_fp32_qint (quant.h:166-211). */
+FLEXLLM_API int flexllm_static_quant(const float* x, long rows, int n, const float* s, int s_stride, float f,
+                         int is_signed, uint8_t* q, void* stream);
+
+/* Walsh-Hadamard transform of each row, natural order, divided by `scale`; bit-identical to
+ * pref_FHT / dec_FHT (Modules/FHT.h:7-129). N a power of two, 2 <= N <= 8192. */
+FLEXLLM_API int flexllm_fht(const float* x, long rows, int N, float scale, float* y, void* stream);
+
+/* Half-split rotary embedding by table, head_dim 64. x,y [T][H][64]; pos [T]; tables [P][32].
+ * Replaces pref_RoPE_layer / dec_RoPE_layer (Modules/RoPE.h:8-173). */
+FLEXLLM_API int flexllm_rope(const float* x, const int32_t* pos, const float* cos_t, const float* sin_t, long T,
+                 int H, float* y, void* stream);
+
+/* Row softmax with the reference's summation order; valid (NULL or [rows]) = number of leading
+ * unmasked entries (the rest are set to -1e32 first). Replaces pref_causal_mask_template
+ * (Modules/MHA.h:246-273) + pref_Softmax / dec_MHA_Softmax (Modules/Softmax.h:6-163, :456-635). */
+FLEXLLM_API int flexllm_softmax(const float* x, long rows, int len, const int32_t* valid, float* p, void* stream);
+
+/* RMSNorm y = (x * r) * gamma with the summation order of `order` (FLEXLLM_NORM_*), optionally
+ * fused with the per-token int8 quantiser that follows it in the model (q, s non-NULL).
+ * y may be NULL when q is given. Replaces pref_Layer_Norm / dec_Layer_Norm
+ * (Modules/LayerNorm.h:28-183, :210-370) [+ quant.h:6-112]. */
+FLEXLLM_API int flexllm_rmsnorm_quant(const float* x, const float* gamma, int M, int D, float eps, int order,
+                          float* y, int8_t* q, float* s, void* stream);
+
+/* y = g / (1 + exp(-g))                      pref_Swish / dec_Swish (Modules/Swish.h) */
+FLEXLLM_API int flexllm_swish(const float* g, long n, float* y, void* stream);
+/* y = a * b                                  pref_Gate_Layer_fp32xfp32 (Linear_Layer.h:612-630) */
+FLEXLLM_API int flexllm_gate(const float* a, const float* b, long n, float* y, void* stream);
+/* y = a + b                                  pref_Residual_Layer (Residual_Layer.h:46-87) */
+FLEXLLM_API int flexllm_residual(const float* a, const float* b, long n, float* y, void* stream);
+
+/* Fused  silu(g)*u -> FHT-N / scale -> per-token int8 quant   (Swish.h + Linear_Layer.h:612-630 +
+ * FHT.h + quant.h:6-112, in the order of SpinQuant_Prefilling.h:1017-1035). g,u [M][N] fp32 ->
+ * q [M][N] s8, s [M]. act (optional) receives silu(g)*u. N == 8192. */
+FLEXLLM_API int flexllm_swiglu_fht_quant(const float* g, const float* u, int M, int N, float scale, int8_t* q,
+                             float* s, float* act, void* stream);
+
+/* Greedy token: argmax with ties to the lowest index = rank 0 of sort_top_k (Logits.h:5-31). */
+FLEXLLM_API int flexllm_logits_argmax(const float* logits, int B, long V, int32_t* idx, void* stream);
+
+/* Q/K preparation: x = (float)q*s -> RoPE(pos) -> FHT-64/8 -> per-head dynamic int8 quant.
+ * q [T][H][64] s8, s [T][H] -> q_out, s_out same shapes (quant.h:242, RoPE.h:61-90, FHT.h at
+ * N=64, quant.h:527-650). */
+FLEXLLM_API int flexllm_qk_prepare(const int8_t* q, const float* s, const int32_t* pos, const float* cos_t,
+                       const float* sin_t, long T, int H, int8_t* q_out, float* s_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXLLM_B200_H */
