@@ -297,9 +297,10 @@ extern "C" const char* flexllm_status_string(int st) {
 extern "C" int flexllm_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, float* s, void* stream) {
-    FLEXLLM_REQUIRE(x && q && s && M >= 0 && K > 0 && (K % 4) == 0 && K <= 8192);
+    FLEXLLM_REQUIRE(M >= 0 && K > 0 && (K % 4) == 0 && K <= 8192);
+    if (M == 0) return FLEXLLM_OK;   // empty batch: nothing to do, pointers may be null
+    FLEXLLM_REQUIRE(x && q && s);
     FLEXLLM_REQUIRE(aligned(x, 16) && aligned(q, 4));
-    if (M == 0) return FLEXLLM_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int nv = K / 4;
     if (nv <= 256) quant_per_token_kernel<1><<<M, 256, 0, st>>>(x, K, q, s);
