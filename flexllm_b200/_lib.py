@@ -27,8 +27,17 @@ SIGNATURES = {
     "flexllm_swiglu_fht_quant": [_P, _P, _I, _I, _F, _P, _P, _P, _P],
     "flexllm_logits_argmax": [_P, _I, _L, _P, _P],
     "flexllm_qk_prepare": [_P, _P, _P, _P, _P, _L, _I, _P, _P, _P],
+    "flexllm_mha_prefill_workspace": [_I, _I, _I, _I],
+    "flexllm_mha_i8xi8_prefill": [_P] * 9 + [_I, _I, _I, _I, _P, _P, _P, _SZ, _P],
+    "flexllm_kv_cache_create": [_P, _I, _I, _I, _I],
+    "flexllm_kv_cache_destroy": [_P],
+    "flexllm_kv_cache_reset": [_P, _P],
+    "flexllm_kv_cache_pools": [_P, _I, _P, _P, _P, _P],
+    "flexllm_mha_decode_workspace": [_I, _I, _I],
+    "flexllm_mha_i8xi8_decode": [_P, _I] + [_P] * 10 + [_I, _P, _I, _I, _I, _P, _P, _P, _SZ, _P],
 }
-RESTYPES = {"flexllm_status_string": C.c_char_p}
+RESTYPES = {"flexllm_status_string": C.c_char_p, "flexllm_mha_prefill_workspace": C.c_size_t,
+            "flexllm_mha_decode_workspace": C.c_size_t}
 
 
 def load():

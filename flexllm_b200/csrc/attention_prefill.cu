@@ -1,0 +1,421 @@
+// Prefill GQA attention, int8 x int8, on tcgen05 tensor cores.
+//
+// Semantics (bit-for-bit the composition the CPU oracle states; reference operators:
+// Modules/MHA.h:189-243 Q.K^T, :246-273 mask, Modules/Softmax.h:25-161, Modules/quant.h:252-295
+// unsigned static quant of P, Modules/MHA.h:339-389 P.V, Modules/quant.h:297-326 dequant):
+//
+//   S[q][k]  = sum_d Q[q][d] K[k][d]                       s8 x s8 -> s32   (tensor cores)
+//   x[q][k]  = (((float)S * qs[q]) * ks[k]) * 0.125         k <= q only
+//   P        = softmax(x): max, e = exp(x - max), four interleaved partial sums over k mod 4 in
+//              increasing k, (p0+p1)+(p2+p3), r = 1/total, P = e * r
+//   U[q][k]  = min(round((P * vs[k]) / a_s), 255)           u8
+//   O[q][d]  = sum_k U[q][k] V[k][d]                        u8 x s8 -> s32   (tensor cores)
+//   out      = (float)O * a_s
+//
+// The reference quantises the FINAL normalised P and accumulates a whole row of P.V in one int32,
+// so a rescaling online softmax cannot reproduce it. The kernel therefore sweeps the keys three
+// times, recomputing the cheap Q.K^T tiles (head_dim 64) instead of materialising S x S scores:
+//   sweep 0: row max           sweep 1: exp + ordered partial sums           sweep 2: U and P.V
+// One thread owns one query row (TMEM lane), so every per-row fp32 chain runs in the reference's
+// order. One CTA = 128 queries of one (batch, query head); 4 softmax warps + TMA warp + MMA warp;
+// TMEM: S (128 columns) + O (64 columns); two CTAs per SM overlap each other's MMA and softmax.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace flexllm {
+using namespace tc;
+
+// ------------------------------------------------------------------ pre-pass
+// Q/K: dequant -> RoPE -> FHT-64/8 -> per-head int8 quant (same arithmetic as qk_prepare_kernel),
+// written head-major [B][H][S][64] with scales [B][H][S] so that one head's rows are contiguous.
+__global__ void __launch_bounds__(256) attn_qk_prepare_kernel(const int8_t* __restrict__ q, const float* __restrict__ s,
+                                                              const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                              int B, int S, int H, int8_t* __restrict__ q_out,
+                                                              float* __restrict__ s_out) {
+    const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const long total = (long)B * S * H;
+    if (w >= total) return;
+    const int h = (int)(w % H);
+    const long bt = w / H;
+    const int t = (int)(bt % S);
+    const int b = (int)(bt / S);
+    const float sc_in = s[w];
+    const float x0 = (float)q[w * 64 + lane] * sc_in;
+    const float x1 = (float)q[w * 64 + 32 + lane] * sc_in;
+    const float c = cos_t[(long)t * 32 + lane], sn = sin_t[(long)t * 32 + lane];
+    float a = x0 * c - x1 * sn;
+    float bb = x0 * sn + x1 * c;
+    auto lane_stage = [&](int bit) {
+        float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
+        float pb = __shfl_xor_sync(0xffffffffu, bb, 1 << bit);
+        if (lane & (1 << bit)) { a = pa - a; bb = pb - bb; }
+        else { a = a + pa; bb = bb + pb; }
+    };
+    lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
+    { float lo = a, hi = bb; a = lo + hi; bb = lo - hi; }
+    lane_stage(0);
+    a = a / 8.0f;
+    bb = bb / 8.0f;
+    const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
+    const float sc = sym_scale_from(mx, mn);
+    const long o = ((long)b * H + h) * S + t;
+    if (lane == 0) s_out[o] = sc;
+    q_out[o * 64 + lane] = quant_s8(a, sc);
+    q_out[o * 64 + 32 + lane] = quant_s8(bb, sc);
+}
+
+// V [B][S][HKV][64] -> V^T [B][HKV][64][S] (keys contiguous, the K-major operand of P.V) and
+// vs [B][S][HKV] -> [B][HKV][S].
+__global__ void __launch_bounds__(256) attn_v_transpose_kernel(const int8_t* __restrict__ v, const float* __restrict__ vs,
+                                                               int B, int S, int HKV, int8_t* __restrict__ vT,
+                                                               float* __restrict__ vsT) {
+    __shared__ int8_t tile[64][64 + 4];
+    const int s0 = blockIdx.x * 64, h = blockIdx.y, b = blockIdx.z;
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+        const int r = i >> 4, c4 = i & 15;   // r: token in tile, c4: group of 4 dims
+        int val = 0;
+        if (s0 + r < S) val = *reinterpret_cast<const int*>(v + (((long)b * S + s0 + r) * HKV + h) * 64 + c4 * 4);
+        *reinterpret_cast<int*>(&tile[r][c4 * 4]) = val;
+    }
+    if (threadIdx.x < 64 && s0 + threadIdx.x < S)
+        vsT[((long)b * HKV + h) * S + s0 + threadIdx.x] = vs[((long)b * S + s0 + threadIdx.x) * HKV + h];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int d = i >> 6, r = i & 63;
+        if (s0 + r < S) vT[(((long)b * HKV + h) * 64 + d) * S + s0 + r] = tile[r][d];
+    }
+}
+
+// ------------------------------------------------------------------ main kernel
+struct AttnArgs {
+    int B, S, HQ, HKV;
+    const float* qs;    // [B][HQ][S]
+    const float* ks;    // [B][HKV][S]
+    const float* vs;    // [B][HKV][S]
+    const float* a_s;   // [HQ]
+    float* out;         // [B][S][HQ*64]
+    int32_t* oacc;      // optional, same shape
+    int* error_flag;
+};
+
+__device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;   // 8 rows of 64 bytes
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;            // SWIZZLE_64B
+    return d;
+}
+
+constexpr int ATT_KSLOTS = 3;
+constexpr int ATT_Q_BYTES = 128 * 64;
+constexpr int ATT_K_BYTES = 128 * 64;
+constexpr int ATT_V_BYTES = 64 * 128;
+constexpr int ATT_SLOT_BYTES = ATT_K_BYTES + ATT_V_BYTES;
+constexpr int ATT_P_BYTES = 128 * 128;
+constexpr int ATT_SMEM = ATT_Q_BYTES + ATT_KSLOTS * ATT_SLOT_BYTES + ATT_P_BYTES + 1024 + 256;
+constexpr int ATT_TMEM_COLS = 256;   // S: columns [0,128), O: columns [128,192)
+
+__global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmapQ,
+                                                              const __grid_constant__ CUtensorMap tmapK,
+                                                              const __grid_constant__ CUtensorMap tmapV,
+                                                              const AttnArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t sQ = base;
+    const uint32_t sKV = sQ + ATT_Q_BYTES;
+    const uint32_t sP = sKV + ATT_KSLOTS * ATT_SLOT_BYTES;
+    uint8_t* sP_ptr = base_ptr + ATT_Q_BYTES + ATT_KSLOTS * ATT_SLOT_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP_ptr + ATT_P_BYTES);
+    // barriers: q_full, k_full[3], k_empty[3], s_full, s_empty, p_full, p_empty, o_full
+    const uint32_t bar_qfull = smem_u32(bars);
+    const uint32_t bar_kfull = bar_qfull + 8;
+    const uint32_t bar_kempty = bar_kfull + 8 * ATT_KSLOTS;
+    const uint32_t bar_sfull = bar_kempty + 8 * ATT_KSLOTS;
+    const uint32_t bar_sempty = bar_sfull + 8;
+    const uint32_t bar_pfull = bar_sempty + 8;
+    const uint32_t bar_pempty = bar_pfull + 8;
+    const uint32_t bar_ofull = bar_pempty + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * ATT_KSLOTS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_qt = (args.S + 127) >> 7;
+    // heavy tiles (late queries) first
+    const int qt = n_qt - 1 - (int)(blockIdx.x % n_qt);
+    const int hq = (int)((blockIdx.x / n_qt) % args.HQ);
+    const int b = (int)(blockIdx.x / ((long)n_qt * args.HQ));
+    const int hkv = hq / (args.HQ / args.HKV);
+    const int n_kt = qt + 1;                        // causal: key tiles 0..qt
+    const int total_it = 3 * n_kt;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_qfull, 1);
+        for (int i = 0; i < ATT_KSLOTS; i++) { mbar_init(bar_kfull + 8 * i, 1); mbar_init(bar_kempty + 8 * i, 1); }
+        mbar_init(bar_sfull, 1); mbar_init(bar_sempty, 4);
+        mbar_init(bar_pfull, 4); mbar_init(bar_pempty, 1);
+        mbar_init(bar_ofull, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 5) { tmem_alloc(smem_u32(tmem_slot), ATT_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmapQ); tma_prefetch_desc(&tmapK); tma_prefetch_desc(&tmapV);
+            mbar_expect_tx(bar_qfull, ATT_Q_BYTES);
+            tma_load_2d(sQ, &tmapQ, bar_qfull, 0, ((b * args.HQ + hq) * args.S) + qt * 128);
+            int slot = 0; uint32_t phase = 0;
+            for (int it = 0; it < total_it; it++) {
+                const int sweep = it / n_kt, j = it - sweep * n_kt;
+                if (!mbar_wait(bar_kempty + 8 * slot, phase ^ 1u, abort_flag)) break;
+                const uint32_t full = bar_kfull + 8 * slot;
+                const uint32_t dst = sKV + slot * ATT_SLOT_BYTES;
+                mbar_expect_tx(full, sweep == 2 ? ATT_SLOT_BYTES : ATT_K_BYTES);
+                tma_load_2d(dst, &tmapK, full, 0, ((b * args.HKV + hkv) * args.S) + j * 128);
+                if (sweep == 2) tma_load_2d(dst + ATT_K_BYTES, &tmapV, full, j * 128, (b * args.HKV + hkv) * 64);
+                if (++slot == ATT_KSLOTS) { slot = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_i8(128, 128, 1, 1);
+            constexpr uint32_t idesc_pv = umma_idesc_i8(128, 64, 0, 1);   // P unsigned, V signed
+            bool ok = mbar_wait(bar_qfull, 0, abort_flag);
+            const uint64_t qdesc = umma_desc_k_sw64(sQ);
+            const uint64_t pdesc = umma_desc_k_sw128(sP);
+            int slot = 0; uint32_t kphase = 0;
+            // S and P are single-buffered: iteration `it` is their phase counter
+            for (int it = 0; ok && it < total_it; it++) {
+                const int sweep = it / n_kt, j = it - sweep * n_kt;
+                if (!mbar_wait(bar_kfull + 8 * slot, kphase, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar_sempty, (uint32_t)(it & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sK = sKV + slot * ATT_SLOT_BYTES;
+                const uint64_t kdesc = umma_desc_k_sw64(sK);
+                umma_i8(tmem_S, qdesc, kdesc, idesc_qk, 0u);
+                umma_i8(tmem_S, qdesc + 2, kdesc + 2, idesc_qk, 1u);
+                umma_commit(bar_sfull);
+                if (sweep < 2) {
+                    umma_commit(bar_kempty + 8 * slot);
+                } else {
+                    // P.V for this tile once the softmax warps have written U into shared memory
+                    if (!mbar_wait(bar_pfull, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t vdesc = umma_desc_k_sw128(sK + ATT_K_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) umma_i8(tmem_O, pdesc + 2 * k, vdesc + 2 * k, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar_pempty);
+                    umma_commit(bar_kempty + 8 * slot);
+                }
+                if (++slot == ATT_KSLOTS) { slot = 0; kphase ^= 1u; }
+            }
+            if (ok) umma_commit(bar_ofull);
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps 0..3
+        const int row_in_tile = warp * 32 + lane;
+        const int qpos = qt * 128 + row_in_tile;               // position of this thread's query
+        const bool q_ok = qpos < args.S;
+        const int qlim = q_ok ? qpos : -1;                   // keys 0..qlim are visible to this row
+        const float qscale = q_ok ? args.qs[((long)b * args.HQ + hq) * args.S + qpos] : 0.0f;
+        const float* ksp = args.ks + ((long)b * args.HKV + hkv) * args.S;
+        const float* vsp = args.vs + ((long)b * args.HKV + hkv) * args.S;
+        const float a_s = args.a_s[hq];
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        float mx = -1e32f;
+        float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+        float rinv = 0.f;
+        bool ok = true;
+        for (int it = 0; ok && it < total_it; it++) {
+            const int sweep = it / n_kt, j = it - sweep * n_kt;
+            if (sweep == 2 && j == 0) rinv = 1.0f / ((ps0 + ps1) + (ps2 + ps3));
+            int got = (lane == 0) ? (mbar_wait(bar_sfull, (uint32_t)(it & 1), abort_flag) ? 1 : 0) : 1;
+            if (sweep == 2 && got && lane == 0) got = mbar_wait(bar_pempty, (uint32_t)(j & 1) ^ 1u, abort_flag) ? 1 : 0;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) { ok = false; break; }
+            tc_fence_after();
+            const int k0 = j * 128;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_S + lane_addr + c * 32, v);
+                tmem_ld_wait();
+                const int kc = k0 + c * 32;
+                if (sweep == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int key = kc + i;
+                        if (key <= qlim) {
+                            const float x = (((float)(int)v[i] * qscale) * __ldg(ksp + key)) * 0.125f;
+                            mx = x > mx ? x : mx;
+                        }
+                    }
+                } else if (sweep == 1) {
+                    float e[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int key = kc + i;
+                        const float x = (((float)(int)v[i] * qscale) * __ldg(ksp + (key < args.S ? key : 0))) * 0.125f;
+                        e[i] = ref_expf(x - mx);
+                    }
+                    // ordered chains: key mod 4 == i mod 4 because kc is a multiple of 32
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (kc + i <= qlim) ps0 += e[i];
+                        if (kc + i + 1 <= qlim) ps1 += e[i + 1];
+                        if (kc + i + 2 <= qlim) ps2 += e[i + 2];
+                        if (kc + i + 3 <= qlim) ps3 += e[i + 3];
+                    }
+                } else {
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int key = kc + i;
+                        uint32_t u = 0;
+                        if (key <= qlim) {
+                            const float x = (((float)(int)v[i] * qscale) * __ldg(ksp + key)) * 0.125f;
+                            const float p = ref_expf(x - mx) * rinv;
+                            const float t = (p * __ldg(vsp + key)) / a_s;
+                            int r = (int)roundf(t);
+                            r = r > 255 ? 255 : r;
+                            u = (uint32_t)r & 0xffu;
+                        }
+                        if ((i & 3) == 0) packed[i >> 2] = u; else packed[i >> 2] |= u << (8 * (i & 3));
+                    }
+                    // row `row_in_tile` of the 128 x 128-byte U tile, 128-byte swizzle: 16-byte chunk
+                    // index XOR (row mod 8)
+                    uint8_t* prow = sP_ptr + row_in_tile * 128;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int chunk = (c * 2 + h) ^ (row_in_tile & 7);
+                        *reinterpret_cast<uint4*>(prow + chunk * 16) =
+                            make_uint4(packed[h * 4], packed[h * 4 + 1], packed[h * 4 + 2], packed[h * 4 + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            if (sweep == 2) fence_proxy_async_smem();   // make the U tile visible to the tensor core
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_sempty);
+                if (sweep == 2) mbar_arrive(bar_pfull);
+            }
+        }
+        // ---- epilogue: O -> out
+        if (ok) {
+            int got = (lane == 0) ? (mbar_wait(bar_ofull, 0, abort_flag) ? 1 : 0) : 1;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (got) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < 2; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_O + lane_addr + c * 32, v);
+                    tmem_ld_wait();
+                    if (q_ok) {
+                        const long o = (((long)b * args.S + qpos) * args.HQ + hq) * 64 + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 r;
+                            r.x = (float)(int)v[i] * a_s; r.y = (float)(int)v[i + 1] * a_s;
+                            r.z = (float)(int)v[i + 2] * a_s; r.w = (float)(int)v[i + 3] * a_s;
+                            *reinterpret_cast<float4*>(args.out + o + i) = r;
+                            if (args.oacc)
+                                *reinterpret_cast<int4*>(args.oacc + o + i) = make_int4((int)v[i], (int)v[i + 1], (int)v[i + 2], (int)v[i + 3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+        if (threadIdx.x == 0 && args.error_flag) atomicExch(args.error_flag, 1);
+        __syncthreads();
+    }
+    if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, ATT_TMEM_COLS); }
+}
+
+int* device_error_flag();
+
+}  // namespace flexllm
+
+using namespace flexllm;
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+extern "C" size_t flexllm_mha_prefill_workspace(int B, int S, int HQ, int HKV) {
+    if (B <= 0 || S <= 0 || HQ <= 0 || HKV <= 0) return 0;
+    size_t n = 0;
+    n += align_up((size_t)B * HQ * S * 64, 1024);          // q2
+    n += align_up((size_t)B * HKV * S * 64, 1024);         // k2
+    n += align_up((size_t)B * HKV * S * 64, 1024);         // v^T
+    n += align_up((size_t)B * HQ * S * 4, 1024);           // qs2
+    n += 2 * align_up((size_t)B * HKV * S * 4, 1024);      // ks2, vs^T
+    return n + 1024;
+}
+
+extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                                         const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
+                                         const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
+                                         void* workspace, size_t workspace_bytes, void* stream) {
+    FLEXLLM_REQUIRE(B >= 0 && S > 0 && HQ > 0 && HKV > 0 && HQ % HKV == 0);
+    if (B == 0) return FLEXLLM_OK;
+    FLEXLLM_REQUIRE(q && qs && k && ks && v && vs && cos_t && sin_t && a_s && out && workspace);
+    if (S % 16 != 0) return FLEXLLM_ENOTSUP;
+    FLEXLLM_REQUIRE(workspace_bytes >= flexllm_mha_prefill_workspace(B, S, HQ, HKV));
+    FLEXLLM_REQUIRE(aligned(out, 16) && (!oacc || aligned(oacc, 16)) && aligned(v, 4));
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* w = (uint8_t*)align_up((size_t)workspace, 1024);
+    int8_t* q2 = (int8_t*)w; w += align_up((size_t)B * HQ * S * 64, 1024);
+    int8_t* k2 = (int8_t*)w; w += align_up((size_t)B * HKV * S * 64, 1024);
+    int8_t* vT = (int8_t*)w; w += align_up((size_t)B * HKV * S * 64, 1024);
+    float* qs2 = (float*)w; w += align_up((size_t)B * HQ * S * 4, 1024);
+    float* ks2 = (float*)w; w += align_up((size_t)B * HKV * S * 4, 1024);
+    float* vsT = (float*)w;
+
+    {
+        const long wq = (long)B * S * HQ, wk = (long)B * S * HKV;
+        attn_qk_prepare_kernel<<<(unsigned)((wq + 7) / 8), 256, 0, st>>>(q, qs, cos_t, sin_t, B, S, HQ, q2, qs2);
+        attn_qk_prepare_kernel<<<(unsigned)((wk + 7) / 8), 256, 0, st>>>(k, ks, cos_t, sin_t, B, S, HKV, k2, ks2);
+        dim3 g((S + 63) / 64, HKV, B);
+        attn_v_transpose_kernel<<<g, 256, 0, st>>>(v, vs, B, S, HKV, vT, vsT);
+        int rc = launch_status();
+        if (rc != FLEXLLM_OK) return rc;
+    }
+    CUtensorMap tq, tk, tv;
+    int rc = make_tmap_2d_u8_box(&tq, q2, (uint64_t)B * HQ * S, 64, 64, 128, 64);
+    if (rc != FLEXLLM_OK) return rc;
+    rc = make_tmap_2d_u8_box(&tk, k2, (uint64_t)B * HKV * S, 64, 64, 128, 64);
+    if (rc != FLEXLLM_OK) return rc;
+    rc = make_tmap_2d_u8_box(&tv, vT, (uint64_t)B * HKV * 64, (uint64_t)S, 128, 64, 128);
+    if (rc != FLEXLLM_OK) return rc;
+    AttnArgs a;
+    a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = qs2; a.ks = ks2; a.vs = vsT; a.a_s = a_s; a.out = out; a.oacc = oacc;
+    a.error_flag = device_error_flag();
+    static bool attr_set = false;
+    if (!attr_set) {
+        FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
+        attr_set = true;
+    }
+    const int n_qt = (S + 127) / 128;
+    const long grid = (long)B * HQ * n_qt;
+    attn_prefill_kernel<<<(unsigned)grid, 192, ATT_SMEM, st>>>(tq, tk, tv, a);
+    return launch_status();
+}

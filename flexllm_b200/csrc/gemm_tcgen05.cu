@@ -47,19 +47,27 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+int make_tmap_2d_u8_box(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes,
+                        uint32_t box_rows, int swizzle_bytes) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return FLEXLLM_ECUDA;
     if (!aligned(base, 16) || (row_bytes % 16) != 0 || box_rows == 0 || box_rows > 256) return FLEXLLM_EINVAL;
+    if ((swizzle_bytes != 64 && swizzle_bytes != 128) || box_bytes == 0 || box_bytes > (uint32_t)swizzle_bytes || (box_bytes % 16) != 0)
+        return FLEXLLM_EINVAL;
     cuuint64_t dims[2] = {row_bytes, rows};
     cuuint64_t strides[1] = {row_bytes};
-    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t box[2] = {box_bytes, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return FLEXLLM_ECUDA; }
     return FLEXLLM_OK;
+}
+
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    return make_tmap_2d_u8_box(out, base, rows, row_bytes, 128, box_rows, 128);
 }
 
 // ------------------------------------------------------------------ kernel
@@ -292,7 +300,7 @@ static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64
     return FLEXLLM_OK;
 }
 
-static int* device_error_flag() {
+int* device_error_flag() {
     static thread_local int* flag[16] = {nullptr};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;

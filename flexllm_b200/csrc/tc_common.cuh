@@ -148,5 +148,8 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Encodes a 2-D tensor map for a row-major int8 matrix [rows][row_bytes] with a box of
 // {128 bytes, box_rows} and 128-byte swizzle. Returns FLEXLLM_* status.
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
+// General form: box of {box_bytes, box_rows}, swizzle_bytes in {64, 128} (box_bytes <= swizzle_bytes).
+int make_tmap_2d_u8_box(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes,
+                        uint32_t box_rows, int swizzle_bytes);
 
 }  // namespace flexllm

@@ -194,3 +194,82 @@ def dec_Logits_argmax(logits):
     idx = torch.empty((B,), dtype=torch.int32, device=logits.device)
     _call("flexllm_logits_argmax", _ptr(logits), B, V, _ptr(idx))
     return idx
+
+
+# ------------------------------------------------------------------------------ MHA_i8xi8
+def MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, cos_t, sin_t, a_s, want_oacc=False):
+    """Prefill GQA attention. q [B,S,HQ,64] s8, qs [B,S,HQ]; k,v [B,S,HKV,64], ks,vs [B,S,HKV];
+    a_s [HQ]. Returns (out fp32 [B,S,HQ*64], oacc int32 | None)."""
+    B, S, HQ, D = q.shape
+    HKV = k.shape[2]
+    assert D == 64
+    nbytes = lib().flexllm_mha_prefill_workspace(B, S, HQ, HKV)
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+    out = torch.empty((B, S, HQ * 64), dtype=torch.float32, device=q.device)
+    oacc = torch.empty((B, S, HQ * 64), dtype=torch.int32, device=q.device) if want_oacc else None
+    _call("flexllm_mha_i8xi8_prefill", _ptr(q), _ptr(qs), _ptr(k), _ptr(ks), _ptr(v), _ptr(vs), _ptr(cos_t),
+          _ptr(sin_t), _ptr(a_s), B, S, HQ, HKV, _ptr(out), _ptr(oacc), _ptr(ws), nbytes)
+    return out, oacc
+
+
+class KVCache:
+    """Paged int8 KV cache (library-owned device memory). Pools of one layer are exposed as torch
+    views: k [n_pages,HKV,64,64] (token-major rows), v [n_pages,HKV,64 dims,64 tokens] (transposed
+    inside the page), ks/vs [n_pages,HKV,64]."""
+
+    def __init__(self, layers, n_pages, hkv, page=64, device="cuda"):
+        self.layers, self.n_pages, self.hkv, self.page = layers, n_pages, hkv, page
+        self._h = C.c_void_p()
+        _check("flexllm_kv_cache_create", lib().flexllm_kv_cache_create(C.byref(self._h), layers, n_pages, hkv, page))
+        self.device = torch.device(device)
+
+    def close(self):
+        if self._h:
+            lib().flexllm_kv_cache_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def reset(self):
+        _check("flexllm_kv_cache_reset", lib().flexllm_kv_cache_reset(self._h, _stream()))
+
+    def _view(self, ptr, shape, dtype):
+        n = 1
+        for d in shape:
+            n *= d
+        esz = torch.empty((), dtype=dtype).element_size()
+        buf = (C.c_byte * (n * esz)).from_address(ptr)
+        # wrap device memory: torch needs a CUDA array interface
+        class _Holder:
+            pass
+        h = _Holder()
+        typestr = {torch.int8: "|i1", torch.float32: "<f4"}[dtype]
+        h.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+        return torch.as_tensor(h, device=self.device)
+
+    def pools(self, layer):
+        k, ks, v, vs = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        _check("flexllm_kv_cache_pools", lib().flexllm_kv_cache_pools(self._h, layer, C.byref(k), C.byref(ks), C.byref(v), C.byref(vs)))
+        P, H, T = self.n_pages, self.hkv, self.page
+        return (self._view(k.value, (P, H, T, 64), torch.int8), self._view(ks.value, (P, H, T), torch.float32),
+                self._view(v.value, (P, H, 64, T), torch.int8), self._view(vs.value, (P, H, T), torch.float32))
+
+
+def MHA_i8xi8_Decoding(cache, layer, q, qs, k, ks, v, vs, cos_t, sin_t, a_s, page_table, ctx, max_ctx, want_oacc=False):
+    """One decode step of attention on `layer`. q [B,HQ,64] s8, qs [B,HQ]; k,v [B,HKV,64], ks,vs [B,HKV];
+    page_table [B,max_pages] int32; ctx [B] int32 (tokens already cached, device); max_ctx >= max(ctx).
+    The new k,v are appended to the cache. Returns (out fp32 [B,HQ*64], oacc | None)."""
+    B, HQ, D = q.shape
+    assert D == 64
+    nbytes = lib().flexllm_mha_decode_workspace(B, HQ, max_ctx)
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+    out = torch.empty((B, HQ * 64), dtype=torch.float32, device=q.device)
+    oacc = torch.empty((B, HQ * 64), dtype=torch.int32, device=q.device) if want_oacc else None
+    _check("flexllm_mha_i8xi8_decode", lib().flexllm_mha_i8xi8_decode(
+        cache._h, layer, _ptr(q), _ptr(qs), _ptr(k), _ptr(ks), _ptr(v), _ptr(vs), _ptr(cos_t), _ptr(sin_t), _ptr(a_s),
+        _ptr(page_table), page_table.shape[1], _ptr(ctx), max_ctx, B, HQ, _ptr(out), _ptr(oacc), _ptr(ws), nbytes, _stream()))
+    return out, oacc

@@ -123,6 +123,46 @@ FLEXLLM_API int flexllm_logits_argmax(const float* logits, int B, long V, int32_
 FLEXLLM_API int flexllm_qk_prepare(const int8_t* q, const float* s, const int32_t* pos, const float* cos_t,
                        const float* sin_t, long T, int H, int8_t* q_out, float* s_out, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Prefill GQA attention, int8 x int8 (replaces the graph MHA_i8xi8_Prefilling_tb,
+ * SpinQuant_Llama_32_1B/MHA_i8xi8.h:369-427, with per-head-per-token scales).
+ * q [B][S][HQ][64] s8, qs [B][S][HQ]; k,v [B][S][HKV][64] s8, ks,vs [B][S][HKV]; a_s [HQ];
+ * out fp32 [B][S][HQ*64]. Steps: qk_prepare on q and k (positions 0..S-1) -> S = q.k^T (s32) ->
+ * score = ((float)S*qs)*ks*0.125 -> causal softmax -> P~ = P*vs[key] -> u8 = min(round(P~/a_s),255)
+ * -> O = u8 x v (s32) -> out = (float)O * a_s.  oacc (optional) receives the int32 O.
+ * workspace: flexllm_mha_prefill_workspace(B,S,HQ,HKV) bytes.
+ * ------------------------------------------------------------------------------------------- */
+FLEXLLM_API size_t flexllm_mha_prefill_workspace(int B, int S, int HQ, int HKV);
+FLEXLLM_API int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                              const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
+                              const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Paged int8 KV cache (replaces dec_K_cache_manager / dec_V_cache_manager and their scale caches,
+ * Modules/MHA.h:393-559, :713-851). One pool per layer set: pages of `page` tokens;
+ * K,V pages [n_pages][HKV][page][64] s8, scale pages [n_pages][HKV][page] fp32, per layer.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct flexllm_kv_cache flexllm_kv_cache;
+FLEXLLM_API int flexllm_kv_cache_create(flexllm_kv_cache** out, int layers, int n_pages, int hkv, int page);
+FLEXLLM_API int flexllm_kv_cache_destroy(flexllm_kv_cache* c);
+FLEXLLM_API int flexllm_kv_cache_reset(flexllm_kv_cache* c, void* stream);
+/* raw device pointers of one layer's pools (for tests and zero-copy hand-off) */
+FLEXLLM_API int flexllm_kv_cache_pools(flexllm_kv_cache* c, int layer, int8_t** k, float** ks, int8_t** v, float** vs);
+
+/* One decode step of attention for B sequences on one layer (replaces the graph
+ * MHA_i8xi8_decoding_tb, MHA_i8xi8.h:1027-1114): qk_prepare of the new q,k at position ctx[b];
+ * append k,v to the cache; attention over ctx[b]+1 keys; out fp32 [B][HQ*64].
+ * q [B][HQ][64], qs [B][HQ]; k,v [B][HKV][64], ks,vs [B][HKV]; page_table [B][max_pages] s32;
+ * ctx [B] s32 (tokens already cached). */
+FLEXLLM_API size_t flexllm_mha_decode_workspace(int B, int HQ, int max_ctx);
+FLEXLLM_API int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs,
+                             const int8_t* k, const float* ks, const int8_t* v, const float* vs,
+                             const float* cos_t, const float* sin_t, const float* a_s,
+                             const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx,
+                             int B, int HQ, float* out, int32_t* oacc, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
