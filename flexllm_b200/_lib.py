@@ -35,7 +35,27 @@ SIGNATURES = {
     "flexllm_kv_cache_pools": [_P, _I, _P, _P, _P, _P],
     "flexllm_mha_decode_workspace": [_I, _I, _I],
     "flexllm_mha_i8xi8_decode": [_P, _I] + [_P] * 10 + [_I, _P, _I, _I, _I, _P, _P, _P, _SZ, _P],
+    "flexllm_model_create": [_P, _P],
+    "flexllm_model_destroy": [_P],
+    "flexllm_model_load_layer": [_P, _I, _P, _P],
+    "flexllm_model_load_head": [_P, _P, _P, _P, _P, _P, _I, _P],
+    "flexllm_model_prefill": [_P, _P, _I, _I, _P, _P],
+    "flexllm_model_begin": [_P, _I, _P],
+    "flexllm_model_decode": [_P, _I, _I, _P],
+    "flexllm_model_generate_host": [_P, _P, _I, _I, _I, _P, _I, _P],
+    "flexllm_model_buffer": [_P, _I, _P],
 }
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [("layers", _I), ("hidden", _I), ("heads_q", _I), ("heads_kv", _I), ("ffn", _I), ("vocab", _I),
+                ("eps", _F), ("fht_scale", _F), ("max_batch", _I), ("max_prefill", _I), ("max_ctx", _I)]
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [(n, _P) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "sq", "sk", "sv", "so", "sg", "su", "sd",
+                                  "gamma0", "gamma1", "a_s")]
+
 RESTYPES = {"flexllm_status_string": C.c_char_p, "flexllm_mha_prefill_workspace": C.c_size_t,
             "flexllm_mha_decode_workspace": C.c_size_t}
 

@@ -59,9 +59,13 @@ static inline KvLayer kv_layer(const flexllm_kv_cache* c, int layer) {
 // ---- 1. append ---------------------------------------------------------------------------------
 // One warp per (sequence, head). Heads [0,HQ) are query heads, [HQ, HQ+HKV) key heads,
 // [HQ+HKV, HQ+2*HKV) value heads.
+// With IN_F32 the inputs are one fp32 row [ (HQ+2*HKV)*64 ] per sequence (q heads, k heads, v heads,
+// the output of the fused q/k/v projection); value heads are then quantised per head here.
+template <bool IN_F32>
 __global__ void __launch_bounds__(256) dec_append_kernel(const int8_t* __restrict__ q, const float* __restrict__ qs,
                                                          const int8_t* __restrict__ k, const float* __restrict__ ks,
                                                          const int8_t* __restrict__ v, const float* __restrict__ vs,
+                                                         const float* __restrict__ qkv_f32,
                                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                          KvLayer cache, const int32_t* __restrict__ page_table, int max_pages,
                                                          const int32_t* __restrict__ ctx, int B, int HQ, int HKV,
@@ -74,21 +78,37 @@ __global__ void __launch_bounds__(256) dec_append_kernel(const int8_t* __restric
     const int pos = ctx[b];
     const long pg = page_table[(long)b * max_pages + pos / PAGE];
     const int slot = pos % PAGE;
-    if (h >= HQ + HKV) {   // value head: plain copy into the transposed page
+    if (h >= HQ + HKV) {   // value head: into the transposed page
         const int hv = h - HQ - HKV;
-        const int8_t* src = v + ((long)b * HKV + hv) * 64;
         int8_t* dst = cache.v + (pg * HKV + hv) * (long)(64 * PAGE);
-        dst[(long)lane * PAGE + slot] = src[lane];
-        dst[(long)(lane + 32) * PAGE + slot] = src[lane + 32];
-        if (lane == 0) cache.vs[(pg * HKV + hv) * PAGE + slot] = vs[(long)b * HKV + hv];
+        if (IN_F32) {
+            const float* src = qkv_f32 + (long)b * heads * 64 + (long)h * 64;
+            const float a = src[lane], bb = src[lane + 32];
+            const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
+            const float sc = sym_scale_from(mx, mn);
+            dst[(long)lane * PAGE + slot] = quant_s8(a, sc);
+            dst[(long)(lane + 32) * PAGE + slot] = quant_s8(bb, sc);
+            if (lane == 0) cache.vs[(pg * HKV + hv) * PAGE + slot] = sc;
+        } else {
+            const int8_t* src = v + ((long)b * HKV + hv) * 64;
+            dst[(long)lane * PAGE + slot] = src[lane];
+            dst[(long)(lane + 32) * PAGE + slot] = src[lane + 32];
+            if (lane == 0) cache.vs[(pg * HKV + hv) * PAGE + slot] = vs[(long)b * HKV + hv];
+        }
         return;
     }
     const bool is_q = h < HQ;
     const int hh = is_q ? h : h - HQ;
-    const int8_t* src = is_q ? q + ((long)b * HQ + hh) * 64 : k + ((long)b * HKV + hh) * 64;
-    const float sc_in = is_q ? qs[(long)b * HQ + hh] : ks[(long)b * HKV + hh];
-    const float x0 = (float)src[lane] * sc_in;
-    const float x1 = (float)src[lane + 32] * sc_in;
+    float x0, x1;
+    if (IN_F32) {
+        const float* src = qkv_f32 + (long)b * heads * 64 + (long)h * 64;
+        x0 = src[lane]; x1 = src[lane + 32];
+    } else {
+        const int8_t* src = is_q ? q + ((long)b * HQ + hh) * 64 : k + ((long)b * HKV + hh) * 64;
+        const float sc_in = is_q ? qs[(long)b * HQ + hh] : ks[(long)b * HKV + hh];
+        x0 = (float)src[lane] * sc_in;
+        x1 = (float)src[lane + 32] * sc_in;
+    }
     const float c = cos_t[(long)pos * 32 + lane], sn = sin_t[(long)pos * 32 + lane];
     float a = x0 * c - x1 * sn;
     float bb = x0 * sn + x1 * c;
@@ -349,6 +369,47 @@ extern "C" size_t flexllm_mha_decode_workspace(int B, int HQ, int max_ctx) {
     return n + 256;
 }
 
+namespace flexllm {
+// Shared body of the int8 and fp32 front ends (qkv_f32 != nullptr selects the latter).
+int mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                   const int8_t* v, const float* vs, const float* qkv_f32, const float* cos_t, const float* sin_t,
+                   const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, int HQ,
+                   float* out, int32_t* oacc, void* workspace, cudaStream_t st);
+
+// K/V of a prefilled batch -> cache pages. k2 [B][HKV][S][64], ks2 [B][HKV][S], vT [B][HKV][64][S],
+// vsT [B][HKV][S] (the prefill attention's workspace layouts); sequence b occupies positions 0..S-1.
+__global__ void __launch_bounds__(256) kv_pack_kernel(const int8_t* __restrict__ k2, const float* __restrict__ ks2,
+                                                      const int8_t* __restrict__ vT, const float* __restrict__ vsT, KvLayer cache,
+                                                      const int32_t* __restrict__ page_table, int max_pages, int S, int HKV) {
+    const int p = blockIdx.x, h = blockIdx.y, b = blockIdx.z;      // page index within the sequence
+    const long pg = page_table[(long)b * max_pages + p];
+    const int t0 = p * PAGE;
+    const int n = min(PAGE, S - t0);
+    const long prow = (pg * HKV + h) * PAGE;
+    const long src_row = ((long)b * HKV + h) * S + t0;
+    // K rows: n x 64 bytes contiguous on both sides
+    for (int i = threadIdx.x; i < n * 16; i += 256)
+        reinterpret_cast<int*>(cache.k + prow * 64)[i] = reinterpret_cast<const int*>(k2 + src_row * 64)[i];
+    for (int i = threadIdx.x; i < n; i += 256) {
+        cache.ks[prow + i] = ks2[src_row + i];
+        cache.vs[prow + i] = vsT[src_row + i];
+    }
+    // V^T: for each dim, n contiguous tokens
+    for (int i = threadIdx.x; i < 64 * PAGE; i += 256) {
+        const int d = i / PAGE, t = i % PAGE;
+        if (t < n) cache.v[prow * 64 + (long)d * PAGE + t] = vT[(((long)b * HKV + h) * 64 + d) * S + t0 + t];
+    }
+}
+
+int kv_pack(flexllm_kv_cache* c, int layer, const int8_t* k2, const float* ks2, const int8_t* vT, const float* vsT,
+            const int32_t* page_table, int max_pages, int B, int S, cudaStream_t st) {
+    KvLayer L = kv_layer(c, layer);
+    dim3 g((S + PAGE - 1) / PAGE, c->hkv, B);
+    kv_pack_kernel<<<g, 256, 0, st>>>(k2, ks2, vT, vsT, L, page_table, max_pages, S, c->hkv);
+    return launch_status();
+}
+}  // namespace flexllm
+
 extern "C" int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs,
                                         const int8_t* k, const float* ks, const int8_t* v, const float* vs,
                                         const float* cos_t, const float* sin_t, const float* a_s,
@@ -358,12 +419,19 @@ extern "C" int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const in
     FLEXLLM_REQUIRE(c && layer >= 0 && layer < c->layers && B >= 0 && HQ > 0 && max_ctx >= 0 && max_pages > 0);
     if (B == 0) return FLEXLLM_OK;
     FLEXLLM_REQUIRE(q && qs && k && ks && v && vs && cos_t && sin_t && a_s && page_table && ctx && out && workspace);
-    const int HKV = c->hkv;
-    FLEXLLM_REQUIRE(HQ % HKV == 0);
-    if (HQ / HKV != 4) return FLEXLLM_ENOTSUP;
+    FLEXLLM_REQUIRE(HQ % c->hkv == 0);
+    if (HQ / c->hkv != 4) return FLEXLLM_ENOTSUP;
     FLEXLLM_REQUIRE((long)max_pages * PAGE > max_ctx);
     FLEXLLM_REQUIRE(workspace_bytes >= flexllm_mha_decode_workspace(B, HQ, max_ctx));
-    cudaStream_t st = (cudaStream_t)stream;
+    return mha_decode_run(c, layer, q, qs, k, ks, v, vs, nullptr, cos_t, sin_t, a_s, page_table, max_pages, ctx, max_ctx, B,
+                          HQ, out, oacc, workspace, (cudaStream_t)stream);
+}
+
+int flexllm::mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                            const int8_t* v, const float* vs, const float* qkv_f32, const float* cos_t, const float* sin_t,
+                            const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B,
+                            int HQ, float* out, int32_t* oacc, void* workspace, cudaStream_t st) {
+    const int HKV = c->hkv;
     const int ctx_stride = (int)align_up((size_t)max_ctx + 1, 64);
     const int nsplit = (ctx_stride + KEYS_PER_CTA - 1) / KEYS_PER_CTA;
     uint8_t* w = (uint8_t*)align_up((size_t)workspace, 256);
@@ -376,8 +444,12 @@ extern "C" int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const in
     KvLayer L = kv_layer(c, layer);
 
     const int warps = B * (HQ + 2 * HKV);
-    dec_append_kernel<<<(warps + 7) / 8, 256, 0, st>>>(q, qs, k, ks, v, vs, cos_t, sin_t, L, page_table, max_pages, ctx, B,
-                                                       HQ, HKV, q2, qs2);
+    if (qkv_f32)
+        dec_append_kernel<true><<<(warps + 7) / 8, 256, 0, st>>>(q, qs, k, ks, v, vs, qkv_f32, cos_t, sin_t, L, page_table,
+                                                                 max_pages, ctx, B, HQ, HKV, q2, qs2);
+    else
+        dec_append_kernel<false><<<(warps + 7) / 8, 256, 0, st>>>(q, qs, k, ks, v, vs, nullptr, cos_t, sin_t, L, page_table,
+                                                                  max_pages, ctx, B, HQ, HKV, q2, qs2);
     dim3 grid(nsplit, HKV, B);
     dec_scores_kernel<4><<<grid, 256, 0, st>>>(q2, qs2, L, page_table, max_pages, ctx, HQ, HKV, ctx_stride, nsplit, scores, smax);
     dec_softmax_kernel<<<B * HQ, 128, 0, st>>>(ctx, HQ, ctx_stride, nsplit, scores, smax, rinv);

@@ -354,21 +354,135 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_const
 
 int* device_error_flag();
 
+// fp32 front end used by the model: qkv [B*S][(HQ+2*HKV)*64] fp32 as the fused q/k/v projection
+// writes it. Query and key heads: RoPE -> FHT-64/8 -> per-head int8 (head-major outputs); value
+// heads: per-head int8 quant (quant.h:527-650) written token-major for the transpose kernel.
+__global__ void __launch_bounds__(256) attn_qkv_prepare_f32_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                                                   const float* __restrict__ sin_t, int B, int S, int HQ, int HKV,
+                                                                   int8_t* __restrict__ q2, float* __restrict__ qs2,
+                                                                   int8_t* __restrict__ k2, float* __restrict__ ks2,
+                                                                   int8_t* __restrict__ v2, float* __restrict__ vs2) {
+    const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int heads = HQ + 2 * HKV;
+    if (w >= (long)B * S * heads) return;
+    const int h = (int)(w % heads);
+    const long bt = w / heads;
+    const int t = (int)(bt % S);
+    const int b = (int)(bt / S);
+    const float* src = qkv + bt * (long)heads * 64 + (long)h * 64;
+    const float x0 = src[lane], x1 = src[lane + 32];
+    float a, bb;
+    const bool rotate = h < HQ + HKV;
+    if (rotate) {
+        const float c = cos_t[(long)t * 32 + lane], sn = sin_t[(long)t * 32 + lane];
+        a = x0 * c - x1 * sn;
+        bb = x0 * sn + x1 * c;
+        auto lane_stage = [&](int bit) {
+            float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
+            float pb = __shfl_xor_sync(0xffffffffu, bb, 1 << bit);
+            if (lane & (1 << bit)) { a = pa - a; bb = pb - bb; }
+            else { a = a + pa; bb = bb + pb; }
+        };
+        lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
+        { float lo = a, hi = bb; a = lo + hi; bb = lo - hi; }
+        lane_stage(0);
+        a = a / 8.0f;
+        bb = bb / 8.0f;
+    } else {
+        a = x0; bb = x1;
+    }
+    const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
+    const float sc = sym_scale_from(mx, mn);
+    int8_t* dst; float* sdst;
+    if (h < HQ) { const long o = ((long)b * HQ + h) * S + t; dst = q2 + o * 64; sdst = qs2 + o; }
+    else if (h < HQ + HKV) { const long o = ((long)b * HKV + (h - HQ)) * S + t; dst = k2 + o * 64; sdst = ks2 + o; }
+    else { const long o = ((long)b * S + t) * HKV + (h - HQ - HKV); dst = v2 + o * 64; sdst = vs2 + o; }
+    if (lane == 0) *sdst = sc;
+    dst[lane] = quant_s8(a, sc);
+    dst[lane + 32] = quant_s8(bb, sc);
+}
+
+static size_t align_up_(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Workspace carve-up shared by both front ends.
+struct PrefillWs {
+    int8_t *q2, *k2, *vT, *v2;
+    float *qs2, *ks2, *vsT, *vs2;
+    static size_t bytes(int B, int S, int HQ, int HKV) {
+        size_t n = 0;
+        n += align_up_((size_t)B * HQ * S * 64, 1024);
+        n += 3 * align_up_((size_t)B * HKV * S * 64, 1024);
+        n += align_up_((size_t)B * HQ * S * 4, 1024);
+        n += 3 * align_up_((size_t)B * HKV * S * 4, 1024);
+        return n + 1024;
+    }
+    PrefillWs(void* ws, int B, int S, int HQ, int HKV) {
+        uint8_t* w = (uint8_t*)align_up_((size_t)ws, 1024);
+        q2 = (int8_t*)w; w += align_up_((size_t)B * HQ * S * 64, 1024);
+        k2 = (int8_t*)w; w += align_up_((size_t)B * HKV * S * 64, 1024);
+        vT = (int8_t*)w; w += align_up_((size_t)B * HKV * S * 64, 1024);
+        v2 = (int8_t*)w; w += align_up_((size_t)B * HKV * S * 64, 1024);
+        qs2 = (float*)w; w += align_up_((size_t)B * HQ * S * 4, 1024);
+        ks2 = (float*)w; w += align_up_((size_t)B * HKV * S * 4, 1024);
+        vsT = (float*)w; w += align_up_((size_t)B * HKV * S * 4, 1024);
+        vs2 = (float*)w;
+    }
+};
+
+static int mha_prefill_core(const PrefillWs& ws, const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
+                            cudaStream_t st) {
+    CUtensorMap tq, tk, tv;
+    int rc = make_tmap_2d_u8_box(&tq, ws.q2, (uint64_t)B * HQ * S, 64, 64, 128, 64);
+    if (rc != FLEXLLM_OK) return rc;
+    rc = make_tmap_2d_u8_box(&tk, ws.k2, (uint64_t)B * HKV * S, 64, 64, 128, 64);
+    if (rc != FLEXLLM_OK) return rc;
+    rc = make_tmap_2d_u8_box(&tv, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, 128, 64, 128);
+    if (rc != FLEXLLM_OK) return rc;
+    AttnArgs a;
+    a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.a_s = a_s; a.out = out; a.oacc = oacc;
+    a.error_flag = device_error_flag();
+    static bool attr_set = false;
+    if (!attr_set) {
+        FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
+        attr_set = true;
+    }
+    const int n_qt = (S + 127) / 128;
+    const long grid = (long)B * HQ * n_qt;
+    attn_prefill_kernel<<<(unsigned)grid, 192, ATT_SMEM, st>>>(tq, tk, tv, a);
+    return launch_status();
+}
+
+size_t mha_prefill_ws_bytes(int B, int S, int HQ, int HKV) { return PrefillWs::bytes(B, S, HQ, HKV); }
+
+// Model path: attention from the fp32 output of the fused q/k/v projection. Leaves the prepared
+// K (head-major int8 + scales) and V^T in the workspace for the KV-cache pack that follows.
+int mha_prefill_f32(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int S, int HQ, int HKV,
+                    float* out, void* workspace, cudaStream_t st, const int8_t** k2, const float** ks2, const int8_t** vT,
+                    const float** vsT) {
+    if (S % 16 != 0) return FLEXLLM_ENOTSUP;
+    PrefillWs ws(workspace, B, S, HQ, HKV);
+    const long warps = (long)B * S * (HQ + 2 * HKV);
+    attn_qkv_prepare_f32_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(qkv, cos_t, sin_t, B, S, HQ, HKV, ws.q2, ws.qs2,
+                                                                            ws.k2, ws.ks2, ws.v2, ws.vs2);
+    dim3 g((S + 63) / 64, HKV, B);
+    attn_v_transpose_kernel<<<g, 256, 0, st>>>(ws.v2, ws.vs2, B, S, HKV, ws.vT, ws.vsT);
+    int rc = launch_status();
+    if (rc != FLEXLLM_OK) return rc;
+    if (k2) *k2 = ws.k2;
+    if (ks2) *ks2 = ws.ks2;
+    if (vT) *vT = ws.vT;
+    if (vsT) *vsT = ws.vsT;
+    return mha_prefill_core(ws, a_s, B, S, HQ, HKV, out, nullptr, st);
+}
+
 }  // namespace flexllm
 
 using namespace flexllm;
 
-static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
-
 extern "C" size_t flexllm_mha_prefill_workspace(int B, int S, int HQ, int HKV) {
     if (B <= 0 || S <= 0 || HQ <= 0 || HKV <= 0) return 0;
-    size_t n = 0;
-    n += align_up((size_t)B * HQ * S * 64, 1024);          // q2
-    n += align_up((size_t)B * HKV * S * 64, 1024);         // k2
-    n += align_up((size_t)B * HKV * S * 64, 1024);         // v^T
-    n += align_up((size_t)B * HQ * S * 4, 1024);           // qs2
-    n += 2 * align_up((size_t)B * HKV * S * 4, 1024);      // ks2, vs^T
-    return n + 1024;
+    return PrefillWs::bytes(B, S, HQ, HKV);
 }
 
 extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
@@ -382,40 +496,13 @@ extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const
     FLEXLLM_REQUIRE(workspace_bytes >= flexllm_mha_prefill_workspace(B, S, HQ, HKV));
     FLEXLLM_REQUIRE(aligned(out, 16) && (!oacc || aligned(oacc, 16)) && aligned(v, 4));
     cudaStream_t st = (cudaStream_t)stream;
-    uint8_t* w = (uint8_t*)align_up((size_t)workspace, 1024);
-    int8_t* q2 = (int8_t*)w; w += align_up((size_t)B * HQ * S * 64, 1024);
-    int8_t* k2 = (int8_t*)w; w += align_up((size_t)B * HKV * S * 64, 1024);
-    int8_t* vT = (int8_t*)w; w += align_up((size_t)B * HKV * S * 64, 1024);
-    float* qs2 = (float*)w; w += align_up((size_t)B * HQ * S * 4, 1024);
-    float* ks2 = (float*)w; w += align_up((size_t)B * HKV * S * 4, 1024);
-    float* vsT = (float*)w;
-
-    {
-        const long wq = (long)B * S * HQ, wk = (long)B * S * HKV;
-        attn_qk_prepare_kernel<<<(unsigned)((wq + 7) / 8), 256, 0, st>>>(q, qs, cos_t, sin_t, B, S, HQ, q2, qs2);
-        attn_qk_prepare_kernel<<<(unsigned)((wk + 7) / 8), 256, 0, st>>>(k, ks, cos_t, sin_t, B, S, HKV, k2, ks2);
-        dim3 g((S + 63) / 64, HKV, B);
-        attn_v_transpose_kernel<<<g, 256, 0, st>>>(v, vs, B, S, HKV, vT, vsT);
-        int rc = launch_status();
-        if (rc != FLEXLLM_OK) return rc;
-    }
-    CUtensorMap tq, tk, tv;
-    int rc = make_tmap_2d_u8_box(&tq, q2, (uint64_t)B * HQ * S, 64, 64, 128, 64);
+    PrefillWs ws(workspace, B, S, HQ, HKV);
+    const long wq = (long)B * S * HQ, wk = (long)B * S * HKV;
+    attn_qk_prepare_kernel<<<(unsigned)((wq + 7) / 8), 256, 0, st>>>(q, qs, cos_t, sin_t, B, S, HQ, ws.q2, ws.qs2);
+    attn_qk_prepare_kernel<<<(unsigned)((wk + 7) / 8), 256, 0, st>>>(k, ks, cos_t, sin_t, B, S, HKV, ws.k2, ws.ks2);
+    dim3 g((S + 63) / 64, HKV, B);
+    attn_v_transpose_kernel<<<g, 256, 0, st>>>(v, vs, B, S, HKV, ws.vT, ws.vsT);
+    int rc = launch_status();
     if (rc != FLEXLLM_OK) return rc;
-    rc = make_tmap_2d_u8_box(&tk, k2, (uint64_t)B * HKV * S, 64, 64, 128, 64);
-    if (rc != FLEXLLM_OK) return rc;
-    rc = make_tmap_2d_u8_box(&tv, vT, (uint64_t)B * HKV * 64, (uint64_t)S, 128, 64, 128);
-    if (rc != FLEXLLM_OK) return rc;
-    AttnArgs a;
-    a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = qs2; a.ks = ks2; a.vs = vsT; a.a_s = a_s; a.out = out; a.oacc = oacc;
-    a.error_flag = device_error_flag();
-    static bool attr_set = false;
-    if (!attr_set) {
-        FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
-        attr_set = true;
-    }
-    const int n_qt = (S + 127) / 128;
-    const long grid = (long)B * HQ * n_qt;
-    attn_prefill_kernel<<<(unsigned)grid, 192, ATT_SMEM, st>>>(tq, tk, tv, a);
-    return launch_status();
+    return mha_prefill_core(ws, a_s, B, S, HQ, HKV, out, oacc, st);
 }

@@ -66,8 +66,12 @@ __device__ __forceinline__ float sym_scale_from(float mx, float mn) {
 
 __device__ __forceinline__ int8_t quant_s8(float x, float s) { return (int8_t)(int)roundf(x / s); }
 
-// exp() used by SiLU and softmax. The reference calls the host libm's expf.
-__device__ __forceinline__ float ref_expf(float x) { return expf(x); }
+// exp() used by SiLU and softmax. The reference calls the C library's expf, whose last-bit
+// rounding the C standard leaves open. This build evaluates the CORRECTLY ROUNDED single-precision
+// exponential: exp in double precision (error below one double ulp), rounded once to fp32. The
+// result is independent of the device math library's fp32 approximation and is reproduced bit for
+// bit by (float)exp((double)x) on any host with an accurate double-precision libm.
+__device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + ref_expf(-g)); }
 

@@ -31,7 +31,7 @@ __device__ __forceinline__ void reg_butterfly(float (&r)[32]) {
 
 // FUSED: 0 = y = FHT(x)/scale (fp32 out); 1 = h = silu(g)*u, FHT, /scale, per-token int8 quant.
 template <int FUSED>
-__global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ x, const float* __restrict__ u,
+__global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ x, const float* __restrict__ u, long ld_in,
                                                       float scale, float* __restrict__ y, int8_t* __restrict__ q,
                                                       float* __restrict__ s, float* __restrict__ act) {
     constexpr int N = 8192;
@@ -39,8 +39,8 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
     __shared__ float red[64];
     const int tid = threadIdx.x;
     const long row = blockIdx.x;
-    const float4* xr = reinterpret_cast<const float4*>(x + row * N);
-    const float4* ur = FUSED ? reinterpret_cast<const float4*>(u + row * N) : nullptr;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * ld_in);   // ld_in: input row stride in floats
+    const float4* ur = FUSED ? reinterpret_cast<const float4*>(u + row * ld_in) : nullptr;
 #pragma unroll
     for (int it = 0; it < N / 1024; it++) {
         const int c = it * 256 + tid;
@@ -164,6 +164,13 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const int8_t* __restric
     q_out[w * 64 + 32 + lane] = quant_s8(b, sc);
 }
 
+// gate and up halves of one fused projection output: rows of `ld` floats, gate at g, up at u
+int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st) {
+    if (M == 0) return FLEXLLM_OK;
+    fht8192_kernel<1><<<M, 256, 0, st>>>(g, u, ld, scale, nullptr, q, s, nullptr);
+    return launch_status();
+}
+
 }  // namespace flexllm
 
 using namespace flexllm;
@@ -173,7 +180,7 @@ extern "C" int flexllm_fht(const float* x, long rows, int N, float scale, float*
     if (rows == 0) return FLEXLLM_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (N == 8192 && aligned(x, 16) && aligned(y, 16)) {
-        fht8192_kernel<0><<<(unsigned)rows, 256, 0, st>>>(x, nullptr, scale, y, nullptr, nullptr, nullptr);
+        fht8192_kernel<0><<<(unsigned)rows, 256, 0, st>>>(x, nullptr, N, scale, y, nullptr, nullptr, nullptr);
     } else {
         int threads = N / 2 < 256 ? (N / 2 < 32 ? 32 : N / 2) : 256;
         fht_generic_kernel<<<(unsigned)rows, threads, N * sizeof(float), st>>>(x, N, scale, y);
@@ -187,7 +194,7 @@ extern "C" int flexllm_swiglu_fht_quant(const float* g, const float* u, int M, i
     if (N != 8192) return FLEXLLM_ENOTSUP;
     FLEXLLM_REQUIRE(aligned(g, 16) && aligned(u, 16) && aligned(q, 8) && (!act || aligned(act, 16)));
     if (M == 0) return FLEXLLM_OK;
-    fht8192_kernel<1><<<M, 256, 0, (cudaStream_t)stream>>>(g, u, scale, nullptr, q, s, act);
+    fht8192_kernel<1><<<M, 256, 0, (cudaStream_t)stream>>>(g, u, N, scale, nullptr, q, s, act);
     return launch_status();
 }
 

@@ -1,0 +1,377 @@
+// Llama-3.2-1B W8A8 SpinQuant forward on one GPU: the operator order of the reference's two
+// top-level graphs, SpinQuant_Prefilling (SpinQuant_Llama_32_1B/SpinQuant_Prefilling.h:807, graph
+// :940-1049) and SpinQuant_Decoding (SpinQuant_Decoding_mem_opt.h:947, graph :1050-1126), driven
+// the way the demo's host program drives them (SpinQuant_Prefilling_Decoding_mem_opt_demo.cpp:
+// prefill launch, KV hand-off, decode launch).
+//
+// Per layer: RMSNorm+quant -> fused q|k|v projection -> RoPE, FHT-64, per-head int8 quant, KV-cache
+// append, int8 attention -> quant -> o projection -> +residual -> RMSNorm+quant -> fused gate|up
+// projection -> silu(gate)*up, FHT-8192, quant -> down projection -> +residual.
+// Head: RMSNorm+quant -> lm_head -> greedy argmax; the next embedding row is
+// (float)lm_head_q[token] * lm_head_s[token] (tied embeddings).
+// Prefill uses the prefill RMSNorm summation order and the tcgen05 GEMM / attention kernels; decode
+// uses the decode order, the weight-streaming linear layers and the paged attention, and is replayed
+// from a CUDA graph (the token feedback stays on the device, as in the reference's decode graph).
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+struct flexllm_kv_cache;
+
+namespace flexllm {
+int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                    int32_t* acc, float* y, cudaStream_t st);
+int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st);
+size_t mha_prefill_ws_bytes(int B, int S, int HQ, int HKV);
+int mha_prefill_f32(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int S, int HQ, int HKV,
+                    float* out, void* workspace, cudaStream_t st, const int8_t** k2, const float** ks2, const int8_t** vT,
+                    const float** vsT);
+int kv_pack(flexllm_kv_cache* c, int layer, const int8_t* k2, const float* ks2, const int8_t* vT, const float* vsT,
+            const int32_t* page_table, int max_pages, int B, int S, cudaStream_t st);
+int mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                   const int8_t* v, const float* vs, const float* qkv_f32, const float* cos_t, const float* sin_t,
+                   const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, int HQ,
+                   float* out, int32_t* oacc, void* workspace, cudaStream_t st);
+int gemm_check_error_flag();
+
+// x[t][:] = (float)lm_w[tok[t]][:] * lm_s[tok[t]]
+__global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ lm_w, const float* __restrict__ lm_s,
+                             int D, float* __restrict__ x) {
+    const int t = blockIdx.x;
+    const int id = tok[t];
+    const float s = lm_s[id];
+    const char4* w = reinterpret_cast<const char4*>(lm_w + (long)id * D);
+    float4* o = reinterpret_cast<float4*>(x + (long)t * D);
+    for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+        const char4 c = w[i];
+        o[i] = make_float4((float)c.x * s, (float)c.y * s, (float)c.z * s, (float)c.w * s);
+    }
+}
+
+// rows (b*S + S-1) of x -> y[b]
+__global__ void gather_last_kernel(const float* __restrict__ x, int S, int D, float* __restrict__ y) {
+    const int b = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + ((long)b * S + S - 1) * D);
+    float4* dst = reinterpret_cast<float4*>(y + (long)b * D);
+    for (int i = threadIdx.x; i < D / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// Device-side generation state: state[0] = next output column, state[1] = number of columns.
+// Records the chosen tokens at column state[0] of out [B][state[1]], then advances the column and
+// (after a decode step) the context lengths.
+__global__ void step_bookkeeping_kernel(const int32_t* __restrict__ next, int B, int32_t* __restrict__ out,
+                                        int32_t* __restrict__ state, int32_t* __restrict__ ctx, int advance_ctx) {
+    const int b = threadIdx.x;
+    const int col = state[0], n_cols = state[1];
+    if (b < B) {
+        if (col < n_cols) out[(long)b * n_cols + col] = next[b];
+        if (advance_ctx) ctx[b] += 1;
+    }
+    __syncthreads();
+    if (b == 0) state[0] = col + 1;
+}
+__global__ void set_state_kernel(int32_t* state, int col, int n_cols) { state[0] = col; state[1] = n_cols; }
+
+__global__ void fill_ctx_kernel(int32_t* ctx, int B, int v) { if (threadIdx.x < B) ctx[threadIdx.x] = v; }
+
+}  // namespace flexllm
+
+using namespace flexllm;
+
+struct LayerW {
+    int8_t *wqkv, *wo, *wgu, *wd;
+    float *sqkv, *so, *sgu, *sd, *g0, *g1, *a_s;
+};
+
+struct flexllm_model {
+    flexllm_model_config cfg;
+    std::vector<LayerW> L;
+    int8_t* lm_w = nullptr; float* lm_s = nullptr; float* g_final = nullptr;
+    float *cos_t = nullptr, *sin_t = nullptr; int table_len = 0;
+    flexllm_kv_cache* cache = nullptr;
+    int max_pages = 0;
+    int32_t *page_table = nullptr, *ctx = nullptr, *next = nullptr, *state = nullptr, *tokens = nullptr, *out_tokens = nullptr;
+    size_t out_capacity = 0;
+    // activations (sized for max_batch * max_prefill rows)
+    float *x = nullptr, *qkv = nullptr, *att = nullptr, *tmp = nullptr, *gu = nullptr, *xs = nullptr, *logits = nullptr, *xlast = nullptr;
+    int8_t *xq = nullptr, *hq = nullptr;
+    void *attn_ws = nullptr, *dec_ws = nullptr;
+    size_t attn_ws_bytes = 0, dec_ws_bytes = 0;
+    // decode state
+    int B = 0, S = 0;
+    cudaGraphExec_t graph = nullptr; int graph_B = 0;
+    std::vector<void*> owned;
+};
+
+template <class T> static int dmalloc(flexllm_model* m, T** p, size_t n) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, n * sizeof(T) + 256);
+    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return e == cudaErrorMemoryAllocation ? FLEXLLM_ENOMEM : FLEXLLM_ECUDA; }
+    m->owned.push_back(q);
+    *p = (T*)q;
+    return FLEXLLM_OK;
+}
+#define TRY(expr) do { int _rc = (expr); if (_rc != FLEXLLM_OK) return _rc; } while (0)
+
+extern "C" int flexllm_model_create(flexllm_model** out, const flexllm_model_config* c) {
+    FLEXLLM_REQUIRE(out && c);
+    FLEXLLM_REQUIRE(c->layers > 0 && c->hidden > 0 && c->heads_q > 0 && c->heads_kv > 0 && c->ffn > 0 && c->vocab > 0);
+    FLEXLLM_REQUIRE(c->max_batch > 0 && c->max_batch <= 64 && c->max_prefill > 0 && c->max_ctx >= c->max_prefill);
+    if (c->heads_q * 64 != c->hidden || c->heads_q != 4 * c->heads_kv || c->ffn != 8192 || c->hidden > 4096) return FLEXLLM_ENOTSUP;
+    flexllm_model* m = new (std::nothrow) flexllm_model();
+    if (!m) return FLEXLLM_ENOMEM;
+    m->cfg = *c;
+    const int D = c->hidden, HQ = c->heads_q, HKV = c->heads_kv, F = c->ffn, V = c->vocab, NL = c->layers;
+    const int QKV = (HQ + 2 * HKV) * 64;
+    const size_t Mmax = (size_t)c->max_batch * c->max_prefill;
+    m->L.resize(NL);
+    int rc = FLEXLLM_OK;
+    auto fail = [&](int r) { flexllm_model_destroy(m); return r; };
+    for (int l = 0; l < NL && rc == FLEXLLM_OK; l++) {
+        LayerW& w = m->L[l];
+        if ((rc = dmalloc(m, &w.wqkv, (size_t)QKV * D))) break;
+        if ((rc = dmalloc(m, &w.wo, (size_t)D * D))) break;
+        if ((rc = dmalloc(m, &w.wgu, (size_t)2 * F * D))) break;
+        if ((rc = dmalloc(m, &w.wd, (size_t)D * F))) break;
+        if ((rc = dmalloc(m, &w.sqkv, QKV))) break;
+        if ((rc = dmalloc(m, &w.so, D))) break;
+        if ((rc = dmalloc(m, &w.sgu, 2 * F))) break;
+        if ((rc = dmalloc(m, &w.sd, D))) break;
+        if ((rc = dmalloc(m, &w.g0, D))) break;
+        if ((rc = dmalloc(m, &w.g1, D))) break;
+        if ((rc = dmalloc(m, &w.a_s, HQ))) break;
+    }
+    if (rc) return fail(rc);
+    if ((rc = dmalloc(m, &m->lm_w, (size_t)V * D)) || (rc = dmalloc(m, &m->lm_s, V)) || (rc = dmalloc(m, &m->g_final, D))) return fail(rc);
+    m->table_len = c->max_ctx + 1;
+    if ((rc = dmalloc(m, &m->cos_t, (size_t)m->table_len * 32)) || (rc = dmalloc(m, &m->sin_t, (size_t)m->table_len * 32))) return fail(rc);
+    m->max_pages = (c->max_ctx + 64) / 64;
+    const int n_pages = m->max_pages * c->max_batch;
+    if ((rc = flexllm_kv_cache_create(&m->cache, NL, n_pages, HKV, 64))) return fail(rc);
+    if ((rc = dmalloc(m, &m->page_table, (size_t)c->max_batch * m->max_pages)) || (rc = dmalloc(m, &m->ctx, 64)) ||
+        (rc = dmalloc(m, &m->next, 64)) || (rc = dmalloc(m, &m->state, 4)) || (rc = dmalloc(m, &m->tokens, Mmax)))
+        return fail(rc);
+    m->out_capacity = (size_t)c->max_batch * (c->max_ctx + 1);
+    if ((rc = dmalloc(m, &m->out_tokens, m->out_capacity))) return fail(rc);
+    {   // identity page table: sequence b owns pages [b*max_pages, (b+1)*max_pages)
+        std::vector<int32_t> pt((size_t)c->max_batch * m->max_pages);
+        for (size_t i = 0; i < pt.size(); i++) pt[i] = (int32_t)i;
+        if (cudaMemcpy(m->page_table, pt.data(), pt.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) return fail(FLEXLLM_ECUDA);
+    }
+    if ((rc = dmalloc(m, &m->x, Mmax * D)) || (rc = dmalloc(m, &m->qkv, Mmax * QKV)) || (rc = dmalloc(m, &m->att, Mmax * D)) ||
+        (rc = dmalloc(m, &m->tmp, Mmax * D)) || (rc = dmalloc(m, &m->gu, Mmax * 2 * F)) || (rc = dmalloc(m, &m->xs, Mmax)) ||
+        (rc = dmalloc(m, &m->xq, Mmax * D)) || (rc = dmalloc(m, &m->hq, Mmax * F)) ||
+        (rc = dmalloc(m, &m->logits, (size_t)c->max_batch * V)) || (rc = dmalloc(m, &m->xlast, (size_t)c->max_batch * D)))
+        return fail(rc);
+    m->attn_ws_bytes = mha_prefill_ws_bytes(c->max_batch, c->max_prefill, HQ, HKV);
+    m->dec_ws_bytes = flexllm_mha_decode_workspace(c->max_batch, HQ, c->max_ctx);
+    uint8_t *a = nullptr, *d = nullptr;
+    if ((rc = dmalloc(m, &a, m->attn_ws_bytes)) || (rc = dmalloc(m, &d, m->dec_ws_bytes))) return fail(rc);
+    m->attn_ws = a; m->dec_ws = d;
+    *out = m;
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_model_destroy(flexllm_model* m) {
+    if (!m) return FLEXLLM_OK;
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    if (m->cache) flexllm_kv_cache_destroy(m->cache);
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+    return FLEXLLM_OK;
+}
+
+static int copy_any(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+    return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, st));
+}
+
+extern "C" int flexllm_model_load_layer(flexllm_model* m, int layer, const flexllm_layer_weights* w, void* stream) {
+    FLEXLLM_REQUIRE(m && w && layer >= 0 && layer < m->cfg.layers);
+    FLEXLLM_REQUIRE(w->wq && w->wk && w->wv && w->wo && w->wg && w->wu && w->wd && w->sq && w->sk && w->sv && w->so && w->sg &&
+                    w->su && w->sd && w->gamma0 && w->gamma1 && w->a_s);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
+    LayerW& L = m->L[layer];
+    const size_t q = (size_t)HQ * 64, kv = (size_t)HKV * 64;
+    TRY(copy_any(L.wqkv, w->wq, q * D, st));
+    TRY(copy_any(L.wqkv + q * D, w->wk, kv * D, st));
+    TRY(copy_any(L.wqkv + (q + kv) * D, w->wv, kv * D, st));
+    TRY(copy_any(L.sqkv, w->sq, q * 4, st));
+    TRY(copy_any(L.sqkv + q, w->sk, kv * 4, st));
+    TRY(copy_any(L.sqkv + q + kv, w->sv, kv * 4, st));
+    TRY(copy_any(L.wo, w->wo, (size_t)D * D, st));
+    TRY(copy_any(L.so, w->so, (size_t)D * 4, st));
+    TRY(copy_any(L.wgu, w->wg, (size_t)F * D, st));
+    TRY(copy_any(L.wgu + (size_t)F * D, w->wu, (size_t)F * D, st));
+    TRY(copy_any(L.sgu, w->sg, (size_t)F * 4, st));
+    TRY(copy_any(L.sgu + F, w->su, (size_t)F * 4, st));
+    TRY(copy_any(L.wd, w->wd, (size_t)D * F, st));
+    TRY(copy_any(L.sd, w->sd, (size_t)D * 4, st));
+    TRY(copy_any(L.g0, w->gamma0, (size_t)D * 4, st));
+    TRY(copy_any(L.g1, w->gamma1, (size_t)D * 4, st));
+    TRY(copy_any(L.a_s, w->a_s, (size_t)HQ * 4, st));
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_model_load_head(flexllm_model* m, const int8_t* lm_w, const float* lm_s, const float* gamma_final,
+                                       const float* cos_t, const float* sin_t, int table_len, void* stream) {
+    FLEXLLM_REQUIRE(m && lm_w && lm_s && gamma_final && cos_t && sin_t && table_len >= m->table_len);
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(copy_any(m->lm_w, lm_w, (size_t)m->cfg.vocab * m->cfg.hidden, st));
+    TRY(copy_any(m->lm_s, lm_s, (size_t)m->cfg.vocab * 4, st));
+    TRY(copy_any(m->g_final, gamma_final, (size_t)m->cfg.hidden * 4, st));
+    TRY(copy_any(m->cos_t, cos_t, (size_t)m->table_len * 32 * 4, st));
+    TRY(copy_any(m->sin_t, sin_t, (size_t)m->table_len * 32 * 4, st));
+    return FLEXLLM_OK;
+}
+
+// lm_head on the rows of xin [B][D] -> logits, argmax -> m->next
+static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaStream_t st) {
+    const int D = m->cfg.hidden, V = m->cfg.vocab;
+    TRY(flexllm_rmsnorm_quant(xin, m->g_final, B, D, m->cfg.eps, order, nullptr, m->xq, m->xs, st));
+    TRY(flexllm_linear_decode_i8(m->xq, m->xs, m->lm_w, m->lm_s, B, V, D, nullptr, m->logits, st));
+    TRY(flexllm_logits_argmax(m->logits, B, V, m->next, st));
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, void* stream) {
+    FLEXLLM_REQUIRE(m && tokens && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill);
+    if (S % 16 != 0) return FLEXLLM_ENOTSUP;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
+    const int QKV = (HQ + 2 * HKV) * 64;
+    const int M = B * S;
+    embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->x);
+    for (int l = 0; l < m->cfg.layers; l++) {
+        const LayerW& L = m->L[l];
+        TRY(flexllm_rmsnorm_quant(m->x, L.g0, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, M, QKV, D, nullptr, m->qkv, st));
+        const int8_t *k2, *vT; const float *ks2, *vsT;
+        TRY(mha_prefill_f32(m->qkv, m->cos_t, m->sin_t, L.a_s, B, S, HQ, HKV, m->att, m->attn_ws, st, &k2, &ks2, &vT, &vsT));
+        TRY(kv_pack(m->cache, l, k2, ks2, vT, vsT, m->page_table, m->max_pages, B, S, st));
+        TRY(flexllm_quant_per_token(m->att, M, D, m->xq, m->xs, st));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wo, L.so, M, D, D, nullptr, m->tmp, st));
+        TRY(flexllm_residual(m->x, m->tmp, (long)M * D, m->x, st));
+        TRY(flexllm_rmsnorm_quant(m->x, L.g1, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, M, 2 * F, D, nullptr, m->gu, st));
+        TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, M, m->cfg.fht_scale, m->hq, m->xs, st));
+        TRY(gemm_i8_prefill(m->hq, m->xs, L.wd, L.sd, M, D, F, nullptr, m->tmp, st));
+        TRY(flexllm_residual(m->x, m->tmp, (long)M * D, m->x, st));
+    }
+    gather_last_kernel<<<B, 256, 0, st>>>(m->x, S, D, m->xlast);
+    TRY(run_head(m, m->xlast, B, FLEXLLM_NORM_PREFILL, st));
+    fill_ctx_kernel<<<1, 64, 0, st>>>(m->ctx, B, S);
+    TRY(launch_status());
+    if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
+    m->B = B; m->S = S;
+    return FLEXLLM_OK;
+}
+
+// One decode step for the B sequences of the last prefill: consumes m->next, leaves the new
+// greedy tokens in m->next (and in the output table), appends to the KV cache and advances ctx.
+static int decode_step(flexllm_model* m, cudaStream_t st) {
+    const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
+    const int QKV = (HQ + 2 * HKV) * 64;
+    const int B = m->B;
+    embed_kernel<<<B, 256, 0, st>>>(m->next, m->lm_w, m->lm_s, D, m->x);
+    for (int l = 0; l < m->cfg.layers; l++) {
+        const LayerW& L = m->L[l];
+        TRY(flexllm_rmsnorm_quant(m->x, L.g0, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
+        TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wqkv, L.sqkv, B, QKV, D, nullptr, m->qkv, st));
+        TRY(mha_decode_run(m->cache, l, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, m->qkv, m->cos_t, m->sin_t, L.a_s,
+                           m->page_table, m->max_pages, m->ctx, m->cfg.max_ctx, B, HQ, m->att, nullptr, m->dec_ws, st));
+        TRY(flexllm_quant_per_token(m->att, B, D, m->xq, m->xs, st));
+        TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wo, L.so, B, D, D, nullptr, m->tmp, st));
+        TRY(flexllm_residual(m->x, m->tmp, (long)B * D, m->x, st));
+        TRY(flexllm_rmsnorm_quant(m->x, L.g1, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
+        TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wgu, L.sgu, B, 2 * F, D, nullptr, m->gu, st));
+        TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, B, m->cfg.fht_scale, m->hq, m->xs, st));
+        TRY(flexllm_linear_decode_i8(m->hq, m->xs, L.wd, L.sd, B, D, F, nullptr, m->tmp, st));
+        TRY(flexllm_residual(m->x, m->tmp, (long)B * D, m->x, st));
+    }
+    TRY(run_head(m, m->x, B, FLEXLLM_NORM_DECODE8, st));
+    step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, B, m->out_tokens, m->state, m->ctx, 1);
+    return launch_status();
+}
+
+// Captures one decode step into a CUDA graph (the launch sequence is identical for every step: the
+// context lengths, the token feedback and the output column all live in device memory).
+static int build_graph(flexllm_model* m) {
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    cudaStream_t cap;
+    FLEXLLM_CHECK_CUDA(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking));
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal);
+    int rc = FLEXLLM_OK;
+    if (e == cudaSuccess) {
+        rc = decode_step(m, cap);
+        cudaError_t e2 = cudaStreamEndCapture(cap, &g);
+        if (e == cudaSuccess) e = e2;
+    }
+    if (e == cudaSuccess && rc == FLEXLLM_OK) e = cudaGraphInstantiate(&m->graph, g, 0);
+    if (g) cudaGraphDestroy(g);
+    cudaStreamDestroy(cap);
+    if (rc != FLEXLLM_OK) return rc;
+    FLEXLLM_CHECK_CUDA(e);
+    m->graph_B = m->B;
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph, void* stream) {
+    FLEXLLM_REQUIRE(m && m->B > 0 && n_steps >= 0);
+    cudaStream_t st = (cudaStream_t)stream;
+    int done = 0;
+    if (use_graph && n_steps > 0 && (!m->graph || m->graph_B != m->B)) {
+        // the first step runs eagerly so that every lazily created resource (function attributes,
+        // tensor maps, split-K scratch) exists before capture
+        TRY(decode_step(m, st));
+        done = 1;
+        FLEXLLM_CHECK_CUDA(cudaStreamSynchronize(st));
+        TRY(build_graph(m));
+    }
+    for (int i = done; i < n_steps; i++) {
+        if (use_graph) FLEXLLM_CHECK_CUDA(cudaGraphLaunch(m->graph, st));
+        else TRY(decode_step(m, st));
+    }
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_model_begin(flexllm_model* m, int n_new, void* stream) {
+    FLEXLLM_REQUIRE(m && m->B > 0 && n_new >= 1 && (size_t)m->B * n_new <= m->out_capacity);
+    FLEXLLM_REQUIRE(m->S + n_new - 1 <= m->cfg.max_ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    set_state_kernel<<<1, 1, 0, st>>>(m->state, 0, n_new);
+    step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, m->B, m->out_tokens, m->state, m->ctx, 0);
+    return launch_status();
+}
+
+// Whole request through host buffers: tokens_host [B][S] -> out_host [B][n_new] (greedy; column 0
+// is the token chosen by the prefill).
+extern "C" int flexllm_model_generate_host(flexllm_model* m, const int32_t* tokens_host, int B, int S, int n_new,
+                                           int32_t* out_host, int use_graph, void* stream) {
+    FLEXLLM_REQUIRE(m && tokens_host && out_host && n_new >= 1);
+    FLEXLLM_REQUIRE(B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill && S + n_new - 1 <= m->cfg.max_ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(m->tokens, tokens_host, (size_t)B * S * 4, cudaMemcpyHostToDevice, st));
+    TRY(flexllm_model_prefill(m, m->tokens, B, S, nullptr, st));
+    TRY(flexllm_model_begin(m, n_new, st));
+    TRY(flexllm_model_decode(m, n_new - 1, use_graph, st));
+    FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(out_host, m->out_tokens, (size_t)B * n_new * 4, cudaMemcpyDeviceToHost, st));
+    FLEXLLM_CHECK_CUDA(cudaStreamSynchronize(st));
+    return gemm_check_error_flag();
+}
+
+// Device pointers of internal buffers, for tests: 0 = residual stream x, 1 = logits of the last head
+// call, 2 = generated tokens table, 3 = context lengths.
+extern "C" int flexllm_model_buffer(flexllm_model* m, int which, void** ptr) {
+    FLEXLLM_REQUIRE(m && ptr);
+    switch (which) {
+        case 0: *ptr = m->x; break;
+        case 1: *ptr = m->logits; break;
+        case 2: *ptr = m->out_tokens; break;
+        case 3: *ptr = m->ctx; break;
+        default: return FLEXLLM_EINVAL;
+    }
+    return FLEXLLM_OK;
+}

@@ -273,3 +273,73 @@ def MHA_i8xi8_Decoding(cache, layer, q, qs, k, ks, v, vs, cos_t, sin_t, a_s, pag
         cache._h, layer, _ptr(q), _ptr(qs), _ptr(k), _ptr(ks), _ptr(v), _ptr(vs), _ptr(cos_t), _ptr(sin_t), _ptr(a_s),
         _ptr(page_table), page_table.shape[1], _ptr(ctx), max_ctx, B, HQ, _ptr(out), _ptr(oacc), _ptr(ws), nbytes, _stream()))
     return out, oacc
+
+
+class Model:
+    """Whole-model runner (SpinQuant_Prefilling + SpinQuant_Decoding graphs). Weights are given as
+    CUDA or CPU torch tensors (the library copies them)."""
+
+    def __init__(self, layers, hidden, heads_q, heads_kv, ffn, vocab, max_batch, max_prefill, max_ctx, eps=1e-5):
+        import math
+        self.cfg = _lib.ModelConfig(layers, hidden, heads_q, heads_kv, ffn, vocab, eps, float(torch.tensor(math.sqrt(ffn), dtype=torch.float32)),
+                                    max_batch, max_prefill, max_ctx)
+        self._h = C.c_void_p()
+        _check("flexllm_model_create", lib().flexllm_model_create(C.byref(self._h), C.byref(self.cfg)))
+
+    def close(self):
+        if self._h:
+            lib().flexllm_model_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _p(t):
+        assert t.is_contiguous()
+        return C.c_void_p(t.data_ptr())
+
+    def load_layer(self, layer, **w):
+        """Keys: wq wk wv wo wg wu wd sq sk sv so sg su sd gamma0 gamma1 a_s."""
+        lw = _lib.LayerWeights(*[self._p(w[n]) for n, _ in _lib.LayerWeights._fields_])
+        _check("flexllm_model_load_layer", lib().flexllm_model_load_layer(self._h, layer, C.byref(lw), _stream()))
+        torch.cuda.current_stream().synchronize()   # sources may be freed by the caller afterwards
+
+    def load_head(self, lm_w, lm_s, gamma_final, cos_t, sin_t):
+        _check("flexllm_model_load_head", lib().flexllm_model_load_head(
+            self._h, self._p(lm_w), self._p(lm_s), self._p(gamma_final), self._p(cos_t), self._p(sin_t), cos_t.shape[0], _stream()))
+        torch.cuda.current_stream().synchronize()
+
+    def prefill(self, tokens):
+        B, S = tokens.shape
+        nxt = torch.empty((B,), dtype=torch.int32, device=tokens.device)
+        _check("flexllm_model_prefill", lib().flexllm_model_prefill(self._h, _ptr(tokens), B, S, _ptr(nxt), _stream()))
+        return nxt
+
+    def begin(self, n_new):
+        _check("flexllm_model_begin", lib().flexllm_model_begin(self._h, n_new, _stream()))
+
+    def decode(self, n_steps, use_graph=True):
+        _check("flexllm_model_decode", lib().flexllm_model_decode(self._h, n_steps, 1 if use_graph else 0, _stream()))
+
+    def generate_host(self, tokens_cpu, n_new, use_graph=True, out=None):
+        """tokens_cpu: pinned or pageable CPU int32 [B,S]. Returns CPU int32 [B,n_new]."""
+        B, S = tokens_cpu.shape
+        if out is None:
+            out = torch.empty((B, n_new), dtype=torch.int32)
+        _check("flexllm_model_generate_host", lib().flexllm_model_generate_host(
+            self._h, C.c_void_p(tokens_cpu.data_ptr()), B, S, n_new, C.c_void_p(out.data_ptr()), 1 if use_graph else 0, _stream()))
+        return out
+
+    def buffer(self, which, shape, dtype):
+        p = C.c_void_p()
+        _check("flexllm_model_buffer", lib().flexllm_model_buffer(self._h, which, C.byref(p)))
+        class _H:
+            pass
+        h = _H()
+        typestr = {torch.int32: "<i4", torch.float32: "<f4"}[dtype]
+        h.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (p.value, False), "version": 2}
+        return torch.as_tensor(h, device="cuda")

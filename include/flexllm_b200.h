@@ -163,6 +163,44 @@ FLEXLLM_API int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const i
                              int B, int HQ, float* out, int32_t* oacc, void* workspace,
                              size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Whole-model runner: the two top-level graphs of the reference, SpinQuant_Prefilling
+ * (SpinQuant_Llama_32_1B/SpinQuant_Prefilling.h:807) and SpinQuant_Decoding
+ * (SpinQuant_Decoding_mem_opt.h:947), and the host flow of its demo
+ * (SpinQuant_Prefilling_Decoding_mem_opt_demo.cpp: prefill, KV hand-off, decode loop).
+ * Greedy decoding; tied embeddings (embedding row t = (float)lm_head_q[t] * lm_head_s[t]).
+ * The model copies the weights it is given (fusing q|k|v and gate|up) and owns its KV cache,
+ * activations and CUDA graph.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct flexllm_model flexllm_model;
+typedef struct {
+    int layers, hidden, heads_q, heads_kv, ffn, vocab;
+    float eps, fht_scale;              /* 1e-5, sqrt(ffn) = 90.50966799 */
+    int max_batch, max_prefill, max_ctx; /* max_ctx = longest prompt + generated tokens */
+} flexllm_model_config;
+typedef struct {                       /* device or host pointers, row-major [N][K] weights */
+    const int8_t *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+    const float *sq, *sk, *sv, *so, *sg, *su, *sd; /* per-output-channel scales */
+    const float *gamma0, *gamma1;      /* RMSNorm weights before attention / before the MLP */
+    const float *a_s;                  /* [heads_q] static scale of the u8 attention probabilities */
+} flexllm_layer_weights;
+FLEXLLM_API int flexllm_model_create(flexllm_model** out, const flexllm_model_config* cfg);
+FLEXLLM_API int flexllm_model_destroy(flexllm_model* m);
+FLEXLLM_API int flexllm_model_load_layer(flexllm_model* m, int layer, const flexllm_layer_weights* w, void* stream);
+FLEXLLM_API int flexllm_model_load_head(flexllm_model* m, const int8_t* lm_w, const float* lm_s, const float* gamma_final,
+                            const float* cos_t, const float* sin_t, int table_len, void* stream);
+/* tokens [B][S] (device) -> KV cache filled, first greedy token per sequence in next_out [B] (device, optional). */
+FLEXLLM_API int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, void* stream);
+/* Start a generation of n_new tokens per sequence after a prefill (records the prefill's token). */
+FLEXLLM_API int flexllm_model_begin(flexllm_model* m, int n_new, void* stream);
+/* n_steps further greedy steps; use_graph != 0 replays one captured CUDA graph per step. */
+FLEXLLM_API int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph, void* stream);
+/* Whole request through HOST buffers: tokens_host [B][S] -> out_host [B][n_new]; synchronises. */
+FLEXLLM_API int flexllm_model_generate_host(flexllm_model* m, const int32_t* tokens_host, int B, int S, int n_new,
+                                int32_t* out_host, int use_graph, void* stream);
+/* Device pointers of internal buffers (tests): 0 residual stream, 1 logits, 2 token table, 3 ctx. */
+FLEXLLM_API int flexllm_model_buffer(flexllm_model* m, int which, void** ptr);
+
 #ifdef __cplusplus
 }
 #endif

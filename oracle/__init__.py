@@ -62,6 +62,32 @@ def _i32(a):
 
 
 # ------------------------------------------------------------------ Tier B (restatement)
+EXP_LIBM, EXP_CORRECTLY_ROUNDED = 0, 1
+
+
+def set_exp_mode(mode):
+    """0: the build machine's libm expf (what a C simulation of the reference computes here);
+    1: correctly rounded expf = (float)exp((double)x), which the CUDA kernels reproduce bit for bit."""
+    _lib.orc_set_exp_mode(C.c_int(mode))
+
+
+def get_exp_mode():
+    return _lib.orc_get_exp_mode()
+
+
+class exp_mode:
+    """Context manager: ``with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED): ...``"""
+
+    def __init__(self, mode):
+        self.mode = mode
+
+    def __enter__(self):
+        self.prev = get_exp_mode(); set_exp_mode(self.mode)
+
+    def __exit__(self, *a):
+        set_exp_mode(self.prev)
+
+
 def quant_per_token(x):
     x = _f32(x); M, K = x.shape
     q = np.empty((M, K), np.int8); s = np.empty(M, np.float32)
@@ -227,6 +253,45 @@ def attn_row(q, qs, k, ks, v, vs, a_s):
     _lib.orc_attn_row(_p(_i8(q)), C.c_float(qs), _p(k), _p(_f32(ks)), _p(_i8(v)), _p(_f32(vs)), C.c_int(nk),
                       C.c_float(a_s), _p(r["out"]), _p(r["oacc"]), _p(r["p"]), _p(r["score"]))
     return r
+
+
+class _OrcModel(C.Structure):
+    _PP = C.POINTER(C.c_void_p)
+    _fields_ = ([("L", C.c_int), ("D", C.c_int), ("HQ", C.c_int), ("HKV", C.c_int), ("F", C.c_int), ("V", C.c_int),
+                 ("eps", C.c_float), ("fht_scale", C.c_float)] +
+                [(n, C.POINTER(C.c_void_p)) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "sq", "sk", "sv", "so", "sg",
+                                                       "su", "sd", "g0", "g1", "a_s")] +
+                [("g_final", C.c_void_p), ("lm_w", C.c_void_p), ("lm_s", C.c_void_p), ("cos_t", C.c_void_p), ("sin_t", C.c_void_p)])
+
+
+def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False):
+    """Full-model greedy generation on the CPU. `weights`: dict with per-layer lists under the keys
+    wq wk wv wo wg wu wd (int8 [N,K]), sq sk sv so sg su sd g0 g1 a_s (fp32) and g_final, lm_w, lm_s,
+    cos_t, sin_t, plus ints HQ, HKV. tokens [B,S] int32. Returns dict(tokens [B,n_new], hidden, logits_prefill,
+    logits_last)."""
+    tokens = _i32(tokens); B, S = tokens.shape
+    L = len(weights["wq"]); D = weights["wq"][0].shape[1]; F = weights["wg"][0].shape[0]; V = weights["lm_w"].shape[0]
+    keep = []
+    m = _OrcModel()
+    m.L, m.D, m.HQ, m.HKV, m.F, m.V = L, D, weights["HQ"], weights["HKV"], F, V
+    m.eps, m.fht_scale = 1e-5, float(np.float32(np.sqrt(F)))
+    for name in ("wq", "wk", "wv", "wo", "wg", "wu", "wd"):
+        arrs = [_i8(a) for a in weights[name]]; keep.append(arrs)
+        ptrs = (C.c_void_p * L)(*[a.ctypes.data for a in arrs]); keep.append(ptrs)
+        setattr(m, name, ptrs)
+    for name in ("sq", "sk", "sv", "so", "sg", "su", "sd", "g0", "g1", "a_s"):
+        arrs = [_f32(a) for a in weights[name]]; keep.append(arrs)
+        ptrs = (C.c_void_p * L)(*[a.ctypes.data for a in arrs]); keep.append(ptrs)
+        setattr(m, name, ptrs)
+    for name, conv in (("g_final", _f32), ("lm_w", _i8), ("lm_s", _f32), ("cos_t", _f32), ("sin_t", _f32)):
+        a = conv(weights[name]); keep.append(a)
+        setattr(m, name, a.ctypes.data)
+    out = np.zeros((B, max(n_new, 1)), np.int32)
+    hidden = np.empty((B * S, D), np.float32) if want_hidden else None
+    lp = np.empty((B, V), np.float32) if want_logits else None
+    ll = np.empty((B, V), np.float32) if (want_logits and n_new > 1) else None
+    _lib.orc_model_generate(C.byref(m), _p(tokens), C.c_int(B), C.c_int(S), C.c_int(n_new), _p(out), _p(hidden), _p(lp), _p(ll))
+    return dict(tokens=out[:, :n_new], hidden=hidden, logits_prefill=lp, logits_last=ll)
 
 
 # ------------------------------------------------------------------ Tier A (reference templates)

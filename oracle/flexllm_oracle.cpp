@@ -24,7 +24,18 @@
 
 #define ORC_API extern "C" __attribute__((visibility("default")))
 
+// exp() flavour. The reference calls `exp(float)` = the C library's expf, whose last-bit rounding is
+// implementation-defined (glibc's differs from the correctly rounded value on about 0.06 % of
+// inputs). Mode 0: the libm expf of the build machine (what a C-simulation of the reference computes
+// here). Mode 1: the correctly rounded single-precision exponential, (float)exp((double)x), which
+// the CUDA kernels reproduce bit for bit.
+static int g_exp_mode = 0;
+ORC_API void orc_set_exp_mode(int mode) { g_exp_mode = mode; }
+ORC_API int orc_get_exp_mode() { return g_exp_mode; }
+
 namespace {
+
+inline float ref_exp(float x) { return g_exp_mode ? (float)std::exp((double)x) : std::exp(x); }
 
 inline float absf(float x) { return std::fabs(x); }
 
@@ -64,7 +75,7 @@ inline void softmax_row(const float* x, int len, float* p) {
     for (int k = 0; k < len; k++) mx = x[k] > mx ? x[k] : mx;
     float ps[4] = {0, 0, 0, 0};
     for (int k = 0; k < len; k++) {
-        float e = std::exp(x[k] - mx);
+        float e = ref_exp(x[k] - mx);
         p[k] = e;
         ps[k & 3] += e;
     }
@@ -72,7 +83,7 @@ inline void softmax_row(const float* x, int len, float* p) {
     for (int k = 0; k < len; k++) p[k] = p[k] * r;
 }
 
-inline float silu(float g) { return g / (1 + std::exp(-g)); }  // Swish.h:19
+inline float silu(float g) { return g / (1 + ref_exp(-g)); }  // Swish.h:19
 
 } // namespace
 
@@ -509,4 +520,159 @@ ORC_API void orc_attn_row(const int8_t* q, float qs, const int8_t* k, const floa
         kp = k + (long)j * 64; ksj = ks[j]; vp = v + (long)j * 64; vsj = vs[j];
     };
     attn_row(q, qs, nk, at, a_s, out, oacc, p, score);
+}
+
+// ----------------------------------------------------------------------------------------------
+// Config 5: the full quantized Llama-3.2-1B forward (operator order of SpinQuant_Prefilling.h:
+// 940-1049 and SpinQuant_Decoding_mem_opt.h:1050-1126, at W8A8 with per-token scales).
+//
+// Per layer, for the rows of x [M][D] at positions pos[m] of sequence seq[m]:
+//   RMSNorm(g0) -> quant -> q,k,v proj -> dequant -> RoPE(q,k) -> FHT-64/8(q,k) -> per-head int8
+//   quant of q,k,v -> cache append -> attention (attn_row) -> quant -> o proj -> dequant -> +x
+//   -> RMSNorm(g1) -> quant -> gate,up -> dequant -> silu(gate)*up -> FHT-F/sqrt(F) -> quant
+//   -> down -> dequant -> +.
+// After the last layer: RMSNorm(g_final) -> quant -> lm_head -> dequant -> greedy argmax.
+// Embedding row t = (float)lm_head_q[t][:] * lm_head_s[t] (tied embeddings).
+// `lanes` selects the RMSNorm order: 0 for prefill, 8 for decode.
+// ----------------------------------------------------------------------------------------------
+struct OrcModel {
+    int L, D, HQ, HKV, F, V;
+    float eps, fht_scale;
+    const int8_t **wq, **wk, **wv, **wo, **wg, **wu, **wd;
+    const float **sq, **sk, **sv, **so, **sg, **su, **sd;
+    const float **g0, **g1, **a_s;
+    const float* g_final;
+    const int8_t* lm_w;
+    const float* lm_s;
+    const float *cos_t, *sin_t;
+};
+
+struct OrcCache {   // contiguous per-sequence cache: [L][B][T][HKV][64]
+    int B, T;
+    std::vector<int8_t> k, v;
+    std::vector<float> ks, vs;
+};
+
+static void model_layer(const OrcModel& m, int l, std::vector<float>& x, int M, const int* seq, const int* pos,
+                        OrcCache& c, int lanes) {
+    const int D = m.D, HQ = m.HQ, HKV = m.HKV, F = m.F, G = HQ / HKV;
+    std::vector<float> xn((size_t)M * D), xs(M);
+    std::vector<int8_t> xq((size_t)M * D);
+    orc_rmsnorm(x.data(), m.g0[l], M, D, m.eps, lanes, xn.data());
+    orc_quant_per_token(xn.data(), M, D, xq.data(), xs.data());
+    std::vector<float> qf((size_t)M * HQ * 64), kf((size_t)M * HKV * 64), vf((size_t)M * HKV * 64);
+    orc_linear_i8(xq.data(), xs.data(), m.wq[l], m.sq[l], M, HQ * 64, D, nullptr, qf.data());
+    orc_linear_i8(xq.data(), xs.data(), m.wk[l], m.sk[l], M, HKV * 64, D, nullptr, kf.data());
+    orc_linear_i8(xq.data(), xs.data(), m.wv[l], m.sv[l], M, HKV * 64, D, nullptr, vf.data());
+    // RoPE + FHT-64 + per-head quant of q and k; per-head quant of v
+    std::vector<int8_t> q2((size_t)M * HQ * 64), k2((size_t)M * HKV * 64), v2((size_t)M * HKV * 64);
+    std::vector<float> qs2((size_t)M * HQ), ks2((size_t)M * HKV), vs2((size_t)M * HKV);
+    auto prep = [&](const float* in, int H, int8_t* out, float* sout, bool rotate) {
+#pragma omp parallel for
+        for (int t = 0; t < M; t++) {
+            const float* cs = m.cos_t + (long)pos[t] * 32;
+            const float* sn = m.sin_t + (long)pos[t] * 32;
+            for (int h = 0; h < H; h++) {
+                long o = ((long)t * H + h) * 64;
+                float y[64];
+                if (rotate) {
+                    for (int k = 0; k < 32; k++) {
+                        float x0 = in[o + k], x1 = in[o + k + 32];
+                        y[k] = x0 * cs[k] - x1 * sn[k];
+                        y[k + 32] = x0 * sn[k] + x1 * cs[k];
+                    }
+                    fht_inplace(y, 64);
+                    for (int k = 0; k < 64; k++) y[k] = y[k] / 8.0f;
+                } else {
+                    for (int k = 0; k < 64; k++) y[k] = in[o + k];
+                }
+                float sc = sym_scale(y, 64, 127.0f);
+                sout[(long)t * H + h] = sc;
+                for (int k = 0; k < 64; k++) out[o + k] = (int8_t)(long long)std::round(y[k] / sc);
+            }
+        }
+    };
+    prep(qf.data(), HQ, q2.data(), qs2.data(), true);
+    prep(kf.data(), HKV, k2.data(), ks2.data(), true);
+    prep(vf.data(), HKV, v2.data(), vs2.data(), false);
+    // append to the cache
+    const size_t lay = (size_t)l * c.B * c.T;
+    for (int t = 0; t < M; t++) {
+        size_t row = (lay + (size_t)seq[t] * c.T + pos[t]) * HKV;
+        std::memcpy(&c.k[row * 64], &k2[(size_t)t * HKV * 64], (size_t)HKV * 64);
+        std::memcpy(&c.v[row * 64], &v2[(size_t)t * HKV * 64], (size_t)HKV * 64);
+        std::memcpy(&c.ks[row], &ks2[(size_t)t * HKV], sizeof(float) * HKV);
+        std::memcpy(&c.vs[row], &vs2[(size_t)t * HKV], sizeof(float) * HKV);
+    }
+    std::vector<float> att((size_t)M * HQ * 64);
+#pragma omp parallel for collapse(2) schedule(dynamic, 4)
+    for (int t = 0; t < M; t++)
+        for (int h = 0; h < HQ; h++) {
+            const int hk = h / G;
+            const size_t base = (lay + (size_t)seq[t] * c.T) * HKV;
+            auto at = [&](int j, const int8_t*& kp, float& ksj, const int8_t*& vp, float& vsj) {
+                size_t row = base + (size_t)j * HKV + hk;
+                kp = &c.k[row * 64]; ksj = c.ks[row]; vp = &c.v[row * 64]; vsj = c.vs[row];
+            };
+            long qi = (long)t * HQ + h;
+            attn_row(&q2[qi * 64], qs2[qi], pos[t] + 1, at, m.a_s[l][h], &att[qi * 64], nullptr, nullptr, nullptr);
+        }
+    std::vector<int8_t> aq((size_t)M * D);
+    std::vector<float> as(M), o((size_t)M * D);
+    orc_quant_per_token(att.data(), M, D, aq.data(), as.data());
+    orc_linear_i8(aq.data(), as.data(), m.wo[l], m.so[l], M, D, D, nullptr, o.data());
+    orc_residual(x.data(), o.data(), (long)M * D, x.data());
+    std::vector<float> out((size_t)M * D);
+    orc_mlp_block(x.data(), m.g1[l], m.wg[l], m.sg[l], m.wu[l], m.su[l], m.wd[l], m.sd[l], M, D, F, m.eps, lanes,
+                  m.fht_scale, out.data(), nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+    x.swap(out);
+}
+
+static void model_embed(const OrcModel& m, const int32_t* tok, int M, std::vector<float>& x) {
+    x.resize((size_t)M * m.D);
+    for (int t = 0; t < M; t++)
+        for (int k = 0; k < m.D; k++) x[(size_t)t * m.D + k] = (float)m.lm_w[(size_t)tok[t] * m.D + k] * m.lm_s[tok[t]];
+}
+
+static void model_head(const OrcModel& m, const float* x, int M, int lanes, float* logits, int32_t* next) {
+    std::vector<float> xn((size_t)M * m.D), xs(M), lg;
+    std::vector<int8_t> xq((size_t)M * m.D);
+    orc_rmsnorm(x, m.g_final, M, m.D, m.eps, lanes, xn.data());
+    orc_quant_per_token(xn.data(), M, m.D, xq.data(), xs.data());
+    if (!logits) { lg.resize((size_t)M * m.V); logits = lg.data(); }
+    orc_linear_i8(xq.data(), xs.data(), m.lm_w, m.lm_s, M, m.V, m.D, nullptr, logits);
+    orc_argmax(logits, M, m.V, next);
+}
+
+// tokens [B][S] -> greedy generation of n_new tokens per sequence: out_tokens [B][n_new].
+// Optional: hidden_prefill [B*S][D] (residual stream after the last layer), logits_prefill [B][V]
+// (last position), logits_last [B][V] (last decode step).
+ORC_API void orc_model_generate(const OrcModel* mp, const int32_t* tokens, int B, int S, int n_new,
+                                int32_t* out_tokens, float* hidden_prefill, float* logits_prefill, float* logits_last) {
+    const OrcModel& m = *mp;
+    OrcCache c;
+    c.B = B; c.T = S + n_new;
+    size_t rows = (size_t)m.L * B * c.T * m.HKV;
+    c.k.assign(rows * 64, 0); c.v.assign(rows * 64, 0); c.ks.assign(rows, 0); c.vs.assign(rows, 0);
+    const int M = B * S;
+    std::vector<int> seq(M), pos(M);
+    for (int i = 0; i < M; i++) { seq[i] = i / S; pos[i] = i % S; }
+    std::vector<float> x;
+    model_embed(m, tokens, M, x);
+    for (int l = 0; l < m.L; l++) model_layer(m, l, x, M, seq.data(), pos.data(), c, 0);
+    if (hidden_prefill) std::memcpy(hidden_prefill, x.data(), sizeof(float) * x.size());
+    std::vector<float> last((size_t)B * m.D);
+    for (int b = 0; b < B; b++) std::memcpy(&last[(size_t)b * m.D], &x[((size_t)b * S + S - 1) * m.D], sizeof(float) * m.D);
+    std::vector<int32_t> next(B);
+    if (n_new <= 0) { if (logits_prefill) model_head(m, last.data(), B, 0, logits_prefill, next.data()); return; }
+    model_head(m, last.data(), B, 0, logits_prefill, next.data());
+    for (int b = 0; b < B; b++) out_tokens[(size_t)b * n_new] = next[b];
+    std::vector<int> dseq(B), dpos(B);
+    for (int step = 1; step < n_new; step++) {
+        for (int b = 0; b < B; b++) { dseq[b] = b; dpos[b] = S + step - 1; }
+        model_embed(m, next.data(), B, x);
+        for (int l = 0; l < m.L; l++) model_layer(m, l, x, B, dseq.data(), dpos.data(), c, 8);
+        model_head(m, x.data(), B, 8, step == n_new - 1 ? logits_last : nullptr, next.data());
+        for (int b = 0; b < B; b++) out_tokens[(size_t)b * n_new + step] = next[b];
+    }
 }

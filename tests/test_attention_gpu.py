@@ -10,6 +10,15 @@ from util import assert_same, max_abs_rel, to_np
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _correctly_rounded_exp():
+    """The CUDA kernels evaluate the correctly rounded expf; pin them against the oracle in the same
+    mode (bit for bit). Tests that quantify the distance to the build machine's libm switch modes
+    themselves."""
+    with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
+        yield
+
+
 @pytest.fixture(scope="module")
 def F():
     import flexllm_b200
@@ -41,15 +50,16 @@ def check_prefill(F, B, S, HQ, HKV, seed):
     torch.cuda.synchronize()
     ref = oracle.mha_prefill(q, qs, k, ks, v, vs, cos_t, sin_t, a_s)
     out = to_np(out); oacc = to_np(oacc)
-    # int32 P.V accumulators: exact unless a device exp() result differs from libm's in the last
-    # bit AND that moves a u8 across a rounding boundary. Count them; the fp32 output must stay
-    # within the 1e-3 max-abs-rel tolerance.
-    bad = np.count_nonzero(oacc != ref["oacc"])
-    err = max_abs_rel(out, ref["out"])
-    print(f"prefill attn B={B} S={S}: {bad}/{oacc.size} int32 accumulators differ, max-abs-rel {err:.2e}")
+    assert_same(oacc, ref["oacc"], "int32 P.V accumulators")
+    assert_same(out, ref["out"], "fp32 output")
+    # distance to the libm flavour of the oracle (a last-bit difference in exp() can move a u8 across
+    # a rounding boundary): count, and require the fp32 tolerance
+    with oracle.exp_mode(oracle.EXP_LIBM):
+        ref_l = oracle.mha_prefill(q, qs, k, ks, v, vs, cos_t, sin_t, a_s)
+    bad = np.count_nonzero(oacc != ref_l["oacc"])
+    err = max_abs_rel(out, ref_l["out"])
+    print(f"prefill attn B={B} S={S}: exact; vs libm expf {bad}/{oacc.size} int32 accumulators differ, max-abs-rel {err:.2e}")
     assert err < 1e-3
-    assert bad <= oacc.size * 2e-2
-    return bad
 
 
 @pytest.mark.parametrize("B,S,HQ,HKV", [(1, 128, 4, 1), (2, 256, 8, 2), (1, 16, 4, 4), (1, 144, 4, 1), (1, 400, 8, 2)])
@@ -119,10 +129,8 @@ def decode_case(F, B, ctx, HQ=32, HKV=8, seed=40, steps=1):
         torch.cuda.synchronize()
         out_o, oacc_o = oracle.mha_decode(q, qs, k, ks, v, vs, cos_t, sin_t, a_s, k_pool, ks_pool, v_pool, vs_pool,
                                           page_table, cur)
-        bad = np.count_nonzero(to_np(oacc) != oacc_o)
-        err = max_abs_rel(to_np(out), out_o)
-        print(f"decode attn B={B} step {step}: {bad}/{oacc_o.size} int32 accumulators differ, max-abs-rel {err:.2e}")
-        assert err < 1e-3 and bad <= oacc_o.size * 2e-2
+        assert_same(to_np(oacc), oacc_o, "int32 P.V accumulators")
+        assert_same(to_np(out), out_o, "fp32 output")
         cur = cur + 1
     # the appended tokens landed in the cache exactly as in the oracle
     assert_same(to_np(kd), k_pool, "K cache"); assert_same(to_np(ksd), ks_pool, "K scales")

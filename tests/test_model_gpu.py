@@ -1,0 +1,76 @@
+"""Whole-model parity (BASELINE config 5 at sizes the CPU oracle finishes in seconds): the GPU
+runner against the oracle's full forward on identical seeded weights and token ids.
+
+Bar: identical greedy tokens, residual stream and logits bit-exact (oracle evaluated with the
+correctly rounded expf, as the kernels do). With random-init weights the attention logits are so
+large that the softmax is nearly one-hot, so a last-bit difference in exp() can flip a whole
+token's output: against the libm flavour of the oracle only the first layers stay within 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import max_abs_rel, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _correctly_rounded_exp():
+    """The CUDA kernels evaluate the correctly rounded expf; pin them against the oracle in the same
+    mode (bit for bit). Tests that quantify the distance to the build machine's libm switch modes
+    themselves."""
+    with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
+        yield
+
+
+@pytest.fixture(scope="module")
+def F():
+    import flexllm_b200
+    flexllm_b200.lib()
+    return flexllm_b200
+
+
+def run_case(F, layers, hidden, hq, hkv, vocab, B, S, n_new, seed, use_graph):
+    from flexllm_b200 import synthetic
+    max_ctx = S + n_new
+    W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, max_ctx, seed=seed)
+    assert np.array_equal(W["cos_t"], oracle.rope_table(max_ctx + 1)[0])      # product table == oracle table
+    tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
+    m = F.Model(layers, hidden, hq, hkv, 8192, vocab, max_batch=B, max_prefill=S, max_ctx=max_ctx)
+    synthetic.load_numpy_weights(m, W)
+    out = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=use_graph)
+    logits_last = to_np(m.buffer(1, (B, vocab), torch.float32))
+    ref = oracle.model_generate(W, tokens, n_new, want_hidden=True, want_logits=True)
+    # prefill residual stream: rerun the prefill alone and read x
+    m.prefill(torch.from_numpy(tokens).cuda())
+    torch.cuda.synchronize()
+    hidden_gpu = to_np(m.buffer(0, (B * S, hidden), torch.float32))
+    logits_prefill = to_np(m.buffer(1, (B, vocab), torch.float32))
+    e_h = max_abs_rel(hidden_gpu, ref["hidden"]); e_lp = max_abs_rel(logits_prefill, ref["logits_prefill"])
+    e_ll = max_abs_rel(logits_last, ref["logits_last"]) if n_new > 1 else 0.0
+    print(f"model L={layers} D={hidden} B={B} S={S} new={n_new}: hidden {e_h:.2e}, logits(prefill) {e_lp:.2e}, "
+          f"logits(last decode) {e_ll:.2e}, tokens equal {np.array_equal(out.numpy(), ref['tokens'])}")
+    assert e_h == 0 and e_lp == 0 and e_ll == 0
+    assert np.array_equal(hidden_gpu.view(np.uint32), ref["hidden"].view(np.uint32))
+    assert np.array_equal(out.numpy(), ref["tokens"])
+    m.close()
+
+
+def test_model_small(F):
+    run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=2, S=32, n_new=5, seed=50, use_graph=False)
+
+
+def test_model_small_graph(F):
+    run_case(F, layers=3, hidden=512, hq=8, hkv=2, vocab=1000, B=3, S=48, n_new=6, seed=51, use_graph=True)
+
+
+def test_model_full_width(F):
+    """Llama-3.2-1B widths (2048 hidden, 32/8 heads, FFN 8192, vocab 128256), 2 of 16 layers."""
+    run_case(F, layers=2, hidden=2048, hq=32, hkv=8, vocab=128256, B=2, S=64, n_new=3, seed=52, use_graph=True)
+
+
+def test_model_batch_over_8(F):
+    """More than 8 sequences sends the decode linear layers down the tensor-core split-K path."""
+    run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=12, S=16, n_new=4, seed=53, use_graph=True)
