@@ -12,6 +12,7 @@ _P, _I, _L, _F, _SZ = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_size_t
 SIGNATURES = {
     "flexllm_version": [],
     "flexllm_last_cuda_error": [],
+    "flexllm_launch_count": [],
     "flexllm_linear_prefill_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_linear_decode_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_quant_per_token": [_P, _I, _I, _P, _P, _P],
@@ -56,7 +57,7 @@ class LayerWeights(C.Structure):
     _fields_ = [(n, _P) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "sq", "sk", "sv", "so", "sg", "su", "sd",
                                   "gamma0", "gamma1", "a_s")]
 
-RESTYPES = {"flexllm_status_string": C.c_char_p, "flexllm_mha_prefill_workspace": C.c_size_t,
+RESTYPES = {"flexllm_status_string": C.c_char_p, "flexllm_launch_count": C.c_ulonglong, "flexllm_mha_prefill_workspace": C.c_size_t,
             "flexllm_mha_decode_workspace": C.c_size_t}
 
 

@@ -456,5 +456,5 @@ int flexllm::mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, con
     FLEXLLM_CHECK_CUDA(cudaMemsetAsync(acc, 0, (size_t)B * HQ * 64 * 4, st));
     dec_pv_kernel<4><<<grid, 256, 0, st>>>(L, page_table, max_pages, ctx, HQ, HKV, ctx_stride, scores, rinv, a_s, acc);
     dec_out_kernel<<<(B * HQ * 64 + 255) / 256, 256, 0, st>>>(acc, a_s, B, HQ, out, oacc);
-    return launch_status();
+    return launch_status(5);
 }

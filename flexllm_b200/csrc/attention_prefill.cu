@@ -467,7 +467,7 @@ int mha_prefill_f32(const float* qkv, const float* cos_t, const float* sin_t, co
                                                                             ws.k2, ws.ks2, ws.v2, ws.vs2);
     dim3 g((S + 63) / 64, HKV, B);
     attn_v_transpose_kernel<<<g, 256, 0, st>>>(ws.v2, ws.vs2, B, S, HKV, ws.vT, ws.vsT);
-    int rc = launch_status();
+    int rc = launch_status(2);
     if (rc != FLEXLLM_OK) return rc;
     if (k2) *k2 = ws.k2;
     if (ks2) *ks2 = ws.ks2;
@@ -502,7 +502,7 @@ extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const
     attn_qk_prepare_kernel<<<(unsigned)((wk + 7) / 8), 256, 0, st>>>(k, ks, cos_t, sin_t, B, S, HKV, ws.k2, ws.ks2);
     dim3 g((S + 63) / 64, HKV, B);
     attn_v_transpose_kernel<<<g, 256, 0, st>>>(v, vs, B, S, HKV, ws.vT, ws.vsT);
-    int rc = launch_status();
+    int rc = launch_status(3);
     if (rc != FLEXLLM_OK) return rc;
     return mha_prefill_core(ws, a_s, B, S, HQ, HKV, out, oacc, st);
 }

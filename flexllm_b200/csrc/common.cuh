@@ -9,14 +9,18 @@
 namespace flexllm {
 
 extern thread_local int g_last_cuda_error;
+// Number of kernels this library has launched in this process (graph replays count the kernels
+// inside the graph). Read through flexllm_launch_count().
+extern unsigned long long g_launch_count;
+inline void note_launches(int n) { g_launch_count += (unsigned long long)n; }
 
 inline int cuda_status(cudaError_t e) {
     if (e == cudaSuccess) return FLEXLLM_OK;
     g_last_cuda_error = (int)e;
     return FLEXLLM_ECUDA;
 }
-// status of the launch that has just been issued
-inline int launch_status() { return cuda_status(cudaGetLastError()); }
+// status of the `n` launches that have just been issued
+inline int launch_status(int n = 1) { note_launches(n); return cuda_status(cudaGetLastError()); }
 
 #define FLEXLLM_CHECK_CUDA(expr)                                   \
     do {                                                           \

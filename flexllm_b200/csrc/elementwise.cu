@@ -6,6 +6,7 @@
 namespace flexllm {
 
 thread_local int g_last_cuda_error = 0;
+unsigned long long g_launch_count = 0;
 
 // ---------------------------------------------------------------------------------------------
 // Per-token symmetric int8 quantisation (Modules/quant.h:6-112, symmetric branch).
@@ -295,6 +296,7 @@ extern "C" const char* flexllm_status_string(int st) {
 }
 
 extern "C" int flexllm_last_cuda_error(void) { return g_last_cuda_error; }
+extern "C" unsigned long long flexllm_launch_count(void) { return g_launch_count; }
 
 extern "C" int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, float* s, void* stream) {
     FLEXLLM_REQUIRE(M >= 0 && K > 0 && (K % 4) == 0 && K <= 8192);

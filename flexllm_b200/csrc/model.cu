@@ -100,7 +100,7 @@ struct flexllm_model {
     size_t attn_ws_bytes = 0, dec_ws_bytes = 0;
     // decode state
     int B = 0, S = 0;
-    cudaGraphExec_t graph = nullptr; int graph_B = 0;
+    cudaGraphExec_t graph = nullptr; int graph_B = 0; int graph_kernels = 0;
     std::vector<void*> owned;
 };
 
@@ -243,6 +243,7 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
     const int QKV = (HQ + 2 * HKV) * 64;
     const int M = B * S;
     embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->x);
+    note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
         TRY(flexllm_rmsnorm_quant(m->x, L.g0, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
@@ -260,6 +261,7 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
         TRY(flexllm_residual(m->x, m->tmp, (long)M * D, m->x, st));
     }
     gather_last_kernel<<<B, 256, 0, st>>>(m->x, S, D, m->xlast);
+    note_launches(1);
     TRY(run_head(m, m->xlast, B, FLEXLLM_NORM_PREFILL, st));
     fill_ctx_kernel<<<1, 64, 0, st>>>(m->ctx, B, S);
     TRY(launch_status());
@@ -275,6 +277,7 @@ static int decode_step(flexllm_model* m, cudaStream_t st) {
     const int QKV = (HQ + 2 * HKV) * 64;
     const int B = m->B;
     embed_kernel<<<B, 256, 0, st>>>(m->next, m->lm_w, m->lm_s, D, m->x);
+    note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
         TRY(flexllm_rmsnorm_quant(m->x, L.g0, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
@@ -305,7 +308,10 @@ static int build_graph(flexllm_model* m) {
     cudaError_t e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal);
     int rc = FLEXLLM_OK;
     if (e == cudaSuccess) {
+        const unsigned long long before = g_launch_count;
         rc = decode_step(m, cap);
+        m->graph_kernels = (int)(g_launch_count - before);   // kernels recorded, not executed
+        g_launch_count = before;
         cudaError_t e2 = cudaStreamEndCapture(cap, &g);
         if (e == cudaSuccess) e = e2;
     }
@@ -331,7 +337,7 @@ extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph
         TRY(build_graph(m));
     }
     for (int i = done; i < n_steps; i++) {
-        if (use_graph) FLEXLLM_CHECK_CUDA(cudaGraphLaunch(m->graph, st));
+        if (use_graph) { FLEXLLM_CHECK_CUDA(cudaGraphLaunch(m->graph, st)); note_launches(m->graph_kernels); }
         else TRY(decode_step(m, st));
     }
     return FLEXLLM_OK;
@@ -343,7 +349,7 @@ extern "C" int flexllm_model_begin(flexllm_model* m, int n_new, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     set_state_kernel<<<1, 1, 0, st>>>(m->state, 0, n_new);
     step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, m->B, m->out_tokens, m->state, m->ctx, 0);
-    return launch_status();
+    return launch_status(2);
 }
 
 // Whole request through host buffers: tokens_host [B][S] -> out_host [B][n_new] (greedy; column 0

@@ -1,0 +1,22 @@
+// Modules/Linear_Layer.h at 8-bit symmetric precision (+ the dequant layer that always follows it)
+#pragma once
+#include "common.hpp"
+namespace flexllm {
+// pref_Linear_Layer_i4xi4 (Linear_Layer.h:294) + pref_dequant_layer_qint_fp32: a [seq_len][K] s8, w [N][K] s8
+inline int pref_Linear_Layer_i8xi8(const int8_t* a, const float* input_s, const int8_t* w, const float* weight_s, int32_t* acc,
+                                   float* y, int seq_len, int output_dim, int input_dim, stream_t st = nullptr) {
+    return flexllm_linear_prefill_i8(a, input_s, w, weight_s, seq_len, output_dim, input_dim, acc, y, st);
+}
+// dec_Linear_Layer_i4xi4 (Linear_Layer.h:863) + dec_dequant_layer_qint_fp32, up to 64 tokens
+inline int dec_Linear_Layer_i8xi8(const int8_t* a, const float* input_s, const int8_t* w, const float* weight_s, int32_t* acc,
+                                  float* y, int tokens, int output_dim, int input_dim, stream_t st = nullptr) {
+    return flexllm_linear_decode_i8(a, input_s, w, weight_s, tokens, output_dim, input_dim, acc, y, st);
+}
+// pref_Gate_Layer_fp32xfp32 (Linear_Layer.h:613) / dec_Gate_Layer_fp32xfp32 (:1104)
+inline int pref_Gate_Layer_fp32xfp32(const float* input, const float* gate, float* y, long n, stream_t st = nullptr) {
+    return flexllm_gate(input, gate, n, y, st);
+}
+inline int dec_Gate_Layer_fp32xfp32(const float* input, const float* gate, float* y, long n, stream_t st = nullptr) {
+    return flexllm_gate(input, gate, n, y, st);
+}
+}  // namespace flexllm

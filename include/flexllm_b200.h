@@ -48,6 +48,8 @@ FLEXLLM_API int flexllm_version(void);
 FLEXLLM_API const char* flexllm_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
 FLEXLLM_API int flexllm_last_cuda_error(void);
+/* Kernels launched by this library in this process so far (a graph replay counts its kernel nodes). */
+FLEXLLM_API unsigned long long flexllm_launch_count(void);
 
 /* ---------------------------------------------------------------------------------------------
  * Linear layers.   acc[m][n] = sum_k a[m][k]*w[n][k]  (exact int32);
