@@ -5,7 +5,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflexllm_b200.so")
 
-OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM = 0, -1, -2, -3, -4, -5
+OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM, ETOOBIG = 0, -1, -2, -3, -4, -5, -6
 
 # name -> argument types, in the order of include/flexllm_b200.h (return type is int unless noted)
 _P, _I, _L, _F, _SZ = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_size_t
@@ -15,6 +15,7 @@ SIGNATURES = {
     "flexllm_launch_count": [],
     "flexllm_linear_prefill_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_linear_decode_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_linear_decode_i8_noalloc": [_P, _P, _P, _P, _I, _I, _I, _P, _P],
     "flexllm_quant_per_token": [_P, _I, _I, _P, _P, _P],
     "flexllm_dequant": [_P, _P, _P, _I, _I, _P, _P],
     "flexllm_static_quant": [_P, _L, _I, _P, _I, _F, _I, _P, _P],

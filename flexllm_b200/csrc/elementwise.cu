@@ -291,6 +291,7 @@ extern "C" const char* flexllm_status_string(int st) {
         case FLEXLLM_ETIMEDOUT: return "device wait timed out";
         case FLEXLLM_ENOTSUP: return "unsupported shape";
         case FLEXLLM_ENOMEM: return "out of memory";
+        case FLEXLLM_ETOOBIG: return "problem exceeds a fixed built-in buffer";
         default: return "unknown status";
     }
 }

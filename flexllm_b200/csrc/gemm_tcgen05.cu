@@ -376,4 +376,74 @@ int gemm_check_error_flag() {
 
 int gemm_sm_count() { return sm_count(); }
 
+// ------------------------------------------------------------------ allocation-free decode linear
+// Built-in scratch for the split-K partial sums of flexllm_linear_decode_i8_noalloc: a fixed array in
+// the library's device image, so the entry point never has to ask the driver for memory. Every GPU
+// that loads the library carries these 4 MiB until the process exits.
+constexpr long kNoAllocMaxElems = 64L * 16384L;   // tokens x output channels, int32 each
+static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocMaxElems];
+static __device__ int g_noalloc_error_flag;
+
+struct NoAllocDev { int32_t* scratch = nullptr; int* flag = nullptr; bool ready = false; };
+
+template <int BN>
+static int launch_gemm_noalloc(const int8_t* w, int N, const int8_t* a, int M, int K, int ksplit, int32_t* acc, int* flag,
+                               cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    CUtensorMap ta, tb;   // encoded on the stack: no cache, nothing retained
+    int rc = make_tmap_2d_u8(&ta, w, (uint64_t)N, (uint64_t)K, 128);
+    if (rc != FLEXLLM_OK) return rc;
+    rc = make_tmap_2d_u8(&tb, a, (uint64_t)M, (uint64_t)K, BN);
+    if (rc != FLEXLLM_OK) return rc;
+    GemmArgs g;
+    g.rowsA = N; g.rowsB = M; g.K = K;
+    g.tilesA = (N + 127) / 128; g.tilesB = 1; g.ksplit = ksplit;
+    g.ldo = N; g.acc = acc; g.y = nullptr; g.sA = nullptr; g.sB = nullptr; g.error_flag = flag;
+    auto kern = gemm_i8_tcgen05_kernel<BN, true>;
+    FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    const int total = g.tilesA * g.ksplit;
+    const int grid = total < sm_count() ? total : sm_count();
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, g);
+    return launch_status();
+}
+
 }  // namespace flexllm
+
+using namespace flexllm;
+
+// See include/flexllm_b200.h. The first call on a device resolves the device addresses of the
+// built-in arrays (cudaGetSymbolAddress: the array's name is only a host-side handle, not a device
+// pointer); make that first call outside any stream capture.
+extern "C" int flexllm_linear_decode_i8_noalloc(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                                int M, int N, int K, float* y, void* stream) {
+    FLEXLLM_REQUIRE(M >= 0 && N > 0 && K > 0 && (K % 16) == 0 && (N % 8) == 0);
+    if (M == 0) return FLEXLLM_OK;
+    FLEXLLM_REQUIRE(a && s_tok && w && s_ch && y);
+    FLEXLLM_REQUIRE(aligned(a, 16) && aligned(w, 16) && aligned(y, 16) && aligned(s_ch, 16));
+    if (M > 64) return FLEXLLM_ENOTSUP;
+    if ((long)M * N > kNoAllocMaxElems) return FLEXLLM_ETOOBIG;   // larger than the built-in scratch
+    static NoAllocDev devs[16];
+    int dev = 0;
+    FLEXLLM_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return FLEXLLM_EINVAL;
+    NoAllocDev& d = devs[dev];
+    if (!d.ready) {
+        FLEXLLM_CHECK_CUDA(cudaGetSymbolAddress((void**)&d.scratch, g_noalloc_scratch));
+        FLEXLLM_CHECK_CUDA(cudaGetSymbolAddress((void**)&d.flag, g_noalloc_error_flag));
+        d.ready = true;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    // split-K as in the allocating entry point: enough CTAs to pull the weights at full HBM rate
+    const int tiles = (N + 127) / 128, num_kb = (K + 127) / 128;
+    int ks = sm_count() / tiles;
+    if (ks > num_kb / 2) ks = num_kb / 2;
+    if (ks < 1) ks = 1;
+    // the array keeps whatever the previous call left in it: the partial sums must start from zero
+    FLEXLLM_CHECK_CUDA(cudaMemsetAsync(d.scratch, 0, (size_t)M * N * sizeof(int32_t), st));
+    int rc;
+    if (M > 32) rc = launch_gemm_noalloc<64>(w, N, a, M, K, ks, d.scratch, d.flag, st);
+    else if (M > 16) rc = launch_gemm_noalloc<32>(w, N, a, M, K, ks, d.scratch, d.flag, st);
+    else rc = launch_gemm_noalloc<16>(w, N, a, M, K, ks, d.scratch, d.flag, st);
+    if (rc != FLEXLLM_OK) return rc;
+    return flexllm_dequant(d.scratch, s_tok, s_ch, M, N, y, stream);
+}

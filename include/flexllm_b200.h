@@ -38,6 +38,7 @@ extern "C" {
 #define FLEXLLM_ETIMEDOUT (-3) /* a bounded device-side wait gave up */
 #define FLEXLLM_ENOTSUP (-4)   /* shape outside what the kernels were built for */
 #define FLEXLLM_ENOMEM (-5)
+#define FLEXLLM_ETOOBIG (-6)   /* problem larger than a fixed built-in buffer */
 
 /* RMSNorm summation orders (Modules/LayerNorm.h:82-130 prefill, :263-321 decode). */
 #define FLEXLLM_NORM_PREFILL 0 /* 4 interleaved partial sums over the whole row          */
@@ -65,6 +66,22 @@ FLEXLLM_API int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, c
                               int M, int N, int K, int32_t* acc, float* y, void* stream);
 FLEXLLM_API int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
                              int M, int N, int K, int32_t* acc, float* y, void* stream);
+
+/* Decode linear layer that never allocates (no counterpart in the reference, whose operators own no
+ * run-time memory at all). For hosts that must not, or cannot, call cudaMalloc around a decode step:
+ * serving loops that have handed the whole device to their own memory pool, and latency-critical
+ * loops where an allocation would stall every stream of the device. Same result as
+ * flexllm_linear_decode_i8 (y only), always on the tensor-core split-K path; the int32 partial sums
+ * live in a 4 MiB array built into the library image (each GPU that loads the library holds it until
+ * exit) instead of a cudaMalloc'd scratch buffer. Limits and rules:
+ *  - M <= 64 and M*N <= 64*16384 (e.g. 64 tokens x the fused gate|up projection); larger problems
+ *    return FLEXLLM_ETOOBIG and leave y untouched;
+ *  - the first call on each device looks up the array's device address; make it before any CUDA
+ *    stream capture begins;
+ *  - all calls share the one array (it is cleared at the start of every call): two calls that can
+ *    run concurrently on the GPU, e.g. on different streams, race -- serialise them. */
+FLEXLLM_API int flexllm_linear_decode_i8_noalloc(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                     int M, int N, int K, float* y, void* stream);
 
 /* Dynamic per-token symmetric int8 quantisation: s = max|x|/127 (0 -> 1), q = round(x/s).
  * Replaces pref_quant_layer_fp32_qint / dec_quant_layer_fp32_qint (quant.h:6-112, :332-431). */
