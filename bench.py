@@ -227,6 +227,52 @@ def kernel_roofline(F, torch, peaks):
             "peak_source": "measured (MEASURED_PEAKS.json)" if peaks.get("hbm_gbs") else "fallback", "per_projection": detail}
 
 
+def micro(args):
+    """Runs one kernel a few times on a small fixed case (for ncu captures; prints its mean time)."""
+    import torch
+    import flexllm_b200 as F
+    from flexllm_b200 import synthetic
+    F.lib()
+    name = args.micro
+    dev = "cuda"
+    if name == "attn_prefill":          # BASELINE config 3: B=4, S=1024, 32/8 heads
+        B, S, HQ, HKV = 4, 1024, 32, 8
+        g = torch.Generator(device=dev).manual_seed(0)
+        r8 = lambda *sh: torch.randint(-127, 128, sh, dtype=torch.int8, device=dev, generator=g)
+        rs = lambda *sh: torch.rand(sh, device=dev, generator=g) * 0.045 + 0.005
+        q, k, v, qs, ks, vs = r8(B, S, HQ, 64), r8(B, S, HKV, 64), r8(B, S, HKV, 64), rs(B, S, HQ), rs(B, S, HKV), rs(B, S, HKV)
+        c, s_ = synthetic.rope_table(S); c = torch.from_numpy(c).to(dev); s_ = torch.from_numpy(s_).to(dev)
+        a_s = torch.full((HQ,), 0.05 / 255, device=dev)
+        fn = lambda: F.MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, c, s_, a_s)
+    elif name in ("gemm_prefill", "gemm_prefill_k8192"):
+        M, N, K = (8192, 8192, 2048) if name == "gemm_prefill" else (8192, 2048, 8192)
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev); w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
+        st = torch.rand(M, device=dev); sc = torch.rand(N, device=dev)
+        fn = lambda: F.pref_Linear_Layer_i8xi8(a, st, w, sc)
+    elif name == "decode_linear":       # gate|up projection of one layer, batch 32; 5 weight sets > L2
+        N, K, B = 16384, 2048, 32
+        ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(5)]
+        a = torch.randint(-127, 128, (B, K), dtype=torch.int8, device=dev); st = torch.rand(B, device=dev); sc = torch.rand(N, device=dev)
+        it = [0]
+        def fn():
+            it[0] += 1
+            return F.dec_Linear_Layer_i8xi8(a, st, ws[it[0] % 5], sc)
+    elif name == "swiglu_fht":
+        gg = torch.randn((4096, 8192), device=dev); uu = torch.randn((4096, 8192), device=dev)
+        fn = lambda: F.swiglu_fht_quant(gg, uu)
+    else:
+        raise SystemExit(f"unknown --micro {name}")
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    print(json.dumps({"micro": name, "ms": e0.elapsed_time(e1) / 3}))
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -326,9 +372,14 @@ def main():
     # profiling aids (the headline workload is the default): shorter decode / skip the side measurements
     ap.add_argument("--decode-len", type=int, default=NEW)
     ap.add_argument("--no-extras", action="store_true", help="skip roofline kernel timing and the CPU baseline")
+    ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, gemm_prefill, "
+                                                  "gemm_prefill_k8192, decode_linear, swiglu_fht)")
     args = ap.parse_args()
     globals()["NEW"] = args.decode_len
     args.warmup = max(args.warmup, 0)
+    if args.micro:
+        micro(args)
+        return
     if args.impl == "reference":
         if env_int("RANK", 0) == 0:
             reference_arm(args)

@@ -15,6 +15,8 @@ SIGNATURES = {
     "flexllm_launch_count": [],
     "flexllm_linear_prefill_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_linear_decode_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_linear_prefill_i8_residual": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_linear_decode_i8_residual": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_linear_decode_i8_noalloc": [_P, _P, _P, _P, _I, _I, _I, _P, _P],
     "flexllm_quant_per_token": [_P, _I, _I, _P, _P, _P],
     "flexllm_dequant": [_P, _P, _P, _I, _I, _P, _P],

@@ -72,10 +72,46 @@ __device__ __forceinline__ int8_t quant_s8(float x, float s) { return (int8_t)(i
 
 // exp() used by SiLU and softmax. The reference calls the C library's expf, whose last-bit
 // rounding the C standard leaves open. This build evaluates the CORRECTLY ROUNDED single-precision
-// exponential: exp in double precision (error below one double ulp), rounded once to fp32. The
-// result is independent of the device math library's fp32 approximation and is reproduced bit for
-// bit by (float)exp((double)x) on any host with an accurate double-precision libm.
-__device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
+// exponential, which (float)exp((double)x) reproduces bit for bit on any host with an accurate
+// double-precision libm.
+//
+// Fast path (|x| < 80), in double precision: x = k*ln2/32 + r with |r| <= ln2/64,
+// exp(x) = 2^(k>>5) * 2^((k&31)/32) * exp(r), exp(r) by a degree-5 Taylor polynomial (truncation
+// error below 2^-48), the 32-entry table of 2^(j/32) generated with exact integer arithmetic
+// (exp_constants.inc). The double result carries a relative error below 2^-45; if it lies within
+// that distance of a float rounding boundary (about one input in two million) the accurate library
+// exp decides instead, as it does outside the fast range.
+#include "exp_constants.inc"
+static __device__ double g_exp2_table[32] = FLEXLLM_EXP2_TABLE;
+
+// out of line on purpose: the rare path must not bloat the unrolled loops that call ref_expf
+__device__ __noinline__ static float ref_expf_accurate(float x) { return __double2float_rn(exp((double)x)); }
+
+__device__ __forceinline__ float ref_expf(float x) {
+    if (x < -104.0f) return 0.0f;                                // exp(x) < 2^-150 rounds to +0
+    const double xd = (double)x;
+    const double shift = 0x1.8p52;                               // 1.5 * 2^52: adding it rounds to an integer
+    const double t = __fma_rn(xd, FLEXLLM_EXP_INV_LN2_32, shift);
+    const int k = __double2loint(t);                             // round(x * 32/ln2), |k| < 3700
+    const double kd = t - shift;
+    double r = __fma_rn(kd, -FLEXLLM_EXP_LN2_32_HI, xd);         // exact: the head has 40 significant bits
+    r = __fma_rn(kd, -FLEXLLM_EXP_LN2_32_LO, r);
+    double p = __fma_rn(r, 1.0 / 120.0, 1.0 / 24.0);
+    p = __fma_rn(p, r, 1.0 / 6.0);
+    p = __fma_rn(p, r, 0.5);
+    p = __fma_rn(p, r, 1.0);
+    p = __fma_rn(p, r, 1.0);
+    const double res = __ldg(&g_exp2_table[k & 31]) * p;         // in [0.98, 2.1): exponent field stays in range below
+    const int hi = __double2hiint(res) + ((k >> 5) << 20);       // multiply by 2^(k>>5)
+    const int lo = __double2loint(res);
+    // rounding to float cuts 29 mantissa bits; the boundary pattern is 1 followed by 28 zeros
+    const unsigned low29 = (unsigned)lo & 0x1fffffffu;
+    const unsigned dist = low29 > 0x10000000u ? low29 - 0x10000000u : 0x10000000u - low29;
+    // one rare branch: near a rounding boundary, or outside the fast range (also NaN, overflow,
+    // subnormal results)
+    if (dist < 256u || !(fabsf(x) < 80.0f)) return ref_expf_accurate(x);
+    return __double2float_rn(__hiloint2double(hi, lo));
+}
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + ref_expf(-g)); }
 

@@ -81,52 +81,23 @@ __global__ void static_quant_kernel(const float* __restrict__ x, long rows, int 
 }
 
 // ---------------------------------------------------------------------------------------------
-// RMSNorm (+ optional per-token int8 quant). One warp per row.
+// RMSNorm (+ optional per-token int8 quant).
 // Sum of squares follows the reference order exactly:
 //   prefill (LayerNorm.h:82-114): 4 chains j = k mod 4 over the whole row, (p0+p1)+(p2+p3);
 //   decode  (LayerNorm.h:263-300): `lanes` contiguous chunks, 4 chains inside each, chunk totals
 //                                  added from 0 in chunk order.
-// Chains are strictly sequential fp32 additions, so each chain is owned by one thread.
+// A chain is a strictly sequential fp32 accumulation, so one thread owns it. To keep all 32 lanes
+// busy a warp runs 32 chains at once: in the prefill order the 4 chains of 8 different rows, in the
+// decode order the (up to) 32 chains of one row. Rows are staged through shared memory in 128-float
+// pieces with coalesced 128-bit loads; the output pass re-reads the row (an L1/L2 hit).
 // ---------------------------------------------------------------------------------------------
-template <int MAXV>  // float4 per lane kept in registers for the output pass (D <= MAXV*128)
-__global__ void __launch_bounds__(128) rmsnorm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                                            int M, int D, float eps, int lanes, float* __restrict__ y,
-                                                            int8_t* __restrict__ q, float* __restrict__ s) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp >= M) return;
-    const float* xr = x + (long)warp * D;
-    float tot;
-    if (lanes == 0) {
-        float ss = 0.0f;
-        if (lane < 4) {
-            const int n = D >> 2;
-#pragma unroll 8
-            for (int k = 0; k < n; k++) { float v = xr[4 * k + lane]; ss += v * v; }
-        }
-        float p0 = __shfl_sync(0xffffffffu, ss, 0), p1 = __shfl_sync(0xffffffffu, ss, 1);
-        float p2 = __shfl_sync(0xffffffffu, ss, 2), p3 = __shfl_sync(0xffffffffu, ss, 3);
-        tot = (p0 + p1) + (p2 + p3);
-    } else {
-        // lanes*4 <= 32 chains: lane = chunk*4 + j
-        const int C = D / lanes;
-        float ss = 0.0f;
-        const int chunk = lane >> 2, j = lane & 3;
-        if (chunk < lanes) {
-            const float* xc = xr + chunk * C;
-            const int n = C >> 2;
-#pragma unroll 8
-            for (int k = 0; k < n; k++) { float v = xc[4 * k + j]; ss += v * v; }
-        }
-        tot = 0.0f;
-        for (int c = 0; c < lanes; c++) {
-            float p0 = __shfl_sync(0xffffffffu, ss, c * 4 + 0), p1 = __shfl_sync(0xffffffffu, ss, c * 4 + 1);
-            float p2 = __shfl_sync(0xffffffffu, ss, c * 4 + 2), p3 = __shfl_sync(0xffffffffu, ss, c * 4 + 3);
-            tot += (p0 + p1) + (p2 + p3);
-        }
-    }
-    const float r = 1.0f / sqrtf(tot / (float)D + eps);
+constexpr int RMS_WARPS = 4;
+constexpr int RMS_PIECE = 128;           // floats per row per staging step
+constexpr int RMS_PSTRIDE = RMS_PIECE + 4;   // padded: rows land in different banks
 
+template <int MAXV>  // float4 per lane kept in registers for the output pass (D <= MAXV*128)
+__device__ __forceinline__ void rmsnorm_output_row(const float* __restrict__ xr, const float* __restrict__ gamma, int D, float r,
+                                                   float* __restrict__ yr, int8_t* __restrict__ qr8, float* __restrict__ srow, int lane) {
     const int nv = D >> 2;
     float4 o[MAXV];
     float mx = -1e32f, mn = 1e32f;
@@ -137,16 +108,16 @@ __global__ void __launch_bounds__(128) rmsnorm_quant_kernel(const float* __restr
             float4 v = reinterpret_cast<const float4*>(xr)[c];
             float4 g = reinterpret_cast<const float4*>(gamma)[c];
             o[i].x = (v.x * r) * g.x; o[i].y = (v.y * r) * g.y; o[i].z = (v.z * r) * g.z; o[i].w = (v.w * r) * g.w;
-            if (y) reinterpret_cast<float4*>(y + (long)warp * D)[c] = o[i];
+            if (yr) reinterpret_cast<float4*>(yr)[c] = o[i];
             mx = fmaxf(mx, fmaxf(fmaxf(o[i].x, o[i].y), fmaxf(o[i].z, o[i].w)));
             mn = fminf(mn, fminf(fminf(o[i].x, o[i].y), fminf(o[i].z, o[i].w)));
         }
     }
-    if (q) {
+    if (qr8) {
         mx = warp_max(mx); mn = warp_min(mn);
         const float sc = sym_scale_from(mx, mn);
-        if (lane == 0) s[warp] = sc;
-        char4* qr = reinterpret_cast<char4*>(q + (long)warp * D);
+        if (lane == 0) *srow = sc;
+        char4* qr = reinterpret_cast<char4*>(qr8);
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
             int c = lane + i * 32;
@@ -157,6 +128,81 @@ __global__ void __launch_bounds__(128) rmsnorm_quant_kernel(const float* __restr
             }
         }
     }
+}
+
+// Prefill order: each warp takes 8 consecutive rows. Requires D % 128 == 0.
+template <int MAXV>
+__global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_prefill_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                         int M, int D, float eps, float* __restrict__ y,
+                                                                         int8_t* __restrict__ q, float* __restrict__ s) {
+    __shared__ __align__(16) float stage[RMS_WARPS][8][RMS_PSTRIDE];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long row0 = ((long)blockIdx.x * RMS_WARPS + w) * 8;
+    if (row0 >= M) return;
+    const int rr = lane >> 2, j = lane & 3;      // chain (row rr of the group, residue j)
+    float ss = 0.0f;
+    for (int p = 0; p < D; p += RMS_PIECE) {
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row0 + r < M) v = *reinterpret_cast<const float4*>(x + (row0 + r) * D + p + lane * 4);
+            *reinterpret_cast<float4*>(&stage[w][r][lane * 4]) = v;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < RMS_PIECE / 4; k++) { const float v = stage[w][rr][4 * k + j]; ss += v * v; }
+        __syncwarp();
+    }
+    // (p0+p1)+(p2+p3) inside each group of four lanes
+    const int base = lane & ~3;
+    const float p0 = __shfl_sync(0xffffffffu, ss, base), p1 = __shfl_sync(0xffffffffu, ss, base + 1);
+    const float p2 = __shfl_sync(0xffffffffu, ss, base + 2), p3 = __shfl_sync(0xffffffffu, ss, base + 3);
+    const float tot = (p0 + p1) + (p2 + p3);
+    const float rinv = 1.0f / sqrtf(tot / (float)D + eps);
+#pragma unroll 1
+    for (int r = 0; r < 8; r++) {
+        const float rr_inv = __shfl_sync(0xffffffffu, rinv, r * 4);
+        const long row = row0 + r;
+        if (row < M)
+            rmsnorm_output_row<MAXV>(x + row * D, gamma, D, rr_inv, y ? y + row * D : nullptr, q ? q + row * D : nullptr,
+                                     s ? s + row : nullptr, lane);
+    }
+}
+
+// Decode order with `lanes` (4 or 8) chunks: one warp per row, lane = chunk*4 + j.
+template <int MAXV>
+__global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_decode_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                        int M, int D, float eps, int lanes, float* __restrict__ y,
+                                                                        int8_t* __restrict__ q, float* __restrict__ s) {
+    extern __shared__ __align__(16) float rowbuf[];          // RMS_WARPS x (D + 4*lanes)
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long row = (long)blockIdx.x * RMS_WARPS + w;
+    if (row >= M) return;
+    const int C = D / lanes;                                  // chunk length, a multiple of 4
+    float* buf = rowbuf + (size_t)w * (D + 4 * lanes);
+    const float* xr = x + row * D;
+    for (int c = lane; c < (D >> 2); c += 32) {               // element i lives at i + 4*(i / C)
+        const float4 v = reinterpret_cast<const float4*>(xr)[c];
+        const int i = c * 4;
+        *reinterpret_cast<float4*>(buf + i + 4 * (i / C)) = v;
+    }
+    __syncwarp();
+    const int chunk = lane >> 2, j = lane & 3;
+    float ss = 0.0f;
+    if (chunk < lanes) {
+        const float* bc = buf + chunk * (C + 4);
+        const int n = C >> 2;
+#pragma unroll 8
+        for (int k = 0; k < n; k++) { const float v = bc[4 * k + j]; ss += v * v; }
+    }
+    float tot = 0.0f;
+    for (int c = 0; c < lanes; c++) {
+        const float p0 = __shfl_sync(0xffffffffu, ss, c * 4 + 0), p1 = __shfl_sync(0xffffffffu, ss, c * 4 + 1);
+        const float p2 = __shfl_sync(0xffffffffu, ss, c * 4 + 2), p3 = __shfl_sync(0xffffffffu, ss, c * 4 + 3);
+        tot += (p0 + p1) + (p2 + p3);
+    }
+    const float rinv = 1.0f / sqrtf(tot / (float)D + eps);
+    rmsnorm_output_row<MAXV>(xr, gamma, D, rinv, y ? y + row * D : nullptr, q ? q + row * D : nullptr, s ? s + row : nullptr, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -338,9 +384,20 @@ extern "C" int flexllm_rmsnorm_quant(const float* x, const float* gamma, int M, 
     FLEXLLM_REQUIRE(aligned(x, 16) && aligned(gamma, 16) && (!y || aligned(y, 16)) && (!q || aligned(q, 4)));
     if (M == 0) return FLEXLLM_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    const int grid = (M + 3) / 4;
-    if (D <= 2048) rmsnorm_quant_kernel<16><<<grid, 128, 0, st>>>(x, gamma, M, D, eps, order, y, q, s);
-    else rmsnorm_quant_kernel<32><<<grid, 128, 0, st>>>(x, gamma, M, D, eps, order, y, q, s);
+    if (order == 0) {
+        if (D % RMS_PIECE != 0) return FLEXLLM_ENOTSUP;
+        const int grid = (M + RMS_WARPS * 8 - 1) / (RMS_WARPS * 8);
+        if (D <= 2048) rmsnorm_prefill_kernel<16><<<grid, RMS_WARPS * 32, 0, st>>>(x, gamma, M, D, eps, y, q, s);
+        else rmsnorm_prefill_kernel<32><<<grid, RMS_WARPS * 32, 0, st>>>(x, gamma, M, D, eps, y, q, s);
+    } else {
+        const int grid = (M + RMS_WARPS - 1) / RMS_WARPS;
+        const size_t smem = (size_t)RMS_WARPS * (D + 4 * order) * sizeof(float);
+        if (D <= 2048) rmsnorm_decode_kernel<16><<<grid, RMS_WARPS * 32, smem, st>>>(x, gamma, M, D, eps, order, y, q, s);
+        else {
+            FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            rmsnorm_decode_kernel<32><<<grid, RMS_WARPS * 32, smem, st>>>(x, gamma, M, D, eps, order, y, q, s);
+        }
+    }
     return launch_status();
 }
 

@@ -80,6 +80,11 @@ struct GemmArgs {
     const float* sA;         // per-row scale of the A side
     const float* sB;         // per-row scale of the B side
     int* error_flag;         // set to 1 if a device-side wait ran out
+    // fused epilogue extras
+    const float* residual;   // optional: y = residual + dequant (same layout as y)
+    int32_t* work;           // split-K: zeroed int32 partial-sum buffer [rowsB][ldo]; the last arriver
+                             // turns it into the outputs and leaves it zeroed again
+    int* counters;           // split-K: zeroed arrival counters, one per (A tile, warp quarter)
 };
 
 template <int BN> struct GemmCfg {
@@ -228,6 +233,10 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                                     r.y = ((float)(int)v[j + 1] * sa) * sb.y;
                                     r.z = ((float)(int)v[j + 2] * sa) * sb.z;
                                     r.w = ((float)(int)v[j + 3] * sa) * sb.w;
+                                    if (args.residual) {
+                                        const float4 rs = *reinterpret_cast<const float4*>(args.residual + o + j);
+                                        r.x = rs.x + r.x; r.y = rs.y + r.y; r.z = rs.z + r.z; r.w = rs.w + r.w;
+                                    }
                                     *reinterpret_cast<float4*>(args.y + o + j) = r;
                                 }
                             }
@@ -241,10 +250,14 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                         if (rowA_ok && tok < args.rowsB) {
                             const long o = (long)tok * args.ldo + rowA;
                             if (args.ksplit > 1) {
-                                atomicAdd(args.acc + o, (int)v[j]);
+                                atomicAdd((args.work ? args.work : args.acc) + o, (int)v[j]);
                             } else {
                                 if (args.acc) args.acc[o] = (int)v[j];
-                                if (args.y) args.y[o] = ((float)(int)v[j] * args.sB[tok]) * sa;
+                                if (args.y) {
+                                    float r = ((float)(int)v[j] * args.sB[tok]) * sa;
+                                    if (args.residual) r = args.residual[o] + r;
+                                    args.y[o] = r;
+                                }
                             }
                         }
                     }
@@ -253,6 +266,52 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * as);
+            if (SWAP && args.ksplit > 1 && args.work) {
+                // split-K with fused finalisation: the warp that arrives last on this (tile, quarter)
+                // reads the complete integer sums, writes the outputs and re-zeroes the work buffer
+                __threadfence();
+                int last = 0;
+                if (lane == 0) last = (atomicAdd(args.counters + ta * 4 + q, 1) == args.ksplit - 1);
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    if (rowA_ok) {
+                        // batches of 16 tokens: the loads of a batch are independent, so their
+                        // L2 latencies overlap
+                        for (int t0 = 0; t0 < args.rowsB; t0 += 16) {
+                            int vv[16];
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                const int tok = t0 + j;
+                                vv[j] = tok < args.rowsB ? __ldcg(args.work + (long)tok * args.ldo + rowA) : 0;
+                            }
+                            float rs[16];
+                            if (args.residual) {
+#pragma unroll
+                                for (int j = 0; j < 16; j++) {
+                                    const int tok = t0 + j;
+                                    rs[j] = tok < args.rowsB ? args.residual[(long)tok * args.ldo + rowA] : 0.0f;
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                const int tok = t0 + j;
+                                if (tok < args.rowsB) {
+                                    const long o = (long)tok * args.ldo + rowA;
+                                    args.work[o] = 0;
+                                    if (args.acc) args.acc[o] = vv[j];
+                                    if (args.y) {
+                                        float r = ((float)vv[j] * args.sB[tok]) * sa;
+                                        if (args.residual) r = rs[j] + r;
+                                        args.y[o] = r;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    if (lane == 0) args.counters[ta * 4 + q] = 0;
+                }
+            }
         }
     }
 
@@ -322,7 +381,8 @@ static int sm_count() {
 
 template <int BN, bool SWAP>
 static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, int K, int ksplit, int ldo,
-                       int32_t* acc, float* y, const float* sA, const float* sB, cudaStream_t st) {
+                       int32_t* acc, float* y, const float* sA, const float* sB, cudaStream_t st,
+                       const float* residual = nullptr, int32_t* work = nullptr, int* counters = nullptr) {
     using Cfg = GemmCfg<BN>;
     CUtensorMap ta, tb;
     int rc = cached_tmap(&ta, A, (uint64_t)rowsA, (uint64_t)K, 128);
@@ -333,6 +393,7 @@ static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, i
     g.rowsA = rowsA; g.rowsB = rowsB; g.K = K;
     g.tilesA = (rowsA + 127) / 128; g.tilesB = (rowsB + BN - 1) / BN; g.ksplit = ksplit;
     g.ldo = ldo; g.acc = acc; g.y = y; g.sA = sA; g.sB = sB; g.error_flag = device_error_flag();
+    g.residual = residual; g.work = work; g.counters = counters;
     auto kern = gemm_i8_tcgen05_kernel<BN, SWAP>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -345,24 +406,26 @@ static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, i
     return launch_status();
 }
 
-// Prefill orientation: activations on the 128-row side.
+// Prefill orientation: activations on the 128-row side. residual (optional): y = residual + dequant.
 int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-                    int32_t* acc, float* y, cudaStream_t st) {
-    if (N > 128) return launch_gemm<256, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
-    if (N > 64) return launch_gemm<128, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
-    if (N > 32) return launch_gemm<64, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
-    if (N > 16) return launch_gemm<32, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
-    return launch_gemm<16, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st);
+                    int32_t* acc, float* y, cudaStream_t st, const float* residual) {
+    if (N > 128) return launch_gemm<256, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st, residual);
+    if (N > 64) return launch_gemm<128, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st, residual);
+    if (N > 32) return launch_gemm<64, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st, residual);
+    if (N > 16) return launch_gemm<32, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st, residual);
+    return launch_gemm<16, false>(a, M, w, N, K, 1, N, acc, y, s_tok, s_ch, st, residual);
 }
 
 // Decode orientation: weights on the 128-row side, M <= 64 tokens on the N side, optional split-K.
-// With ksplit > 1 the caller passes a ZEROED int32 buffer in `acc` and dequantises afterwards.
+// With ksplit > 1 the partial sums go through `work` (zeroed int32 [M][N]) and `counters` (zeroed,
+// 4 per 128-channel tile); the last-arriving warp writes acc / y (+ residual) and re-zeroes both.
 int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-                   int ksplit, int32_t* acc, float* y, cudaStream_t st) {
+                   int ksplit, int32_t* acc, float* y, cudaStream_t st, const float* residual, int32_t* work, int* counters) {
     if (M > 64) return FLEXLLM_ENOTSUP;
-    if (M > 32) return launch_gemm<64, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st);
-    if (M > 16) return launch_gemm<32, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st);
-    return launch_gemm<16, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st);
+    if (ksplit > 1 && !(work && counters)) return FLEXLLM_EINVAL;
+    if (M > 32) return launch_gemm<64, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters);
+    if (M > 16) return launch_gemm<32, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters);
+    return launch_gemm<16, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters);
 }
 
 int gemm_check_error_flag() {
@@ -399,6 +462,7 @@ static int launch_gemm_noalloc(const int8_t* w, int N, const int8_t* a, int M, i
     g.rowsA = N; g.rowsB = M; g.K = K;
     g.tilesA = (N + 127) / 128; g.tilesB = 1; g.ksplit = ksplit;
     g.ldo = N; g.acc = acc; g.y = nullptr; g.sA = nullptr; g.sB = nullptr; g.error_flag = flag;
+    g.residual = nullptr; g.work = nullptr; g.counters = nullptr;
     auto kern = gemm_i8_tcgen05_kernel<BN, true>;
     FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     const int total = g.tilesA * g.ksplit;

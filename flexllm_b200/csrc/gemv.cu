@@ -24,7 +24,7 @@ template <int BT, int R>
 __global__ void __launch_bounds__(128) gemv_i8_kernel(const int8_t* __restrict__ a, const float* __restrict__ s_tok,
                                                       const int8_t* __restrict__ w, const float* __restrict__ s_ch,
                                                       int M, int N, int K, int32_t* __restrict__ acc_out,
-                                                      float* __restrict__ y) {
+                                                      float* y, const float* residual) {
     extern __shared__ int4 a_sm[];   // [BT][K/16]
     const int kv = K >> 4;
     for (int i = threadIdx.x; i < BT * kv; i += blockDim.x) {
@@ -87,7 +87,11 @@ __global__ void __launch_bounds__(128) gemv_i8_kernel(const int8_t* __restrict__
                 for (int b = 0; b < BT; b++)
                     if (b < M) {
                         if (acc_out) acc_out[(long)b * N + n] = acc[r][b];
-                        if (y) y[(long)b * N + n] = ((float)acc[r][b] * s_tok[b]) * sc;
+                        if (y) {
+                            float v = ((float)acc[r][b] * s_tok[b]) * sc;
+                            if (residual) v = residual[(long)b * N + n] + v;   // y may alias residual
+                            y[(long)b * N + n] = v;
+                        }
                     }
             }
         }
@@ -96,31 +100,31 @@ __global__ void __launch_bounds__(128) gemv_i8_kernel(const int8_t* __restrict__
 
 template <int BT>
 static int launch_gemv(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-                       int32_t* acc, float* y, cudaStream_t st) {
+                       int32_t* acc, float* y, const float* residual, cudaStream_t st) {
     const size_t smem = (size_t)BT * K;
     // rows per warp: keep at least ~4 CTAs per SM worth of grid
     if (N >= 148 * 4 * 4 * 4) {
         constexpr int R = 4;
         auto kern = gemv_i8_kernel<BT, R>;
         if (smem > 48 * 1024) FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<(N + 4 * R - 1) / (4 * R), 128, smem, st>>>(a, s_tok, w, s_ch, M, N, K, acc, y);
+        kern<<<(N + 4 * R - 1) / (4 * R), 128, smem, st>>>(a, s_tok, w, s_ch, M, N, K, acc, y, residual);
     } else {
         constexpr int R = 2;
         auto kern = gemv_i8_kernel<BT, R>;
         if (smem > 48 * 1024) FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<(N + 4 * R - 1) / (4 * R), 128, smem, st>>>(a, s_tok, w, s_ch, M, N, K, acc, y);
+        kern<<<(N + 4 * R - 1) / (4 * R), 128, smem, st>>>(a, s_tok, w, s_ch, M, N, K, acc, y, residual);
     }
     return launch_status();
 }
 
 // M <= 8 tokens. Returns FLEXLLM_ENOTSUP for larger M (the caller then uses the tensor-core path).
 int gemv_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-            int32_t* acc, float* y, cudaStream_t st) {
+            int32_t* acc, float* y, const float* residual, cudaStream_t st) {
     if (M > 8) return FLEXLLM_ENOTSUP;
-    if (M <= 1) return launch_gemv<1>(a, s_tok, w, s_ch, M, N, K, acc, y, st);
-    if (M <= 2) return launch_gemv<2>(a, s_tok, w, s_ch, M, N, K, acc, y, st);
-    if (M <= 4) return launch_gemv<4>(a, s_tok, w, s_ch, M, N, K, acc, y, st);
-    return launch_gemv<8>(a, s_tok, w, s_ch, M, N, K, acc, y, st);
+    if (M <= 1) return launch_gemv<1>(a, s_tok, w, s_ch, M, N, K, acc, y, residual, st);
+    if (M <= 2) return launch_gemv<2>(a, s_tok, w, s_ch, M, N, K, acc, y, residual, st);
+    if (M <= 4) return launch_gemv<4>(a, s_tok, w, s_ch, M, N, K, acc, y, residual, st);
+    return launch_gemv<8>(a, s_tok, w, s_ch, M, N, K, acc, y, residual, st);
 }
 
 }  // namespace flexllm

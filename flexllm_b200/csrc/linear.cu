@@ -4,18 +4,22 @@
 
 namespace flexllm {
 int gemv_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-            int32_t* acc, float* y, cudaStream_t st);
+            int32_t* acc, float* y, const float* residual, cudaStream_t st);
 int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-                    int32_t* acc, float* y, cudaStream_t st);
+                    int32_t* acc, float* y, cudaStream_t st, const float* residual);
 int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-                   int ksplit, int32_t* acc, float* y, cudaStream_t st);
+                   int ksplit, int32_t* acc, float* y, cudaStream_t st, const float* residual, int32_t* work, int* counters);
 int gemm_sm_count();
 
-// Library-owned int32 scratch for split-K partial sums, one per device, grown on demand.
+// Library-owned split-K scratch, one per device, grown on demand: int32 partial sums followed by the
+// arrival counters. Invariant: all zero between launches (the kernel's last arriver restores it), so
+// launches on one stream can share it without a memset. Launches on different streams must not
+// overlap (they would mix their partial sums).
 struct Scratch { void* p = nullptr; size_t bytes = 0; };
 static Scratch g_scratch[16];
+constexpr size_t kCounterBytes = 16384;   // 4 counters per 128-channel tile, up to 131072 channels
 
-int scratch_get(size_t bytes, void** out) {
+int scratch_get(size_t bytes, int32_t** work, int** counters) {
     int dev = 0;
     FLEXLLM_CHECK_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 16) return FLEXLLM_EINVAL;
@@ -23,10 +27,12 @@ int scratch_get(size_t bytes, void** out) {
     if (s.bytes < bytes) {
         if (s.p) { FLEXLLM_CHECK_CUDA(cudaDeviceSynchronize()); FLEXLLM_CHECK_CUDA(cudaFree(s.p)); s.p = nullptr; s.bytes = 0; }
         size_t want = bytes < (size_t)(8 << 20) ? (size_t)(8 << 20) : bytes;
-        FLEXLLM_CHECK_CUDA(cudaMalloc(&s.p, want));
+        FLEXLLM_CHECK_CUDA(cudaMalloc(&s.p, want + kCounterBytes));
+        FLEXLLM_CHECK_CUDA(cudaMemset(s.p, 0, want + kCounterBytes));
         s.bytes = want;
     }
-    *out = s.p;
+    *work = (int32_t*)s.p;
+    *counters = (int*)((char*)s.p + s.bytes);
     return FLEXLLM_OK;
 }
 
@@ -53,34 +59,48 @@ static int check_linear(const int8_t* a, const float* s_tok, const int8_t* w, co
     return FLEXLLM_OK;
 }
 
-extern "C" int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
-                                         int M, int N, int K, int32_t* acc, float* y, void* stream) {
+static int linear_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                          int32_t* acc, float* y, const float* residual, void* stream) {
     int rc = check_linear(a, s_tok, w, s_ch, M, N, K, acc, y);
     if (rc != FLEXLLM_OK) return rc;
+    FLEXLLM_REQUIRE(!residual || (y && aligned(residual, 16)));
     if (M == 0) return FLEXLLM_OK;
-    return gemm_i8_prefill(a, s_tok, w, s_ch, M, N, K, acc, y, (cudaStream_t)stream);
+    return gemm_i8_prefill(a, s_tok, w, s_ch, M, N, K, acc, y, (cudaStream_t)stream, residual);
 }
 
-extern "C" int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
-                                        int M, int N, int K, int32_t* acc, float* y, void* stream) {
+static int linear_decode(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
+                         int32_t* acc, float* y, const float* residual, void* stream) {
     int rc = check_linear(a, s_tok, w, s_ch, M, N, K, acc, y);
     if (rc != FLEXLLM_OK) return rc;
+    FLEXLLM_REQUIRE(!residual || y);
     if (M == 0) return FLEXLLM_OK;
     if (M > 64) return FLEXLLM_ENOTSUP;
     cudaStream_t st = (cudaStream_t)stream;
-    if (M <= 8) return gemv_i8(a, s_tok, w, s_ch, M, N, K, acc, y, st);
+    if (M <= 8) return gemv_i8(a, s_tok, w, s_ch, M, N, K, acc, y, residual, st);
     const int ks = decode_ksplit(N, K);
-    if (ks == 1) return gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, 1, acc, y, st);
-    int32_t* part = acc;
-    if (!part) {
-        void* p = nullptr;
-        rc = scratch_get((size_t)M * N * sizeof(int32_t), &p);
-        if (rc != FLEXLLM_OK) return rc;
-        part = (int32_t*)p;
-    }
-    FLEXLLM_CHECK_CUDA(cudaMemsetAsync(part, 0, (size_t)M * N * sizeof(int32_t), st));
-    rc = gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, ks, part, nullptr, st);
+    if (ks == 1) return gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, 1, acc, y, st, residual, nullptr, nullptr);
+    if ((size_t)((N + 127) / 128) * 16 > kCounterBytes) return FLEXLLM_ENOTSUP;
+    int32_t* work = nullptr; int* counters = nullptr;
+    rc = scratch_get((size_t)M * N * sizeof(int32_t), &work, &counters);
     if (rc != FLEXLLM_OK) return rc;
-    if (y) return flexllm_dequant(part, s_tok, s_ch, M, N, y, stream);
-    return FLEXLLM_OK;
+    return gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, ks, acc, y, st, residual, work, counters);
+}
+
+extern "C" int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                         int M, int N, int K, int32_t* acc, float* y, void* stream) {
+    return linear_prefill(a, s_tok, w, s_ch, M, N, K, acc, y, nullptr, stream);
+}
+extern "C" int flexllm_linear_prefill_i8_residual(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                                  int M, int N, int K, const float* residual, float* y, void* stream) {
+    FLEXLLM_REQUIRE(residual);
+    return linear_prefill(a, s_tok, w, s_ch, M, N, K, nullptr, y, residual, stream);
+}
+extern "C" int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                        int M, int N, int K, int32_t* acc, float* y, void* stream) {
+    return linear_decode(a, s_tok, w, s_ch, M, N, K, acc, y, nullptr, stream);
+}
+extern "C" int flexllm_linear_decode_i8_residual(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                                 int M, int N, int K, const float* residual, float* y, void* stream) {
+    FLEXLLM_REQUIRE(residual);
+    return linear_decode(a, s_tok, w, s_ch, M, N, K, nullptr, y, residual, stream);
 }

@@ -21,7 +21,7 @@ struct flexllm_kv_cache;
 
 namespace flexllm {
 int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
-                    int32_t* acc, float* y, cudaStream_t st);
+                    int32_t* acc, float* y, cudaStream_t st, const float* residual);
 int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st);
 size_t mha_prefill_ws_bytes(int B, int S, int HQ, int HKV);
 int mha_prefill_f32(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int S, int HQ, int HKV,
@@ -247,18 +247,16 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
         TRY(flexllm_rmsnorm_quant(m->x, L.g0, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
-        TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, M, QKV, D, nullptr, m->qkv, st));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, M, QKV, D, nullptr, m->qkv, st, nullptr));
         const int8_t *k2, *vT; const float *ks2, *vsT;
         TRY(mha_prefill_f32(m->qkv, m->cos_t, m->sin_t, L.a_s, B, S, HQ, HKV, m->att, m->attn_ws, st, &k2, &ks2, &vT, &vsT));
         TRY(kv_pack(m->cache, l, k2, ks2, vT, vsT, m->page_table, m->max_pages, B, S, st));
         TRY(flexllm_quant_per_token(m->att, M, D, m->xq, m->xs, st));
-        TRY(gemm_i8_prefill(m->xq, m->xs, L.wo, L.so, M, D, D, nullptr, m->tmp, st));
-        TRY(flexllm_residual(m->x, m->tmp, (long)M * D, m->x, st));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wo, L.so, M, D, D, nullptr, m->x, st, m->x));       // x += o_proj
         TRY(flexllm_rmsnorm_quant(m->x, L.g1, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
-        TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, M, 2 * F, D, nullptr, m->gu, st));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, M, 2 * F, D, nullptr, m->gu, st, nullptr));
         TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, M, m->cfg.fht_scale, m->hq, m->xs, st));
-        TRY(gemm_i8_prefill(m->hq, m->xs, L.wd, L.sd, M, D, F, nullptr, m->tmp, st));
-        TRY(flexllm_residual(m->x, m->tmp, (long)M * D, m->x, st));
+        TRY(gemm_i8_prefill(m->hq, m->xs, L.wd, L.sd, M, D, F, nullptr, m->x, st, m->x));       // x += down_proj
     }
     gather_last_kernel<<<B, 256, 0, st>>>(m->x, S, D, m->xlast);
     note_launches(1);
@@ -285,13 +283,11 @@ static int decode_step(flexllm_model* m, cudaStream_t st) {
         TRY(mha_decode_run(m->cache, l, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, m->qkv, m->cos_t, m->sin_t, L.a_s,
                            m->page_table, m->max_pages, m->ctx, m->cfg.max_ctx, B, HQ, m->att, nullptr, m->dec_ws, st));
         TRY(flexllm_quant_per_token(m->att, B, D, m->xq, m->xs, st));
-        TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wo, L.so, B, D, D, nullptr, m->tmp, st));
-        TRY(flexllm_residual(m->x, m->tmp, (long)B * D, m->x, st));
+        TRY(flexllm_linear_decode_i8_residual(m->xq, m->xs, L.wo, L.so, B, D, D, m->x, m->x, st));
         TRY(flexllm_rmsnorm_quant(m->x, L.g1, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
         TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wgu, L.sgu, B, 2 * F, D, nullptr, m->gu, st));
         TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, B, m->cfg.fht_scale, m->hq, m->xs, st));
-        TRY(flexllm_linear_decode_i8(m->hq, m->xs, L.wd, L.sd, B, D, F, nullptr, m->tmp, st));
-        TRY(flexllm_residual(m->x, m->tmp, (long)B * D, m->x, st));
+        TRY(flexllm_linear_decode_i8_residual(m->hq, m->xs, L.wd, L.sd, B, D, F, m->x, m->x, st));
     }
     TRY(run_head(m, m->x, B, FLEXLLM_NORM_DECODE8, st));
     step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, B, m->out_tokens, m->state, m->ctx, 1);

@@ -49,18 +49,27 @@ def _call(name, *args):
 
 
 # ------------------------------------------------------------------------------ linear layers
-def pref_Linear_Layer_i8xi8(a, s_tok, w, s_ch, want_acc=False, want_y=True):
-    """Prefill W8A8 linear layer. a [M,K] int8, w [N,K] int8. Returns (acc int32 | None, y fp32 | None)."""
+def pref_Linear_Layer_i8xi8(a, s_tok, w, s_ch, want_acc=False, want_y=True, residual=None):
+    """Prefill W8A8 linear layer. a [M,K] int8, w [N,K] int8. Returns (acc int32 | None, y fp32 | None).
+    With residual [M,N] the following Residual_Layer is fused: y = residual + dequant."""
     M, K = a.shape; N = w.shape[0]
+    if residual is not None:
+        y = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        _call("flexllm_linear_prefill_i8_residual", _ptr(a), _ptr(s_tok), _ptr(w), _ptr(s_ch), M, N, K, _ptr(residual), _ptr(y))
+        return None, y
     acc = torch.empty((M, N), dtype=torch.int32, device=a.device) if want_acc else None
     y = torch.empty((M, N), dtype=torch.float32, device=a.device) if want_y else None
     _call("flexllm_linear_prefill_i8", _ptr(a), _ptr(s_tok), _ptr(w), _ptr(s_ch), M, N, K, _ptr(acc), _ptr(y))
     return acc, y
 
 
-def dec_Linear_Layer_i8xi8(a, s_tok, w, s_ch, want_acc=False, want_y=True):
-    """Decode W8A8 linear layer, M <= 64 tokens."""
+def dec_Linear_Layer_i8xi8(a, s_tok, w, s_ch, want_acc=False, want_y=True, residual=None):
+    """Decode W8A8 linear layer, M <= 64 tokens (optionally fused with the residual add)."""
     M, K = a.shape; N = w.shape[0]
+    if residual is not None:
+        y = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        _call("flexllm_linear_decode_i8_residual", _ptr(a), _ptr(s_tok), _ptr(w), _ptr(s_ch), M, N, K, _ptr(residual), _ptr(y))
+        return None, y
     acc = torch.empty((M, N), dtype=torch.int32, device=a.device) if want_acc else None
     y = torch.empty((M, N), dtype=torch.float32, device=a.device) if want_y else None
     _call("flexllm_linear_decode_i8", _ptr(a), _ptr(s_tok), _ptr(w), _ptr(s_ch), M, N, K, _ptr(acc), _ptr(y))

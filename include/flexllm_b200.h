@@ -67,6 +67,14 @@ FLEXLLM_API int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, c
 FLEXLLM_API int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
                              int M, int N, int K, int32_t* acc, float* y, void* stream);
 
+/* The same two layers fused with the residual add that follows them in the model
+ * (pref_Residual_Layer / dec_Residual_Layer, Residual_Layer.h:46-87): y = residual + dequant(acc).
+ * residual and y have the layout of y above and may alias. */
+FLEXLLM_API int flexllm_linear_prefill_i8_residual(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                       int M, int N, int K, const float* residual, float* y, void* stream);
+FLEXLLM_API int flexllm_linear_decode_i8_residual(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
+                                      int M, int N, int K, const float* residual, float* y, void* stream);
+
 /* Decode linear layer that never allocates (no counterpart in the reference, whose operators own no
  * run-time memory at all). For hosts that must not, or cannot, call cudaMalloc around a decode step:
  * serving loops that have handed the whole device to their own memory pool, and latency-critical

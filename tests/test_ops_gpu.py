@@ -200,6 +200,19 @@ def test_elementwise(F):
     assert ulp.max() <= 2
 
 
+def test_exp_dense(F):
+    """The device exponential is the correctly rounded one: silu and 2-element softmax rows over
+    millions of arguments, including the ranges where the fast path hands over (|x| >= 80), where
+    exp overflows fp32 and where its result is subnormal."""
+    g = rng(12)
+    a = np.concatenate([g.uniform(-110, 110, 3_000_000), g.uniform(-1, 1, 500_000), g.standard_normal(500_000) * 8,
+                        [0.0, -0.0, 79.99999, 80.0, -80.0, 88.72, 88.73, -87.3, -87.4, -103.9, -104.0, -150.0, 200.0]]).astype(np.float32)
+    assert_same(to_np(F.pref_Swish(dev(a))), oracle.silu(a))
+    x = np.zeros((a.size, 2), np.float32)
+    x[:, 1] = -np.abs(a)
+    assert_same(to_np(F.pref_Softmax(dev(x))), oracle.softmax(x))
+
+
 def test_argmax(F):
     g = rng(11)
     l = g.standard_normal((5, 128256)).astype(np.float32)
@@ -258,6 +271,29 @@ def test_linear_decode_tcgen05(F, M, N, K):
     assert_same(to_np(acc), acc_o, "acc"); assert_same(to_np(y), y_o, "y")
     _, y2 = F.dec_Linear_Layer_i8xi8(dev(a), dev(st), dev(w), dev(sc), want_acc=False)   # library scratch path
     assert_same(to_np(y2), y_o, "y (scratch)")
+
+
+@pytest.mark.parametrize("M,N,K,decode", [(200, 2048, 2048, False), (130, 264, 144, False), (1, 2048, 2048, True), (5, 512, 2048, True),
+                                            (32, 2048, 2048, True), (64, 2048, 8192, True), (20, 3072, 2048, True)])
+def test_linear_fused_residual(F, M, N, K, decode):
+    a, st, w, sc = lin_inputs(M, N, K, 24)
+    res = rng(25).standard_normal((M, N)).astype(np.float32) * 50
+    fn = F.dec_Linear_Layer_i8xi8 if decode else F.pref_Linear_Layer_i8xi8
+    want = oracle.residual(res, oracle.linear_i8(a, st, w, sc)[1])
+    for _ in range(3):   # repeated calls: the split-K scratch must come back zeroed every time
+        _, y = fn(dev(a), dev(st), dev(w), dev(sc), residual=dev(res))
+        assert_same(to_np(y), want, "residual + linear")
+    # in place: y aliases the residual
+    r = dev(res)
+    lib = F.lib()
+    name = "flexllm_linear_decode_i8_residual" if decode else "flexllm_linear_prefill_i8_residual"
+    import ctypes as C
+    p = lambda t: C.c_void_p(t.data_ptr())
+    ad, std, wd, scd = dev(a), dev(st), dev(w), dev(sc)
+    rc = getattr(lib, name)(p(ad), p(std), p(wd), p(scd), M, N, K, p(r), p(r), None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert_same(to_np(r), want, "in-place residual")
 
 
 def test_linear_golden(F):
