@@ -310,6 +310,7 @@ __global__ void __launch_bounds__(NT) dec_attn_fused_kernel(const int8_t* __rest
     __shared__ __align__(16) int8_t q_sm[G][64];
     __shared__ float q_scale[G], red[G][NT / 32], row_max[G], row_rinv[G], part[G][4];
     __shared__ int pt_sm[160];                                        // this sequence's page-table row
+    pdl_sync();
     const int hkv = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
     const int pos = ctx[b];
@@ -675,13 +676,13 @@ int flexllm::mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, con
         if (qkv_f32) {
             auto kern = dec_attn_fused_kernel<true, 512>;
             if (fused_smem > 48 * 1024) FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem));
-            kern<<<fg, 512, fused_smem, st>>>(q, qs, k, ks, v, vs, qkv_f32, cos_t, sin_t, a_s, L, page_table, max_pages, ctx, HQ, HKV,
-                                              ctx_stride, out, oacc);
+            launch_k(kern, fg, dim3(512), fused_smem, st, q, qs, k, ks, v, vs, qkv_f32, cos_t, sin_t, a_s, L, page_table, max_pages, ctx,
+                     HQ, HKV, ctx_stride, out, oacc);
         } else {
             auto kern = dec_attn_fused_kernel<false, 512>;
             if (fused_smem > 48 * 1024) FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem));
-            kern<<<fg, 512, fused_smem, st>>>(q, qs, k, ks, v, vs, nullptr, cos_t, sin_t, a_s, L, page_table, max_pages, ctx, HQ, HKV,
-                                              ctx_stride, out, oacc);
+            launch_k(kern, fg, dim3(512), fused_smem, st, q, qs, k, ks, v, vs, (const float*)nullptr, cos_t, sin_t, a_s, L, page_table,
+                     max_pages, ctx, HQ, HKV, ctx_stride, out, oacc);
         }
         return launch_status(1);
     }

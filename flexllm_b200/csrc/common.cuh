@@ -22,6 +22,29 @@ inline int cuda_status(cudaError_t e) {
 // status of the `n` launches that have just been issued
 inline int launch_status(int n = 1) { note_launches(n); return cuda_status(cudaGetLastError()); }
 
+// Programmatic dependent launch (decode path): when g_pdl is set by the model runner, kernels are
+// launched with the stream-serialization attribute relaxed, so the next kernel's launch and CTA
+// scheduling overlap the tail of the previous one. Every kernel launched this way calls pdl_sync()
+// before it touches memory: it first lets its own dependents start launching, then waits until the
+// kernel before it has completed and flushed (so data hazards are exactly those of an ordinary stream).
+extern thread_local int g_pdl;
+__device__ __forceinline__ void pdl_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <class... KArgs, class... Args>
+inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    if (g_pdl) {
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+    }
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 #define FLEXLLM_CHECK_CUDA(expr)                                   \
     do {                                                           \
         int _st = ::flexllm::cuda_status((expr));                  \

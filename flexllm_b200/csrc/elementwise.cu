@@ -6,6 +6,7 @@
 namespace flexllm {
 
 thread_local int g_last_cuda_error = 0;
+thread_local int g_pdl = 0;
 unsigned long long g_launch_count = 0;
 
 // ---------------------------------------------------------------------------------------------
@@ -16,6 +17,7 @@ template <int VPT>  // float4 vectors per thread
 __global__ void __launch_bounds__(256) quant_per_token_kernel(const float* __restrict__ x, int K,
                                                               int8_t* __restrict__ q, float* __restrict__ s) {
     __shared__ float red[64];
+    pdl_sync();
     const long row = blockIdx.x;
     const float4* xr = reinterpret_cast<const float4*>(x + row * K);
     const int nv = K >> 2;
@@ -169,22 +171,33 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_prefill_kernel(const f
     }
 }
 
-// Decode order with `lanes` (4 or 8) chunks: one warp per row, lane = chunk*4 + j.
+// Decode order with `lanes` (4 or 8) chunks: one warp per row, lane = chunk*4 + j. The row and gamma
+// are fetched with one batch of independent 128-bit loads and stay in registers for the output pass
+// (a decode step is latency-bound: one global round trip instead of one per loop iteration).
 template <int MAXV>
 __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_decode_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                         int M, int D, float eps, int lanes, float* __restrict__ y,
                                                                         int8_t* __restrict__ q, float* __restrict__ s) {
     extern __shared__ __align__(16) float rowbuf[];          // RMS_WARPS x (D + 4*lanes)
+    pdl_sync();
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long row = (long)blockIdx.x * RMS_WARPS + w;
     if (row >= M) return;
     const int C = D / lanes;                                  // chunk length, a multiple of 4
+    const int nv = D >> 2;
     float* buf = rowbuf + (size_t)w * (D + 4 * lanes);
     const float* xr = x + row * D;
-    for (int c = lane; c < (D >> 2); c += 32) {               // element i lives at i + 4*(i / C)
-        const float4 v = reinterpret_cast<const float4*>(xr)[c];
-        const int i = c * 4;
-        *reinterpret_cast<float4*>(buf + i + 4 * (i / C)) = v;
+    constexpr bool KEEP_G = MAXV <= 16;                       // gamma in registers too when it fits
+    float4 v[MAXV], g[KEEP_G ? MAXV : 1];
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+        const int c = lane + i * 32;
+        if (c < nv) { v[i] = reinterpret_cast<const float4*>(xr)[c]; if (KEEP_G) g[i] = reinterpret_cast<const float4*>(gamma)[c]; }
+    }
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+        const int c = lane + i * 32;
+        if (c < nv) { const int e = c * 4; *reinterpret_cast<float4*>(buf + e + 4 * (e / C)) = v[i]; }   // element e at e + 4*(e / C)
     }
     __syncwarp();
     const int chunk = lane >> 2, j = lane & 3;
@@ -193,7 +206,7 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_decode_kernel(const fl
         const float* bc = buf + chunk * (C + 4);
         const int n = C >> 2;
 #pragma unroll 8
-        for (int k = 0; k < n; k++) { const float v = bc[4 * k + j]; ss += v * v; }
+        for (int k = 0; k < n; k++) { const float t = bc[4 * k + j]; ss += t * t; }
     }
     float tot = 0.0f;
     for (int c = 0; c < lanes; c++) {
@@ -201,8 +214,36 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_decode_kernel(const fl
         const float p2 = __shfl_sync(0xffffffffu, ss, c * 4 + 2), p3 = __shfl_sync(0xffffffffu, ss, c * 4 + 3);
         tot += (p0 + p1) + (p2 + p3);
     }
-    const float rinv = 1.0f / sqrtf(tot / (float)D + eps);
-    rmsnorm_output_row<MAXV>(xr, gamma, D, rinv, y ? y + row * D : nullptr, q ? q + row * D : nullptr, s ? s + row : nullptr, lane);
+    const float r = 1.0f / sqrtf(tot / (float)D + eps);
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+        const int c = lane + i * 32;
+        if (c < nv) {
+            const float4 gg = KEEP_G ? g[KEEP_G ? i : 0] : reinterpret_cast<const float4*>(gamma)[c];
+            float4 o;
+            o.x = (v[i].x * r) * gg.x; o.y = (v[i].y * r) * gg.y; o.z = (v[i].z * r) * gg.z; o.w = (v[i].w * r) * gg.w;
+            v[i] = o;
+            if (y) reinterpret_cast<float4*>(y + row * D)[c] = o;
+            mx = fmaxf(mx, fmaxf(fmaxf(o.x, o.y), fmaxf(o.z, o.w)));
+            mn = fminf(mn, fminf(fminf(o.x, o.y), fminf(o.z, o.w)));
+        }
+    }
+    if (q) {
+        mx = warp_max(mx); mn = warp_min(mn);
+        const float sc = sym_scale_from(mx, mn);
+        if (lane == 0) s[row] = sc;
+        char4* qr = reinterpret_cast<char4*>(q + row * D);
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            const int c = lane + i * 32;
+            if (c < nv) {
+                char4 o;
+                o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc); o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+                qr[c] = o;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -286,6 +327,7 @@ __global__ void softmax_kernel(const float* __restrict__ x, long rows, int len, 
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, long V, int32_t* __restrict__ idx) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_sync();
     const float* l = logits + (long)blockIdx.x * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -352,10 +394,10 @@ extern "C" int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, 
     FLEXLLM_REQUIRE(aligned(x, 16) && aligned(q, 4));
     cudaStream_t st = (cudaStream_t)stream;
     const int nv = K / 4;
-    if (nv <= 256) quant_per_token_kernel<1><<<M, 256, 0, st>>>(x, K, q, s);
-    else if (nv <= 512) quant_per_token_kernel<2><<<M, 256, 0, st>>>(x, K, q, s);
-    else if (nv <= 1024) quant_per_token_kernel<4><<<M, 256, 0, st>>>(x, K, q, s);
-    else quant_per_token_kernel<8><<<M, 256, 0, st>>>(x, K, q, s);
+    if (nv <= 256) launch_k(quant_per_token_kernel<1>, dim3(M), dim3(256), 0, st, x, K, q, s);
+    else if (nv <= 512) launch_k(quant_per_token_kernel<2>, dim3(M), dim3(256), 0, st, x, K, q, s);
+    else if (nv <= 1024) launch_k(quant_per_token_kernel<4>, dim3(M), dim3(256), 0, st, x, K, q, s);
+    else launch_k(quant_per_token_kernel<8>, dim3(M), dim3(256), 0, st, x, K, q, s);
     return launch_status();
 }
 
@@ -392,7 +434,7 @@ extern "C" int flexllm_rmsnorm_quant(const float* x, const float* gamma, int M, 
     } else {
         const int grid = (M + RMS_WARPS - 1) / RMS_WARPS;
         const size_t smem = (size_t)RMS_WARPS * (D + 4 * order) * sizeof(float);
-        if (D <= 2048) rmsnorm_decode_kernel<16><<<grid, RMS_WARPS * 32, smem, st>>>(x, gamma, M, D, eps, order, y, q, s);
+        if (D <= 2048) launch_k(rmsnorm_decode_kernel<16>, dim3(grid), dim3(RMS_WARPS * 32), smem, st, x, gamma, M, D, eps, order, y, q, s);
         else {
             FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             rmsnorm_decode_kernel<32><<<grid, RMS_WARPS * 32, smem, st>>>(x, gamma, M, D, eps, order, y, q, s);
@@ -439,6 +481,6 @@ extern "C" int flexllm_softmax(const float* x, long rows, int len, const int32_t
 extern "C" int flexllm_logits_argmax(const float* logits, int B, long V, int32_t* idx, void* stream) {
     FLEXLLM_REQUIRE(logits && idx && B >= 0 && V > 0);
     if (B == 0) return FLEXLLM_OK;
-    argmax_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(logits, V, idx);
+    launch_k(argmax_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream, logits, V, idx);
     return launch_status();
 }

@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
     constexpr int N = 8192;
     __shared__ float buf[N + N / 32];
     __shared__ float red[64];
+    pdl_sync();
     const int tid = threadIdx.x;
     const long row = blockIdx.x;
     const float4* xr = reinterpret_cast<const float4*>(x + row * ld_in);   // ld_in: input row stride in floats
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const int8_t* __restric
 // gate and up halves of one fused projection output: rows of `ld` floats, gate at g, up at u
 int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st) {
     if (M == 0) return FLEXLLM_OK;
-    fht8192_kernel<1><<<M, 256, 0, st>>>(g, u, ld, scale, nullptr, q, s, nullptr);
+    launch_k(fht8192_kernel<1>, dim3(M), dim3(256), 0, st, g, u, ld, scale, (float*)nullptr, q, s, (float*)nullptr);
     return launch_status();
 }
 

@@ -19,6 +19,7 @@
 //
 // Replaces pref_Linear_Layer_i4xi4 / dec_Linear_Layer_i4xi4 + the dequant layers
 // (Modules/Linear_Layer.h:293-341, :862-923; Modules/quant.h:115-164, :434-524) at 8-bit precision.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -66,6 +67,21 @@ int make_tmap_2d_u8_box(CUtensorMap* out, const void* base, uint64_t rows, uint6
     return FLEXLLM_OK;
 }
 
+int make_tmap_3d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, uint32_t kch) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return FLEXLLM_ECUDA;
+    if (!aligned(base, 16) || (row_bytes % 128) != 0 || box_rows == 0 || box_rows > 256 || kch == 0 || kch > 8) return FLEXLLM_EINVAL;
+    cuuint64_t dims[3] = {128, rows, row_bytes / 128};
+    cuuint64_t strides[2] = {row_bytes, 128};
+    cuuint32_t box[3] = {128, box_rows, kch};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return FLEXLLM_ECUDA; }
+    return FLEXLLM_OK;
+}
+
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
     return make_tmap_2d_u8_box(out, base, rows, row_bytes, 128, box_rows, 128);
 }
@@ -87,20 +103,26 @@ struct GemmArgs {
     int* counters;           // split-K: zeroed arrival counters, one per (A tile, warp quarter)
 };
 
-template <int BN> struct GemmCfg {
-    static constexpr int A_BYTES = 128 * 128;
-    static constexpr int B_BYTES = BN * 128;
+// KCH = 128-byte K chunks per pipeline stage (1 for prefill; > 1 for the weight-streaming decode
+// orientation, where fetching KCH*128 contiguous bytes per weight row keeps HBM pages open).
+template <int BN, int KCH = 1> struct GemmCfg {
+    static constexpr int A_TILE = 128 * 128;
+    static constexpr int B_TILE = BN * 128;
+    static constexpr int A_BYTES = KCH * A_TILE;
+    static constexpr int B_BYTES = KCH * B_TILE;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : BN == 32 ? 8 : 10;
+    static constexpr int STAGES_MAX = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = KCH > 1 ? (STAGES_MAX > 8 ? 8 : STAGES_MAX)
+                                          : (BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : BN == 32 ? 8 : 10);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, int KCH = 1>
 __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmapA,
                                                                  const __grid_constant__ CUtensorMap tmapB,
                                                                  const GemmArgs args) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, KCH>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned operand ring, then barriers
@@ -116,8 +138,9 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
+    pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (args.K + 127) >> 7;
+    const int num_kb = ((args.K + 127) >> 7) / KCH;      // pipeline steps of KCH chunks (K % (128*KCH) == 0 when KCH > 1)
     const int total_tiles = args.tilesA * args.tilesB * args.ksplit;
 
     if (threadIdx.x == 0) {
@@ -153,8 +176,13 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                     const uint32_t full = bar_full + 8 * stage;
                     mbar_expect_tx(full, Cfg::STAGE_BYTES);
                     const uint32_t dstA = ring + stage * Cfg::STAGE_BYTES;
-                    tma_load_2d(dstA, &tmapA, full, kb * 128, ta * 128);
-                    tma_load_2d(dstA + Cfg::A_BYTES, &tmapB, full, kb * 128, tb * BN);
+                    if (KCH == 1) {
+                        tma_load_2d(dstA, &tmapA, full, kb * 128, ta * 128);
+                        tma_load_2d(dstA + Cfg::A_BYTES, &tmapB, full, kb * 128, tb * BN);
+                    } else {
+                        tma_load_3d(dstA, &tmapA, full, 0, ta * 128, kb * KCH);
+                        tma_load_3d(dstA + Cfg::A_BYTES, &tmapB, full, 0, tb * BN, kb * KCH);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -179,11 +207,14 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = ring + stage * Cfg::STAGE_BYTES;
-                    const uint64_t adesc = umma_desc_k_sw128(sa);
-                    const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 4; k++)   // 32 int8 = 32 bytes = 2 descriptor address units per step
-                        umma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    for (int c = 0; c < KCH; c++) {
+                        const uint64_t adesc = umma_desc_k_sw128(sa + c * Cfg::A_TILE);
+                        const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::A_BYTES + c * Cfg::B_TILE);
+#pragma unroll
+                        for (int k = 0; k < 4; k++)   // 32 int8 = 32 bytes = 2 descriptor address units per step
+                            umma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || c > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(bar_empty + 8 * stage);   // slot is free once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -200,16 +231,23 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
             const int ta = t / (args.ksplit * args.tilesB);
             const int as = it & 1;
             const uint32_t aphase = (it >> 1) & 1;
+            // everything the epilogue needs besides the accumulator is fetched BEFORE the wait, so its
+            // global-memory latency hides behind the main loop
+            const int rowA = ta * 128 + q * 32 + lane;
+            const bool rowA_ok = rowA < args.rowsA;
+            const float sa = (rowA_ok && args.sA) ? args.sA[rowA] : 0.0f;
+            float sbv[SWAP ? BN : 1];
+            if (SWAP && args.sB) {
+#pragma unroll
+                for (int j = 0; j < BN; j++) { const int tok = tb * BN + j; sbv[j] = tok < args.rowsB ? args.sB[tok] : 0.0f; }
+            }
             // lane 0 polls; the verdict is broadcast so that the warp stays converged for the
             // warp-collective TMEM loads below
             int got = (lane == 0) ? (mbar_wait(bar_tfull + 8 * as, aphase, abort_flag) ? 1 : 0) : 1;
             got = __shfl_sync(0xffffffffu, got, 0);
             if (!got) { ok = false; break; }
             tc_fence_after();
-            const int rowA = ta * 128 + q * 32 + lane;
-            const bool rowA_ok = rowA < args.rowsA;
-            const float sa = (rowA_ok && args.sA) ? args.sA[rowA] : 0.0f;
-#pragma unroll 1
+        #pragma unroll (SWAP ? BN / 16 : 1)
             for (int c = 0; c < BN / 16; c++) {
                 uint32_t v[16];
                 tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + c * 16, v);
@@ -254,7 +292,7 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                             } else {
                                 if (args.acc) args.acc[o] = (int)v[j];
                                 if (args.y) {
-                                    float r = ((float)(int)v[j] * args.sB[tok]) * sa;
+                                    float r = ((float)(int)v[j] * sbv[SWAP ? c * 16 + j : 0]) * sa;
                                     if (args.residual) r = args.residual[o] + r;
                                     args.y[o] = r;
                                 }
@@ -301,7 +339,7 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                                     args.work[o] = 0;
                                     if (args.acc) args.acc[o] = vv[j];
                                     if (args.y) {
-                                        float r = ((float)vv[j] * args.sB[tok]) * sa;
+                                        float r = ((float)vv[j] * args.sB[tok]) * sa;   // L1/L2 hit: fetched before the wait
                                         if (args.residual) r = rs[j] + r;
                                         args.y[o] = r;
                                     }
@@ -333,26 +371,28 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
 
 // ------------------------------------------------------------------ host launcher
 struct TmapKey {
-    const void* base; uint64_t rows, row_bytes; uint32_t box_rows;
-    bool operator==(const TmapKey& o) const { return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows; }
+    const void* base; uint64_t rows, row_bytes; uint32_t box_rows, kch;   // kch 0: 2-D map
+    bool operator==(const TmapKey& o) const {
+        return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows && kch == o.kch;
+    }
 };
 struct TmapKeyHash {
     size_t operator()(const TmapKey& k) const {
         size_t h = std::hash<const void*>()(k.base);
-        h ^= std::hash<uint64_t>()(k.rows * 1000003ull + k.row_bytes * 31ull + k.box_rows) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h ^= std::hash<uint64_t>()(k.rows * 1000003ull + k.row_bytes * 31ull + k.box_rows + 977ull * k.kch) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
         return h;
     }
 };
 // Encoding a tensor map costs a few microseconds of host time; the same weights and activation
 // buffers come back every layer call, so maps are cached by (pointer, shape, box).
-static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, uint32_t kch = 0) {
     static std::mutex mu;
     static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-    TmapKey key{base, rows, row_bytes, box_rows};
+    TmapKey key{base, rows, row_bytes, box_rows, kch};
     std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return FLEXLLM_OK; }
-    int st = make_tmap_2d_u8(out, base, rows, row_bytes, box_rows);
+    int st = kch ? make_tmap_3d_u8(out, base, rows, row_bytes, box_rows, kch) : make_tmap_2d_u8(out, base, rows, row_bytes, box_rows);
     if (st != FLEXLLM_OK) return st;
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, *out);
@@ -379,22 +419,22 @@ static int sm_count() {
     return n[dev] > 0 ? n[dev] : 148;
 }
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, int KCH = 1>
 static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, int K, int ksplit, int ldo,
                        int32_t* acc, float* y, const float* sA, const float* sB, cudaStream_t st,
                        const float* residual = nullptr, int32_t* work = nullptr, int* counters = nullptr) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, KCH>;
     CUtensorMap ta, tb;
-    int rc = cached_tmap(&ta, A, (uint64_t)rowsA, (uint64_t)K, 128);
+    int rc = cached_tmap(&ta, A, (uint64_t)rowsA, (uint64_t)K, 128, KCH > 1 ? KCH : 0);
     if (rc != FLEXLLM_OK) return rc;
-    rc = cached_tmap(&tb, B, (uint64_t)rowsB, (uint64_t)K, BN);
+    rc = cached_tmap(&tb, B, (uint64_t)rowsB, (uint64_t)K, BN, KCH > 1 ? KCH : 0);
     if (rc != FLEXLLM_OK) return rc;
     GemmArgs g;
     g.rowsA = rowsA; g.rowsB = rowsB; g.K = K;
     g.tilesA = (rowsA + 127) / 128; g.tilesB = (rowsB + BN - 1) / BN; g.ksplit = ksplit;
     g.ldo = ldo; g.acc = acc; g.y = y; g.sA = sA; g.sB = sB; g.error_flag = device_error_flag();
     g.residual = residual; g.work = work; g.counters = counters;
-    auto kern = gemm_i8_tcgen05_kernel<BN, SWAP>;
+    auto kern = gemm_i8_tcgen05_kernel<BN, SWAP, KCH>;
     static bool attr_set = false;
     if (!attr_set) {
         FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -402,7 +442,7 @@ static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, i
     }
     const int total = g.tilesA * g.tilesB * g.ksplit;
     const int grid = total < sm_count() ? total : sm_count();
-    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, g);
+    launch_k(kern, dim3(grid), dim3(192), (size_t)Cfg::SMEM_BYTES, st, ta, tb, g);
     return launch_status();
 }
 
@@ -422,10 +462,22 @@ int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const 
 int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
                    int ksplit, int32_t* acc, float* y, cudaStream_t st, const float* residual, int32_t* work, int* counters) {
     if (M > 64) return FLEXLLM_ENOTSUP;
+    // chunks of K per pipeline stage: KCH*128 contiguous bytes per weight row and TMA request
+    int kch = 1;
+    if (K % 512 == 0) kch = 4;
+    else if (K % 256 == 0) kch = 2;
+    const int steps = (K + 127) / 128 / kch;
+    if (ksplit > steps) ksplit = steps;
+    if (ksplit < 1) ksplit = 1;
     if (ksplit > 1 && !(work && counters)) return FLEXLLM_EINVAL;
-    if (M > 32) return launch_gemm<64, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters);
-    if (M > 16) return launch_gemm<32, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters);
-    return launch_gemm<16, true>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters);
+#define FLEXLLM_DEC(BN_, KCH_) \
+    return launch_gemm<BN_, true, KCH_>(w, N, a, M, K, ksplit, N, acc, y, s_ch, s_tok, st, residual, work, counters)
+    if (M > 32) { if (kch == 4) FLEXLLM_DEC(64, 4); if (kch == 2) FLEXLLM_DEC(64, 2); FLEXLLM_DEC(64, 1); }
+    if (M > 16) { if (kch == 4) FLEXLLM_DEC(32, 4); if (kch == 2) FLEXLLM_DEC(32, 2); FLEXLLM_DEC(32, 1); }
+    if (kch == 4) FLEXLLM_DEC(16, 4);
+    if (kch == 2) FLEXLLM_DEC(16, 2);
+    FLEXLLM_DEC(16, 1);
+#undef FLEXLLM_DEC
 }
 
 int gemm_check_error_flag() {

@@ -12,6 +12,7 @@
 // Prefill uses the prefill RMSNorm summation order and the tcgen05 GEMM / attention kernels; decode
 // uses the decode order, the weight-streaming linear layers and the paged attention, and is replayed
 // from a CUDA graph (the token feedback stays on the device, as in the reference's decode graph).
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -38,6 +39,7 @@ int gemm_check_error_flag();
 // x[t][:] = (float)lm_w[tok[t]][:] * lm_s[tok[t]]
 __global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ lm_w, const float* __restrict__ lm_s,
                              int D, float* __restrict__ x) {
+    pdl_sync();
     const int t = blockIdx.x;
     const int id = tok[t];
     const float s = lm_s[id];
@@ -62,6 +64,7 @@ __global__ void gather_last_kernel(const float* __restrict__ x, int S, int D, fl
 // (after a decode step) the context lengths.
 __global__ void step_bookkeeping_kernel(const int32_t* __restrict__ next, int B, int32_t* __restrict__ out,
                                         int32_t* __restrict__ state, int32_t* __restrict__ ctx, int advance_ctx) {
+    pdl_sync();
     const int b = threadIdx.x;
     const int col = state[0], n_cols = state[1];
     if (b < B) {
@@ -270,11 +273,20 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
 
 // One decode step for the B sequences of the last prefill: consumes m->next, leaves the new
 // greedy tokens in m->next (and in the output table), appends to the KV cache and advances ctx.
+static int decode_step_body(flexllm_model* m, cudaStream_t st);
 static int decode_step(flexllm_model* m, cudaStream_t st) {
+    static int use_pdl = -1;
+    if (use_pdl < 0) { const char* e = getenv("FLEXLLM_PDL"); use_pdl = e ? atoi(e) : 1; }
+    g_pdl = use_pdl;
+    const int rc = decode_step_body(m, st);
+    g_pdl = 0;
+    return rc;
+}
+static int decode_step_body(flexllm_model* m, cudaStream_t st) {
     const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
     const int QKV = (HQ + 2 * HKV) * 64;
     const int B = m->B;
-    embed_kernel<<<B, 256, 0, st>>>(m->next, m->lm_w, m->lm_s, D, m->x);
+    launch_k(embed_kernel, dim3(B), dim3(256), 0, st, (const int32_t*)m->next, (const int8_t*)m->lm_w, (const float*)m->lm_s, D, m->x);
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
@@ -290,7 +302,7 @@ static int decode_step(flexllm_model* m, cudaStream_t st) {
         TRY(flexllm_linear_decode_i8_residual(m->hq, m->xs, L.wd, L.sd, B, D, F, m->x, m->x, st));
     }
     TRY(run_head(m, m->x, B, FLEXLLM_NORM_DECODE8, st));
-    step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, B, m->out_tokens, m->state, m->ctx, 1);
+    launch_k(step_bookkeeping_kernel, dim3(1), dim3(64), 0, st, (const int32_t*)m->next, B, m->out_tokens, m->state, m->ctx, 1);
     return launch_status();
 }
 

@@ -67,6 +67,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tma
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// 3-D form: coordinates {x = byte in the 128-byte chunk, y = row, z = chunk index along K}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
@@ -151,5 +158,9 @@ int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 // General form: box of {box_bytes, box_rows}, swizzle_bytes in {64, 128} (box_bytes <= swizzle_bytes).
 int make_tmap_2d_u8_box(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes,
                         uint32_t box_rows, int swizzle_bytes);
+// Row-major int8 matrix [rows][row_bytes] (row_bytes % 128 == 0) seen as {128 bytes, rows, row_bytes/128}:
+// one box = `kch` consecutive 128-byte chunks of `box_rows` rows, i.e. kch standard 128-byte-swizzled
+// tiles back to back in shared memory, fetched as kch*128 contiguous bytes per row.
+int make_tmap_3d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, uint32_t kch);
 
 }  // namespace flexllm
