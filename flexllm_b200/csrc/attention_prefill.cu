@@ -96,6 +96,7 @@ struct AttnArgs {
     const float* a_s;   // [HQ]
     float* out;         // [B][S][HQ*64]
     int32_t* oacc;      // optional, same shape
+    uint8_t* ecache;    // exp values of sweep 1 kept for sweep 2 (attn_ecache_head_bytes per (batch, head))
     int* error_flag;
 };
 
@@ -109,16 +110,24 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
     return d;
 }
 
-constexpr int ATT_KSLOTS = 3;
+// Key tile = 64 keys. TMEM per CTA: S (64 columns) + O (64 columns) = 128 columns, so four CTAs share
+// an SM (16 softmax warps per SM hide each other's latencies).
+constexpr int ATT_KT = 64;                    // keys per tile
+constexpr int ATT_SLOTS = 4;                  // K / V^T tile ring
 constexpr int ATT_Q_BYTES = 128 * 64;
-constexpr int ATT_K_BYTES = 128 * 64;
-constexpr int ATT_V_BYTES = 64 * 128;
-constexpr int ATT_SLOT_BYTES = ATT_K_BYTES + ATT_V_BYTES;
-constexpr int ATT_P_BYTES = 128 * 128;
-constexpr int ATT_SMEM = ATT_Q_BYTES + ATT_KSLOTS * ATT_SLOT_BYTES + ATT_P_BYTES + 1024 + 256;
-constexpr int ATT_TMEM_COLS = 256;   // S: columns [0,128), O: columns [128,192)
+constexpr int ATT_TILE_BYTES = 64 * 64;       // one K tile [64 keys][64 B] or one V^T tile [64 dims][64 keys]
+constexpr int ATT_P_BYTES = 128 * 64;         // U tile [128 queries][64 keys] u8
+constexpr int ATT_SMEM = ATT_Q_BYTES + ATT_SLOTS * ATT_TILE_BYTES + 2 * ATT_P_BYTES + 1024 + 256;
+constexpr int ATT_TMEM_COLS = 128;
 
-__global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmapQ,
+// Bytes of exp-cache one (batch, query head) needs: for every 128-query tile qt its 2*(qt+1) key
+// tiles of 128 x 64 fp32.
+__host__ __device__ inline size_t attn_ecache_head_bytes(int S) {
+    const size_t n_qt = (S + 127) / 128;
+    return n_qt * (n_qt + 1) * (size_t)(128 * ATT_KT * 4);   // sum_{qt} 2*(qt+1) tiles
+}
+
+__global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmapQ,
                                                               const __grid_constant__ CUtensorMap tmapK,
                                                               const __grid_constant__ CUtensorMap tmapV,
                                                               const AttnArgs args) {
@@ -127,37 +136,38 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_const
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t sQ = base;
-    const uint32_t sKV = sQ + ATT_Q_BYTES;
-    const uint32_t sP = sKV + ATT_KSLOTS * ATT_SLOT_BYTES;
-    uint8_t* sP_ptr = base_ptr + ATT_Q_BYTES + ATT_KSLOTS * ATT_SLOT_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP_ptr + ATT_P_BYTES);
-    // barriers: q_full, k_full[3], k_empty[3], s_full, s_empty, p_full, p_empty, o_full
+    const uint32_t sT = sQ + ATT_Q_BYTES;                         // tile ring
+    const uint32_t sP = sT + ATT_SLOTS * ATT_TILE_BYTES;          // two U tiles
+    uint8_t* sP_ptr = base_ptr + ATT_Q_BYTES + ATT_SLOTS * ATT_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP_ptr + 2 * ATT_P_BYTES);
+    // barriers: q_full, t_full[4], t_empty[4], s_full, s_empty, p_full[2], p_empty[2], o_full
     const uint32_t bar_qfull = smem_u32(bars);
-    const uint32_t bar_kfull = bar_qfull + 8;
-    const uint32_t bar_kempty = bar_kfull + 8 * ATT_KSLOTS;
-    const uint32_t bar_sfull = bar_kempty + 8 * ATT_KSLOTS;
+    const uint32_t bar_tfull = bar_qfull + 8;
+    const uint32_t bar_tempty = bar_tfull + 8 * ATT_SLOTS;
+    const uint32_t bar_sfull = bar_tempty + 8 * ATT_SLOTS;
     const uint32_t bar_sempty = bar_sfull + 8;
     const uint32_t bar_pfull = bar_sempty + 8;
-    const uint32_t bar_pempty = bar_pfull + 8;
-    const uint32_t bar_ofull = bar_pempty + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * ATT_KSLOTS);
+    const uint32_t bar_pempty = bar_pfull + 16;
+    const uint32_t bar_ofull = bar_pempty + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * ATT_SLOTS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (args.S + 127) >> 7;
-    // heavy tiles (late queries) first
-    const int qt = n_qt - 1 - (int)(blockIdx.x % n_qt);
+    const int qt = n_qt - 1 - (int)(blockIdx.x % n_qt);            // heavy tiles (late queries) first
     const int hq = (int)((blockIdx.x / n_qt) % args.HQ);
     const int b = (int)(blockIdx.x / ((long)n_qt * args.HQ));
     const int hkv = hq / (args.HQ / args.HKV);
-    const int n_kt = qt + 1;                        // causal: key tiles 0..qt
-    const int total_it = 3 * n_kt;
+    const int n_kt = 2 * (qt + 1);                                 // causal: 64-key tiles 0 .. 2*qt+1
+    // this CTA's slice of the exp cache: [n_kt][16 float4 chunks][128 rows] float4
+    float4* ecache = reinterpret_cast<float4*>(args.ecache + ((size_t)b * args.HQ + hq) * attn_ecache_head_bytes(args.S) +
+                                               (size_t)qt * (qt + 1) * (size_t)(128 * ATT_KT * 4));
 
     if (threadIdx.x == 0) {
         mbar_init(bar_qfull, 1);
-        for (int i = 0; i < ATT_KSLOTS; i++) { mbar_init(bar_kfull + 8 * i, 1); mbar_init(bar_kempty + 8 * i, 1); }
+        for (int i = 0; i < ATT_SLOTS; i++) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 1); }
         mbar_init(bar_sfull, 1); mbar_init(bar_sempty, 4);
-        mbar_init(bar_pfull, 4); mbar_init(bar_pempty, 1);
+        for (int i = 0; i < 2; i++) { mbar_init(bar_pfull + 8 * i, 4); mbar_init(bar_pempty + 8 * i, 1); }
         mbar_init(bar_ofull, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -167,59 +177,60 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 64;
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
+        // iterations 0 .. 2*n_kt-1: K tiles of sweeps 0 and 1; then n_kt V^T tiles for sweep 2
         if (lane == 0) {
             tma_prefetch_desc(&tmapQ); tma_prefetch_desc(&tmapK); tma_prefetch_desc(&tmapV);
             mbar_expect_tx(bar_qfull, ATT_Q_BYTES);
             tma_load_2d(sQ, &tmapQ, bar_qfull, 0, ((b * args.HQ + hq) * args.S) + qt * 128);
             int slot = 0; uint32_t phase = 0;
-            for (int it = 0; it < total_it; it++) {
+            for (int it = 0; it < 3 * n_kt; it++) {
                 const int sweep = it / n_kt, j = it - sweep * n_kt;
-                if (!mbar_wait(bar_kempty + 8 * slot, phase ^ 1u, abort_flag)) break;
-                const uint32_t full = bar_kfull + 8 * slot;
-                const uint32_t dst = sKV + slot * ATT_SLOT_BYTES;
-                mbar_expect_tx(full, sweep == 2 ? ATT_SLOT_BYTES : ATT_K_BYTES);
-                tma_load_2d(dst, &tmapK, full, 0, ((b * args.HKV + hkv) * args.S) + j * 128);
-                if (sweep == 2) tma_load_2d(dst + ATT_K_BYTES, &tmapV, full, j * 128, (b * args.HKV + hkv) * 64);
-                if (++slot == ATT_KSLOTS) { slot = 0; phase ^= 1u; }
+                if (!mbar_wait(bar_tempty + 8 * slot, phase ^ 1u, abort_flag)) break;
+                const uint32_t full = bar_tfull + 8 * slot;
+                const uint32_t dst = sT + slot * ATT_TILE_BYTES;
+                mbar_expect_tx(full, ATT_TILE_BYTES);
+                if (sweep < 2) tma_load_2d(dst, &tmapK, full, 0, ((b * args.HKV + hkv) * args.S) + j * ATT_KT);
+                else tma_load_2d(dst, &tmapV, full, j * ATT_KT, (b * args.HKV + hkv) * 64);
+                if (++slot == ATT_SLOTS) { slot = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc_i8(128, 128, 1, 1);
-            constexpr uint32_t idesc_pv = umma_idesc_i8(128, 64, 0, 1);   // P unsigned, V signed
+            constexpr uint32_t idesc_qk = umma_idesc_i8(128, ATT_KT, 1, 1);
+            constexpr uint32_t idesc_pv = umma_idesc_i8(128, 64, 0, 1);   // U unsigned, V signed
             bool ok = mbar_wait(bar_qfull, 0, abort_flag);
             const uint64_t qdesc = umma_desc_k_sw64(sQ);
-            const uint64_t pdesc = umma_desc_k_sw128(sP);
-            int slot = 0; uint32_t kphase = 0;
-            // S and P are single-buffered: iteration `it` is their phase counter
-            for (int it = 0; ok && it < total_it; it++) {
+            int slot = 0; uint32_t tphase = 0;
+            for (int it = 0; ok && it < 3 * n_kt; it++) {
                 const int sweep = it / n_kt, j = it - sweep * n_kt;
-                if (!mbar_wait(bar_kfull + 8 * slot, kphase, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(bar_sempty, (uint32_t)(it & 1) ^ 1u, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t sK = sKV + slot * ATT_SLOT_BYTES;
-                const uint64_t kdesc = umma_desc_k_sw64(sK);
-                umma_i8(tmem_S, qdesc, kdesc, idesc_qk, 0u);
-                umma_i8(tmem_S, qdesc + 2, kdesc + 2, idesc_qk, 1u);
-                umma_commit(bar_sfull);
+                if (!mbar_wait(bar_tfull + 8 * slot, tphase, abort_flag)) { ok = false; break; }
+                const uint32_t sTile = sT + slot * ATT_TILE_BYTES;
                 if (sweep < 2) {
-                    umma_commit(bar_kempty + 8 * slot);
-                } else {
-                    // P.V for this tile once the softmax warps have written U into shared memory
-                    if (!mbar_wait(bar_pfull, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+                    // S = Q.K^T for this key tile (S is single-buffered: iteration it is its phase)
+                    if (!mbar_wait(bar_sempty, (uint32_t)(it & 1) ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t vdesc = umma_desc_k_sw128(sK + ATT_K_BYTES);
-#pragma unroll
-                    for (int k = 0; k < 4; k++) umma_i8(tmem_O, pdesc + 2 * k, vdesc + 2 * k, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(bar_pempty);
-                    umma_commit(bar_kempty + 8 * slot);
+                    const uint64_t kdesc = umma_desc_k_sw64(sTile);
+                    umma_i8(tmem_S, qdesc, kdesc, idesc_qk, 0u);
+                    umma_i8(tmem_S, qdesc + 2, kdesc + 2, idesc_qk, 1u);
+                    umma_commit(bar_sfull);
+                } else {
+                    // O += U.V for this key tile once the softmax warps have written U
+                    const int pb = j & 1;
+                    if (!mbar_wait(bar_pfull + 8 * pb, (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t pdesc = umma_desc_k_sw64(sP + pb * ATT_P_BYTES);
+                    const uint64_t vdesc = umma_desc_k_sw64(sTile);
+                    umma_i8(tmem_O, pdesc, vdesc, idesc_pv, j > 0 ? 1u : 0u);
+                    umma_i8(tmem_O, pdesc + 2, vdesc + 2, idesc_pv, 1u);
+                    umma_commit(bar_pempty + 8 * pb);
                 }
-                if (++slot == ATT_KSLOTS) { slot = 0; kphase ^= 1u; }
+                umma_commit(bar_tempty + 8 * slot);
+                if (++slot == ATT_SLOTS) { slot = 0; tphase ^= 1u; }
             }
             if (ok) umma_commit(bar_ofull);
         }
@@ -228,7 +239,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_const
         const int row_in_tile = warp * 32 + lane;
         const int qpos = qt * 128 + row_in_tile;               // position of this thread's query
         const bool q_ok = qpos < args.S;
-        const int qlim = q_ok ? qpos : -1;                   // keys 0..qlim are visible to this row
+        const int qlim = q_ok ? qpos : -1;                     // keys 0..qlim are visible to this row
         const float qscale = q_ok ? args.qs[((long)b * args.HQ + hq) * args.S + qpos] : 0.0f;
         const float* ksp = args.ks + ((long)b * args.HKV + hkv) * args.S;
         const float* vsp = args.vs + ((long)b * args.HKV + hkv) * args.S;
@@ -236,82 +247,100 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_const
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float mx = -1e32f;
         float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
-        float rinv = 0.f;
         bool ok = true;
-        for (int it = 0; ok && it < total_it; it++) {
+        // ---- sweeps 0 and 1: scores from the tensor core, 16 columns at a time
+        for (int it = 0; ok && it < 2 * n_kt; it++) {
             const int sweep = it / n_kt, j = it - sweep * n_kt;
-            if (sweep == 2 && j == 0) rinv = 1.0f / ((ps0 + ps1) + (ps2 + ps3));
             int got = (lane == 0) ? (mbar_wait(bar_sfull, (uint32_t)(it & 1), abort_flag) ? 1 : 0) : 1;
-            if (sweep == 2 && got && lane == 0) got = mbar_wait(bar_pempty, (uint32_t)(j & 1) ^ 1u, abort_flag) ? 1 : 0;
             got = __shfl_sync(0xffffffffu, got, 0);
             if (!got) { ok = false; break; }
             tc_fence_after();
-            const int k0 = j * 128;
+            const int k0 = j * ATT_KT;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_S + lane_addr + c * 32, v);
+            for (int c = 0; c < ATT_KT / 16; c++) {
+                uint32_t v[16];
+                tmem_ld_32x16(tmem_S + lane_addr + c * 16, v);
+                const int kc = k0 + c * 16;
+                // key scales of these 16 keys (same addresses for the whole warp); keys beyond S are masked
+                float ksv[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    const float4 t = (kc + i < args.S) ? *reinterpret_cast<const float4*>(ksp + kc + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    ksv[i] = t.x; ksv[i + 1] = t.y; ksv[i + 2] = t.z; ksv[i + 3] = t.w;
+                }
                 tmem_ld_wait();
-                const int kc = k0 + c * 32;
                 if (sweep == 0) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int key = kc + i;
-                        if (key <= qlim) {
-                            const float x = (((float)(int)v[i] * qscale) * __ldg(ksp + key)) * 0.125f;
-                            mx = x > mx ? x : mx;
-                        }
-                    }
-                } else if (sweep == 1) {
-                    float e[32];
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int key = kc + i;
-                        const float x = (((float)(int)v[i] * qscale) * __ldg(ksp + (key < args.S ? key : 0))) * 0.125f;
-                        e[i] = ref_expf(x - mx);
-                    }
-                    // ordered chains: key mod 4 == i mod 4 because kc is a multiple of 32
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        if (kc + i <= qlim) ps0 += e[i];
-                        if (kc + i + 1 <= qlim) ps1 += e[i + 1];
-                        if (kc + i + 2 <= qlim) ps2 += e[i + 2];
-                        if (kc + i + 3 <= qlim) ps3 += e[i + 3];
+                    for (int i = 0; i < 16; i++) {
+                        float x = (((float)(int)v[i] * qscale) * ksv[i]) * 0.125f;
+                        x = (kc + i <= qlim) ? x : -1e32f;                       // causal mask (MHA.h:262-267)
+                        mx = x > mx ? x : mx;
                     }
                 } else {
-                    uint32_t packed[8];
+                    float e[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int key = kc + i;
-                        uint32_t u = 0;
-                        if (key <= qlim) {
-                            const float x = (((float)(int)v[i] * qscale) * __ldg(ksp + key)) * 0.125f;
-                            const float p = ref_expf(x - mx) * rinv;
-                            const float t = (p * __ldg(vsp + key)) / a_s;
-                            int r = (int)roundf(t);
-                            r = r > 255 ? 255 : r;
-                            u = (uint32_t)r & 0xffu;
-                        }
-                        if ((i & 3) == 0) packed[i >> 2] = u; else packed[i >> 2] |= u << (8 * (i & 3));
+                    for (int i = 0; i < 16; i++) {
+                        const float x = (((float)(int)v[i] * qscale) * ksv[i]) * 0.125f;
+                        e[i] = (kc + i <= qlim) ? ref_expf(x - mx) : 0.0f;      // exp(-1e32 - max) is exactly 0
                     }
-                    // row `row_in_tile` of the 128 x 128-byte U tile, 128-byte swizzle: 16-byte chunk
-                    // index XOR (row mod 8)
-                    uint8_t* prow = sP_ptr + row_in_tile * 128;
+                    // ordered chains: key mod 4 == i mod 4 because kc is a multiple of 16; adding the
+                    // exact zeros of masked keys leaves the sums unchanged, as in the reference
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int chunk = (c * 2 + h) ^ (row_in_tile & 7);
-                        *reinterpret_cast<uint4*>(prow + chunk * 16) =
-                            make_uint4(packed[h * 4], packed[h * 4 + 1], packed[h * 4 + 2], packed[h * 4 + 3]);
-                    }
+                    for (int i = 0; i < 16; i += 4) { ps0 += e[i]; ps1 += e[i + 1]; ps2 += e[i + 2]; ps3 += e[i + 3]; }
+                    float4* dst = ecache + ((size_t)(j * 16 + c * 4) * 128 + row_in_tile);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) dst[(size_t)i * 128] = make_float4(e[4 * i], e[4 * i + 1], e[4 * i + 2], e[4 * i + 3]);
                 }
             }
             tc_fence_before();
-            if (sweep == 2) fence_proxy_async_smem();   // make the U tile visible to the tensor core
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_sempty);
-                if (sweep == 2) mbar_arrive(bar_pfull);
+            if (lane == 0) mbar_arrive(bar_sempty);
+        }
+        // ---- sweep 2: U = min(round((e * r * vs) / a_s), 255) from the cached e, into shared memory
+        const float rinv = 1.0f / ((ps0 + ps1) + (ps2 + ps3));
+        for (int j = 0; ok && j < n_kt; j++) {
+            const int pb = j & 1;
+            // fetch the first half of this tile's e values before waiting for the buffer
+            float4 ev[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) ev[i] = ecache[((size_t)(j * 16 + i) * 128 + row_in_tile)];
+            int got = (lane == 0) ? (mbar_wait(bar_pempty + 8 * pb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag) ? 1 : 0) : 1;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) { ok = false; break; }
+            const int k0 = j * ATT_KT;
+            uint8_t* prow = sP_ptr + pb * ATT_P_BYTES + row_in_tile * 64;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {          // 16 keys = one 16-byte chunk of the U row
+                if (c == 2) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) ev[i] = ecache[((size_t)(j * 16 + 8 + i) * 128 + row_in_tile)];
+                }
+                uint32_t packed[4];
+#pragma unroll
+                for (int i4 = 0; i4 < 4; i4++) {
+                    const int kk = k0 + c * 16 + i4 * 4;
+                    const float4 vs4 = (kk < args.S) ? *reinterpret_cast<const float4*>(vsp + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 e4 = ev[(c & 1) * 4 + i4];
+                    const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
+                    const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float p = ee[i] * rinv;
+                        const float t = (p * vv[i]) / a_s;
+                        int r = (int)roundf(t);
+                        r = r > 255 ? 255 : r;
+                        w |= ((uint32_t)r & 0xffu) << (8 * i);
+                    }
+                    packed[i4] = w;
+                }
+                // 64-byte rows with 64-byte swizzle: chunk index XOR ((row >> 1) & 3)
+                const int chunk = c ^ ((row_in_tile >> 1) & 3);
+                *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
+            fence_proxy_async_smem();   // make the U tile visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pfull + 8 * pb);
         }
         // ---- epilogue: O -> out
         if (ok) {
@@ -320,14 +349,14 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_kernel(const __grid_const
             if (got) {
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < 2; c++) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_O + lane_addr + c * 32, v);
+                for (int c = 0; c < 4; c++) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(tmem_O + lane_addr + c * 16, v);
                     tmem_ld_wait();
                     if (q_ok) {
-                        const long o = (((long)b * args.S + qpos) * args.HQ + hq) * 64 + c * 32;
+                        const long o = (((long)b * args.S + qpos) * args.HQ + hq) * 64 + c * 16;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
+                        for (int i = 0; i < 16; i += 4) {
                             float4 r;
                             r.x = (float)(int)v[i] * a_s; r.y = (float)(int)v[i + 1] * a_s;
                             r.z = (float)(int)v[i + 2] * a_s; r.w = (float)(int)v[i + 3] * a_s;
@@ -409,12 +438,14 @@ static size_t align_up_(size_t x, size_t a) { return (x + a - 1) / a * a; }
 struct PrefillWs {
     int8_t *q2, *k2, *vT, *v2;
     float *qs2, *ks2, *vsT, *vs2;
+    uint8_t* ecache;
     static size_t bytes(int B, int S, int HQ, int HKV) {
         size_t n = 0;
         n += align_up_((size_t)B * HQ * S * 64, 1024);
         n += 3 * align_up_((size_t)B * HKV * S * 64, 1024);
         n += align_up_((size_t)B * HQ * S * 4, 1024);
         n += 3 * align_up_((size_t)B * HKV * S * 4, 1024);
+        n += align_up_((size_t)B * HQ * attn_ecache_head_bytes(S), 1024);
         return n + 1024;
     }
     PrefillWs(void* ws, int B, int S, int HQ, int HKV) {
@@ -426,7 +457,8 @@ struct PrefillWs {
         qs2 = (float*)w; w += align_up_((size_t)B * HQ * S * 4, 1024);
         ks2 = (float*)w; w += align_up_((size_t)B * HKV * S * 4, 1024);
         vsT = (float*)w; w += align_up_((size_t)B * HKV * S * 4, 1024);
-        vs2 = (float*)w;
+        vs2 = (float*)w; w += align_up_((size_t)B * HKV * S * 4, 1024);
+        ecache = w;
     }
 };
 
@@ -435,12 +467,12 @@ static int mha_prefill_core(const PrefillWs& ws, const float* a_s, int B, int S,
     CUtensorMap tq, tk, tv;
     int rc = make_tmap_2d_u8_box(&tq, ws.q2, (uint64_t)B * HQ * S, 64, 64, 128, 64);
     if (rc != FLEXLLM_OK) return rc;
-    rc = make_tmap_2d_u8_box(&tk, ws.k2, (uint64_t)B * HKV * S, 64, 64, 128, 64);
+    rc = make_tmap_2d_u8_box(&tk, ws.k2, (uint64_t)B * HKV * S, 64, 64, ATT_KT, 64);
     if (rc != FLEXLLM_OK) return rc;
-    rc = make_tmap_2d_u8_box(&tv, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, 128, 64, 128);
+    rc = make_tmap_2d_u8_box(&tv, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, ATT_KT, 64, 64);
     if (rc != FLEXLLM_OK) return rc;
     AttnArgs a;
-    a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.a_s = a_s; a.out = out; a.oacc = oacc;
+    a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.a_s = a_s; a.out = out; a.oacc = oacc; a.ecache = ws.ecache;
     a.error_flag = device_error_flag();
     static bool attr_set = false;
     if (!attr_set) {
