@@ -39,7 +39,15 @@ SIGNATURES = {
     "flexllm_kv_cache_pools": [_P, _I, _P, _P, _P, _P],
     "flexllm_mha_decode_workspace": [_I, _I, _I],
     "flexllm_mha_i8xi8_decode": [_P, _I] + [_P] * 10 + [_I, _P, _I, _I, _I, _P, _P, _P, _SZ, _P],
+    "flexllm_tp_unique_id": [_P, C.c_char_p],
+    "flexllm_tp_init": [_P, _I, _I, _P, C.c_char_p],
+    "flexllm_tp_destroy": [_P],
+    "flexllm_tp_rank": [_P],
+    "flexllm_tp_size": [_P],
+    "flexllm_tp_allreduce_s32": [_P, _P, _SZ, _P],
+    "flexllm_tp_allgather": [_P, _P, _P, _SZ, _P],
     "flexllm_model_create": [_P, _P],
+    "flexllm_model_create_tp": [_P, _P, _P],
     "flexllm_model_destroy": [_P],
     "flexllm_model_load_layer": [_P, _I, _P, _P],
     "flexllm_model_load_head": [_P, _P, _P, _P, _P, _P, _I, _P],

@@ -29,11 +29,14 @@ __device__ __forceinline__ void reg_butterfly(float (&r)[32]) {
     }
 }
 
-// FUSED: 0 = y = FHT(x)/scale (fp32 out); 1 = h = silu(g)*u, FHT, /scale, per-token int8 quant.
+// FUSED: 0 = y = FHT(x)/scale (fp32 out); 1 = h = silu(g)*u, FHT, /scale, per-token int8 quant;
+// 2 = like 1 without the silu, input gathered from `win.g` ranks as x[g][rows][N/g], int8 output only
+// for the column window [win.col0, win.col0 + win.cols) written compactly (tensor-parallel down_proj).
+struct FhtWindow { int g; long rows; int col0, cols; };
 template <int FUSED>
 __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ x, const float* __restrict__ u, long ld_in,
                                                       float scale, float* __restrict__ y, int8_t* __restrict__ q,
-                                                      float* __restrict__ s, float* __restrict__ act) {
+                                                      float* __restrict__ s, float* __restrict__ act, FhtWindow win) {
     constexpr int N = 8192;
     __shared__ float buf[N + N / 32];
     __shared__ float red[64];
@@ -45,8 +48,14 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
 #pragma unroll
     for (int it = 0; it < N / 1024; it++) {
         const int c = it * 256 + tid;
-        float4 v = xr[c];
-        if (FUSED) {
+        float4 v;
+        if (FUSED == 2) {
+            const int segw = N / win.g, e = c * 4, seg = e / segw;
+            v = *reinterpret_cast<const float4*>(x + ((long)seg * win.rows + row) * segw + (e - seg * segw));
+        } else {
+            v = xr[c];
+        }
+        if (FUSED == 1) {
             float4 w = ur[c];
             v.x = silu_f(v.x) * w.x; v.y = silu_f(v.y) * w.y; v.z = silu_f(v.z) * w.z; v.w = silu_f(v.w) * w.w;
             if (act) reinterpret_cast<float4*>(act + row * N)[c] = v;
@@ -106,7 +115,13 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
             union { int8_t b[8]; int2 v; } o;
 #pragma unroll
             for (int c = 0; c < 8; c++) o.b[c] = quant_s8(r[hi * 8 + c], sc);
-            *reinterpret_cast<int2*>(q + row * N + hi * 2048 + tid * 8) = o.v;
+            const int idx0 = hi * 2048 + tid * 8;
+            if (FUSED == 2) {
+                if (idx0 >= win.col0 && idx0 < win.col0 + win.cols)
+                    *reinterpret_cast<int2*>(q + row * win.cols + (idx0 - win.col0)) = o.v;
+            } else {
+                *reinterpret_cast<int2*>(q + row * N + idx0) = o.v;
+            }
         }
     }
 }
@@ -168,7 +183,17 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const int8_t* __restric
 // gate and up halves of one fused projection output: rows of `ld` floats, gate at g, up at u
 int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st) {
     if (M == 0) return FLEXLLM_OK;
-    launch_k(fht8192_kernel<1>, dim3(M), dim3(256), 0, st, g, u, ld, scale, (float*)nullptr, q, s, (float*)nullptr);
+    launch_k(fht8192_kernel<1>, dim3(M), dim3(256), 0, st, g, u, ld, scale, (float*)nullptr, q, s, (float*)nullptr, FhtWindow{1, 0, 0, 0});
+    return launch_status();
+}
+
+// h gathered from g ranks as [g][M][8192/g] -> FHT-8192/scale -> per-token int8 (scale from the whole
+// row), this rank's columns [r*8192/g, (r+1)*8192/g) written compactly.
+int fht_quant_gathered(const float* h, int M, int g, int r, float scale, int8_t* q, float* s, cudaStream_t st) {
+    if (M == 0) return FLEXLLM_OK;
+    const int W = 8192 / g;
+    launch_k(fht8192_kernel<2>, dim3(M), dim3(256), 0, st, h, (const float*)nullptr, 0L, scale, (float*)nullptr, q, s, (float*)nullptr,
+             FhtWindow{g, (long)M, r * W, W});
     return launch_status();
 }
 
@@ -181,7 +206,7 @@ extern "C" int flexllm_fht(const float* x, long rows, int N, float scale, float*
     if (rows == 0) return FLEXLLM_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (N == 8192 && aligned(x, 16) && aligned(y, 16)) {
-        fht8192_kernel<0><<<(unsigned)rows, 256, 0, st>>>(x, nullptr, N, scale, y, nullptr, nullptr, nullptr);
+        fht8192_kernel<0><<<(unsigned)rows, 256, 0, st>>>(x, nullptr, N, scale, y, nullptr, nullptr, nullptr, FhtWindow{1, 0, 0, 0});
     } else {
         int threads = N / 2 < 256 ? (N / 2 < 32 ? 32 : N / 2) : 256;
         fht_generic_kernel<<<(unsigned)rows, threads, N * sizeof(float), st>>>(x, N, scale, y);
@@ -195,7 +220,7 @@ extern "C" int flexllm_swiglu_fht_quant(const float* g, const float* u, int M, i
     if (N != 8192) return FLEXLLM_ENOTSUP;
     FLEXLLM_REQUIRE(aligned(g, 16) && aligned(u, 16) && aligned(q, 8) && (!act || aligned(act, 16)));
     if (M == 0) return FLEXLLM_OK;
-    fht8192_kernel<1><<<M, 256, 0, (cudaStream_t)stream>>>(g, u, N, scale, nullptr, q, s, act);
+    fht8192_kernel<1><<<M, 256, 0, (cudaStream_t)stream>>>(g, u, N, scale, nullptr, q, s, act, FhtWindow{1, 0, 0, 0});
     return launch_status();
 }
 

@@ -19,6 +19,7 @@
 #include "common.cuh"
 
 struct flexllm_kv_cache;
+struct flexllm_tp;
 
 namespace flexllm {
 int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
@@ -35,6 +36,13 @@ int mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float*
                    const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, int HQ,
                    float* out, int32_t* oacc, void* workspace, cudaStream_t st);
 int gemm_check_error_flag();
+int quant_gathered(const float* x, int M, int W, int g, int r, int8_t* q, float* s, cudaStream_t st);
+int swiglu_slice(const float* gu, long M, int W, float* h, cudaStream_t st);
+int dequant_residual(const int32_t* acc, const float* s_tok, const float* s_ch, long M, int N, const float* residual, float* y,
+                     cudaStream_t st);
+int argmax_pair(const float* logits, int B, long V, int offset, void* pairs, cudaStream_t st);
+int argmax_select(const void* pairs, int g, int B, int32_t* idx, cudaStream_t st);
+int fht_quant_gathered(const float* h, int M, int g, int r, float scale, int8_t* q, float* s, cudaStream_t st);
 
 // x[t][:] = (float)lm_w[tok[t]][:] * lm_s[tok[t]]
 __global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ lm_w, const float* __restrict__ lm_s,
@@ -105,6 +113,12 @@ struct flexllm_model {
     int B = 0, S = 0;
     cudaGraphExec_t graph = nullptr; int graph_B = 0; int graph_kernels = 0;
     std::vector<void*> owned;
+    // tensor parallelism: g ranks, this one is r; *l = local (per-rank) sizes
+    flexllm_tp* tp = nullptr;
+    int g = 1, r = 0, HQl = 0, HKVl = 0, Fl = 0, Dl = 0, Vl = 0;
+    float *gath = nullptr, *hloc = nullptr;     // all-gather target / local silu(gate)*up slice
+    int32_t* acc32 = nullptr;                   // row-parallel partial sums
+    void *pairs_l = nullptr, *pairs_g = nullptr;
 };
 
 template <class T> static int dmalloc(flexllm_model* m, T** p, size_t n) {
@@ -118,6 +132,10 @@ template <class T> static int dmalloc(flexllm_model* m, T** p, size_t n) {
 #define TRY(expr) do { int _rc = (expr); if (_rc != FLEXLLM_OK) return _rc; } while (0)
 
 extern "C" int flexllm_model_create(flexllm_model** out, const flexllm_model_config* c) {
+    return flexllm_model_create_tp(out, c, nullptr);
+}
+
+extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_config* c, flexllm_tp* tp) {
     FLEXLLM_REQUIRE(out && c);
     FLEXLLM_REQUIRE(c->layers > 0 && c->hidden > 0 && c->heads_q > 0 && c->heads_kv > 0 && c->ffn > 0 && c->vocab > 0);
     FLEXLLM_REQUIRE(c->max_batch > 0 && c->max_batch <= 64 && c->max_prefill > 0 && c->max_ctx >= c->max_prefill);
@@ -125,7 +143,12 @@ extern "C" int flexllm_model_create(flexllm_model** out, const flexllm_model_con
     flexllm_model* m = new (std::nothrow) flexllm_model();
     if (!m) return FLEXLLM_ENOMEM;
     m->cfg = *c;
-    const int D = c->hidden, HQ = c->heads_q, HKV = c->heads_kv, F = c->ffn, V = c->vocab, NL = c->layers;
+    const int D = c->hidden, F = c->ffn, V = c->vocab, NL = c->layers;
+    m->tp = tp; m->g = flexllm_tp_size(tp); m->r = flexllm_tp_rank(tp);
+    const int g = m->g;
+    if (c->heads_kv % g || D % (g * 16) || F % g || V % (g * 8)) { delete m; return FLEXLLM_ENOTSUP; }
+    m->HQl = c->heads_q / g; m->HKVl = c->heads_kv / g; m->Fl = F / g; m->Dl = D / g; m->Vl = V / g;
+    const int HQ = m->HQl, HKV = m->HKVl;            // everything below is sized per rank
     const int QKV = (HQ + 2 * HKV) * 64;
     const size_t Mmax = (size_t)c->max_batch * c->max_prefill;
     m->L.resize(NL);
@@ -134,16 +157,16 @@ extern "C" int flexllm_model_create(flexllm_model** out, const flexllm_model_con
     for (int l = 0; l < NL && rc == FLEXLLM_OK; l++) {
         LayerW& w = m->L[l];
         if ((rc = dmalloc(m, &w.wqkv, (size_t)QKV * D))) break;
-        if ((rc = dmalloc(m, &w.wo, (size_t)D * D))) break;
-        if ((rc = dmalloc(m, &w.wgu, (size_t)2 * F * D))) break;
-        if ((rc = dmalloc(m, &w.wd, (size_t)D * F))) break;
+        if ((rc = dmalloc(m, &w.wo, (size_t)D * m->Dl))) break;
+        if ((rc = dmalloc(m, &w.wgu, (size_t)2 * m->Fl * D))) break;
+        if ((rc = dmalloc(m, &w.wd, (size_t)D * m->Fl))) break;
         if ((rc = dmalloc(m, &w.sqkv, QKV))) break;
         if ((rc = dmalloc(m, &w.so, D))) break;
-        if ((rc = dmalloc(m, &w.sgu, 2 * F))) break;
+        if ((rc = dmalloc(m, &w.sgu, 2 * m->Fl))) break;
         if ((rc = dmalloc(m, &w.sd, D))) break;
         if ((rc = dmalloc(m, &w.g0, D))) break;
         if ((rc = dmalloc(m, &w.g1, D))) break;
-        if ((rc = dmalloc(m, &w.a_s, HQ))) break;
+        if ((rc = dmalloc(m, &w.a_s, HQ))) break;   // local heads
     }
     if (rc) return fail(rc);
     if ((rc = dmalloc(m, &m->lm_w, (size_t)V * D)) || (rc = dmalloc(m, &m->lm_s, V)) || (rc = dmalloc(m, &m->g_final, D))) return fail(rc);
@@ -163,10 +186,17 @@ extern "C" int flexllm_model_create(flexllm_model** out, const flexllm_model_con
         if (cudaMemcpy(m->page_table, pt.data(), pt.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) return fail(FLEXLLM_ECUDA);
     }
     if ((rc = dmalloc(m, &m->x, Mmax * D)) || (rc = dmalloc(m, &m->qkv, Mmax * QKV)) || (rc = dmalloc(m, &m->att, Mmax * D)) ||
-        (rc = dmalloc(m, &m->tmp, Mmax * D)) || (rc = dmalloc(m, &m->gu, Mmax * 2 * F)) || (rc = dmalloc(m, &m->xs, Mmax)) ||
-        (rc = dmalloc(m, &m->xq, Mmax * D)) || (rc = dmalloc(m, &m->hq, Mmax * F)) ||
+        (rc = dmalloc(m, &m->tmp, Mmax * D)) || (rc = dmalloc(m, &m->gu, Mmax * 2 * m->Fl)) || (rc = dmalloc(m, &m->xs, Mmax)) ||
+        (rc = dmalloc(m, &m->xq, Mmax * D)) || (rc = dmalloc(m, &m->hq, Mmax * m->Fl)) ||
         (rc = dmalloc(m, &m->logits, (size_t)c->max_batch * V)) || (rc = dmalloc(m, &m->xlast, (size_t)c->max_batch * D)))
         return fail(rc);
+    if (g > 1) {
+        if ((rc = dmalloc(m, &m->gath, Mmax * F)) || (rc = dmalloc(m, &m->hloc, Mmax * m->Fl)) || (rc = dmalloc(m, &m->acc32, Mmax * D)))
+            return fail(rc);
+        uint8_t *pl = nullptr, *pg = nullptr;
+        if ((rc = dmalloc(m, &pl, (size_t)64 * 8)) || (rc = dmalloc(m, &pg, (size_t)64 * 8 * g))) return fail(rc);
+        m->pairs_l = pl; m->pairs_g = pg;
+    }
     m->attn_ws_bytes = mha_prefill_ws_bytes(c->max_batch, c->max_prefill, HQ, HKV);
     m->dec_ws_bytes = flexllm_mha_decode_workspace(c->max_batch, HQ, c->max_ctx);
     uint8_t *a = nullptr, *d = nullptr;
@@ -189,31 +219,38 @@ static int copy_any(void* dst, const void* src, size_t bytes, cudaStream_t st) {
     return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, st));
 }
 
+static int copy_cols(void* dst, const void* src, size_t rows, size_t src_row_bytes, size_t col0_bytes, size_t width_bytes, cudaStream_t st) {
+    return cuda_status(cudaMemcpy2DAsync(dst, width_bytes, (const char*)src + col0_bytes, src_row_bytes, width_bytes, rows,
+                                         cudaMemcpyDefault, st));
+}
+
+// Takes the FULL layer weights; with tensor parallelism each rank keeps its slice: rows of q/k/v and
+// gate/up (column-parallel, by heads / FFN channels), columns of o and down (row-parallel).
 extern "C" int flexllm_model_load_layer(flexllm_model* m, int layer, const flexllm_layer_weights* w, void* stream) {
     FLEXLLM_REQUIRE(m && w && layer >= 0 && layer < m->cfg.layers);
     FLEXLLM_REQUIRE(w->wq && w->wk && w->wv && w->wo && w->wg && w->wu && w->wd && w->sq && w->sk && w->sv && w->so && w->sg &&
                     w->su && w->sd && w->gamma0 && w->gamma1 && w->a_s);
     cudaStream_t st = (cudaStream_t)stream;
-    const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
+    const int D = m->cfg.hidden, F = m->cfg.ffn, r = m->r;
+    const size_t q = (size_t)m->HQl * 64, kv = (size_t)m->HKVl * 64, Fl = m->Fl, Dl = m->Dl;
     LayerW& L = m->L[layer];
-    const size_t q = (size_t)HQ * 64, kv = (size_t)HKV * 64;
-    TRY(copy_any(L.wqkv, w->wq, q * D, st));
-    TRY(copy_any(L.wqkv + q * D, w->wk, kv * D, st));
-    TRY(copy_any(L.wqkv + (q + kv) * D, w->wv, kv * D, st));
-    TRY(copy_any(L.sqkv, w->sq, q * 4, st));
-    TRY(copy_any(L.sqkv + q, w->sk, kv * 4, st));
-    TRY(copy_any(L.sqkv + q + kv, w->sv, kv * 4, st));
-    TRY(copy_any(L.wo, w->wo, (size_t)D * D, st));
+    TRY(copy_any(L.wqkv, w->wq + r * q * D, q * D, st));
+    TRY(copy_any(L.wqkv + q * D, w->wk + r * kv * D, kv * D, st));
+    TRY(copy_any(L.wqkv + (q + kv) * D, w->wv + r * kv * D, kv * D, st));
+    TRY(copy_any(L.sqkv, w->sq + r * q, q * 4, st));
+    TRY(copy_any(L.sqkv + q, w->sk + r * kv, kv * 4, st));
+    TRY(copy_any(L.sqkv + q + kv, w->sv + r * kv, kv * 4, st));
+    TRY(copy_cols(L.wo, w->wo, D, D, r * Dl, Dl, st));
     TRY(copy_any(L.so, w->so, (size_t)D * 4, st));
-    TRY(copy_any(L.wgu, w->wg, (size_t)F * D, st));
-    TRY(copy_any(L.wgu + (size_t)F * D, w->wu, (size_t)F * D, st));
-    TRY(copy_any(L.sgu, w->sg, (size_t)F * 4, st));
-    TRY(copy_any(L.sgu + F, w->su, (size_t)F * 4, st));
-    TRY(copy_any(L.wd, w->wd, (size_t)D * F, st));
+    TRY(copy_any(L.wgu, w->wg + r * Fl * D, Fl * D, st));
+    TRY(copy_any(L.wgu + Fl * D, w->wu + r * Fl * D, Fl * D, st));
+    TRY(copy_any(L.sgu, w->sg + r * Fl, Fl * 4, st));
+    TRY(copy_any(L.sgu + Fl, w->su + r * Fl, Fl * 4, st));
+    TRY(copy_cols(L.wd, w->wd, D, F, r * Fl, Fl, st));
     TRY(copy_any(L.sd, w->sd, (size_t)D * 4, st));
     TRY(copy_any(L.g0, w->gamma0, (size_t)D * 4, st));
     TRY(copy_any(L.g1, w->gamma1, (size_t)D * 4, st));
-    TRY(copy_any(L.a_s, w->a_s, (size_t)HQ * 4, st));
+    TRY(copy_any(L.a_s, w->a_s + r * m->HQl, (size_t)m->HQl * 4, st));
     return FLEXLLM_OK;
 }
 
@@ -233,8 +270,17 @@ extern "C" int flexllm_model_load_head(flexllm_model* m, const int8_t* lm_w, con
 static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaStream_t st) {
     const int D = m->cfg.hidden, V = m->cfg.vocab;
     TRY(flexllm_rmsnorm_quant(xin, m->g_final, B, D, m->cfg.eps, order, nullptr, m->xq, m->xs, st));
-    TRY(flexllm_linear_decode_i8(m->xq, m->xs, m->lm_w, m->lm_s, B, V, D, nullptr, m->logits, st));
-    TRY(flexllm_logits_argmax(m->logits, B, V, m->next, st));
+    if (m->g == 1) {
+        TRY(flexllm_linear_decode_i8(m->xq, m->xs, m->lm_w, m->lm_s, B, V, D, nullptr, m->logits, st));
+        TRY(flexllm_logits_argmax(m->logits, B, V, m->next, st));
+        return FLEXLLM_OK;
+    }
+    // vocab-parallel: this rank's rows of the (replicated) lm_head, local argmax, gather, select
+    const int Vl = m->Vl, off = m->r * Vl;
+    TRY(flexllm_linear_decode_i8(m->xq, m->xs, m->lm_w + (size_t)off * D, m->lm_s + off, B, Vl, D, nullptr, m->logits, st));
+    TRY(argmax_pair(m->logits, B, Vl, off, m->pairs_l, st));
+    TRY(flexllm_tp_allgather(m->tp, m->pairs_l, m->pairs_g, (size_t)B * 8, st));
+    TRY(argmax_select(m->pairs_g, m->g, B, m->next, st));
     return FLEXLLM_OK;
 }
 
@@ -242,9 +288,10 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
     FLEXLLM_REQUIRE(m && tokens && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill);
     if (S % 16 != 0) return FLEXLLM_ENOTSUP;
     cudaStream_t st = (cudaStream_t)stream;
-    const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
+    const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl, F = m->cfg.ffn;
     const int QKV = (HQ + 2 * HKV) * 64;
     const int M = B * S;
+    const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
     embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->x);
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
@@ -254,12 +301,29 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
         const int8_t *k2, *vT; const float *ks2, *vsT;
         TRY(mha_prefill_f32(m->qkv, m->cos_t, m->sin_t, L.a_s, B, S, HQ, HKV, m->att, m->attn_ws, st, &k2, &ks2, &vT, &vsT));
         TRY(kv_pack(m->cache, l, k2, ks2, vT, vsT, m->page_table, m->max_pages, B, S, st));
-        TRY(flexllm_quant_per_token(m->att, M, D, m->xq, m->xs, st));
-        TRY(gemm_i8_prefill(m->xq, m->xs, L.wo, L.so, M, D, D, nullptr, m->x, st, m->x));       // x += o_proj
-        TRY(flexllm_rmsnorm_quant(m->x, L.g1, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
-        TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, M, 2 * F, D, nullptr, m->gu, st, nullptr));
-        TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, M, m->cfg.fht_scale, m->hq, m->xs, st));
-        TRY(gemm_i8_prefill(m->hq, m->xs, L.wd, L.sd, M, D, F, nullptr, m->x, st, m->x));       // x += down_proj
+        if (g == 1) {
+            TRY(flexllm_quant_per_token(m->att, M, D, m->xq, m->xs, st));
+            TRY(gemm_i8_prefill(m->xq, m->xs, L.wo, L.so, M, D, D, nullptr, m->x, st, m->x));       // x += o_proj
+            TRY(flexllm_rmsnorm_quant(m->x, L.g1, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
+            TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, M, 2 * F, D, nullptr, m->gu, st, nullptr));
+            TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, M, m->cfg.fht_scale, m->hq, m->xs, st));
+            TRY(gemm_i8_prefill(m->hq, m->xs, L.wd, L.sd, M, D, F, nullptr, m->x, st, m->x));       // x += down_proj
+        } else {
+            // heads are local: gather the attention output, quantise whole rows, keep this rank's columns
+            TRY(flexllm_tp_allgather(m->tp, m->att, m->gath, (size_t)M * Dl * 4, st));
+            TRY(quant_gathered(m->gath, M, Dl, g, r, m->xq, m->xs, st));
+            TRY(gemm_i8_prefill(m->xq, nullptr, L.wo, nullptr, M, D, Dl, m->acc32, nullptr, st, nullptr));   // partial o_proj
+            TRY(flexllm_tp_allreduce_s32(m->tp, m->acc32, (size_t)M * D, st));
+            TRY(dequant_residual(m->acc32, m->xs, L.so, M, D, m->x, m->x, st));
+            TRY(flexllm_rmsnorm_quant(m->x, L.g1, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
+            TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, M, 2 * Fl, D, nullptr, m->gu, st, nullptr));
+            TRY(swiglu_slice(m->gu, M, Fl, m->hloc, st));
+            TRY(flexllm_tp_allgather(m->tp, m->hloc, m->gath, (size_t)M * Fl * 4, st));
+            TRY(fht_quant_gathered(m->gath, M, g, r, m->cfg.fht_scale, m->hq, m->xs, st));
+            TRY(gemm_i8_prefill(m->hq, nullptr, L.wd, nullptr, M, D, Fl, m->acc32, nullptr, st, nullptr));   // partial down_proj
+            TRY(flexllm_tp_allreduce_s32(m->tp, m->acc32, (size_t)M * D, st));
+            TRY(dequant_residual(m->acc32, m->xs, L.sd, M, D, m->x, m->x, st));
+        }
     }
     gather_last_kernel<<<B, 256, 0, st>>>(m->x, S, D, m->xlast);
     note_launches(1);
@@ -283,9 +347,10 @@ static int decode_step(flexllm_model* m, cudaStream_t st) {
     return rc;
 }
 static int decode_step_body(flexllm_model* m, cudaStream_t st) {
-    const int D = m->cfg.hidden, HQ = m->cfg.heads_q, HKV = m->cfg.heads_kv, F = m->cfg.ffn;
+    const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl, F = m->cfg.ffn;
     const int QKV = (HQ + 2 * HKV) * 64;
     const int B = m->B;
+    const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
     launch_k(embed_kernel, dim3(B), dim3(256), 0, st, (const int32_t*)m->next, (const int8_t*)m->lm_w, (const float*)m->lm_s, D, m->x);
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
@@ -294,12 +359,28 @@ static int decode_step_body(flexllm_model* m, cudaStream_t st) {
         TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wqkv, L.sqkv, B, QKV, D, nullptr, m->qkv, st));
         TRY(mha_decode_run(m->cache, l, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, m->qkv, m->cos_t, m->sin_t, L.a_s,
                            m->page_table, m->max_pages, m->ctx, m->cfg.max_ctx, B, HQ, m->att, nullptr, m->dec_ws, st));
-        TRY(flexllm_quant_per_token(m->att, B, D, m->xq, m->xs, st));
-        TRY(flexllm_linear_decode_i8_residual(m->xq, m->xs, L.wo, L.so, B, D, D, m->x, m->x, st));
-        TRY(flexllm_rmsnorm_quant(m->x, L.g1, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
-        TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wgu, L.sgu, B, 2 * F, D, nullptr, m->gu, st));
-        TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, B, m->cfg.fht_scale, m->hq, m->xs, st));
-        TRY(flexllm_linear_decode_i8_residual(m->hq, m->xs, L.wd, L.sd, B, D, F, m->x, m->x, st));
+        if (g == 1) {
+            TRY(flexllm_quant_per_token(m->att, B, D, m->xq, m->xs, st));
+            TRY(flexllm_linear_decode_i8_residual(m->xq, m->xs, L.wo, L.so, B, D, D, m->x, m->x, st));
+            TRY(flexllm_rmsnorm_quant(m->x, L.g1, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
+            TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wgu, L.sgu, B, 2 * F, D, nullptr, m->gu, st));
+            TRY(swiglu_fht_quant_strided(m->gu, m->gu + F, 2L * F, B, m->cfg.fht_scale, m->hq, m->xs, st));
+            TRY(flexllm_linear_decode_i8_residual(m->hq, m->xs, L.wd, L.sd, B, D, F, m->x, m->x, st));
+        } else {
+            TRY(flexllm_tp_allgather(m->tp, m->att, m->gath, (size_t)B * Dl * 4, st));
+            TRY(quant_gathered(m->gath, B, Dl, g, r, m->xq, m->xs, st));
+            TRY(flexllm_linear_decode_i8(m->xq, nullptr, L.wo, nullptr, B, D, Dl, m->acc32, nullptr, st));
+            TRY(flexllm_tp_allreduce_s32(m->tp, m->acc32, (size_t)B * D, st));
+            TRY(dequant_residual(m->acc32, m->xs, L.so, B, D, m->x, m->x, st));
+            TRY(flexllm_rmsnorm_quant(m->x, L.g1, B, D, m->cfg.eps, FLEXLLM_NORM_DECODE8, nullptr, m->xq, m->xs, st));
+            TRY(flexllm_linear_decode_i8(m->xq, m->xs, L.wgu, L.sgu, B, 2 * Fl, D, nullptr, m->gu, st));
+            TRY(swiglu_slice(m->gu, B, Fl, m->hloc, st));
+            TRY(flexllm_tp_allgather(m->tp, m->hloc, m->gath, (size_t)B * Fl * 4, st));
+            TRY(fht_quant_gathered(m->gath, B, g, r, m->cfg.fht_scale, m->hq, m->xs, st));
+            TRY(flexllm_linear_decode_i8(m->hq, nullptr, L.wd, nullptr, B, D, Fl, m->acc32, nullptr, st));
+            TRY(flexllm_tp_allreduce_s32(m->tp, m->acc32, (size_t)B * D, st));
+            TRY(dequant_residual(m->acc32, m->xs, L.sd, B, D, m->x, m->x, st));
+        }
     }
     TRY(run_head(m, m->x, B, FLEXLLM_NORM_DECODE8, st));
     launch_k(step_bookkeeping_kernel, dim3(1), dim3(64), 0, st, (const int32_t*)m->next, B, m->out_tokens, m->state, m->ctx, 1);

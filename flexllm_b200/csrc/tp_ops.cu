@@ -1,0 +1,165 @@
+// Small kernels that exist only for the tensor-parallel partition: they read activations in the
+// rank-blocked layout an all-gather produces ([ranks][rows][W], rank r holding columns
+// [r*W, (r+1)*W) of each logical row) and write this rank's compact column slice.
+#include "common.cuh"
+
+namespace flexllm {
+
+// Per-token int8 quantisation of logical rows of D = g*W values gathered as x[g][M][W]: the scale
+// comes from the whole row (quant.h:84-96), only this rank's W columns are written.
+template <int VPT>
+__global__ void __launch_bounds__(256) quant_gathered_kernel(const float* __restrict__ x, int M, int W, int g, int r,
+                                                             int8_t* __restrict__ q, float* __restrict__ s) {
+    __shared__ float red[64];
+    pdl_sync();
+    const long row = blockIdx.x;
+    const int wv = W >> 2, nv = g * wv;
+    float4 v[VPT];
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        const int c = threadIdx.x + i * 256;
+        if (c < nv) {
+            const int seg = c / wv, o = c - seg * wv;
+            v[i] = reinterpret_cast<const float4*>(x + ((long)seg * M + row) * W)[o];
+            mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            mn = fminf(mn, fminf(fminf(v[i].x, v[i].y), fminf(v[i].z, v[i].w)));
+        }
+    }
+    block_max_min(mx, mn, red);
+    const float sc = sym_scale_from(mx, mn);
+    if (threadIdx.x == 0) s[row] = sc;
+    char4* qr = reinterpret_cast<char4*>(q + row * W);
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        const int c = threadIdx.x + i * 256;
+        if (c < nv && c / wv == r) {
+            char4 o;
+            o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc); o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+            qr[c - r * wv] = o;
+        }
+    }
+}
+
+// h[m][c] = silu(gate[m][c]) * up[m][c] on this rank's W channels; gu rows are [gate W | up W].
+__global__ void swiglu_slice_kernel(const float* __restrict__ gu, long M, int W, float* __restrict__ h) {
+    pdl_sync();
+    const int wv = W >> 2;
+    const long nv = M * wv;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+        const long m = i / wv; const int c = (int)(i - m * wv);
+        const float4 g = reinterpret_cast<const float4*>(gu + m * 2 * W)[c];
+        const float4 u = reinterpret_cast<const float4*>(gu + m * 2 * W + W)[c];
+        float4 o;
+        o.x = silu_f(g.x) * u.x; o.y = silu_f(g.y) * u.y; o.z = silu_f(g.z) * u.z; o.w = silu_f(g.w) * u.w;
+        reinterpret_cast<float4*>(h)[i] = o;
+    }
+}
+
+// y = residual + ((float)acc * s_tok[m]) * s_ch[n]   (dequant after the int32 all-reduce, fused with
+// the residual add; quant.h:151 + Residual_Layer.h:61). y may alias residual.
+__global__ void dequant_residual_kernel(const int32_t* __restrict__ acc, const float* __restrict__ s_tok,
+                                        const float* __restrict__ s_ch, long M, int N, const float* residual, float* y) {
+    pdl_sync();
+    const int nv4 = N >> 2;
+    const long nv = M * nv4;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+        const long m = i / nv4; const int c = (int)(i - m * nv4);
+        const int4 a = reinterpret_cast<const int4*>(acc)[i];
+        const float4 w = reinterpret_cast<const float4*>(s_ch)[c];
+        const float st = s_tok[m];
+        float4 o;
+        o.x = ((float)a.x * st) * w.x; o.y = ((float)a.y * st) * w.y; o.z = ((float)a.z * st) * w.z; o.w = ((float)a.w * st) * w.w;
+        if (residual) {
+            const float4 rs = reinterpret_cast<const float4*>(residual)[i];
+            o.x = rs.x + o.x; o.y = rs.y + o.y; o.z = rs.z + o.z; o.w = rs.w + o.w;
+        }
+        reinterpret_cast<float4*>(y)[i] = o;
+    }
+}
+
+// Vocab-parallel greedy token. Each rank's argmax over its slice is gathered as (value, global
+// index); the winner is the largest value, ties to the lowest index (Logits.h:13-17).
+struct ArgPair { float val; int idx; };
+__global__ void __launch_bounds__(1024) argmax_pair_kernel(const float* __restrict__ logits, long V, int offset, ArgPair* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_sync();
+    const float* l = logits + (long)blockIdx.x * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (long v = threadIdx.x; v < V; v += blockDim.x) {
+        const float t = l[v];
+        if (t > best || bi == 0x7fffffff) { best = t; bi = (int)v; }
+    }
+    auto better = [](float a, int ai, float b, int bi2) { return a > b || (a == b && ai < bi2); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ob, oi, best, bi)) { best = ob; bi = oi; }
+    }
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ob, oi, best, bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) { out[blockIdx.x].val = best; out[blockIdx.x].idx = bi + offset; }
+    }
+}
+// pairs [g][B] -> idx [B]
+__global__ void argmax_select_kernel(const ArgPair* __restrict__ pairs, int g, int B, int32_t* __restrict__ idx) {
+    pdl_sync();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    ArgPair best = pairs[b];
+    for (int r = 1; r < g; r++) {
+        const ArgPair p = pairs[(long)r * B + b];
+        if (p.val > best.val || (p.val == best.val && p.idx < best.idx)) best = p;
+    }
+    idx[b] = best.idx;
+}
+
+int quant_gathered(const float* x, int M, int W, int g, int r, int8_t* q, float* s, cudaStream_t st) {
+    if (M == 0) return FLEXLLM_OK;
+    const int nv = g * W / 4;
+    if (nv <= 256) launch_k(quant_gathered_kernel<1>, dim3(M), dim3(256), 0, st, x, M, W, g, r, q, s);
+    else if (nv <= 512) launch_k(quant_gathered_kernel<2>, dim3(M), dim3(256), 0, st, x, M, W, g, r, q, s);
+    else if (nv <= 1024) launch_k(quant_gathered_kernel<4>, dim3(M), dim3(256), 0, st, x, M, W, g, r, q, s);
+    else if (nv <= 2048) launch_k(quant_gathered_kernel<8>, dim3(M), dim3(256), 0, st, x, M, W, g, r, q, s);
+    else return FLEXLLM_ENOTSUP;
+    return launch_status();
+}
+int swiglu_slice(const float* gu, long M, int W, float* h, cudaStream_t st) {
+    if (M == 0) return FLEXLLM_OK;
+    long blocks = (M * (W / 4) + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    launch_k(swiglu_slice_kernel, dim3((unsigned)blocks), dim3(256), 0, st, gu, M, W, h);
+    return launch_status();
+}
+int dequant_residual(const int32_t* acc, const float* s_tok, const float* s_ch, long M, int N, const float* residual, float* y,
+                     cudaStream_t st) {
+    if (M == 0) return FLEXLLM_OK;
+    long blocks = (M * (N / 4) + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    launch_k(dequant_residual_kernel, dim3((unsigned)blocks), dim3(256), 0, st, acc, s_tok, s_ch, M, N, residual, y);
+    return launch_status();
+}
+int argmax_pair(const float* logits, int B, long V, int offset, void* pairs, cudaStream_t st) {
+    launch_k(argmax_pair_kernel, dim3(B), dim3(1024), 0, st, logits, V, offset, (ArgPair*)pairs);
+    return launch_status();
+}
+int argmax_select(const void* pairs, int g, int B, int32_t* idx, cudaStream_t st) {
+    launch_k(argmax_select_kernel, dim3((B + 63) / 64), dim3(64), 0, st, (const ArgPair*)pairs, g, B, idx);
+    return launch_status();
+}
+
+}  // namespace flexllm

@@ -284,16 +284,51 @@ def MHA_i8xi8_Decoding(cache, layer, q, qs, k, ks, v, vs, cos_t, sin_t, a_s, pag
     return out, oacc
 
 
+def tp_unique_id():
+    """128-byte NCCL id made on one rank; hand it to the others (e.g. torch.distributed broadcast)."""
+    from . import build
+    buf = (C.c_ubyte * 128)()
+    _check("flexllm_tp_unique_id", lib().flexllm_tp_unique_id(buf, build.nccl_library().encode()))
+    return bytes(buf)
+
+
+class TensorParallel:
+    """Communicator of one tensor-parallel rank (one process per GPU; the current CUDA device is used)."""
+
+    def __init__(self, rank, size, unique_id):
+        from . import build
+        self.rank, self.size = rank, size
+        self._h = C.c_void_p()
+        idbuf = (C.c_ubyte * 128).from_buffer_copy(unique_id)
+        _check("flexllm_tp_init", lib().flexllm_tp_init(C.byref(self._h), rank, size, idbuf, build.nccl_library().encode()))
+
+    def close(self):
+        if self._h:
+            lib().flexllm_tp_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def allreduce_s32(self, t):
+        _check("flexllm_tp_allreduce_s32", lib().flexllm_tp_allreduce_s32(self._h, _ptr(t), t.numel(), _stream()))
+        return t
+
+    def allgather(self, t):
+        out = torch.empty((self.size,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        _check("flexllm_tp_allgather", lib().flexllm_tp_allgather(self._h, _ptr(t), _ptr(out), t.numel() * t.element_size(), _stream()))
+        return out
+
+
 class Model:
     """Whole-model runner (SpinQuant_Prefilling + SpinQuant_Decoding graphs). Weights are given as
-    CUDA or CPU torch tensors (the library copies them)."""
+    CUDA or CPU torch tensors (the library copies them; with `tp` every rank passes the full weights
+    and keeps its slice)."""
 
-    def __init__(self, layers, hidden, heads_q, heads_kv, ffn, vocab, max_batch, max_prefill, max_ctx, eps=1e-5):
+    def __init__(self, layers, hidden, heads_q, heads_kv, ffn, vocab, max_batch, max_prefill, max_ctx, eps=1e-5, tp=None):
         import math
         self.cfg = _lib.ModelConfig(layers, hidden, heads_q, heads_kv, ffn, vocab, eps, float(torch.tensor(math.sqrt(ffn), dtype=torch.float32)),
                                     max_batch, max_prefill, max_ctx)
         self._h = C.c_void_p()
-        _check("flexllm_model_create", lib().flexllm_model_create(C.byref(self._h), C.byref(self.cfg)))
+        self.tp = tp
+        _check("flexllm_model_create_tp", lib().flexllm_model_create_tp(C.byref(self._h), C.byref(self.cfg), tp._h if tp else None))
 
     def close(self):
         if self._h:

@@ -191,6 +191,22 @@ FLEXLLM_API int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const i
                              size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Tensor parallelism over the GPUs of one node (no counterpart in the reference, a single-FPGA
+ * design): one process per GPU; q/k/v and gate/up column-parallel (by heads / FFN channels), o and
+ * down row-parallel with an all-reduce of the exact int32 partial sums, lm_head vocab-parallel.
+ * Results are bit-identical to the single-GPU model. Collectives run on NCCL, loaded at run time
+ * (nccl_lib_path: fallback path of libnccl.so.2 when the process has not loaded it yet).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct flexllm_tp flexllm_tp;
+FLEXLLM_API int flexllm_tp_unique_id(unsigned char* id128, const char* nccl_lib_path);   /* rank 0; share the 128 bytes */
+FLEXLLM_API int flexllm_tp_init(flexllm_tp** out, int rank, int size, const unsigned char* id128, const char* nccl_lib_path);
+FLEXLLM_API int flexllm_tp_destroy(flexllm_tp* t);
+FLEXLLM_API int flexllm_tp_rank(const flexllm_tp* t);
+FLEXLLM_API int flexllm_tp_size(const flexllm_tp* t);
+FLEXLLM_API int flexllm_tp_allreduce_s32(flexllm_tp* t, int32_t* buf, size_t count, void* stream);
+FLEXLLM_API int flexllm_tp_allgather(flexllm_tp* t, const void* send, void* recv, size_t bytes_per_rank, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Whole-model runner: the two top-level graphs of the reference, SpinQuant_Prefilling
  * (SpinQuant_Llama_32_1B/SpinQuant_Prefilling.h:807) and SpinQuant_Decoding
  * (SpinQuant_Decoding_mem_opt.h:947), and the host flow of its demo
@@ -212,6 +228,9 @@ typedef struct {                       /* device or host pointers, row-major [N]
     const float *a_s;                  /* [heads_q] static scale of the u8 attention probabilities */
 } flexllm_layer_weights;
 FLEXLLM_API int flexllm_model_create(flexllm_model** out, const flexllm_model_config* cfg);
+/* The same model partitioned over the ranks of `tp` (NULL = single GPU). Every rank passes the FULL
+ * weights to flexllm_model_load_layer / _load_head and keeps its own slice. */
+FLEXLLM_API int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_config* cfg, flexllm_tp* tp);
 FLEXLLM_API int flexllm_model_destroy(flexllm_model* m);
 FLEXLLM_API int flexllm_model_load_layer(flexllm_model* m, int layer, const flexllm_layer_weights* w, void* stream);
 FLEXLLM_API int flexllm_model_load_head(flexllm_model* m, const int8_t* lm_w, const float* lm_s, const float* gamma_final,
