@@ -178,10 +178,14 @@ def reference_arm(args):
     print(json.dumps(line))
 
 
-def workload_config():
-    return {"workload": "config5: Llama-3.2-1B W8A8 SpinQuant, random-init weights, batch 32 per GPU, prefill 1024 + greedy decode 256",
-            "global_batch_per_gpu": BATCH, "prefill_len": PREFILL, "decode_len": NEW, "layers": CFG["layers"],
-            "l2": "weights (1.24 GB) and activations exceed the 126 MB L2; no flush needed", "parallelism": "batch-parallel replicas"}
+def workload_config(world=1, parallel="dp"):
+    tp = parallel == "tp" and world > 1
+    return {"workload": "config5: Llama-3.2-1B W8A8 SpinQuant, random-init weights, batch 32" + (" in total" if tp else " per GPU") +
+                        ", prefill 1024 + greedy decode 256",
+            "global_batch": BATCH if tp else BATCH * world, "prefill_len": PREFILL, "decode_len": NEW, "layers": CFG["layers"],
+            "l2": "weights (1.24 GB) and activations exceed the 126 MB L2; no flush needed",
+            "parallelism": (f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + NCCL int32 all-reduce, vocab-parallel lm_head"
+                            if tp else ("single GPU" if world == 1 else f"dp{world}: batch-parallel replicas, no data-path collective"))}
 
 
 # ------------------------------------------------------------------------------------ GPU arm
@@ -290,50 +294,96 @@ def gpu_arm(args):
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except Exception:
         pass
-    m = F.Model(max_batch=BATCH, max_prefill=PREFILL, max_ctx=PREFILL + NEW, **CFG)
-    synthetic.load_random_weights(m, max_ctx=PREFILL + NEW, seed=rank, **CFG)
-    gen = torch.Generator().manual_seed(1234 + rank)
-    tok_host = torch.randint(0, CFG["vocab"], (BATCH, PREFILL), dtype=torch.int32, generator=gen).pin_memory()
-    out_host = torch.empty((BATCH, NEW), dtype=torch.int32).pin_memory()
-    tok_dev = tok_host.cuda()
-    tokens_per_step = BATCH * (PREFILL + NEW)
+    tp_comm = [None]
+
+    def communicator():
+        if tp_comm[0] is None:
+            idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+            if rank == 0:
+                idt.copy_(torch.frombuffer(bytearray(F.tp_unique_id()), dtype=torch.uint8))
+            dist.broadcast(idt, src=0)
+            tp_comm[0] = F.TensorParallel(rank, world, idt.cpu().numpy().tobytes())
+        return tp_comm[0]
 
     def barrier():
         if multi:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step_device():
-        m.prefill(tok_dev); m.begin(NEW); m.decode(NEW - 1, True)
+    def measure(use_tp, steps, with_e2e=True):
+        """One partition of the N GPUs. Tensor parallel: every rank holds a slice of the SAME model and
+        works on the same batch of 32 (total work fixed: strong scaling). Replicas: every rank runs its own
+        model and batch with no data-path collective (weak scaling)."""
+        seed = 0 if use_tp else rank
+        m = F.Model(max_batch=BATCH, max_prefill=PREFILL, max_ctx=PREFILL + NEW, tp=communicator() if use_tp else None, **CFG)
+        synthetic.load_random_weights(m, max_ctx=PREFILL + NEW, seed=seed, **CFG)
+        gen = torch.Generator().manual_seed(1234 + seed)
+        tok_host = torch.randint(0, CFG["vocab"], (BATCH, PREFILL), dtype=torch.int32, generator=gen).pin_memory()
+        out_host = torch.empty((BATCH, NEW), dtype=torch.int32).pin_memory()
+        tok_dev = tok_host.cuda()
 
-    def step_host():
-        m.generate_host(tok_host, NEW, True, out=out_host)
+        def step_device():
+            m.prefill(tok_dev); m.begin(NEW); m.decode(NEW - 1, True)
 
-    def timed(fn, phases=False):
-        for _ in range(args.warmup):
-            fn()
-        barrier()
-        sampler = ClockSampler(local); sampler.start()
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        l0 = lib.flexllm_launch_count()
-        e0.record()
-        for _ in range(args.steps):
-            fn()
-        e1.record()
-        barrier()
-        launches = lib.flexllm_launch_count() - l0
-        ms = e0.elapsed_time(e1)
-        clocks = sampler.stop()
+        def step_host():
+            m.generate_host(tok_host, NEW, True, out=out_host)
+
+        def timed(fn):
+            for _ in range(args.warmup):
+                fn()
+            barrier()
+            sampler = ClockSampler(local); sampler.start()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            l0 = lib.flexllm_launch_count()
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            barrier()
+            launches = lib.flexllm_launch_count() - l0
+            ms = e0.elapsed_time(e1)
+            clocks = sampler.stop()
+            if multi:
+                t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+            return ms, launches, clocks
+
+        r = {}
+        r["ms_dev"], r["launches"], r["clocks"] = timed(step_device)
+        r["ms_e2e"] = timed(step_host)[0] if with_e2e else None
+        # phase split (device-resident), one extra step
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record(); m.prefill(tok_dev); m.begin(NEW); ev[1].record(); m.decode(NEW - 1, True); ev[2].record(); torch.cuda.synchronize()
+        tt = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device="cuda")
         if multi:
-            t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
-        return ms, launches, clocks
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        r["t_pre"], r["t_dec"] = float(tt[0]), float(tt[1])
+        r["units"] = BATCH * (PREFILL + NEW) * (1 if use_tp else world)
+        r["value"] = r["units"] * steps / (r["ms_dev"] / 1e3)
+        m.close()
+        del m
+        torch.cuda.empty_cache()
+        return r
 
-    ms_dev, launches, clocks = timed(step_device)
-    ms_e2e, _, _ = timed(step_host)
-    # phase split (device-resident), one extra step
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    ev[0].record(); m.prefill(tok_dev); m.begin(NEW); ev[1].record(); m.decode(NEW - 1, True); ev[2].record(); torch.cuda.synchronize()
-    t_pre, t_dec = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+    def phases(r, nb):
+        dec_bytes = 1235746816 + 16 * 1088 * BATCH * (PREFILL + NEW / 2)
+        return {"prefill_ms": round(r["t_pre"], 3), "prefill_tokens_per_s": round(nb * PREFILL / r["t_pre"] * 1e3, 1),
+                "prefill_tops": round(6.60e13 * nb / BATCH / r["t_pre"] / 1e9, 1),
+                "decode_ms_per_step": round(r["t_dec"] / (NEW - 1), 4),
+                "decode_tokens_per_s": round(nb * (NEW - 1) / r["t_dec"] * 1e3, 1),
+                "decode_hbm_frac_of_measured": round(dec_bytes / (r["t_dec"] / (NEW - 1) / 1e3) / 1e9 / (peaks.get("hbm_gbs") or 6650.0), 4)}
+
+    # N > 1: the headline partition is --parallel (replicas by default: for a 1.2 GB model every
+    # collective only adds latency, so independent batch-parallel replicas are the faster use of N
+    # GPUs); the other partition is measured in the same run and reported beside it
+    use_tp = multi and args.parallel == "tp"
+    main_r = measure(use_tp, args.steps)
+    other = None
+    if multi and not args.no_extras:
+        o = measure(not use_tp, min(args.steps, 2), with_e2e=False)
+        nb_o = BATCH if not use_tp else BATCH * world
+        other = {"parallelism": workload_config(world, "dp" if use_tp else "tp")["parallelism"],
+                 "scaling": "weak" if use_tp else "strong", "value": round(o["value"], 1), "unit": "tokens/s",
+                 "ms_per_step": round(o["ms_dev"] / min(args.steps, 2), 3), "phases": phases(o, nb_o)}
 
     if rank == 0:
         roof = cpu = None
@@ -343,21 +393,22 @@ def gpu_arm(args):
                 cpu = cpu_port_baseline()
             except Exception as e:  # the CPU figure is a reported baseline only
                 cpu = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {e}"}
-        value = tokens_per_step * world * args.steps / (ms_dev / 1e3)
-        e2e = tokens_per_step * world * args.steps / (ms_e2e / 1e3)
-        dec_bytes = 1235746816 + 16 * 1088 * BATCH * (PREFILL + NEW / 2)
-        line = {"metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "s8", "data": "synthetic", "config": workload_config(),
+        r = main_r
+        e2e = r["units"] * args.steps / (r["ms_e2e"] / 1e3)
+        nb = BATCH if use_tp else BATCH * world
+        line = {"metric": METRIC, "value": round(r["value"], 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(r["ms_dev"] / args.steps, 3), "higher_is_better": True,
+                "scaling": "strong" if use_tp else "weak",
+                "vs_baseline": None, "dtype": "s8", "data": "synthetic", "config": workload_config(world, args.parallel),
                 "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": BATCH * PREFILL * 4,
-                        "d2h_bytes_per_step": BATCH * NEW * 4, "ms_per_step": round(ms_e2e / args.steps, 3)},
-                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
-                "phases": {"prefill_ms": round(t_pre, 3), "prefill_tokens_per_s": round(BATCH * PREFILL / t_pre * 1e3, 1),
-                           "prefill_tops": round(6.60e13 / t_pre / 1e9, 1), "decode_ms_per_step": round(t_dec / (NEW - 1), 4),
-                           "decode_tokens_per_s": round(BATCH * (NEW - 1) / t_dec * 1e3, 1),
-                           "decode_hbm_frac_of_measured": round(dec_bytes / (t_dec / (NEW - 1) / 1e3) / 1e9 / (peaks.get("hbm_gbs") or 6650.0), 4)}}
+                        "d2h_bytes_per_step": BATCH * NEW * 4, "ms_per_step": round(r["ms_e2e"] / args.steps, 3)},
+                "gpu_launches": int(r["launches"]), "clocks": r["clocks"], "roofline": roof, "cpu_baseline": cpu,
+                "phases": phases(r, nb)}
+        if other is not None:
+            line["other_partition"] = other
         print(json.dumps(line))
-    m.close()
+    if tp_comm[0] is not None:
+        tp_comm[0].close()
     if multi:
         dist.barrier()
         dist.destroy_process_group()
@@ -370,6 +421,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     # profiling aids (the headline workload is the default): shorter decode / skip the side measurements
+    ap.add_argument("--parallel", default="dp", choices=["tp", "dp"],
+                    help="N > 1: headline partition - independent batch-parallel replicas (default) or tensor parallel over "
+                         "the N GPUs with a fixed total batch; the other one is reported under other_partition")
     ap.add_argument("--decode-len", type=int, default=NEW)
     ap.add_argument("--no-extras", action="store_true", help="skip roofline kernel timing and the CPU baseline")
     ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, gemm_prefill, "
