@@ -14,11 +14,15 @@
 //
 // The reference quantises the FINAL normalised P and accumulates a whole row of P.V in one int32,
 // so a rescaling online softmax cannot reproduce it. The kernel therefore sweeps the keys three
-// times, recomputing the cheap Q.K^T tiles (head_dim 64) instead of materialising S x S scores:
-//   sweep 0: row max           sweep 1: exp + ordered partial sums           sweep 2: U and P.V
+// times instead of materialising S x S scores in one pass:
+//   sweep 0: Q.K^T tile -> row max
+//   sweep 1: Q.K^T tile again -> e = exp(x - max), ordered partial sums; e is parked in a global
+//            scratch (128 x 64 fp32 per tile, written and read back by the same thread, L2-resident)
+//   sweep 2: e read back -> U (u8, 64-byte-swizzled shared memory) -> O += U.V
 // One thread owns one query row (TMEM lane), so every per-row fp32 chain runs in the reference's
-// order. One CTA = 128 queries of one (batch, query head); 4 softmax warps + TMA warp + MMA warp;
-// TMEM: S (128 columns) + O (64 columns); two CTAs per SM overlap each other's MMA and softmax.
+// order. One CTA = 128 queries of one (batch, query head) against 64-key tiles; 4 softmax warps +
+// TMA warp + MMA warp; TMEM: S (64 columns) + O (64 columns) = 128 columns, so four CTAs share an SM
+// and their 16 softmax warps hide each other's latencies.
 #include "common.cuh"
 #include "tc_common.cuh"
 
