@@ -1,0 +1,281 @@
+// Device code shared by the decode attention kernel and the persistent decode-step kernel: the
+// paged KV-cache view and the fused per-(sequence, KV head) attention step.
+#pragma once
+#include "common.cuh"
+
+// Paged int8 KV cache, all layers (layout at the top of attention_decode.cu).
+struct flexllm_kv_cache {
+    int layers, n_pages, hkv, page;
+    int8_t* k; float* ks; int8_t* v; float* vs;   // [layers][...]
+    size_t page_bytes, scale_bytes;               // per layer
+};
+
+namespace flexllm {
+
+// d = c + sum_i a.u8[i] * b.s8[i]
+__device__ __forceinline__ int dp4a_u8s8(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+constexpr int PAGE = 64;
+constexpr int KEYS_PER_CTA = 512;   // 8 pages per CTA in the score and P.V kernels
+
+struct KvLayer { int8_t* k; float* ks; int8_t* v; float* vs; };
+
+
+// Inputs of the new token, one of three forms (MODE): 0 = int8 heads with per-head scales,
+// 1 = one fp32 row [(HQ + 2 HKV) * 64] per sequence, 2 = the int32 split-K partial sums of the fused q|k|v
+// projection with the per-token and per-channel scales (summed and dequantised here).
+struct DecAttnIn {
+    const int8_t *q, *k, *v; const float *qs, *ks, *vs;
+    const float* qkv_f32;
+    const int32_t* qkv_acc; const float* tok_scale; const float* ch_scale;
+    int n_slabs; long slab_stride;     // MODE 2: split-K partial sums, slab s at qkv_acc + s * slab_stride
+};
+
+// Small per-call shared-memory state of dec_attn_fused_body (one per group of threads that runs it).
+struct DecAttnSmem {
+    __align__(16) int8_t q_sm[4][64];
+    float q_scale[4], red[4][16], row_max[4], row_rinv[4], part[4][4];
+    int pt_sm[160];
+};
+
+// One call by a group of NT threads per (sequence b, KV head hkv) does the whole step for its GQA group of 4 query
+// heads: Q/K/V preparation and cache append, scores, max, exp, the ordered partial sums, the u8
+// quantiser and P.V, with the score row kept in shared memory (`dsm`: 20 bytes per key, at least
+// 4096 bytes). The group's NT threads (256 or 512; `tid` = index in the group) synchronise on named
+// barrier `bar`.
+template <int MODE, int NT>
+__device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const float* __restrict__ cos_t,
+                                                    const float* __restrict__ sin_t, const float* __restrict__ a_s,
+                                                    const KvLayer& cache, const int32_t* __restrict__ page_table, int max_pages,
+                                                    const int32_t* __restrict__ ctx, int HQ, int HKV, int cs,
+                                                    float* __restrict__ out, int32_t* __restrict__ oacc,
+                                                    const int hkv, const int b, uint8_t* dsm, DecAttnSmem& sm, const int tid,
+                                                    const int bar) {
+    constexpr int G = 4;
+    float* sc = reinterpret_cast<float*>(dsm);                       // [G][cs]
+    uint8_t* u_sm = dsm + (size_t)G * cs * 4;                        // [G][cs]
+    int8_t (*q_sm)[64] = sm.q_sm;
+    float* q_scale = sm.q_scale; float (*red)[16] = sm.red; float* row_max = sm.row_max; float* row_rinv = sm.row_rinv;
+    float (*part)[4] = sm.part;
+    int* pt_sm = sm.pt_sm;                                            // this sequence's page-table row
+    named_sync_id<NT>(bar);   // a CTA may run several (sequence, head) items back to back
+    const int w = tid >> 5, lane = tid & 31;
+    const int pos = ctx[b];
+    const int nk = pos + 1;
+    const int heads = HQ + 2 * HKV;
+    const int npages_all = (nk + PAGE - 1) / PAGE;
+    const bool pt_cached = npages_all <= 160;
+    if (pt_cached)
+        for (int i = tid; i < npages_all; i += NT) pt_sm[i] = page_table[(long)b * max_pages + i];
+    // warm L2 with this head's V pages while the scores are computed (V is first needed in step G)
+    for (int i = tid; i < npages_all * 32; i += NT) {
+        const long pg = page_table[(long)b * max_pages + (i >> 5)];
+        const int8_t* line = cache.v + (pg * HKV + hkv) * (long)(64 * PAGE) + (long)(i & 31) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+    }
+
+    // ---- A. prepare: warps 0..3 the query heads, warp 4 the key head, warp 5 the value head
+    if (w < 6) {
+        const long pg = page_table[(long)b * max_pages + pos / PAGE];
+        const int slot = pos % PAGE;
+        const int h = w < 4 ? hkv * G + w : (w == 4 ? HQ + hkv : HQ + HKV + hkv);   // index in the fused row
+        float x0, x1;
+        if (MODE == 2) {
+            // int32 partial sums of the fused q|k|v projection (one slab per K split): add them up
+            // (integers: exact in any order) and dequantise here
+            const int32_t* src = in.qkv_acc + (long)b * heads * 64 + (long)h * 64;
+            const float st = __ldcg(in.tok_scale + b);
+            int a0 = 0, a1 = 0;
+            for (int sl = 0; sl < in.n_slabs; sl++) {
+                a0 += __ldcg(src + sl * in.slab_stride + lane);
+                a1 += __ldcg(src + sl * in.slab_stride + lane + 32);
+            }
+            x0 = ((float)a0 * st) * in.ch_scale[h * 64 + lane];
+            x1 = ((float)a1 * st) * in.ch_scale[h * 64 + lane + 32];
+        } else if (MODE == 1) {
+            const float* src = in.qkv_f32 + (long)b * heads * 64 + (long)h * 64;
+            x0 = src[lane]; x1 = src[lane + 32];
+        } else {
+            const int8_t* src = w < 4 ? in.q + ((long)b * HQ + hkv * G + w) * 64 : (w == 4 ? in.k : in.v) + ((long)b * HKV + hkv) * 64;
+            const float sc_in = w < 4 ? in.qs[(long)b * HQ + hkv * G + w] : (w == 4 ? in.ks : in.vs)[(long)b * HKV + hkv];
+            x0 = (float)src[lane]; x1 = (float)src[lane + 32];
+            if (w < 5) { x0 = x0 * sc_in; x1 = x1 * sc_in; }
+            if (w == 5) {   // int8 value head: plain copy
+                int8_t* dst = cache.v + (pg * HKV + hkv) * (long)(64 * PAGE);
+                dst[(long)lane * PAGE + slot] = src[lane];
+                dst[(long)(lane + 32) * PAGE + slot] = src[lane + 32];
+                if (lane == 0) cache.vs[(pg * HKV + hkv) * PAGE + slot] = sc_in;
+            }
+        }
+        if (MODE != 0 || w < 5) {
+            float a = x0, bb = x1;
+            if (w < 5) {
+                const float c = cos_t[(long)pos * 32 + lane], sn = sin_t[(long)pos * 32 + lane];
+                a = x0 * c - x1 * sn;
+                bb = x0 * sn + x1 * c;
+                auto lane_stage = [&](int bit) {
+                    float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
+                    float pb = __shfl_xor_sync(0xffffffffu, bb, 1 << bit);
+                    if (lane & (1 << bit)) { a = pa - a; bb = pb - bb; }
+                    else { a = a + pa; bb = bb + pb; }
+                };
+                lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
+                { float lo = a, hi = bb; a = lo + hi; bb = lo - hi; }
+                lane_stage(0);
+                a = a / 8.0f;
+                bb = bb / 8.0f;
+            }
+            const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
+            const float s2 = sym_scale_from(mx, mn);
+            const int8_t qa = quant_s8(a, s2), qb = quant_s8(bb, s2);
+            if (w < 4) {
+                q_sm[w][lane] = qa; q_sm[w][lane + 32] = qb;
+                if (lane == 0) q_scale[w] = s2;
+            } else if (w == 4) {
+                int8_t* dst = cache.k + ((pg * HKV + hkv) * PAGE + slot) * 64L;
+                dst[lane] = qa; dst[lane + 32] = qb;
+                if (lane == 0) cache.ks[(pg * HKV + hkv) * PAGE + slot] = s2;
+            } else {
+                int8_t* dst = cache.v + (pg * HKV + hkv) * (long)(64 * PAGE);
+                dst[(long)lane * PAGE + slot] = qa;
+                dst[(long)(lane + 32) * PAGE + slot] = qb;
+                if (lane == 0) cache.vs[(pg * HKV + hkv) * PAGE + slot] = s2;
+            }
+        }
+    }
+    named_sync_id<NT>(bar);
+
+    // ---- B. scores: four lanes share one key (16 bytes of its row each), NT/4 keys per iteration
+    const int l4 = tid & 3, slot = tid >> 2;
+    int qreg[G][4];
+    float qsc[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) qreg[g][i] = reinterpret_cast<const int*>(q_sm[g])[l4 * 4 + i];
+        qsc[g] = q_scale[g];
+    }
+    float mymax = -1e32f;                      // lane l4 tracks the maximum of head g = l4
+#pragma unroll 8
+    for (int key0 = 0; key0 < nk; key0 += NT / 4) {
+        const int key = key0 + slot;
+        const bool valid = key < nk;
+        const int kk = valid ? key : nk - 1;
+        const long pg = pt_cached ? pt_sm[kk / PAGE] : page_table[(long)b * max_pages + kk / PAGE];
+        const long row = (pg * HKV + hkv) * PAGE + (kk % PAGE);
+        const int4 kv4 = *reinterpret_cast<const int4*>(cache.k + row * 64 + l4 * 16);
+        const float ksc = cache.ks[row];
+        float xg = 0.0f;
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            int acc = __dp4a(qreg[g][0], kv4.x, 0);
+            acc = __dp4a(qreg[g][1], kv4.y, acc); acc = __dp4a(qreg[g][2], kv4.z, acc); acc = __dp4a(qreg[g][3], kv4.w, acc);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            const float x = (((float)acc * qsc[g]) * ksc) * 0.125f;
+            if (g == l4) xg = x;
+        }
+        if (valid) {
+            sc[l4 * cs + key] = xg;
+            mymax = xg > mymax ? xg : mymax;
+        }
+    }
+    // maximum over the lanes with the same l4 (xor 4, 8, 16), then over the warps
+    mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 4));
+    mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 8));
+    mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 16));
+    if (lane < 4) red[lane][w] = mymax;
+    named_sync_id<NT>(bar);
+    if (tid < G) {
+        float m = red[tid][0];
+        for (int i = 1; i < NT / 32; i++) m = fmaxf(m, red[tid][i]);
+        row_max[tid] = m;
+    }
+    named_sync_id<NT>(bar);
+    // ---- D. e = exp(x - max), in place
+    for (int g = 0; g < G; g++) {
+        const float m = row_max[g];
+        for (int key = tid; key < nk; key += NT) sc[g * cs + key] = ref_expf(sc[g * cs + key] - m);
+    }
+    named_sync_id<NT>(bar);
+    // ---- E. the four ordered chains of each row (Softmax.h:514-553): one thread per chain
+    if (tid < 4 * G) {
+        const int g = tid >> 2, j = tid & 3;
+        const float* e = sc + g * cs;
+        float ps = 0.0f;
+#pragma unroll 8
+        for (int i = j; i < nk; i += 4) ps += e[i];
+        part[g][j] = ps;
+    }
+    named_sync_id<NT>(bar);
+    if (tid < G) row_rinv[tid] = 1.0f / ((part[tid][0] + part[tid][1]) + (part[tid][2] + part[tid][3]));
+    named_sync_id<NT>(bar);
+    // ---- F. u8 probabilities (zero beyond the last key up to the page boundary)
+    const int nk_pad = (nk + PAGE - 1) / PAGE * PAGE;
+    for (int key = tid; key < nk_pad; key += NT) {
+        float vsc = 0.0f;
+        if (key < nk) {
+            const long pg = pt_cached ? pt_sm[key / PAGE] : page_table[(long)b * max_pages + key / PAGE];
+            vsc = cache.vs[(pg * HKV + hkv) * PAGE + (key % PAGE)];
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            uint8_t u = 0;
+            if (key < nk) {
+                const float p = sc[g * cs + key] * row_rinv[g];
+                const float tt = (p * vsc) / a_s[hkv * G + g];
+                int r = (int)roundf(tt);
+                r = r > 255 ? 255 : r;
+                u = (uint8_t)r;
+            }
+            u_sm[g * cs + key] = u;
+        }
+    }
+    named_sync_id<NT>(bar);
+    // ---- G. P.V: four lanes share one V^T row (16 keys of the page each); thread = (page slot, d, quarter)
+    {
+        const int d = (tid >> 2) & 63, ps = tid >> 8;     // ps: which of the NT/256 pages of an iteration
+        int acc[G] = {0, 0, 0, 0};
+        const int npages = nk_pad / PAGE;
+#pragma unroll 8
+        for (int p = ps; p < npages; p += NT / 256) {
+            const long pg = pt_cached ? pt_sm[p] : page_table[(long)b * max_pages + p];
+            const int4 v4 = *reinterpret_cast<const int4*>(cache.v + ((pg * HKV + hkv) * 64L + d) * PAGE + l4 * 16);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const int4 u4 = *reinterpret_cast<const int4*>(u_sm + g * cs + p * PAGE + l4 * 16);
+                int a = acc[g];
+                a = dp4a_u8s8((unsigned)u4.x, v4.x, a); a = dp4a_u8s8((unsigned)u4.y, v4.y, a);
+                a = dp4a_u8s8((unsigned)u4.z, v4.z, a); a = dp4a_u8s8((unsigned)u4.w, v4.w, a);
+                acc[g] = a;
+            }
+        }
+        int mine = 0;
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            int a = acc[g];
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            if (g == l4) mine = a;
+        }
+        // combine the NT/256 page slots through shared memory (integer adds: exact)
+        int* pv_sm = reinterpret_cast<int*>(sc);          // scores are no longer needed: reuse [NT/256][G][64]
+        named_sync_id<NT>(bar);
+        pv_sm[(ps * G + l4) * 64 + d] = mine;
+        named_sync_id<NT>(bar);
+        if (ps == 0) {
+            int tot = 0;
+            for (int i = 0; i < NT / 256; i++) tot += pv_sm[(i * G + l4) * 64 + d];
+            const int hq = hkv * G + l4;
+            const long o = ((long)b * HQ + hq) * 64 + d;
+            out[o] = (float)tot * a_s[hq];
+            if (oacc) oacc[o] = tot;
+        }
+    }
+}
+
+}  // namespace flexllm

@@ -58,6 +58,19 @@ inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
 
 inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
 
+// bar.sync on a named barrier: the NT threads that call it (all of them must) wait for each other.
+// BAR = 0 with NT = blockDim synchronises like __syncthreads().
+template <int BAR, int NT> __device__ __forceinline__ void named_sync() {
+    // the non-aligned form: lanes of a warp may arrive separately (one lane of a warp can be busy
+    // issuing TMA or MMA work while the others already wait)
+    asm volatile("barrier.sync %0, %1;" ::"n"(BAR), "n"(NT) : "memory");
+}
+
+// the barrier number chosen at run time
+template <int NT> __device__ __forceinline__ void named_sync_id(int bar) {
+    asm volatile("barrier.sync %0, %1;" ::"r"(bar), "n"(NT) : "memory");
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -77,6 +90,22 @@ __device__ __forceinline__ void block_max_min(float& mx, float& mn, float* red) 
     __syncthreads();
     if (l == 0) { red[w] = mx; red[32 + w] = mn; }
     __syncthreads();
+    float a = (l < nw) ? red[l] : -1e32f;
+    float b = (l < nw) ? red[32 + l] : 1e32f;
+    mx = warp_max(a);
+    mn = warp_min(b);
+}
+
+// Same for a group of NT threads (thread index `tid` within the group) that synchronises on named
+// barrier BAR, so that other warps of the CTA need not take part.
+template <int BAR, int NT> __device__ __forceinline__ void group_max_min(float& mx, float& mn, float* red, int tid) {
+    mx = warp_max(mx);
+    mn = warp_min(mn);
+    const int w = tid >> 5, l = tid & 31;
+    constexpr int nw = NT / 32;
+    named_sync<BAR, NT>();
+    if (l == 0) { red[w] = mx; red[32 + w] = mn; }
+    named_sync<BAR, NT>();
     float a = (l < nw) ? red[l] : -1e32f;
     float b = (l < nw) ? red[32 + l] : 1e32f;
     mx = warp_max(a);

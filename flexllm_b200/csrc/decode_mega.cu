@@ -1,0 +1,755 @@
+// One decode step of the whole model as ONE persistent kernel.
+//
+// At batch <= 64 every kernel of a decode step is latency-bound (a 4 MB projection streams in under
+// a microsecond; its launch, prologue, split-K hand-off and tail cost ten times that), and a step
+// is a chain of ~150 such kernels. Here one cooperative grid of one CTA per SM walks the same
+// operator order (SpinQuant_Llama_32_1B/SpinQuant_Decoding_mem_opt.h:1050-1126) phase by phase
+// with a grid-wide barrier (one atomic arrive + one polled load, about a microsecond) between
+// phases instead of a kernel boundary:
+//
+//   per layer   A  x += dequant(down partial sums) [embedding for layer 0], RMSNorm, int8 quant
+//               .  fused q|k|v projection          (tcgen05 kind::i8, split-K over the CTAs)
+//               .  attention per (sequence, KV head): dequant, RoPE, FHT-64, quant, cache append,
+//                  scores, ordered softmax, u8 quant, P.V
+//               B  int8 quant of the attention output rows
+//               .  o projection
+//               C  x += dequant(o partial sums), RMSNorm, int8 quant
+//               .  fused gate|up projection
+//               D  dequant, silu(gate)*up, FHT-8192, int8 quant
+//               .  down projection
+//   head        E  x += dequant(down partial sums), final RMSNorm, quant;  lm_head;  greedy argmax,
+//                  token feedback, context lengths + 1
+//
+// Projections leave raw int32 sums (split-K: one slab of partial sums per split, plain coalesced
+// stores; the reader adds the slabs -- integers, exact in any order); the row phase that follows
+// applies ((float)acc * s_tok) * s_ch itself, so a
+// projection's result crosses HBM/L2 once. One thread issues both the TMA loads and the MMAs: as
+// soon as it has issued the last MMA of one projection it starts streaming the WEIGHT tiles of the
+// next one into the ring -- weights do not depend on the phases in between -- and only the small
+// activation tiles wait for the grid barrier. Arithmetic is the same device code the stand-alone
+// kernels use (attention_decode.cuh, fht_core.cuh, rmsnorm_core.cuh), hence bit-identical.
+//
+// Every wait (mbarrier, grid barrier) is bounded; on a timeout the CTA raises the global error
+// flag, all CTAs leave through the tear-down and the host sees FLEXLLM_ETIMEDOUT.
+#include <cstdio>
+#include <string>
+#include <cstdlib>
+#include <new>
+#include <vector>
+
+#include "attention_decode.cuh"
+#include "common.cuh"
+#include "fht_core.cuh"
+#include "rmsnorm_core.cuh"
+#include "tc_common.cuh"
+
+namespace flexllm {
+using namespace tc;
+
+
+constexpr int MG_WORKERS = 512;                 // 16 warps; in a projection phase warps 0..3 run the epilogue and one
+                                                // thread of warp 5 issues the TMA loads and the MMAs
+constexpr int MG_THREADS = MG_WORKERS;
+constexpr int MG_MAX_STAGES = 8;
+constexpr int MG_BAR_WORK = 1;                  // named barrier of the 512 workers
+constexpr int MG_BAR_FHT = 2;                   // named barrier of the 256 FHT threads
+constexpr int MG_BAR_HALF0 = 3, MG_BAR_HALF1 = 4;  // named barriers of the two 256-thread halves (attention)
+constexpr int MG_MAX_KS = 10;                   // most split-K slabs a projection may use
+constexpr int MG_A_TILE = 128 * 128;            // weight tile: 128 channels x 128 bytes of K
+constexpr int MG_PHASES_PER_LAYER = 9;
+constexpr int MG_FHT_SCRATCH = (8192 + 256 + 80) * 4;   // padded row + reduction slots
+
+struct MegaLayer {
+    const float *sqkv, *so, *sgu, *sd, *g0, *g1, *a_s;
+    KvLayer kv;
+};
+
+struct MegaArgs {
+    const CUtensorMap* maps;      // [0] activations xq [BN][D], [1] activations hq [BN][F], [2 + 4l + j] layer weights, [2 + 4L] lm_head
+    const MegaLayer* layers;
+    int n_layers, B, D, HQ, HKV, F, V;
+    float eps, fht_scale;
+    float* x; int8_t* xq; float* xs; int8_t* hq; float* att; float* logits;
+    int32_t *w_qkv, *w_o, *w_gu, *w_d;
+    const int8_t* lm_w; const float* lm_s; const float* g_final;
+    const float *cos_t, *sin_t;
+    const int32_t* page_table; int max_pages;
+    int32_t *ctx, *next, *out_tokens, *state;
+    unsigned long long* sync_ctr; int* error_flag;
+    unsigned long long* trace;    // optional phase timeline [barrier][arrive, leave][CTA] in globaltimer ns (last launch)
+    int stages, cs, scratch_bytes;
+    int attn_bytes;               // per-half attention scratch: score rows (20 bytes per key) + DecAttnSmem
+    int ks_qkv, ks_o, ks_d;       // split-K factors (gate|up and lm_head have enough tiles: 1)
+    int slab_rows;                // rows (tokens) per split-K slab = max batch
+};
+
+// One projection as the producer, the MMA issuer and the epilogue see it.
+struct MegaJob {
+    const CUtensorMap *tmA, *tmB;
+    int N, tilesA, ksplit, num_kb, ldo;
+    int32_t* out;                 // int32 sums; nullptr for the lm_head (fp32 logits)
+};
+
+__device__ __forceinline__ MegaJob mega_job(const MegaArgs& a, int layer, int kind) {
+    MegaJob j;
+    const int QKV = (a.HQ + 2 * a.HKV) * 64;
+    j.tmB = a.maps + (kind == 3 ? 1 : 0);
+    if (kind == 4) {   // lm_head
+        j.tmA = a.maps + 2 + 4 * a.n_layers;
+        j.N = a.V; j.ksplit = 1; j.num_kb = a.D >> 7; j.out = nullptr; j.ldo = a.V;
+    } else {
+        j.tmA = a.maps + 2 + 4 * layer + kind;
+        if (kind == 0) { j.N = QKV; j.ksplit = a.ks_qkv; j.num_kb = a.D >> 7; j.out = a.w_qkv; }
+        else if (kind == 1) { j.N = a.D; j.ksplit = a.ks_o; j.num_kb = a.D >> 7; j.out = a.w_o; }
+        else if (kind == 2) { j.N = 2 * a.F; j.ksplit = 1; j.num_kb = a.D >> 7; j.out = a.w_gu; }
+        else { j.N = a.D; j.ksplit = a.ks_d; j.num_kb = a.F >> 7; j.out = a.w_d; }
+        j.ldo = j.N;
+    }
+    j.tilesA = (j.N + 127) >> 7;
+    return j;
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_volatile_s32(const int* p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Polls the grid-barrier counter until it reaches `target`. Bounded: gives up after the wait
+// limit, or as soon as this CTA (shared flag) or any CTA (global flag) has given up.
+__device__ __noinline__ bool mega_wait_counter(const unsigned long long* ctr, unsigned long long target, volatile int* abort_flag,
+                                               int* error_flag) {
+    if (ld_acquire_u64(ctr) >= target) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    for (uint32_t it = 1;; it++) {
+        if (ld_acquire_u64(ctr) >= target) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (ld_volatile_s32(error_flag)) { *abort_flag = 1; return false; }
+            if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
+        }
+    }
+}
+
+// Grid-wide barrier of the worker threads: everything the CTA wrote before it is visible to every
+// CTA after it. Returns false when the step is being abandoned.
+__device__ __forceinline__ bool mega_grid_sync(unsigned long long* ctr, unsigned long long target, volatile int* abort_flag,
+                                               volatile int* go_flag, int* error_flag, unsigned long long* trace) {
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (trace) trace[blockIdx.x] = globaltimer_ns();
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(ctr), "l"(1ull) : "memory");
+        mega_wait_counter(ctr, target, abort_flag, error_flag);
+        if (trace) trace[gridDim.x + blockIdx.x] = globaltimer_ns();
+        __threadfence();
+        *go_flag = (*abort_flag == 0);      // one verdict for the whole CTA, fixed before anyone reads it
+    }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    return *go_flag != 0;
+}
+
+// ---- row phases (all 512 threads of the CTA that owns the row; one float4 per thread) -------------
+// x[row] (+)= dequantised projection sums (or the embedding row), then RMSNorm in the reference's
+// decode summation order (Modules/LayerNorm.h:210-370: 8 chunks of 4 interleaved chains; the same
+// statements as rmsnorm_decode_row, with the row spread over the CTA instead of one warp) and the
+// per-token quantiser. acc: `ks` slabs [max_batch][D] of split-K partial sums (integer adds: exact in
+// any order), nullptr for the embedding. buf: D + 32 floats, red: 65 floats of shared memory.
+__device__ __forceinline__ void mega_row_norm(const MegaArgs& a, int row, const int32_t* acc, int ks, const float* s_ch,
+                                              const float* gamma, float* buf, float* red, int tid) {
+    constexpr int NT = MG_WORKERS, LANES = 8;
+    const int D = a.D, nv = D >> 2, C = D / LANES;
+    const int lane = tid & 31, c = tid;
+    const bool active = c < nv;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f), g = v;
+    float4* xr = reinterpret_cast<float4*>(a.x + (long)row * D);
+    if (active) {
+        g = __ldg(reinterpret_cast<const float4*>(gamma) + c);
+        if (acc == nullptr) {
+            const int id = a.next[row];
+            const float s = a.lm_s[id];
+            const char4 t = reinterpret_cast<const char4*>(a.lm_w + (long)id * D)[c];
+            v = make_float4((float)t.x * s, (float)t.y * s, (float)t.z * s, (float)t.w * s);
+        } else {
+            const float st = __ldcg(a.xs + row);
+            const int4* ar = reinterpret_cast<const int4*>(acc + (long)row * D) + c;
+            const long slab4 = (long)a.slab_rows * D / 4;
+            int4 part[MG_MAX_KS];
+#pragma unroll
+            for (int s = 0; s < MG_MAX_KS; s++)
+                if (s < ks) part[s] = __ldcg(ar + s * slab4);
+            v = __ldcg(xr + c);
+            const float4 sc = __ldg(reinterpret_cast<const float4*>(s_ch) + c);
+            int4 sum = make_int4(0, 0, 0, 0);
+#pragma unroll
+            for (int s = 0; s < MG_MAX_KS; s++)
+                if (s < ks) { sum.x += part[s].x; sum.y += part[s].y; sum.z += part[s].z; sum.w += part[s].w; }
+            float4 r;
+            r.x = ((float)sum.x * st) * sc.x; r.y = ((float)sum.y * st) * sc.y;
+            r.z = ((float)sum.z * st) * sc.z; r.w = ((float)sum.w * st) * sc.w;
+            v.x = v.x + r.x; v.y = v.y + r.y; v.z = v.z + r.z; v.w = v.w + r.w;
+        }
+        xr[c] = v;
+        const int e = c * 4;
+        *reinterpret_cast<float4*>(buf + e + 4 * (e / C)) = v;      // element e at e + 4*(e / C)
+    }
+    named_sync<MG_BAR_WORK, NT>();
+    if (tid < 32) {
+        const int chunk = lane >> 2, j = lane & 3;
+        float ss = 0.0f;
+        {
+            const float* bc = buf + chunk * (C + 4);
+            const int n = C >> 2;
+#pragma unroll 8
+            for (int k = 0; k < n; k++) { const float t = bc[4 * k + j]; ss += t * t; }
+        }
+        float tot = 0.0f;
+        for (int cc = 0; cc < LANES; cc++) {
+            const float p0 = __shfl_sync(0xffffffffu, ss, cc * 4 + 0), p1 = __shfl_sync(0xffffffffu, ss, cc * 4 + 1);
+            const float p2 = __shfl_sync(0xffffffffu, ss, cc * 4 + 2), p3 = __shfl_sync(0xffffffffu, ss, cc * 4 + 3);
+            tot += (p0 + p1) + (p2 + p3);
+        }
+        if (lane == 0) red[64] = 1.0f / sqrtf(tot / (float)D + a.eps);
+    }
+    named_sync<MG_BAR_WORK, NT>();
+    const float r = red[64];
+    float mx = -1e32f, mn = 1e32f;
+    if (active) {
+        float4 o;
+        o.x = (v.x * r) * g.x; o.y = (v.y * r) * g.y; o.z = (v.z * r) * g.z; o.w = (v.w * r) * g.w;
+        v = o;
+        mx = fmaxf(fmaxf(o.x, o.y), fmaxf(o.z, o.w));
+        mn = fminf(fminf(o.x, o.y), fminf(o.z, o.w));
+    }
+    group_max_min<MG_BAR_WORK, NT>(mx, mn, red, tid);
+    const float sc = sym_scale_from(mx, mn);
+    if (tid == 0) a.xs[row] = sc;
+    if (active) {
+        char4 o;
+        o.x = quant_s8(v.x, sc); o.y = quant_s8(v.y, sc); o.z = quant_s8(v.z, sc); o.w = quant_s8(v.w, sc);
+        reinterpret_cast<char4*>(a.xq + (long)row * D)[c] = o;
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // xq is read by other CTAs' TMA (async proxy)
+    }
+}
+
+// int8 quantiser of one attention output row (Modules/quant.h:349-430)
+__device__ __forceinline__ void mega_row_quant(const MegaArgs& a, int row, float* red, int tid) {
+    constexpr int NT = MG_WORKERS;
+    const int D = a.D, nv = D >> 2, c = tid;
+    const bool active = c < nv;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    float mx = -1e32f, mn = 1e32f;
+    if (active) {
+        v = __ldcg(reinterpret_cast<const float4*>(a.att + (long)row * D) + c);
+        mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+        mn = fminf(fminf(v.x, v.y), fminf(v.z, v.w));
+    }
+    group_max_min<MG_BAR_WORK, NT>(mx, mn, red, tid);
+    const float sc = sym_scale_from(mx, mn);
+    if (tid == 0) a.xs[row] = sc;
+    if (active) {
+        char4 o;
+        o.x = quant_s8(v.x, sc); o.y = quant_s8(v.y, sc); o.z = quant_s8(v.z, sc); o.w = quant_s8(v.w, sc);
+        reinterpret_cast<char4*>(a.xq + (long)row * D)[c] = o;
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // xq is read by other CTAs' TMA (async proxy)
+    }
+}
+
+// dequant(gate|up sums) -> silu(gate)*up -> FHT-8192 / scale -> int8 quant. All 512 threads fetch and
+// activate the row (every load of a thread in flight at once), threads 0..255 run the butterflies.
+__device__ __forceinline__ void mega_row_fht(const MegaArgs& a, const MegaLayer& L, int row, float* buf, float* red, int tid) {
+    constexpr int N = 8192;
+    const float st = __ldcg(a.xs + row);
+    const int4* gr = reinterpret_cast<const int4*>(a.w_gu + (long)row * 2 * N);
+    const int4* ur = gr + N / 4;
+    const float4* sg = reinterpret_cast<const float4*>(L.sgu);
+    const float4* su = sg + N / 4;
+    {
+        int4 ga[4], ua[4];
+        float4 s1[4], s2[4];
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int c = it * MG_WORKERS + tid;
+            ga[it] = __ldcg(gr + c); ua[it] = __ldcg(ur + c); s1[it] = __ldg(sg + c); s2[it] = __ldg(su + c);
+        }
+#pragma unroll 1
+        for (int it = 0; it < 4; it++) {
+            const int c = it * MG_WORKERS + tid;
+            // (rolled loop: pick this iteration's registers without dynamic indexing)
+            const int4 g4 = it == 0 ? ga[0] : it == 1 ? ga[1] : it == 2 ? ga[2] : ga[3];
+            const int4 u4 = it == 0 ? ua[0] : it == 1 ? ua[1] : it == 2 ? ua[2] : ua[3];
+            const float4 a1 = it == 0 ? s1[0] : it == 1 ? s1[1] : it == 2 ? s1[2] : s1[3];
+            const float4 a2 = it == 0 ? s2[0] : it == 1 ? s2[1] : it == 2 ? s2[2] : s2[3];
+            float4 g, u, v;
+            g.x = ((float)g4.x * st) * a1.x; g.y = ((float)g4.y * st) * a1.y; g.z = ((float)g4.z * st) * a1.z; g.w = ((float)g4.w * st) * a1.w;
+            u.x = ((float)u4.x * st) * a2.x; u.y = ((float)u4.y * st) * a2.y; u.z = ((float)u4.z * st) * a2.z; u.w = ((float)u4.w * st) * a2.w;
+            v.x = silu_f(g.x) * u.x; v.y = silu_f(g.y) * u.y; v.z = silu_f(g.z) * u.z; v.w = silu_f(g.w) * u.w;
+            const int p = pad32(c * 4);
+            buf[p] = v.x; buf[p + 1] = v.y; buf[p + 2] = v.z; buf[p + 3] = v.w;
+        }
+    }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (tid >= 256) return;
+    float r[32];
+    fht8192_passes<MG_BAR_FHT>(buf, tid, r);
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int v = 0; v < 32; v++) {
+        r[v] = r[v] / a.fht_scale;
+        mx = fmaxf(mx, r[v]);
+        mn = fminf(mn, r[v]);
+    }
+    group_max_min<MG_BAR_FHT, 256>(mx, mn, red, tid);
+    const float sc = sym_scale_from(mx, mn);
+    if (tid == 0) a.xs[row] = sc;
+#pragma unroll
+    for (int hi = 0; hi < 4; hi++) {
+        union { int8_t b[8]; int2 v; } o;
+#pragma unroll
+        for (int c = 0; c < 8; c++) o.b[c] = quant_s8(r[hi * 8 + c], sc);
+        *reinterpret_cast<int2*>(a.hq + (long)row * N + hi * 2048 + tid * 8) = o.v;
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");   // hq is read by other CTAs' TMA (async proxy)
+}
+
+// greedy token of one row by the 512 workers (ties to the lowest index, Logits.h:13-17), then the
+// step's bookkeeping for that sequence
+__device__ __forceinline__ void mega_row_argmax(const MegaArgs& a, int row, int col, int n_cols, float* sv, int* si) {
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+    const float* l = a.logits + (long)row * a.V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int v = tid; v < a.V; v += MG_WORKERS) {
+        const float t = __ldcg(l + v);
+        if (t > best || bi == 0x7fffffff) { best = t; bi = v; }
+    }
+    auto better = [](float x, int xi, float y, int yi) { return x > y || (x == y && xi < yi); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ob, oi, best, bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (w == 0) {
+        best = lane < MG_WORKERS / 32 ? sv[lane] : -INFINITY;
+        bi = lane < MG_WORKERS / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ob, oi, best, bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) {
+            a.next[row] = bi;
+            if (col < n_cols) a.out_tokens[(long)row * n_cols + col] = bi;
+            a.ctx[row] += 1;
+        }
+    }
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid_constant__ MegaArgs a) {
+    constexpr int STAGE_BYTES = MG_A_TILE + BN * 128;
+    constexpr int TMEM_COLS = 2 * BN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;
+    uint8_t* ring_ptr = smem_raw + (ring - raw);
+    const int STAGES = a.stages;
+    uint8_t* scratch = ring_ptr + (size_t)STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(scratch + a.scratch_bytes);
+    const uint32_t bar_full = smem_u32(bars);
+    const uint32_t bar_empty = bar_full + 8 * MG_MAX_STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * MG_MAX_STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    unsigned long long* base_slot = reinterpret_cast<unsigned long long*>(bars + 2 * MG_MAX_STAGES + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_slot + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* go_flag = abort_flag + 1;
+    __shared__ float arg_v[MG_WORKERS / 32];
+    __shared__ int arg_i[MG_WORKERS / 32];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, G = gridDim.x;
+    const int L = a.n_layers;
+    const int n_barriers = MG_PHASES_PER_LAYER * L + 2;
+    const int col = a.state[0], n_cols = a.state[1];      // read before anyone can reach the last phase
+
+    if (tid == 0) {
+        for (int s = 0; s < MG_MAX_STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(bar_tfull + 8 * s, 1); mbar_init(bar_tempty + 8 * s, 4); }
+        *abort_flag = 0;
+        // every launch adds exactly n_barriers * G arrivals, so the launch's base is the counter rounded
+        // down to a multiple of that (no CTA can be a whole launch ahead of another)
+        const unsigned long long per = (unsigned long long)n_barriers * (unsigned long long)G;
+        *base_slot = ld_acquire_u64(a.sync_ctr) / per * per;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const unsigned long long ctr_base = *base_slot;
+    auto target_of = [&](int barrier_index) { return ctr_base + (unsigned long long)(barrier_index + 1) * (unsigned long long)G; };
+
+    // ---- per-thread pipeline bookkeeping (each role uses its own part; the rest is carried unused)
+    int pstage = 0; uint32_t pphase = 0;         // TMA thread: position in the ring
+    int early_n = 0, early_stage0 = 0;           // TMA thread: weight tiles of the NEXT projection already in flight
+    int cstage = 0; uint32_t cphase = 0;         // MMA thread: position in the ring
+    int item_base = 0;                           // items (tile, split) this CTA has processed so far
+    const bool is_tma = (warp == 4 && lane == 0), is_mma = (warp == 5 && lane == 0);
+
+    // k blocks of this CTA in a projection, in issue order: items t = cta, cta + G, ...; inside an item kb0..kb1-1
+    struct KbIter {
+        int t, kb, kb0, kb1, n_items, ksplit, num_kb, G;
+        __device__ void range() {
+            const int split = t % ksplit;
+            kb0 = kb = (int)((long)split * num_kb / ksplit);
+            kb1 = (int)((long)(split + 1) * num_kb / ksplit);
+        }
+        __device__ void init(const MegaJob& j, int cta, int G_) {
+            n_items = j.tilesA * j.ksplit; ksplit = j.ksplit; num_kb = j.num_kb; G = G_; t = cta; kb = kb0 = kb1 = 0;
+            if (t < n_items) range();
+        }
+        __device__ bool valid() const { return t < n_items; }
+        __device__ void next() { if (++kb == kb1) { t += G; if (t < n_items) range(); } }
+    };
+    // Weight tiles of the first k blocks of projection j, as many as the ring holds: issued before the
+    // phases in between have run (weights do not depend on them). The activation half of each stage
+    // follows at the start of j's own phase; the stage's barrier expects both. TMA thread only.
+    auto prefetch_weights = [&](const MegaJob& j) {
+        KbIter it; it.init(j, cta, G);
+        tma_prefetch_desc(j.tmA);
+        early_n = 0; early_stage0 = pstage;
+        while (early_n < STAGES && it.valid()) {
+            if (!mbar_wait(bar_empty + 8 * pstage, pphase ^ 1u, abort_flag)) return;
+            mbar_expect_tx(bar_full + 8 * pstage, STAGE_BYTES);
+            tma_load_2d(ring + pstage * STAGE_BYTES, j.tmA, bar_full + 8 * pstage, it.kb * 128, (it.t / j.ksplit) * 128);
+            if (++pstage == STAGES) { pstage = 0; pphase ^= 1u; }
+            early_n++;
+            it.next();
+        }
+    };
+    // One projection. Roles: warp 4 lane 0 TMA, warp 5 lane 0 MMA, warps 0..3 epilogue.
+    auto gemm_phase = [&](const MegaJob& j, const MegaJob* next_job) {
+        const int n_items = j.tilesA * j.ksplit;
+        const int n_mine = cta < n_items ? (n_items - cta + G - 1) / G : 0;
+        if (is_tma) {
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            KbIter it; it.init(j, cta, G);
+            // activation halves of the stages whose weights are already on their way
+            int s2 = early_stage0;
+            for (int i = 0; i < early_n; i++) {
+                tma_load_2d(ring + s2 * STAGE_BYTES + MG_A_TILE, j.tmB, bar_full + 8 * s2, it.kb * 128, 0);
+                if (++s2 == STAGES) s2 = 0;
+                it.next();
+            }
+            early_n = 0;
+            bool pok = true;
+            while (it.valid()) {
+                if (!mbar_wait(bar_empty + 8 * pstage, pphase ^ 1u, abort_flag)) { pok = false; break; }
+                const uint32_t full = bar_full + 8 * pstage;
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_2d(ring + pstage * STAGE_BYTES, j.tmA, full, it.kb * 128, (it.t / j.ksplit) * 128);
+                tma_load_2d(ring + pstage * STAGE_BYTES + MG_A_TILE, j.tmB, full, it.kb * 128, 0);
+                if (++pstage == STAGES) { pstage = 0; pphase ^= 1u; }
+                it.next();
+            }
+            if (pok && next_job) prefetch_weights(*next_job);
+        } else if (is_mma) {
+            constexpr uint32_t idesc = umma_idesc_i8(128, BN, 1, 1);
+            KbIter it; it.init(j, cta, G);
+            int i = 0;
+            while (it.valid()) {
+                const int idx = item_base + i, as = idx & 1;
+                if (it.kb == it.kb0) {
+                    if (!mbar_wait(bar_tempty + 8 * as, (uint32_t)((idx >> 1) & 1) ^ 1u, abort_flag)) break;
+                    tc_fence_after();
+                }
+                if (!mbar_wait(bar_full + 8 * cstage, cphase, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + as * BN;
+                const uint32_t sa = ring + cstage * STAGE_BYTES;
+                const uint64_t adesc = umma_desc_k_sw128(sa), bdesc = umma_desc_k_sw128(sa + MG_A_TILE);
+#pragma unroll
+                for (int k = 0; k < 4; k++) umma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (it.kb > it.kb0 || k > 0) ? 1u : 0u);
+                umma_commit(bar_empty + 8 * cstage);
+                if (++cstage == STAGES) { cstage = 0; cphase ^= 1u; }
+                if (it.kb + 1 == it.kb1) { umma_commit(bar_tfull + 8 * as); i++; }
+                it.next();
+            }
+        } else if (warp < 4) {
+            const int q = warp;
+            // per-token scales for the lm_head epilogue: lane holds tokens lane and lane + 32
+            float xs0 = 0.f, xs1 = 0.f;
+            if (j.out == nullptr) {
+                if (lane < a.B) xs0 = __ldcg(a.xs + lane);
+                if (lane + 32 < a.B) xs1 = __ldcg(a.xs + lane + 32);
+            }
+            for (int i = 0; i < n_mine; i++) {
+                const int t = cta + i * G;
+                const int ta = t / j.ksplit, split = t - ta * j.ksplit;
+                const int idx = item_base + i, as = idx & 1;
+                const int rowA = ta * 128 + q * 32 + lane;
+                const bool row_ok = rowA < j.N;
+                const float sa = (j.out == nullptr && row_ok) ? a.lm_s[rowA] : 0.0f;
+                int32_t* slab = j.out ? j.out + (long)split * a.slab_rows * j.ldo : nullptr;   // this split's partial sums
+                int got = (lane == 0) ? (mbar_wait(bar_tfull + 8 * as, (uint32_t)((idx >> 1) & 1), abort_flag) ? 1 : 0) : 1;
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (!got) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < BN / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int jj = 0; jj < 32; jj++) {
+                        const int tok = c * 32 + jj;
+                        const float st = __shfl_sync(0xffffffffu, c == 0 ? xs0 : xs1, jj);
+                        if (row_ok && tok < a.B) {
+                            const long o = (long)tok * j.ldo + rowA;
+                            if (slab) slab[o] = (int)v[jj];
+                            else a.logits[o] = ((float)(int)v[jj] * st) * sa;
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * as);
+            }
+        }
+        item_base += n_mine;
+    };
+
+    if (is_tma) {
+        tma_prefetch_desc(a.maps); tma_prefetch_desc(a.maps + 1);
+        prefetch_weights(mega_job(a, 0, 0));
+    }
+    float* rowbuf = reinterpret_cast<float*>(scratch);
+    float* rowred = rowbuf + 8192 + 256;
+    // ---- the step: phases 9l + k of layer l (k = 0..8), then the head (k = 9, 10, 11); one call site per
+    //      kind of phase keeps the kernel's code small enough to stay in the instruction cache
+    const int n_phases = MG_PHASES_PER_LAYER * L + 3;
+    for (int p = 0; p < n_phases; p++) {
+        int l = p / MG_PHASES_PER_LAYER, k = p - MG_PHASES_PER_LAYER * l;
+        if (l >= L) { k = MG_PHASES_PER_LAYER + (p - MG_PHASES_PER_LAYER * L); l = L - 1; }
+        const MegaLayer& ly = a.layers[l];
+        if (k == 0 || k == 5 || k == 9) {
+            if (cta < a.B) {
+                const int32_t* acc; int ks; const float *s_ch, *gamma;
+                if (k == 5) { acc = a.w_o; ks = a.ks_o; s_ch = ly.so; gamma = ly.g1; }
+                else if (k == 9) { acc = a.w_d; ks = a.ks_d; s_ch = ly.sd; gamma = a.g_final; }
+                else { acc = p == 0 ? nullptr : a.w_d; ks = a.ks_d; s_ch = p == 0 ? nullptr : a.layers[l - 1].sd; gamma = ly.g0; }
+                mega_row_norm(a, cta, acc, ks, s_ch, gamma, rowbuf, rowred, tid);
+            }
+        } else if (k == 2) {
+            DecAttnIn in;
+            in.q = in.k = in.v = nullptr; in.qs = in.ks = in.vs = nullptr; in.qkv_f32 = nullptr;
+            in.qkv_acc = a.w_qkv; in.tok_scale = a.xs; in.ch_scale = ly.sqkv;
+            in.n_slabs = a.ks_qkv; in.slab_stride = (long)a.slab_rows * (a.HQ + 2 * a.HKV) * 64;
+            // two (sequence, KV head) items at a time, one per half of the CTA: an item is a chain of
+            // global-memory round trips, so two chains side by side nearly double the throughput
+            const int half = tid >> 8;
+            uint8_t* dsm = scratch + (size_t)half * a.attn_bytes;
+            DecAttnSmem& sm = *reinterpret_cast<DecAttnSmem*>(dsm + a.attn_bytes - sizeof(DecAttnSmem));
+            for (int idx = 2 * cta + half; idx < a.B * a.HKV; idx += 2 * G)
+                dec_attn_fused_body<2, 256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
+                                            a.att, nullptr, idx % a.HKV, idx / a.HKV, dsm, sm, tid & 255, MG_BAR_HALF0 + half);
+        } else if (k == 3) {
+            if (cta < a.B) mega_row_quant(a, cta, rowred, tid);
+        } else if (k == 7) {
+            if (cta < a.B) mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
+        } else if (k == 11) {
+            if (cta < a.B) mega_row_argmax(a, cta, col, n_cols, arg_v, arg_i);
+            if (cta == 0 && tid == 0) a.state[0] = col + 1;
+        } else {
+            const int kind = k == 1 ? 0 : k == 4 ? 1 : k == 6 ? 2 : k == 8 ? 3 : 4;
+            const MegaJob j = mega_job(a, l, kind);
+            const MegaJob nj = kind < 3 ? mega_job(a, l, kind + 1) : (p + 1 < MG_PHASES_PER_LAYER * L ? mega_job(a, l + 1, 0) : mega_job(a, 0, 4));
+            gemm_phase(j, kind == 4 ? nullptr : &nj);
+        }
+        if (p + 1 < n_phases) {
+            if (!mega_grid_sync(a.sync_ctr, target_of(p), abort_flag, go_flag, a.error_flag,
+                                a.trace ? a.trace + (size_t)p * 2 * G : nullptr))
+                break;
+        }
+    }
+
+    // ---------------------------------------------------------------- tear-down
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: give copies still in flight time to land before shared memory is released
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+        if (tid == 0) atomicExch(a.error_flag, 1);
+        __syncthreads();
+    }
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+}  // namespace flexllm
+
+// ------------------------------------------------------------------------------------------ host
+#include "decode_mega.h"
+
+
+namespace flexllm {
+
+int* device_error_flag();
+int gemm_sm_count();
+
+struct MegaPlan {
+    MegaArgs args;
+    void* dev_maps = nullptr; void* dev_layers = nullptr; void* dev_work = nullptr; void* dev_ctr = nullptr; void* dev_trace = nullptr;
+    size_t trace_bytes = 0;
+    size_t work_bytes = 0;
+    int grid = 0, bn = 0;
+    size_t smem = 0;
+};
+
+void mega_destroy(MegaPlan* p) {
+    if (!p) return;
+    // FLEXLLM_MEGA_TRACE=<file>: the phase timeline of the last step, raw u64 [barrier][arrive, leave][CTA]
+    const char* tf = getenv("FLEXLLM_MEGA_TRACE");
+    if (tf && p->dev_trace) {
+        std::vector<unsigned long long> h(p->trace_bytes / 8);
+        if (cudaMemcpy(h.data(), p->dev_trace, p->trace_bytes, cudaMemcpyDeviceToHost) == cudaSuccess) {
+            if (FILE* f = fopen(tf, "wb")) { fwrite(h.data(), 1, p->trace_bytes, f); fclose(f); }
+        }
+    }
+    cudaFree(p->dev_trace);
+    cudaFree(p->dev_maps); cudaFree(p->dev_layers); cudaFree(p->dev_work); cudaFree(p->dev_ctr);
+    delete p;
+}
+
+int mega_create(const MegaModelView& v, MegaPlan** out) {
+    *out = nullptr;
+    const char* env = getenv("FLEXLLM_MEGA");
+    if (env && atoi(env) == 0) return FLEXLLM_ENOTSUP;
+    const int QKV = (v.HQ + 2 * v.HKV) * 64;
+    if (v.D % 128 || v.D > 2048 || v.F != 8192 || v.HQ != 4 * v.HKV || v.HQ * 64 != v.D || v.max_batch > 64) return FLEXLLM_ENOTSUP;
+    int dev = 0, coop = 0, optin = 0;
+    FLEXLLM_CHECK_CUDA(cudaGetDevice(&dev));
+    FLEXLLM_CHECK_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    FLEXLLM_CHECK_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (!coop) return FLEXLLM_ENOTSUP;
+    const int G = gemm_sm_count();
+    if (v.max_batch > G) return FLEXLLM_ENOTSUP;
+    const int bn = v.max_batch <= 32 ? 32 : 64;
+    const void* kern = bn == 32 ? (const void*)decode_mega_kernel<32> : (const void*)decode_mega_kernel<64>;
+    cudaFuncAttributes fa;
+    FLEXLLM_CHECK_CUDA(cudaFuncGetAttributes(&fa, kern));
+    const int stage_bytes = MG_A_TILE + bn * 128;
+    const int cs = (v.max_ctx + 1 + 63) / 64 * 64;
+    int attn_bytes = (20 * cs < 4096 ? 4096 : 20 * cs) + (int)sizeof(DecAttnSmem);
+    attn_bytes = (attn_bytes + 127) / 128 * 128;
+    int scratch = MG_FHT_SCRATCH;
+    if (2 * attn_bytes > scratch) scratch = 2 * attn_bytes;
+    scratch = (scratch + 127) / 128 * 128;
+    const long avail = (long)optin - (long)fa.sharedSizeBytes - 1024 - 256 - scratch;
+    int stages = (int)(avail / stage_bytes);
+    if (stages > MG_MAX_STAGES) stages = MG_MAX_STAGES;
+    if (stages < 3) return FLEXLLM_ENOTSUP;      // long contexts: the per-operator kernels take over
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + scratch + 256;
+    FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int per_sm = 0;
+    FLEXLLM_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MG_THREADS, smem));
+    if (per_sm < 1) return FLEXLLM_ENOTSUP;
+
+    MegaPlan* p = new (std::nothrow) MegaPlan();
+    if (!p) return FLEXLLM_ENOMEM;
+    p->grid = G; p->bn = bn; p->smem = smem;
+    const int n_maps = 2 + 4 * v.layers + 1;
+    std::vector<CUtensorMap> maps(n_maps);
+    std::vector<MegaLayer> layers(v.layers);
+    int rc = make_tmap_2d_u8(&maps[0], v.xq, (uint64_t)v.max_batch, (uint64_t)v.D, bn);
+    if (rc == FLEXLLM_OK) rc = make_tmap_2d_u8(&maps[1], v.hq, (uint64_t)v.max_batch, (uint64_t)v.F, bn);
+    for (int l = 0; rc == FLEXLLM_OK && l < v.layers; l++) {
+        const MegaLayerView& s = v.L[l];
+        rc = make_tmap_2d_u8(&maps[2 + 4 * l + 0], s.wqkv, (uint64_t)QKV, (uint64_t)v.D, 128);
+        if (rc == FLEXLLM_OK) rc = make_tmap_2d_u8(&maps[2 + 4 * l + 1], s.wo, (uint64_t)v.D, (uint64_t)v.D, 128);
+        if (rc == FLEXLLM_OK) rc = make_tmap_2d_u8(&maps[2 + 4 * l + 2], s.wgu, (uint64_t)2 * v.F, (uint64_t)v.D, 128);
+        if (rc == FLEXLLM_OK) rc = make_tmap_2d_u8(&maps[2 + 4 * l + 3], s.wd, (uint64_t)v.D, (uint64_t)v.F, 128);
+        MegaLayer& d = layers[l];
+        d.sqkv = s.sqkv; d.so = s.so; d.sgu = s.sgu; d.sd = s.sd; d.g0 = s.g0; d.g1 = s.g1; d.a_s = s.a_s;
+        d.kv.k = v.cache->k + (size_t)l * v.cache->page_bytes;
+        d.kv.v = v.cache->v + (size_t)l * v.cache->page_bytes;
+        d.kv.ks = v.cache->ks + (size_t)l * (v.cache->scale_bytes / 4);
+        d.kv.vs = v.cache->vs + (size_t)l * (v.cache->scale_bytes / 4);
+    }
+    if (rc == FLEXLLM_OK) rc = make_tmap_2d_u8(&maps[2 + 4 * v.layers], v.lm_w, (uint64_t)v.V, (uint64_t)v.D, 128);
+    if (rc != FLEXLLM_OK) { mega_destroy(p); return rc; }
+
+    auto split = [&](int tiles, int num_kb) { int k = G / tiles; if (k < 1) k = 1; if (k > num_kb) k = num_kb; if (k > MG_MAX_KS) k = MG_MAX_KS; return k; };
+    const int ks_qkv = split((QKV + 127) / 128, v.D / 128), ks_o = split(v.D / 128, v.D / 128), ks_d = split(v.D / 128, v.F / 128);
+    // split-K partial sums: one slab [max_batch][N] per split, written with plain stores and summed by the reader
+    const size_t n_qkv = (size_t)ks_qkv * v.max_batch * QKV, n_o = (size_t)ks_o * v.max_batch * v.D, n_d = (size_t)ks_d * v.max_batch * v.D,
+                 n_gu = (size_t)v.max_batch * 2 * v.F;
+    p->work_bytes = (n_qkv + n_o + n_d + n_gu) * sizeof(int32_t);
+    cudaError_t e = cudaMalloc(&p->dev_maps, n_maps * sizeof(CUtensorMap));
+    if (e == cudaSuccess) e = cudaMalloc(&p->dev_layers, v.layers * sizeof(MegaLayer));
+    if (e == cudaSuccess) e = cudaMalloc(&p->dev_work, p->work_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->dev_ctr, 256);
+    if (e == cudaSuccess) e = cudaMemcpy(p->dev_maps, maps.data(), n_maps * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(p->dev_layers, layers.data(), v.layers * sizeof(MegaLayer), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(p->dev_work, 0, p->work_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->dev_ctr, 0, 256);
+    if (e == cudaSuccess && getenv("FLEXLLM_MEGA_TRACE")) {
+        p->trace_bytes = (size_t)(MG_PHASES_PER_LAYER * v.layers + 2) * 2 * G * sizeof(unsigned long long);
+        e = cudaMalloc(&p->dev_trace, p->trace_bytes);
+        if (e == cudaSuccess) e = cudaMemset(p->dev_trace, 0, p->trace_bytes);
+    }
+    if (e != cudaSuccess) {
+        mega_destroy(p);
+        g_last_cuda_error = (int)e;
+        return e == cudaErrorMemoryAllocation ? FLEXLLM_ENOMEM : FLEXLLM_ECUDA;
+    }
+    MegaArgs& a = p->args;
+    a.maps = (const CUtensorMap*)p->dev_maps; a.layers = (const MegaLayer*)p->dev_layers;
+    a.n_layers = v.layers; a.B = 0; a.D = v.D; a.HQ = v.HQ; a.HKV = v.HKV; a.F = v.F; a.V = v.V;
+    a.eps = v.eps; a.fht_scale = v.fht_scale;
+    a.x = v.x; a.xq = v.xq; a.xs = v.xs; a.hq = v.hq; a.att = v.att; a.logits = v.logits;
+    a.w_qkv = (int32_t*)p->dev_work; a.w_o = a.w_qkv + n_qkv; a.w_d = a.w_o + n_o; a.w_gu = a.w_d + n_d;
+    a.lm_w = v.lm_w; a.lm_s = v.lm_s; a.g_final = v.g_final; a.cos_t = v.cos_t; a.sin_t = v.sin_t;
+    a.page_table = v.page_table; a.max_pages = v.max_pages;
+    a.ctx = v.ctx; a.next = v.next; a.out_tokens = v.out_tokens; a.state = v.state;
+    a.sync_ctr = (unsigned long long*)p->dev_ctr; a.error_flag = device_error_flag();
+    a.trace = (unsigned long long*)p->dev_trace;
+    a.stages = stages; a.cs = cs; a.scratch_bytes = scratch; a.attn_bytes = attn_bytes;
+    a.ks_qkv = ks_qkv; a.ks_o = ks_o; a.ks_d = ks_d; a.slab_rows = v.max_batch;
+    if (!a.error_flag) { mega_destroy(p); return FLEXLLM_ECUDA; }
+    *out = p;
+    return FLEXLLM_OK;
+}
+
+int mega_reset(MegaPlan* p, cudaStream_t st) {
+    FLEXLLM_CHECK_CUDA(cudaMemsetAsync(p->dev_ctr, 0, 256, st));
+    return FLEXLLM_OK;
+}
+
+int mega_launch(MegaPlan* p, int B, cudaStream_t st) {
+    if (B < 1 || B > p->bn) return FLEXLLM_EINVAL;
+    p->args.B = B;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p->grid); cfg.blockDim = dim3(MG_THREADS); cfg.dynamicSmemBytes = p->smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative;     // all CTAs co-resident: the grid barrier cannot starve
+    at[0].val.cooperative = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (p->bn == 32) cudaLaunchKernelEx(&cfg, decode_mega_kernel<32>, p->args);
+    else cudaLaunchKernelEx(&cfg, decode_mega_kernel<64>, p->args);
+    return launch_status();
+}
+
+}  // namespace flexllm

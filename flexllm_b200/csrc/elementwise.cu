@@ -2,6 +2,7 @@
 // static quantisation, RMSNorm(+quant), SiLU, gate, residual, RoPE, softmax, greedy argmax.
 // All are HBM-bound: one pass over the data with 128-bit accesses where the layout allows.
 #include "common.cuh"
+#include "rmsnorm_core.cuh"
 
 namespace flexllm {
 
@@ -183,7 +184,6 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_decode_kernel(const fl
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long row = (long)blockIdx.x * RMS_WARPS + w;
     if (row >= M) return;
-    const int C = D / lanes;                                  // chunk length, a multiple of 4
     const int nv = D >> 2;
     float* buf = rowbuf + (size_t)w * (D + 4 * lanes);
     const float* xr = x + row * D;
@@ -194,56 +194,8 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_decode_kernel(const fl
         const int c = lane + i * 32;
         if (c < nv) { v[i] = reinterpret_cast<const float4*>(xr)[c]; if (KEEP_G) g[i] = reinterpret_cast<const float4*>(gamma)[c]; }
     }
-#pragma unroll
-    for (int i = 0; i < MAXV; i++) {
-        const int c = lane + i * 32;
-        if (c < nv) { const int e = c * 4; *reinterpret_cast<float4*>(buf + e + 4 * (e / C)) = v[i]; }   // element e at e + 4*(e / C)
-    }
-    __syncwarp();
-    const int chunk = lane >> 2, j = lane & 3;
-    float ss = 0.0f;
-    if (chunk < lanes) {
-        const float* bc = buf + chunk * (C + 4);
-        const int n = C >> 2;
-#pragma unroll 8
-        for (int k = 0; k < n; k++) { const float t = bc[4 * k + j]; ss += t * t; }
-    }
-    float tot = 0.0f;
-    for (int c = 0; c < lanes; c++) {
-        const float p0 = __shfl_sync(0xffffffffu, ss, c * 4 + 0), p1 = __shfl_sync(0xffffffffu, ss, c * 4 + 1);
-        const float p2 = __shfl_sync(0xffffffffu, ss, c * 4 + 2), p3 = __shfl_sync(0xffffffffu, ss, c * 4 + 3);
-        tot += (p0 + p1) + (p2 + p3);
-    }
-    const float r = 1.0f / sqrtf(tot / (float)D + eps);
-    float mx = -1e32f, mn = 1e32f;
-#pragma unroll
-    for (int i = 0; i < MAXV; i++) {
-        const int c = lane + i * 32;
-        if (c < nv) {
-            const float4 gg = KEEP_G ? g[KEEP_G ? i : 0] : reinterpret_cast<const float4*>(gamma)[c];
-            float4 o;
-            o.x = (v[i].x * r) * gg.x; o.y = (v[i].y * r) * gg.y; o.z = (v[i].z * r) * gg.z; o.w = (v[i].w * r) * gg.w;
-            v[i] = o;
-            if (y) reinterpret_cast<float4*>(y + row * D)[c] = o;
-            mx = fmaxf(mx, fmaxf(fmaxf(o.x, o.y), fmaxf(o.z, o.w)));
-            mn = fminf(mn, fminf(fminf(o.x, o.y), fminf(o.z, o.w)));
-        }
-    }
-    if (q) {
-        mx = warp_max(mx); mn = warp_min(mn);
-        const float sc = sym_scale_from(mx, mn);
-        if (lane == 0) s[row] = sc;
-        char4* qr = reinterpret_cast<char4*>(q + row * D);
-#pragma unroll
-        for (int i = 0; i < MAXV; i++) {
-            const int c = lane + i * 32;
-            if (c < nv) {
-                char4 o;
-                o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc); o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
-                qr[c] = o;
-            }
-        }
-    }
+    rmsnorm_decode_row<MAXV, KEEP_G>(v, g, gamma, D, eps, lanes, buf, lane, y ? y + row * D : nullptr, q ? q + row * D : nullptr,
+                                     s ? s + row : nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -12,22 +12,9 @@
 //  * qk_prepare      : R3, the 64-point transform on Q/K heads, in registers with warp shuffles,
 //                      fused with dequant, RoPE and the per-head int8 quantiser.
 #include "common.cuh"
+#include "fht_core.cuh"
 
 namespace flexllm {
-
-__device__ __forceinline__ int pad32(int i) { return i + (i >> 5); }
-
-template <int B>
-__device__ __forceinline__ void reg_butterfly(float (&r)[32]) {
-#pragma unroll
-    for (int v = 0; v < 32; v++) {
-        if (!(v & (1 << B))) {
-            float lo = r[v], hi = r[v | (1 << B)];
-            r[v] = lo + hi;
-            r[v | (1 << B)] = lo - hi;
-        }
-    }
-}
 
 // FUSED: 0 = y = FHT(x)/scale (fp32 out); 1 = h = silu(g)*u, FHT, /scale, per-token int8 quant;
 // 2 = like 1 without the silu, input gathered from `win.g` ranks as x[g][rows][N/g], int8 output only
@@ -63,35 +50,8 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
         const int p = pad32(c * 4);
         buf[p] = v.x; buf[p + 1] = v.y; buf[p + 2] = v.z; buf[p + 3] = v.w;
     }
-    __syncthreads();
     float r[32];
-    // pass 1: index bits 1..5 in registers
-    {
-        const int base = (tid & 1) | ((tid >> 1) << 6);
-#pragma unroll
-        for (int v = 0; v < 32; v++) r[v] = buf[pad32(base | (v << 1))];
-        reg_butterfly<0>(r); reg_butterfly<1>(r); reg_butterfly<2>(r); reg_butterfly<3>(r); reg_butterfly<4>(r);
-#pragma unroll
-        for (int v = 0; v < 32; v++) buf[pad32(base | (v << 1))] = r[v];
-    }
-    __syncthreads();
-    // pass 2: index bits 6..10
-    {
-        const int base = (tid & 63) | ((tid >> 6) << 11);
-#pragma unroll
-        for (int v = 0; v < 32; v++) r[v] = buf[pad32(base | (v << 6))];
-        reg_butterfly<0>(r); reg_butterfly<1>(r); reg_butterfly<2>(r); reg_butterfly<3>(r); reg_butterfly<4>(r);
-#pragma unroll
-        for (int v = 0; v < 32; v++) buf[pad32(base | (v << 6))] = r[v];
-    }
-    __syncthreads();
-    // pass 3: index bits 11, 12, then 0. Register v: bits 0..2 -> index bits 0..2, bits 3,4 -> 11,12
-    {
-        const int base = tid << 3;
-#pragma unroll
-        for (int v = 0; v < 32; v++) r[v] = buf[pad32(base | (v & 7) | ((v >> 3) << 11))];
-        reg_butterfly<3>(r); reg_butterfly<4>(r); reg_butterfly<0>(r);
-    }
+    fht8192_passes<0>(buf, tid, r);
     float mx = -1e32f, mn = 1e32f;
 #pragma unroll
     for (int v = 0; v < 32; v++) {
@@ -107,7 +67,7 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
             yo[1] = make_float4(r[hi * 8 + 4], r[hi * 8 + 5], r[hi * 8 + 6], r[hi * 8 + 7]);
         }
     } else {
-        block_max_min(mx, mn, red);
+        group_max_min<0, 256>(mx, mn, red, tid);
         const float sc = sym_scale_from(mx, mn);
         if (tid == 0) s[row] = sc;
 #pragma unroll

@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "decode_mega.h"
 
 struct flexllm_kv_cache;
 struct flexllm_tp;
@@ -119,6 +120,8 @@ struct flexllm_model {
     float *gath = nullptr, *hloc = nullptr;     // all-gather target / local silu(gate)*up slice
     int32_t* acc32 = nullptr;                   // row-parallel partial sums
     void *pairs_l = nullptr, *pairs_g = nullptr;
+    // persistent decode-step kernel: -1 not tried yet, 0 not usable for this model, 1 ready
+    flexllm::MegaPlan* mega = nullptr; int mega_state = -1;
 };
 
 template <class T> static int dmalloc(flexllm_model* m, T** p, size_t n) {
@@ -209,6 +212,7 @@ extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_
 extern "C" int flexllm_model_destroy(flexllm_model* m) {
     if (!m) return FLEXLLM_OK;
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    mega_destroy(m->mega);
     if (m->cache) flexllm_kv_cache_destroy(m->cache);
     for (void* p : m->owned) cudaFree(p);
     delete m;
@@ -337,8 +341,34 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
 
 // One decode step for the B sequences of the last prefill: consumes m->next, leaves the new
 // greedy tokens in m->next (and in the output table), appends to the KV cache and advances ctx.
+// Builds the persistent decode-step kernel's plan on first use (single GPU only). Shapes or devices
+// it does not cover leave the kernel-per-operator path in charge.
+static int mega_prepare(flexllm_model* m) {
+    if (m->mega_state >= 0) return FLEXLLM_OK;
+    m->mega_state = 0;
+    if (m->g != 1) return FLEXLLM_OK;
+    std::vector<MegaLayerView> lv(m->cfg.layers);
+    for (int l = 0; l < m->cfg.layers; l++) {
+        const LayerW& w = m->L[l];
+        lv[l] = MegaLayerView{w.wqkv, w.wo, w.wgu, w.wd, w.sqkv, w.so, w.sgu, w.sd, w.g0, w.g1, w.a_s};
+    }
+    MegaModelView v;
+    v.layers = m->cfg.layers; v.D = m->cfg.hidden; v.HQ = m->cfg.heads_q; v.HKV = m->cfg.heads_kv; v.F = m->cfg.ffn; v.V = m->cfg.vocab;
+    v.max_batch = m->cfg.max_batch; v.max_ctx = m->cfg.max_ctx; v.eps = m->cfg.eps; v.fht_scale = m->cfg.fht_scale;
+    v.L = lv.data(); v.lm_w = m->lm_w; v.lm_s = m->lm_s; v.g_final = m->g_final; v.cos_t = m->cos_t; v.sin_t = m->sin_t;
+    v.cache = m->cache; v.page_table = m->page_table; v.max_pages = m->max_pages;
+    v.ctx = m->ctx; v.next = m->next; v.out_tokens = m->out_tokens; v.state = m->state;
+    v.x = m->x; v.xq = m->xq; v.xs = m->xs; v.hq = m->hq; v.att = m->att; v.logits = m->logits;
+    const int rc = mega_create(v, &m->mega);
+    if (rc == FLEXLLM_OK) m->mega_state = 1;
+    else if (rc != FLEXLLM_ENOTSUP) return rc;
+    return FLEXLLM_OK;
+}
+
 static int decode_step_body(flexllm_model* m, cudaStream_t st);
 static int decode_step(flexllm_model* m, cudaStream_t st) {
+    TRY(mega_prepare(m));
+    if (m->mega_state == 1) return mega_launch(m->mega, m->B, st);
     static int use_pdl = -1;
     if (use_pdl < 0) { const char* e = getenv("FLEXLLM_PDL"); use_pdl = e ? atoi(e) : 1; }
     g_pdl = use_pdl;
@@ -438,6 +468,8 @@ extern "C" int flexllm_model_begin(flexllm_model* m, int n_new, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     set_state_kernel<<<1, 1, 0, st>>>(m->state, 0, n_new);
     step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, m->B, m->out_tokens, m->state, m->ctx, 0);
+    TRY(mega_prepare(m));
+    if (m->mega_state == 1) TRY(mega_reset(m->mega, st));
     return launch_status(2);
 }
 
