@@ -35,6 +35,25 @@ struct DecAttnIn {
     int n_slabs; long slab_stride;     // MODE 2: split-K partial sums, slab s at qkv_acc + s * slab_stride
 };
 
+// Asks L2 for everything one (sequence, KV head) item will read: its K and V pages (4 KB each) and
+// their scale rows. `n_threads` threads (index `t`) share the work. Pure hint: no data is returned.
+__device__ __forceinline__ void dec_attn_prefetch_l2(const KvLayer& cache, const int32_t* __restrict__ page_table, int max_pages,
+                                                     const int32_t* __restrict__ ctx, int HKV, int hkv, int b, int t, int n_threads) {
+    const int npages = (ctx[b] + 1 + PAGE - 1) / PAGE;
+    // per page: 32 lines of K, 32 lines of V, 2 lines of K scales, 2 lines of V scales (128 bytes each)
+    for (int i = t; i < npages * 68; i += n_threads) {
+        const int p = i / 68, j = i - p * 68;
+        const long pg = page_table[(long)b * max_pages + p];
+        const long base = pg * HKV + hkv;
+        const void* line;
+        if (j < 32) line = cache.k + base * (long)(64 * PAGE) + (long)j * 128;
+        else if (j < 64) line = cache.v + base * (long)(64 * PAGE) + (long)(j - 32) * 128;
+        else if (j < 66) line = cache.ks + base * PAGE + (j - 64) * 32;
+        else line = cache.vs + base * PAGE + (j - 66) * 32;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+    }
+}
+
 // Small per-call shared-memory state of dec_attn_fused_body (one per group of threads that runs it).
 struct DecAttnSmem {
     __align__(16) int8_t q_sm[4][64];
@@ -64,14 +83,35 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
     int* pt_sm = sm.pt_sm;                                            // this sequence's page-table row
     named_sync_id<NT>(bar);   // a CTA may run several (sequence, head) items back to back
     const int w = tid >> 5, lane = tid & 31;
+    const int heads = HQ + 2 * HKV;
+    // MODE 2: the split-K partial sums of this warp's head do not depend on the context length, so
+    // their loads go out first and overlap the context / page-table round trips below
+    int a0 = 0, a1 = 0;
+    if (MODE == 2 && w < 6) {
+        const int h = w < 4 ? hkv * G + w : (w == 4 ? HQ + hkv : HQ + HKV + hkv);
+        const int32_t* src = in.qkv_acc + (long)b * heads * 64 + (long)h * 64 + lane;
+#pragma unroll 1
+        for (int sl = 0; sl < in.n_slabs; sl += 4) {
+            int p0[4], p1[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const bool on = sl + i < in.n_slabs;
+                p0[i] = on ? __ldcg(src + (sl + i) * in.slab_stride) : 0;
+                p1[i] = on ? __ldcg(src + (sl + i) * in.slab_stride + 32) : 0;
+            }
+            a0 += (p0[0] + p0[1]) + (p0[2] + p0[3]);
+            a1 += (p1[0] + p1[1]) + (p1[2] + p1[3]);
+        }
+    }
     const int pos = ctx[b];
     const int nk = pos + 1;
-    const int heads = HQ + 2 * HKV;
     const int npages_all = (nk + PAGE - 1) / PAGE;
     const bool pt_cached = npages_all <= 160;
     if (pt_cached)
         for (int i = tid; i < npages_all; i += NT) pt_sm[i] = page_table[(long)b * max_pages + i];
-    // warm L2 with this head's V pages while the scores are computed (V is first needed in step G)
+    // warm L2 with this head's V pages while the scores are computed (V is first needed in step G);
+    // the persistent kernel (MODE 2) has asked for them a phase earlier
+    if (MODE != 2)
     for (int i = tid; i < npages_all * 32; i += NT) {
         const long pg = page_table[(long)b * max_pages + (i >> 5)];
         const int8_t* line = cache.v + (pg * HKV + hkv) * (long)(64 * PAGE) + (long)(i & 31) * 128;
@@ -85,15 +125,9 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         const int h = w < 4 ? hkv * G + w : (w == 4 ? HQ + hkv : HQ + HKV + hkv);   // index in the fused row
         float x0, x1;
         if (MODE == 2) {
-            // int32 partial sums of the fused q|k|v projection (one slab per K split): add them up
-            // (integers: exact in any order) and dequantise here
-            const int32_t* src = in.qkv_acc + (long)b * heads * 64 + (long)h * 64;
+            // int32 partial sums of the fused q|k|v projection (one slab per K split), added up above
+            // (integers: exact in any order); dequantise here
             const float st = __ldcg(in.tok_scale + b);
-            int a0 = 0, a1 = 0;
-            for (int sl = 0; sl < in.n_slabs; sl++) {
-                a0 += __ldcg(src + sl * in.slab_stride + lane);
-                a1 += __ldcg(src + sl * in.slab_stride + lane + 32);
-            }
             x0 = ((float)a0 * st) * in.ch_scale[h * 64 + lane];
             x1 = ((float)a1 * st) * in.ch_scale[h * 64 + lane + 32];
         } else if (MODE == 1) {
@@ -160,28 +194,39 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         qsc[g] = q_scale[g];
     }
     float mymax = -1e32f;                      // lane l4 tracks the maximum of head g = l4
-#pragma unroll 8
-    for (int key0 = 0; key0 < nk; key0 += NT / 4) {
-        const int key = key0 + slot;
-        const bool valid = key < nk;
-        const int kk = valid ? key : nk - 1;
-        const long pg = pt_cached ? pt_sm[kk / PAGE] : page_table[(long)b * max_pages + kk / PAGE];
-        const long row = (pg * HKV + hkv) * PAGE + (kk % PAGE);
-        const int4 kv4 = *reinterpret_cast<const int4*>(cache.k + row * 64 + l4 * 16);
-        const float ksc = cache.ks[row];
-        float xg = 0.0f;
+    // batches of UB iterations: all of a batch's K rows and scales are requested before any is used
+    // (the stores into the score row would otherwise keep the next iteration's loads from starting)
+    constexpr int UB = 4;
+#pragma unroll 1
+    for (int key0 = 0; key0 < nk; key0 += UB * (NT / 4)) {
+        int4 kv4[UB];
+        float ksc[UB];
 #pragma unroll
-        for (int g = 0; g < G; g++) {
-            int acc = __dp4a(qreg[g][0], kv4.x, 0);
-            acc = __dp4a(qreg[g][1], kv4.y, acc); acc = __dp4a(qreg[g][2], kv4.z, acc); acc = __dp4a(qreg[g][3], kv4.w, acc);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            const float x = (((float)acc * qsc[g]) * ksc) * 0.125f;
-            if (g == l4) xg = x;
+        for (int u = 0; u < UB; u++) {
+            const int key = key0 + u * (NT / 4) + slot;
+            const int kk = key < nk ? key : nk - 1;
+            const long pg = pt_cached ? pt_sm[kk / PAGE] : page_table[(long)b * max_pages + kk / PAGE];
+            const long row = (pg * HKV + hkv) * PAGE + (kk % PAGE);
+            kv4[u] = *reinterpret_cast<const int4*>(cache.k + row * 64 + l4 * 16);
+            ksc[u] = cache.ks[row];
         }
-        if (valid) {
-            sc[l4 * cs + key] = xg;
-            mymax = xg > mymax ? xg : mymax;
+#pragma unroll
+        for (int u = 0; u < UB; u++) {
+            const int key = key0 + u * (NT / 4) + slot;
+            float xg = 0.0f;
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                int acc = __dp4a(qreg[g][0], kv4[u].x, 0);
+                acc = __dp4a(qreg[g][1], kv4[u].y, acc); acc = __dp4a(qreg[g][2], kv4[u].z, acc); acc = __dp4a(qreg[g][3], kv4[u].w, acc);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                const float x = (((float)acc * qsc[g]) * ksc[u]) * 0.125f;
+                if (g == l4) xg = x;
+            }
+            if (key < nk) {
+                sc[l4 * cs + key] = xg;
+                mymax = xg > mymax ? xg : mymax;
+            }
         }
     }
     // maximum over the lanes with the same l4 (xor 4, 8, 16), then over the warps
@@ -196,6 +241,19 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         row_max[tid] = m;
     }
     named_sync_id<NT>(bar);
+    // the V scales of this thread's first UF keys (step F) are requested now: their latency hides behind
+    // the exponentials and the ordered sums
+    constexpr int UF = 6;
+    float vsc_pre[UF];
+#pragma unroll
+    for (int u = 0; u < UF; u++) {
+        const int key = tid + u * NT;
+        vsc_pre[u] = 0.0f;
+        if (key < nk) {
+            const long pg = pt_cached ? pt_sm[key / PAGE] : page_table[(long)b * max_pages + key / PAGE];
+            vsc_pre[u] = cache.vs[(pg * HKV + hkv) * PAGE + (key % PAGE)];
+        }
+    }
     // ---- D. e = exp(x - max), in place
     for (int g = 0; g < G; g++) {
         const float m = row_max[g];
@@ -216,23 +274,37 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
     named_sync_id<NT>(bar);
     // ---- F. u8 probabilities (zero beyond the last key up to the page boundary)
     const int nk_pad = (nk + PAGE - 1) / PAGE * PAGE;
-    for (int key = tid; key < nk_pad; key += NT) {
-        float vsc = 0.0f;
-        if (key < nk) {
-            const long pg = pt_cached ? pt_sm[key / PAGE] : page_table[(long)b * max_pages + key / PAGE];
-            vsc = cache.vs[(pg * HKV + hkv) * PAGE + (key % PAGE)];
-        }
+    {
+        float rinv_g[G];
+        DivBy as_g[G];
 #pragma unroll
-        for (int g = 0; g < G; g++) {
-            uint8_t u = 0;
-            if (key < nk) {
-                const float p = sc[g * cs + key] * row_rinv[g];
-                const float tt = (p * vsc) / a_s[hkv * G + g];
-                int r = (int)roundf(tt);
-                r = r > 255 ? 255 : r;
-                u = (uint8_t)r;
+        for (int g = 0; g < G; g++) { rinv_g[g] = row_rinv[g]; as_g[g] = div_by(a_s[hkv * G + g]); }
+        auto quantise_key = [&](int key, float vsc) {
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                uint8_t uq = 0;
+                if (key < nk) {
+                    const float p = sc[g * cs + key] * rinv_g[g];
+                    const float tt = div_for_rounding(p * vsc, as_g[g]);
+                    int r = (int)roundf(tt);
+                    r = r > 255 ? 255 : r;
+                    uq = (uint8_t)r;
+                }
+                u_sm[g * cs + key] = uq;
             }
-            u_sm[g * cs + key] = u;
+        };
+#pragma unroll
+        for (int u = 0; u < UF; u++) {
+            const int key = tid + u * NT;
+            if (key < nk_pad) quantise_key(key, vsc_pre[u]);
+        }
+        for (int key = tid + UF * NT; key < nk_pad; key += NT) {      // contexts beyond UF * NT keys
+            float vsc = 0.0f;
+            if (key < nk) {
+                const long pg = pt_cached ? pt_sm[key / PAGE] : page_table[(long)b * max_pages + key / PAGE];
+                vsc = cache.vs[(pg * HKV + hkv) * PAGE + (key % PAGE)];
+            }
+            quantise_key(key, vsc);
         }
     }
     named_sync_id<NT>(bar);

@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
         const float* ksp = args.ks + ((long)b * args.HKV + hkv) * args.S;
         const float* vsp = args.vs + ((long)b * args.HKV + hkv) * args.S;
         const float a_s = args.a_s[hq];
+        const DivBy d_as = div_by(a_s);
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float mx = -1e32f;
         float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
@@ -331,7 +332,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const float p = ee[i] * rinv;
-                        const float t = (p * vv[i]) / a_s;
+                        const float t = div_for_rounding(p * vv[i], d_as);
                         int r = (int)roundf(t);
                         r = r > 255 ? 255 : r;
                         w |= ((uint32_t)r & 0xffu) << (8 * i);

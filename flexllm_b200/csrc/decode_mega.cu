@@ -298,20 +298,21 @@ __device__ __forceinline__ void mega_row_fht(const MegaArgs& a, const MegaLayer&
     float r[32];
     fht8192_passes<MG_BAR_FHT>(buf, tid, r);
     float mx = -1e32f, mn = 1e32f;
+    div_rn_array(r, div_by(a.fht_scale));
 #pragma unroll
     for (int v = 0; v < 32; v++) {
-        r[v] = r[v] / a.fht_scale;
         mx = fmaxf(mx, r[v]);
         mn = fminf(mn, r[v]);
     }
     group_max_min<MG_BAR_FHT, 256>(mx, mn, red, tid);
     const float sc = sym_scale_from(mx, mn);
+    const DivBy dsc = div_by(sc);
     if (tid == 0) a.xs[row] = sc;
 #pragma unroll
     for (int hi = 0; hi < 4; hi++) {
         union { int8_t b[8]; int2 v; } o;
 #pragma unroll
-        for (int c = 0; c < 8; c++) o.b[c] = quant_s8(r[hi * 8 + c], sc);
+        for (int c = 0; c < 8; c++) o.b[c] = (int8_t)(int)roundf(div_for_rounding(r[hi * 8 + c], dsc));
         *reinterpret_cast<int2*>(a.hq + (long)row * N + hi * 2048 + tid * 8) = o.v;
     }
     asm volatile("fence.proxy.async.global;" ::: "memory");   // hq is read by other CTAs' TMA (async proxy)
@@ -551,6 +552,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 else if (k == 9) { acc = a.w_d; ks = a.ks_d; s_ch = ly.sd; gamma = a.g_final; }
                 else { acc = p == 0 ? nullptr : a.w_d; ks = a.ks_d; s_ch = p == 0 ? nullptr : a.layers[l - 1].sd; gamma = ly.g0; }
                 mega_row_norm(a, cta, acc, ks, s_ch, gamma, rowbuf, rowred, tid);
+            } else if (p == 0 && G > a.B) {
+                // CTAs without a row ask L2 for the KV pages the first layer's attention will read
+                for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
+                    dec_attn_prefetch_l2(ly.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
             }
         } else if (k == 2) {
             DecAttnIn in;
@@ -569,6 +574,13 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             if (cta < a.B) mega_row_quant(a, cta, rowred, tid);
         } else if (k == 7) {
             if (cta < a.B) mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
+            else if (l + 1 < L) {
+                // this phase keeps only B CTAs busy for a long time: the others ask L2 for the KV pages of the
+                // NEXT layer's attention (any CTA can do this for any item: L2 is shared)
+                const MegaLayer& nx = a.layers[l + 1];
+                for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
+                    dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
+            }
         } else if (k == 11) {
             if (cta < a.B) mega_row_argmax(a, cta, col, n_cols, arg_v, arg_i);
             if (cta == 0 && tid == 0) a.state[0] = col + 1;

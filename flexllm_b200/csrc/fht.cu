@@ -53,9 +53,9 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
     float r[32];
     fht8192_passes<0>(buf, tid, r);
     float mx = -1e32f, mn = 1e32f;
+    div_rn_array(r, div_by(scale));
 #pragma unroll
     for (int v = 0; v < 32; v++) {
-        r[v] = r[v] / scale;
         mx = fmaxf(mx, r[v]);
         mn = fminf(mn, r[v]);
     }
@@ -69,12 +69,13 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
     } else {
         group_max_min<0, 256>(mx, mn, red, tid);
         const float sc = sym_scale_from(mx, mn);
+        const DivBy dsc = div_by(sc);
         if (tid == 0) s[row] = sc;
 #pragma unroll
         for (int hi = 0; hi < 4; hi++) {
             union { int8_t b[8]; int2 v; } o;
 #pragma unroll
-            for (int c = 0; c < 8; c++) o.b[c] = quant_s8(r[hi * 8 + c], sc);
+            for (int c = 0; c < 8; c++) o.b[c] = (int8_t)(int)roundf(div_for_rounding(r[hi * 8 + c], dsc));
             const int idx0 = hi * 2048 + tid * 8;
             if (FUSED == 2) {
                 if (idx0 >= win.col0 && idx0 < win.col0 + win.cols)
