@@ -235,10 +235,26 @@ def kernel_roofline(F, torch, peaks):
         detail[name] = {"us": round(ms * 1e3, 2), "GB/s": round(nbytes / ms / 1e6, 1)}
         total_bytes += nbytes; total_ms += ms
     achieved = total_bytes / total_ms / 1e6
-    peak = peaks.get("hbm_gbs") or 6650.0
-    return {"bound": "hbm", "kernel": "decode linear layers (gemv / tcgen05 skinny GEMM), one layer's four projections, batch 32",
-            "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
-            "peak_source": "measured (MEASURED_PEAKS.json)" if peaks.get("hbm_gbs") else "fallback", "per_projection": detail}
+    return {"kernel": "decode linear layers as stand-alone launches (gemv / tcgen05 skinny GEMM), one layer's four projections, batch 32",
+            "achieved": round(achieved, 1), "unit": "GB/s", "per_projection": detail}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch: ncu capture at context 131..136
+# (1.358 GB read + 0.107 GB written, profiles/decode_mega_kernel_batch32_ctx131.md) plus the KV pages the
+# bench's mean context of 1152 adds (16 layers x 1088 B x 32 sequences x 1019 tokens; KV traffic is proportional)
+DRAM_TRAFFIC_PER_LAUNCH = int(1.358e9 + 0.107e9 + 16 * 1088 * 32 * 1019)
+
+
+def decode_step_bytes():
+    """Algorithmic bytes one decode step has to read: every int8 weight once (layers + lm_head), the
+    scales, and the int8 KV pages of all layers for the step's context lengths (K and V rows of 64
+    bytes per KV head plus two fp32 scales per head: 1088 bytes per cached token and layer)."""
+    D, F, V, L = CFG["hidden"], CFG["ffn"], CFG["vocab"], CFG["layers"]
+    qkv = (CFG["heads_q"] + 2 * CFG["heads_kv"]) * 64
+    weights = L * (qkv * D + D * D + 2 * F * D + D * F) + V * D
+    scales = 4 * (L * (qkv + D + 2 * F + D + 2 * D) + V + D)
+    kv = L * 1088 * BATCH * (PREFILL + NEW / 2)
+    return weights + scales + kv
 
 
 def micro(args):
@@ -274,6 +290,18 @@ def micro(args):
     elif name == "swiglu_fht":
         gg = torch.randn((4096, 8192), device=dev); uu = torch.randn((4096, 8192), device=dev)
         fn = lambda: F.swiglu_fht_quant(gg, uu)
+    elif name == "decode_step":         # whole-model decode steps (one persistent kernel each) at a short context: small enough for ncu
+        S, n = 128, 6
+        m = F.Model(max_batch=BATCH, max_prefill=S, max_ctx=S + 16, **CFG)
+        synthetic.load_random_weights(m, max_ctx=S + 16, seed=0, **CFG)
+        tok = torch.randint(0, CFG["vocab"], (BATCH, S), dtype=torch.int32).cuda()
+        m.prefill(tok); m.begin(16)
+        m.decode(2, False); torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(); m.decode(n, False); e1.record(); torch.cuda.synchronize()
+        print(json.dumps({"micro": name, "ms": e0.elapsed_time(e1) / n, "context": f"{S + 3}..{S + 2 + n}"}))
+        m.close()
+        return
     else:
         raise SystemExit(f"unknown --micro {name}")
     for _ in range(2):
@@ -375,7 +403,7 @@ def gpu_arm(args):
         return r
 
     def phases(r, nb):
-        dec_bytes = 1235746816 + 16 * 1088 * BATCH * (PREFILL + NEW / 2)
+        dec_bytes = decode_step_bytes()
         return {"prefill_ms": round(r["t_pre"], 3), "prefill_tokens_per_s": round(nb * PREFILL / r["t_pre"] * 1e3, 1),
                 "prefill_tops": round(6.60e13 * nb / BATCH / r["t_pre"] / 1e9, 1),
                 "decode_ms_per_step": round(r["t_dec"] / (NEW - 1), 4),
@@ -397,8 +425,18 @@ def gpu_arm(args):
 
     if rank == 0:
         roof = cpu = None
+        # the dominant kernel: one persistent launch per decode step (256 of the job's launches, ~3/4 of its
+        # time); its duration is the CUDA-event time of the decode loop / launches, measured above
+        hbm_peak = peaks.get("hbm_gbs") or 6650.0
+        step_ms = main_r["t_dec"] / (NEW - 1)
+        nbytes = decode_step_bytes()
+        roof = {"bound": "hbm", "kernel": "decode_mega_kernel (whole decode step, batch 32, context 1024..1279)" if not use_tp
+                else "decode step (tensor-parallel kernel sequence)", "achieved": round(nbytes / step_ms / 1e6, 1), "peak": hbm_peak, "unit": "GB/s",
+                "frac": round(nbytes / step_ms / 1e6 / hbm_peak, 4), "traffic": DRAM_TRAFFIC_PER_LAUNCH,
+                "algorithmic_bytes_per_launch": int(nbytes), "us_per_launch": round(step_ms * 1e3, 1),
+                "peak_source": "measured (MEASURED_PEAKS.json)" if peaks.get("hbm_gbs") else "fallback"}
         if not args.no_extras:
-            roof = kernel_roofline(F, torch, peaks)
+            roof["standalone_linear"] = kernel_roofline(F, torch, peaks)
             try:
                 cpu = cpu_port_baseline()
             except Exception as e:  # the CPU figure is a reported baseline only
@@ -437,7 +475,7 @@ def main():
     ap.add_argument("--decode-len", type=int, default=NEW)
     ap.add_argument("--no-extras", action="store_true", help="skip roofline kernel timing and the CPU baseline")
     ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, gemm_prefill, "
-                                                  "gemm_prefill_k8192, decode_linear, swiglu_fht)")
+                                                  "gemm_prefill_k8192, decode_linear, swiglu_fht, decode_step)")
     args = ap.parse_args()
     globals()["NEW"] = args.decode_len
     args.warmup = max(args.warmup, 0)
