@@ -115,7 +115,11 @@ template <int BN, int KCH = 1> struct GemmCfg {
     static constexpr int STAGES = KCH > 1 ? (STAGES_MAX > 8 ? 8 : STAGES_MAX)
                                           : (BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : BN == 32 ? 8 : 10);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // prefill orientation: per-warp staging (32 rows x 32 fp32, plus the tile's column scales) that turns the accumulator rows a thread
+    // owns into row-contiguous 128-byte global stores
+    static constexpr int STG_WARP_FLOATS = 32 * 32 + 256;      // one 32 x 32 chunk + the tile's column scales
+    static constexpr int STG_BYTES = BN >= 32 ? 4 * STG_WARP_FLOATS * 4 : 0;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STG_BYTES;
 };
 
 template <int BN, bool SWAP, int KCH = 1>
@@ -241,12 +245,99 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
 #pragma unroll
                 for (int j = 0; j < BN; j++) { const int tok = tb * BN + j; sbv[j] = tok < args.rowsB ? args.sB[tok] : 0.0f; }
             }
+            float* stg = reinterpret_cast<float*>(ring_ptr + STAGES * Cfg::STAGE_BYTES + 256) + q * Cfg::STG_WARP_FLOATS;
+            if (!SWAP && BN >= 32) {
+                // column scales of this tile into shared memory, and the residual rows into L2
+                float* sbw = stg + 1024;
+                if (args.sB)
+                    for (int i = lane; i < BN; i += 32) sbw[i] = tb * BN + i < args.rowsB ? args.sB[tb * BN + i] : 0.0f;
+                if (args.residual) {
+                    for (int i = lane; i < 32 * (BN / 32); i += 32) {
+                        const int rr = i / (BN / 32), seg = i - rr * (BN / 32);
+                        const int row = ta * 128 + q * 32 + rr, col = tb * BN + seg * 32;
+                        if (row < args.rowsA && col < args.rowsB)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(args.residual + (long)row * args.ldo + col));
+                    }
+                }
+            }
             // lane 0 polls; the verdict is broadcast so that the warp stays converged for the
             // warp-collective TMEM loads below
             int got = (lane == 0) ? (mbar_wait(bar_tfull + 8 * as, aphase, abort_flag) ? 1 : 0) : 1;
             got = __shfl_sync(0xffffffffu, got, 0);
             if (!got) { ok = false; break; }
             tc_fence_after();
+            if (!SWAP && BN >= 32) {
+                // ---- prefill orientation, staged: lane = token row of the tile. 32 columns at a time are
+                // dequantised into this warp's staging buffer (16-byte granules XOR-swizzled by the row), then
+                // written out with every warp instruction covering 4 rows x 128 contiguous bytes (the direct
+                // form stores 32 rows x 16 bytes per instruction and was bound by the store path).
+                const float* sbw = stg + 1024;
+                __syncwarp();
+                // the TMEM load of chunk c + 1 is in flight while chunk c is processed
+                constexpr int NCH = BN / 32;
+                const uint32_t tsrc = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
+                auto process = [&](const uint32_t (&v)[32], const int c) {
+                    const int colB0 = tb * BN + c * 32;
+                    if (args.acc && rowA_ok) {
+                        const long o = (long)rowA * args.ldo + colB0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            if (colB0 + j < args.rowsB)
+                                *reinterpret_cast<int4*>(args.acc + o + j) = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
+                    }
+                    if (args.y) {
+                        float* buf = stg;
+                        const int g = lane & 7;
+                        // this lane's share of the residual for the write-out below, requested first
+                        float4 rs[8];
+                        if (args.residual) {
+#pragma unroll
+                            for (int it = 0; it < 8; it++) {
+                                const int rr = it * 4 + (lane >> 3);
+                                const int row = ta * 128 + q * 32 + rr, col = colB0 + 4 * g;
+                                rs[it] = (row < args.rowsA && col < args.rowsB)
+                                             ? *reinterpret_cast<const float4*>(args.residual + (long)row * args.ldo + col)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+#pragma unroll
+                        for (int gg = 0; gg < 8; gg++) {
+                            const float4 sb = *reinterpret_cast<const float4*>(sbw + c * 32 + 4 * gg);
+                            float4 r;
+                            r.x = ((float)(int)v[4 * gg] * sa) * sb.x;
+                            r.y = ((float)(int)v[4 * gg + 1] * sa) * sb.y;
+                            r.z = ((float)(int)v[4 * gg + 2] * sa) * sb.z;
+                            r.w = ((float)(int)v[4 * gg + 3] * sa) * sb.w;
+                            *reinterpret_cast<float4*>(buf + lane * 32 + ((gg ^ (lane & 7)) << 2)) = r;
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int it = 0; it < 8; it++) {
+                            const int rr = it * 4 + (lane >> 3);
+                            const int row = ta * 128 + q * 32 + rr, col = colB0 + 4 * g;
+                            if (row < args.rowsA && col < args.rowsB) {
+                                float4 r = *reinterpret_cast<const float4*>(buf + rr * 32 + ((g ^ (rr & 7)) << 2));
+                                if (args.residual) { r.x = rs[it].x + r.x; r.y = rs[it].y + r.y; r.z = rs[it].z + r.z; r.w = rs[it].w + r.w; }
+                                *reinterpret_cast<float4*>(args.y + (long)row * args.ldo + col) = r;
+                            }
+                        }
+                        __syncwarp();      // the staging buffer is reused by the next chunk
+                    }
+                };
+                uint32_t va[32], vb[32];
+                tmem_ld_32x32(tsrc, va);
+#pragma unroll 1
+                for (int c = 0; c < NCH; c += 2) {
+                    tmem_ld_wait();
+                    if (c + 1 < NCH) tmem_ld_32x32(tsrc + (c + 1) * 32, vb);
+                    process(va, c);
+                    if (c + 1 < NCH) {
+                        tmem_ld_wait();
+                        if (c + 2 < NCH) tmem_ld_32x32(tsrc + (c + 2) * 32, va);
+                        process(vb, c + 1);
+                    }
+                }
+            } else {
         #pragma unroll (SWAP ? BN / 16 : 1)
             for (int c = 0; c < BN / 16; c++) {
                 uint32_t v[16];
@@ -300,6 +391,7 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
                         }
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
