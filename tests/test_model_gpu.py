@@ -32,13 +32,13 @@ def F():
     return flexllm_b200
 
 
-def run_case(F, layers, hidden, hq, hkv, vocab, B, S, n_new, seed, use_graph):
+def run_case(F, layers, hidden, hq, hkv, vocab, B, S, n_new, seed, use_graph, max_batch=None):
     from flexllm_b200 import synthetic
     max_ctx = S + n_new
     W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, max_ctx, seed=seed)
     assert np.array_equal(W["cos_t"], oracle.rope_table(max_ctx + 1)[0])      # product table == oracle table
     tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
-    m = F.Model(layers, hidden, hq, hkv, 8192, vocab, max_batch=B, max_prefill=S, max_ctx=max_ctx)
+    m = F.Model(layers, hidden, hq, hkv, 8192, vocab, max_batch=max_batch or B, max_prefill=S, max_ctx=max_ctx)
     synthetic.load_numpy_weights(m, W)
     out = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=use_graph)
     logits_last = to_np(m.buffer(1, (B, vocab), torch.float32))
@@ -73,4 +73,21 @@ def test_model_full_width(F):
 
 def test_model_batch_over_8(F):
     """More than 8 sequences sends the decode linear layers down the tensor-core split-K path."""
+    run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=12, S=16, n_new=4, seed=53, use_graph=True)
+
+
+def test_model_batch_over_32(F):
+    """33..64 sequences: the persistent decode kernel's 64-token instantiation."""
+    run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=40, S=16, n_new=4, seed=54, use_graph=True)
+
+
+def test_model_single_sequence_in_a_larger_model(F):
+    """One sequence in a model sized for 8: partial-sum slabs and activation boxes are laid out for max_batch."""
+    run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=1, S=32, n_new=6, seed=55, use_graph=False, max_batch=8)
+
+
+def test_model_kernel_per_operator_decode(F, monkeypatch):
+    """FLEXLLM_MEGA=0 keeps the decode step on the kernel-per-operator path (the one tensor parallelism and
+    shapes outside the persistent kernel's range use): same bits."""
+    monkeypatch.setenv("FLEXLLM_MEGA", "0")
     run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=12, S=16, n_new=4, seed=53, use_graph=True)
