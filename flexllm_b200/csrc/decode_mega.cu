@@ -76,6 +76,8 @@ struct MegaArgs {
     const int32_t* page_table; int max_pages;
     int32_t *ctx, *next, *out_tokens, *state;
     unsigned long long* sync_ctr; int* error_flag;
+    float* fht_x;                 // FHT phase split over 4 CTAs per row: the parts' locally transformed values [max_batch][F]
+    int* fht_flags;               // [3][max_batch]: parts published, parts' maxima merged, merged |max| as float bits
     unsigned long long* trace;    // optional phase timeline [barrier][arrive, leave][CTA] in globaltimer ns (last launch)
     int stages, cs, scratch_bytes;
     int attn_bytes;               // per-half attention scratch: score rows (20 bytes per key) + DecAttnSmem
@@ -128,6 +130,21 @@ __device__ __noinline__ bool mega_wait_counter(const unsigned long long* ctr, un
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t it = 1;; it++) {
         if (ld_acquire_u64(ctr) >= target) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (ld_volatile_s32(error_flag)) { *abort_flag = 1; return false; }
+            if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
+        }
+    }
+}
+
+// Polls an int flag until it reaches `target` (bounded like the counter wait).
+__device__ __noinline__ bool mega_wait_flag(const int* flag, int target, volatile int* abort_flag, int* error_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (uint32_t it = 1;; it++) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= target) return true;
         if ((it & 63u) == 0) {
             if (*abort_flag) return false;
             if (ld_volatile_s32(error_flag)) { *abort_flag = 1; return false; }
@@ -315,6 +332,102 @@ __device__ __forceinline__ void mega_row_fht(const MegaArgs& a, const MegaLayer&
         for (int c = 0; c < 8; c++) o.b[c] = (int8_t)(int)roundf(div_for_rounding(r[hi * 8 + c], dsc));
         *reinterpret_cast<int2*>(a.hq + (long)row * N + hi * 2048 + tid * 8) = o.v;
     }
+    asm volatile("fence.proxy.async.global;" ::: "memory");   // hq is read by other CTAs' TMA (async proxy)
+}
+
+// The same phase with the row split over FOUR CTAs (used when 4 * B CTAs exist): part p owns elements
+// p*2048 .. p*2048+2047. The 8192-point transform factors as: stages on index bits 1..10 inside each part,
+// stages 11 and 12 across the parts (element i of every part), then the stage on bit 0 inside the part
+// again -- the reference's stage order, so the same additions in the same order. Two small exchanges
+// through global memory, each guarded by a per-row arrival counter: the locally transformed parts, and
+// the row's largest magnitude for the quantiser (maximum of non-negative floats = maximum of their bits).
+__device__ __forceinline__ void mega_row_fht4(const MegaArgs& a, const MegaLayer& L, int row, int part, float* buf, float* red, int tid,
+                                              volatile int* abort_flag) {
+    constexpr int N = 8192, NP = 2048;
+    int* flag_a = a.fht_flags + row;
+    int* flag_b = a.fht_flags + a.slab_rows + row;
+    unsigned* amax_bits = reinterpret_cast<unsigned*>(a.fht_flags + 2 * a.slab_rows) + row;
+    {   // 1. this part's 2048 values: dequantise gate and up, silu(gate) * up (one float4 per thread)
+        const float st = __ldcg(a.xs + row);
+        const int c = part * (NP / 4) + tid;
+        const int4* gr = reinterpret_cast<const int4*>(a.w_gu + (long)row * 2 * N);
+        const int4 g4 = __ldcg(gr + c), u4 = __ldcg(gr + N / 4 + c);
+        const float4 a1 = __ldg(reinterpret_cast<const float4*>(L.sgu) + c), a2 = __ldg(reinterpret_cast<const float4*>(L.sgu) + N / 4 + c);
+        float4 g, u;
+        g.x = ((float)g4.x * st) * a1.x; g.y = ((float)g4.y * st) * a1.y; g.z = ((float)g4.z * st) * a1.z; g.w = ((float)g4.w * st) * a1.w;
+        u.x = ((float)u4.x * st) * a2.x; u.y = ((float)u4.y * st) * a2.y; u.z = ((float)u4.z * st) * a2.z; u.w = ((float)u4.w * st) * a2.w;
+        const int p = pad32(tid * 4);
+        buf[p] = silu_f(g.x) * u.x; buf[p + 1] = silu_f(g.y) * u.y; buf[p + 2] = silu_f(g.z) * u.z; buf[p + 3] = silu_f(g.w) * u.w;
+    }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (tid < 256) {   // 2. stages on bits 1..10: four passes over groups of three index bits, 8 values per thread
+        float r[8];
+        auto pass = [&](const int b0, const int which) {      // group = bits b0..b0+2; which: 0 all three, 1 the lower two, 2 the upper two
+            const int base = (tid & ((1 << b0) - 1)) | ((tid >> b0) << (b0 + 3));
+#pragma unroll
+            for (int v = 0; v < 8; v++) r[v] = buf[pad32(base | (v << b0))];
+            if (which != 2) reg_butterfly<0>(r);
+            reg_butterfly<1>(r);
+            if (which != 1) reg_butterfly<2>(r);
+#pragma unroll
+            for (int v = 0; v < 8; v++) buf[pad32(base | (v << b0))] = r[v];
+            named_sync<MG_BAR_FHT, 256>();
+        };
+        pass(1, 0); pass(4, 0); pass(7, 1); pass(8, 2);
+    }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    // 3. publish the part, wait for the other three
+    float4 own;
+    {
+        const int p = pad32(tid * 4);
+        own = make_float4(buf[p], buf[p + 1], buf[p + 2], buf[p + 3]);
+        reinterpret_cast<float4*>(a.fht_x + (long)row * N + part * NP)[tid] = own;
+    }
+    __threadfence();
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (tid == 0) {
+        atomicAdd(flag_a, 1);
+        mega_wait_flag(flag_a, 4, abort_flag, a.error_flag);
+        __threadfence();
+    }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (*abort_flag) return;
+    // 4. stages 11 and 12 across the parts, then bit 0 inside the thread's four consecutive elements
+    float x[4];
+    {
+        float4 w[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            w[q] = q == part ? own : __ldcg(reinterpret_cast<const float4*>(a.fht_x + (long)row * N + q * NP) + tid);
+        auto bf = [](float& lo, float& hi) { const float s = lo + hi, d = lo - hi; lo = s; hi = d; };
+        bf(w[0].x, w[1].x); bf(w[0].y, w[1].y); bf(w[0].z, w[1].z); bf(w[0].w, w[1].w);     // bit 11
+        bf(w[2].x, w[3].x); bf(w[2].y, w[3].y); bf(w[2].z, w[3].z); bf(w[2].w, w[3].w);
+        bf(w[0].x, w[2].x); bf(w[0].y, w[2].y); bf(w[0].z, w[2].z); bf(w[0].w, w[2].w);     // bit 12
+        bf(w[1].x, w[3].x); bf(w[1].y, w[3].y); bf(w[1].z, w[3].z); bf(w[1].w, w[3].w);
+        const float4 m = part == 0 ? w[0] : part == 1 ? w[1] : part == 2 ? w[2] : w[3];
+        x[0] = m.x + m.y; x[1] = m.x - m.y; x[2] = m.z + m.w; x[3] = m.z - m.w;             // bit 0
+    }
+    div_rn_array(x, div_by(a.fht_scale));
+    float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
+    group_max_min<MG_BAR_WORK, MG_WORKERS>(mx, mn, red, tid);
+    if (tid == 0) {   // 5. the row's largest magnitude over the four parts
+        const float am = fmaxf(fabsf(mx), fabsf(mn));
+        atomicMax(amax_bits, __float_as_uint(am));
+        __threadfence();
+        atomicAdd(flag_b, 1);
+        mega_wait_flag(flag_b, 4, abort_flag, a.error_flag);
+        __threadfence();
+    }
+    named_sync<MG_BAR_WORK, MG_WORKERS>();
+    if (*abort_flag) return;
+    float sc = __uint_as_float(__ldcg(amax_bits)) / 127.0f;          // sym_scale_from on the merged maximum
+    if (sc == 0.0f) sc = 1.0f;
+    const DivBy dsc = div_by(sc);
+    if (part == 0 && tid == 0) a.xs[row] = sc;
+    char4 o;
+    o.x = (int8_t)(int)roundf(div_for_rounding(x[0], dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(x[1], dsc));
+    o.z = (int8_t)(int)roundf(div_for_rounding(x[2], dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(x[3], dsc));
+    reinterpret_cast<char4*>(a.hq + (long)row * N + part * NP)[tid] = o;
     asm volatile("fence.proxy.async.global;" ::: "memory");   // hq is read by other CTAs' TMA (async proxy)
 }
 
@@ -552,10 +665,13 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 else if (k == 9) { acc = a.w_d; ks = a.ks_d; s_ch = ly.sd; gamma = a.g_final; }
                 else { acc = p == 0 ? nullptr : a.w_d; ks = a.ks_d; s_ch = p == 0 ? nullptr : a.layers[l - 1].sd; gamma = ly.g0; }
                 mega_row_norm(a, cta, acc, ks, s_ch, gamma, rowbuf, rowred, tid);
-            } else if (p == 0 && G > a.B) {
-                // CTAs without a row ask L2 for the KV pages the first layer's attention will read
+            } else if ((p == 0 || (k == 5 && l + 1 < L)) && G > a.B) {
+                // CTAs without a row ask L2 for the KV pages an attention phase will read (any CTA can do this
+                // for any item: L2 is shared): the first layer's at the start of the step, and in every phase C
+                // those of the NEXT layer, long before they are needed
+                const MegaLayer& nx = a.layers[p == 0 ? 0 : l + 1];
                 for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
-                    dec_attn_prefetch_l2(ly.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
+                    dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
             }
         } else if (k == 2) {
             DecAttnIn in;
@@ -573,19 +689,17 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
         } else if (k == 3) {
             if (cta < a.B) mega_row_quant(a, cta, rowred, tid);
         } else if (k == 7) {
-            if (cta < a.B) mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
-            else if (l + 1 < L) {
-                // this phase keeps only B CTAs busy for a long time: the others ask L2 for the KV pages of the
-                // NEXT layer's attention (any CTA can do this for any item: L2 is shared)
-                const MegaLayer& nx = a.layers[l + 1];
-                for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
-                    dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
+            const int parts = 4 * a.B <= G ? 4 : 1;         // CTAs per row
+            if (cta < parts * a.B) {
+                if (parts == 4) mega_row_fht4(a, ly, cta >> 2, cta & 3, rowbuf, rowred, tid, abort_flag);
+                else mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
             }
         } else if (k == 11) {
             if (cta < a.B) mega_row_argmax(a, cta, col, n_cols, arg_v, arg_i);
             if (cta == 0 && tid == 0) a.state[0] = col + 1;
         } else {
             const int kind = k == 1 ? 0 : k == 4 ? 1 : k == 6 ? 2 : k == 8 ? 3 : 4;
+            if (kind == 3 && cta == G - 1 && tid < 3 * a.slab_rows) a.fht_flags[tid] = 0;   // idle until the next FHT phase
             const MegaJob j = mega_job(a, l, kind);
             const MegaJob nj = kind < 3 ? mega_job(a, l, kind + 1) : (p + 1 < MG_PHASES_PER_LAYER * L ? mega_job(a, l + 1, 0) : mega_job(a, 0, 4));
             gemm_phase(j, kind == 4 ? nullptr : &nj);
@@ -624,6 +738,7 @@ int gemm_sm_count();
 struct MegaPlan {
     MegaArgs args;
     void* dev_maps = nullptr; void* dev_layers = nullptr; void* dev_work = nullptr; void* dev_ctr = nullptr; void* dev_trace = nullptr;
+    void* dev_fht_x = nullptr; void* dev_fht_flags = nullptr; int n_flags = 0;
     size_t trace_bytes = 0;
     size_t work_bytes = 0;
     int grid = 0, bn = 0;
@@ -642,6 +757,7 @@ void mega_destroy(MegaPlan* p) {
     }
     cudaFree(p->dev_trace);
     cudaFree(p->dev_maps); cudaFree(p->dev_layers); cudaFree(p->dev_work); cudaFree(p->dev_ctr);
+    cudaFree(p->dev_fht_x); cudaFree(p->dev_fht_flags);
     delete p;
 }
 
@@ -717,6 +833,10 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     if (e == cudaSuccess) e = cudaMemcpy(p->dev_layers, layers.data(), v.layers * sizeof(MegaLayer), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(p->dev_work, 0, p->work_bytes);
     if (e == cudaSuccess) e = cudaMemset(p->dev_ctr, 0, 256);
+    p->n_flags = 3 * v.max_batch;
+    if (e == cudaSuccess) e = cudaMalloc(&p->dev_fht_x, (size_t)v.max_batch * v.F * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&p->dev_fht_flags, p->n_flags * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p->dev_fht_flags, 0, p->n_flags * sizeof(int));
     if (e == cudaSuccess && getenv("FLEXLLM_MEGA_TRACE")) {
         p->trace_bytes = (size_t)(MG_PHASES_PER_LAYER * v.layers + 2) * 2 * G * sizeof(unsigned long long);
         e = cudaMalloc(&p->dev_trace, p->trace_bytes);
@@ -737,6 +857,7 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     a.page_table = v.page_table; a.max_pages = v.max_pages;
     a.ctx = v.ctx; a.next = v.next; a.out_tokens = v.out_tokens; a.state = v.state;
     a.sync_ctr = (unsigned long long*)p->dev_ctr; a.error_flag = device_error_flag();
+    a.fht_x = (float*)p->dev_fht_x; a.fht_flags = (int*)p->dev_fht_flags;
     a.trace = (unsigned long long*)p->dev_trace;
     a.stages = stages; a.cs = cs; a.scratch_bytes = scratch; a.attn_bytes = attn_bytes;
     a.ks_qkv = ks_qkv; a.ks_o = ks_o; a.ks_d = ks_d; a.slab_rows = v.max_batch;
@@ -747,6 +868,7 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
 
 int mega_reset(MegaPlan* p, cudaStream_t st) {
     FLEXLLM_CHECK_CUDA(cudaMemsetAsync(p->dev_ctr, 0, 256, st));
+    FLEXLLM_CHECK_CUDA(cudaMemsetAsync(p->dev_fht_flags, 0, p->n_flags * sizeof(int), st));
     return FLEXLLM_OK;
 }
 

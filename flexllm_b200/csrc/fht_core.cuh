@@ -8,10 +8,10 @@ namespace flexllm {
 
 __device__ __forceinline__ int pad32(int i) { return i + (i >> 5); }
 
-template <int B>
-__device__ __forceinline__ void reg_butterfly(float (&r)[32]) {
+template <int B, int N>
+__device__ __forceinline__ void reg_butterfly(float (&r)[N]) {
 #pragma unroll
-    for (int v = 0; v < 32; v++) {
+    for (int v = 0; v < N; v++) {
         if (!(v & (1 << B))) {
             float lo = r[v], hi = r[v | (1 << B)];
             r[v] = lo + hi;
