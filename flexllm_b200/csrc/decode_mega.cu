@@ -159,12 +159,12 @@ __device__ __forceinline__ bool mega_grid_sync(unsigned long long* ctr, unsigned
                                                volatile int* go_flag, int* error_flag, unsigned long long* trace) {
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (threadIdx.x == 0) {
-        __threadfence();
+        // release at GPU scope: orders this thread's writes and, through the CTA barrier above, every write of
+        // the CTA before the arrival; the acquire loads of the wait plus the CTA barrier below do the reverse
         if (trace) trace[blockIdx.x] = globaltimer_ns();
         asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(ctr), "l"(1ull) : "memory");
         mega_wait_counter(ctr, target, abort_flag, error_flag);
         if (trace) trace[gridDim.x + blockIdx.x] = globaltimer_ns();
-        __threadfence();
         *go_flag = (*abort_flag == 0);      // one verdict for the whole CTA, fixed before anyone reads it
     }
     named_sync<MG_BAR_WORK, MG_WORKERS>();
@@ -383,12 +383,10 @@ __device__ __forceinline__ void mega_row_fht4(const MegaArgs& a, const MegaLayer
         own = make_float4(buf[p], buf[p + 1], buf[p + 2], buf[p + 3]);
         reinterpret_cast<float4*>(a.fht_x + (long)row * N + part * NP)[tid] = own;
     }
-    __threadfence();
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (tid == 0) {
-        atomicAdd(flag_a, 1);
+        asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(flag_a), "r"(1) : "memory");
         mega_wait_flag(flag_a, 4, abort_flag, a.error_flag);
-        __threadfence();
     }
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (*abort_flag) return;
@@ -413,10 +411,8 @@ __device__ __forceinline__ void mega_row_fht4(const MegaArgs& a, const MegaLayer
     if (tid == 0) {   // 5. the row's largest magnitude over the four parts
         const float am = fmaxf(fabsf(mx), fabsf(mn));
         atomicMax(amax_bits, __float_as_uint(am));
-        __threadfence();
-        atomicAdd(flag_b, 1);
+        asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(flag_b), "r"(1) : "memory");
         mega_wait_flag(flag_b, 4, abort_flag, a.error_flag);
-        __threadfence();
     }
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (*abort_flag) return;
