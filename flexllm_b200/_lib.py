@@ -30,6 +30,7 @@ SIGNATURES = {
     "flexllm_residual": [_P, _P, _L, _P, _P],
     "flexllm_swiglu_fht_quant": [_P, _P, _I, _I, _F, _P, _P, _P, _P],
     "flexllm_logits_argmax": [_P, _I, _L, _P, _P],
+    "flexllm_topk_sample": [_P, _I, _L, _I, _I, _P, _P, _P, _P, _P],
     "flexllm_qk_prepare": [_P, _P, _P, _P, _P, _L, _I, _P, _P, _P],
     "flexllm_mha_prefill_workspace": [_I, _I, _I, _I],
     "flexllm_mha_i8xi8_prefill": [_P] * 9 + [_I, _I, _I, _I, _P, _P, _P, _SZ, _P],

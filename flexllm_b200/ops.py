@@ -205,6 +205,18 @@ def dec_Logits_argmax(logits):
     return idx
 
 
+def dec_Sampling_Layer(logits, rnd, lanes=32, top_k=5, details=False):
+    """Top-k sampling of dec_Sampling_Embedding_Layer (Logits.h:145-279) without the embedding gather.
+    logits [B,V] fp32, rnd [B] uniform numbers in [0,1) -> token ids [B] (and the merged top-k list)."""
+    B, V = logits.shape
+    idx = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    ti = torch.empty((B, top_k), dtype=torch.int32, device=logits.device) if details else None
+    tv = torch.empty((B, top_k), dtype=torch.float32, device=logits.device) if details else None
+    _call("flexllm_topk_sample", _ptr(logits), B, V, lanes, top_k, _ptr(rnd), _ptr(idx), _ptr(ti) if details else None,
+          _ptr(tv) if details else None)
+    return (idx, ti, tv) if details else idx
+
+
 # ------------------------------------------------------------------------------ MHA_i8xi8
 def MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, cos_t, sin_t, a_s, want_oacc=False):
     """Prefill GQA attention. q [B,S,HQ,64] s8, qs [B,S,HQ]; k,v [B,S,HKV,64], ks,vs [B,S,HKV];

@@ -144,6 +144,15 @@ FLEXLLM_API int flexllm_swiglu_fht_quant(const float* g, const float* u, int M, 
 /* Greedy token: argmax with ties to the lowest index = rank 0 of sort_top_k (Logits.h:5-31). */
 FLEXLLM_API int flexllm_logits_argmax(const float* logits, int B, long V, int32_t* idx, void* stream);
 
+/* Top-k sampling = dec_Sampling_Embedding_Layer without the embedding gather (Logits.h:145-279, instantiated as in
+ * SpinQuant_Decoding_mem_opt.h:934: inner_block_parallel 1, enable_sub_max): `lanes` lanes each keep a sorted top-k of
+ * their contiguous V/lanes slice (strict '>' insertion in index order), the lists are merged rank by rank, softmax over the
+ * k winners, and the token is the first k whose cumulative probability exceeds rnd[b] (a uniform number in [0,1) from the
+ * host, the reference's rand_seeds_mmap), else the last. logits [B][V] fp32, rnd [B] -> idx [B]; top_idx / top_val
+ * (optional) [B][top_k] receive the merged list. V % lanes == 0, top_k <= 8, lanes <= 64 (the reference: 16..32 lanes, k = 5). */
+FLEXLLM_API int flexllm_topk_sample(const float* logits, int B, long V, int lanes, int top_k, const float* rnd, int32_t* idx,
+                                    int32_t* top_idx, float* top_val, void* stream);
+
 /* Q/K preparation: x = (float)q*s -> RoPE(pos) -> FHT-64/8 -> per-head dynamic int8 quant.
  * q [T][H][64] s8, s [T][H] -> q_out, s_out same shapes (quant.h:242, RoPE.h:61-90, FHT.h at
  * N=64, quant.h:527-650). */

@@ -188,6 +188,17 @@ def argmax(logits):
     return idx
 
 
+def topk_sample(logits, rnd, lanes=32, top_k=5, details=False):
+    """Top-k sampling of Logits.h:145-279 with `lanes` lanes; rnd: one uniform number per row."""
+    logits = _f32(logits); B, V = logits.shape
+    rnd = _f32(np.asarray(rnd).reshape(B))
+    idx = np.empty(B, np.int32); ti = np.empty((B, top_k), np.int32); tv = np.empty((B, top_k), np.float32); tp = np.empty((B, top_k), np.float32)
+    rc = _lib.orc_topk_sample(_p(logits), C.c_int(B), C.c_long(V), C.c_int(lanes), C.c_int(top_k), _p(rnd), _p(idx), _p(ti), _p(tv), _p(tp))
+    if rc != 0:
+        raise ValueError("orc_topk_sample: unsupported shape")
+    return (idx, ti, tv, tp) if details else idx
+
+
 def linear_i8(a, s_tok, w, s_ch):
     a = _i8(a); w = _i8(w); M, K = a.shape; N = w.shape[0]
     acc = np.empty((M, N), np.int32); y = np.empty((M, N), np.float32)
@@ -413,6 +424,17 @@ class _Ref:
         rc = self.lib.ref_mha_axv(_p(p), _p(v), C.c_int(S), C.c_int(G), _p(acc))
         assert rc == 0
         return acc
+
+    def topk_sample(self, logits, rnd, lanes=32):
+        """The reference's dec_Sampling_Embedding_Layer (top_k = 5) row by row."""
+        logits = _f32(logits); B, V = logits.shape; idx = np.empty(B, np.int32)
+        one = np.empty(1, np.int32)
+        for b in range(B):
+            rc = self.lib.ref_topk_sample(_p(np.ascontiguousarray(logits[b])), C.c_int(V), C.c_int(lanes), C.c_float(float(rnd[b])), _p(one))
+            if rc != 0:
+                raise ValueError("ref_topk_sample: unsupported shape")
+            idx[b] = one[0]
+        return idx
 
     def argmax(self, logits):
         logits = _f32(logits); B, V = logits.shape; idx = np.empty(B, np.int32)

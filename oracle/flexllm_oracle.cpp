@@ -300,6 +300,57 @@ ORC_API void orc_argmax(const float* logits, int B, long V, int32_t* idx) {
 }
 
 // ----------------------------------------------------------------------------------------------
+// Top-k sampling (Logits.h:145-279, as instantiated by the decode graphs: inner_block_parallel 1,
+// enable_sub_max). `lanes` lanes each own a contiguous V/lanes slice of the vocabulary and keep an
+// insertion-sorted top-k of it (sort_top_k, Logits.h:5-31: strict '>', so equal values stay in
+// arrival order); the lanes' lists are merged by inserting rank 0 of every lane, then rank 1, ...
+// (:215-224); softmax over the k winners with two interleaved partial sums (:232-247); the token is
+// the first k whose cumulative probability exceeds the uniform number `rnd`, else the last (:252-271).
+// Outputs: sampled index per row; optionally the merged top-k indices / values / probabilities.
+// ----------------------------------------------------------------------------------------------
+static void orc_sort_top_k(int* ids, float* vals, int top_k, int v_idx, float v) {
+    int pos = top_k;
+    for (int k = 0; k < top_k; k++)
+        if (v > vals[k] && pos == top_k) pos = k;
+    for (int k = top_k - 1; k >= 0; k--) {
+        if (k > pos) { ids[k] = ids[k - 1]; vals[k] = vals[k - 1]; }
+        else if (k == pos) { ids[k] = v_idx; vals[k] = v; }
+    }
+}
+ORC_API int orc_topk_sample(const float* logits, int B, long V, int lanes, int top_k, const float* rnd, int32_t* idx,
+                            int32_t* top_idx, float* top_val, float* top_prob) {
+    if (top_k < 1 || top_k > 16 || lanes < 1 || V % lanes || V / lanes < top_k) return -1;
+    const long seg = V / lanes;
+    for (int b = 0; b < B; b++) {
+        const float* l = logits + (long)b * V;
+        std::vector<int> lid((size_t)lanes * top_k, -1);
+        std::vector<float> lval((size_t)lanes * top_k, -1e32f);
+        for (int i = 0; i < lanes; i++)
+            for (long t = 0; t < seg; t++) orc_sort_top_k(&lid[(size_t)i * top_k], &lval[(size_t)i * top_k], top_k, (int)(i * seg + t), l[i * seg + t]);
+        int fid[16]; float fval[16], prob[16], cdf[16];
+        for (int k = 0; k < top_k; k++) { fid[k] = -1; fval[k] = -1e32f; }
+        for (int K = 0; K < top_k; K++)
+            for (int i = 0; i < lanes; i++) orc_sort_top_k(fid, fval, top_k, lid[(size_t)i * top_k + K], lval[(size_t)i * top_k + K]);
+        float part[2] = {0.0f, 0.0f};
+        for (int k = 0; k < top_k; k++) { prob[k] = ref_exp(fval[k] - fval[0]); part[k % 2] += prob[k]; }
+        const float sum = part[0] + part[1];
+        for (int k = 0; k < top_k; k++) prob[k] /= sum;
+        cdf[0] = prob[0];
+        for (int k = 1; k < top_k; k++) cdf[k] = prob[k] + cdf[k - 1];
+        int sel = top_k - 1;
+        for (int k = 0; k < top_k; k++)
+            if (rnd[b] < cdf[k] && sel == top_k - 1) sel = k;
+        idx[b] = fid[sel];
+        for (int k = 0; k < top_k; k++) {
+            if (top_idx) top_idx[(long)b * top_k + k] = fid[k];
+            if (top_val) top_val[(long)b * top_k + k] = fval[k];
+            if (top_prob) top_prob[(long)b * top_k + k] = prob[k];
+        }
+    }
+    return 0;
+}
+
+// ----------------------------------------------------------------------------------------------
 // Config 1: one W8A8 linear layer on already-quantised activations.
 // ----------------------------------------------------------------------------------------------
 ORC_API void orc_linear_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,

@@ -435,3 +435,32 @@ REF_API void ref_argmax(const float* logits, int B, long V, int32_t* idx) {
         idx[b] = ids[0];
     }
 }
+
+// ---- Logits.h:145-279 dec_Sampling_Embedding_Layer: per-lane top-k, merge, softmax over k, inverse-CDF
+// sample from a host-supplied uniform number. Instantiated like the decode graphs do it
+// (SpinQuant_Llama_32_1B/SpinQuant_Decoding_mem_opt.h:934: top_k = 5, inner_block_parallel = 1,
+// enable_sub_max) with P = 16 or 32 lanes; the embedding gather that follows reads a dummy table.
+template <int P>
+static int ref_topk_sample_p(const float* logits, int V, float rnd, int32_t* idx) {
+    constexpr int MAXV = 1 << 17, HID = 64, BPE = 16;
+    if (V > MAXV || V % P) return -1;
+    tapa::stream<hls::vector<float, P>> ls;
+    for (int t = 0; t < V / P; t++) {
+        hls::vector<float, P> v;
+        for (int i = 0; i < P; i++) v[i] = logits[(long)i * (V / P) + t];
+        ls.write(v);
+    }
+    std::vector<hls::vector<float, BPE>> vocab((size_t)V * HID / BPE);
+    tapa::mmap<hls::vector<float, BPE>> vm(vocab.data());
+    tapa::stream<hls::vector<float, BPE>> es;
+    int sampled = -1;
+    dec_Sampling_Embedding_Layer<float, P, MAXV, 5, BPE, HID, P * 8>(ls, vm, es, rnd, sampled, V, HID);
+    for (int i = 0; i < HID / BPE; i++) (void)es.read();
+    *idx = sampled;
+    return 0;
+}
+REF_API int ref_topk_sample(const float* logits, int V, int lanes, float rnd, int32_t* idx) {
+    if (lanes == 16) return ref_topk_sample_p<16>(logits, V, rnd, idx);
+    if (lanes == 32) return ref_topk_sample_p<32>(logits, V, rnd, idx);
+    return -1;
+}

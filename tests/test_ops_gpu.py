@@ -318,3 +318,25 @@ def test_linear_full_size_linearity(F):
     assert torch.equal(acc1 + acc2, acc12)
     rows = g.choice(M, 16, replace=False)
     assert_same(to_np(acc1[torch.from_numpy(rows).cuda()]), oracle.gemm_s8s8(a1[rows], w))
+
+
+@pytest.mark.parametrize("lanes,V", [(16, 16 * 250), (32, 128256), (32, 32 * 8)])
+def test_topk_sampling(F, lanes, V):
+    """Top-k sampling (Logits.h:145-279) against the oracle: sampled index and the merged top-5 list, on random
+    logits, on logits with very few distinct values (ties inside and across lanes) and for random numbers that
+    select every rank."""
+    rng = np.random.default_rng(31 + lanes + V)
+    B = 12
+    x = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+    x[4:8] = rng.integers(-2, 3, (4, V)).astype(np.float32)
+    x[8, 7] = 50.0; x[8, V - 3] = 50.0; x[8, V // 2 + 1] = 50.0
+    x[9] = -1e33                      # nothing exceeds the initial -1e32: the list stays empty (index -1)
+    x[10, :5] = [3, 3, 3, 3, 3]
+    for rnd_value in [0.0, 0.2, 0.45, 0.7, 0.9, 0.9999]:
+        rnd = np.full(B, rnd_value, np.float32); rnd[11] = rng.random()
+        with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
+            want, wi, wv, _ = oracle.topk_sample(x, rnd, lanes=lanes, details=True)
+        got, gi, gv = F.dec_Sampling_Layer(torch.from_numpy(x).cuda(), torch.from_numpy(rnd).cuda(), lanes=lanes, details=True)
+        assert np.array_equal(to_np(gi), wi), (rnd_value, to_np(gi)[:3], wi[:3])
+        assert np.array_equal(to_np(gv).view(np.uint32), wv.view(np.uint32))
+        assert np.array_equal(to_np(got), want), (rnd_value, to_np(got), want)

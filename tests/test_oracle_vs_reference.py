@@ -192,3 +192,28 @@ def test_attention_row_composition():
     oacc = R.gemm_u8s8(pq, np.ascontiguousarray(v.T))
     same(r["oacc"], oacc[0])
     same(r["out"], R.dequant(oacc, [a_s], np.ones(64, np.float32))[0])
+
+
+@pytest.mark.parametrize("lanes", [16, 32])
+def test_topk_sample_restatement_vs_reference(lanes):
+    """Logits.h:145-279 top-k sampling: restatement vs the reference template, including exact ties inside and
+    across lanes and every rank being picked by some random number."""
+    if oracle.ref is None:
+        pytest.skip("reference templates not built")
+    rng = np.random.default_rng(90 + lanes)
+    V = lanes * 96
+    rows = []
+    x = rng.standard_normal((6, V)).astype(np.float32) * 2
+    rows.append(x)
+    t = rng.integers(-3, 4, (6, V)).astype(np.float32)          # few distinct values: many ties everywhere
+    rows.append(t)
+    peak = rng.standard_normal((4, V)).astype(np.float32)
+    peak[:, 5] = 9.0; peak[:, V - 7] = 9.0; peak[:, V // 2] = 9.0  # equal maxima in different lanes
+    rows.append(peak)
+    logits = np.concatenate(rows)
+    for rnd_value in [0.0, 0.13, 0.37, 0.62, 0.81, 0.97, 0.999999]:
+        rnd = np.full(len(logits), rnd_value, np.float32)
+        with oracle.exp_mode(oracle.EXP_LIBM):                   # the reference calls the C library's exp
+            got = oracle.topk_sample(logits, rnd, lanes=lanes)
+        want = oracle.ref.topk_sample(logits, rnd, lanes=lanes)
+        assert np.array_equal(got, want), (rnd_value, got, want)
