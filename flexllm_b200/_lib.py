@@ -56,6 +56,7 @@ SIGNATURES = {
     "flexllm_model_begin": [_P, _I, _P],
     "flexllm_model_decode": [_P, _I, _I, _P],
     "flexllm_model_generate_host": [_P, _P, _I, _I, _I, _P, _I, _P],
+    "flexllm_model_set_sampling": [_P, _I, _I, _P],
     "flexllm_model_buffer": [_P, _I, _P],
 }
 

@@ -41,6 +41,7 @@
 #include "common.cuh"
 #include "fht_core.cuh"
 #include "rmsnorm_core.cuh"
+#include "sampling.cuh"
 #include "tc_common.cuh"
 
 namespace flexllm {
@@ -75,6 +76,7 @@ struct MegaArgs {
     const float *cos_t, *sin_t;
     const int32_t* page_table; int max_pages;
     int32_t *ctx, *next, *out_tokens, *state;
+    int sample_lanes, sample_k; const float* sample_rnd;     // top-k sampling (sample_k == 0: greedy)
     unsigned long long* sync_ctr; int* error_flag;
     float* fht_x;                 // FHT phase split over 4 CTAs per row: the parts' locally transformed values [max_batch][F]
     int* fht_flags;               // [3][max_batch]: parts published, parts' maxima merged, merged |max| as float bits
@@ -464,6 +466,18 @@ __device__ __forceinline__ void mega_row_argmax(const MegaArgs& a, int row, int 
     }
 }
 
+// top-k sampling of one row by the 512 workers (sampling.cuh), then the same bookkeeping. Out of line: it runs
+// once per step and must not weigh on the register allocation of the phases that run every layer.
+__device__ __noinline__ void mega_row_sample(const MegaArgs& a, int row, int col, int n_cols, SampleSmem& sm) {
+    const int s = topk_sample_row<MG_WORKERS>(a.logits + (long)row * a.V, a.V, a.sample_lanes, a.sample_k,
+                                              a.sample_rnd[(long)col * a.B + row], sm, (int)threadIdx.x, MG_BAR_WORK, nullptr, nullptr);
+    if (threadIdx.x == 0) {
+        a.next[row] = s;
+        if (col < n_cols) a.out_tokens[(long)row * n_cols + col] = s;
+        a.ctx[row] += 1;
+    }
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------
 template <int BN>
 __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid_constant__ MegaArgs a) {
@@ -691,7 +705,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 else mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
             }
         } else if (k == 11) {
-            if (cta < a.B) mega_row_argmax(a, cta, col, n_cols, arg_v, arg_i);
+            if (cta < a.B) {
+                if (a.sample_k > 0) mega_row_sample(a, cta, col, n_cols, *reinterpret_cast<SampleSmem*>(scratch));
+                else mega_row_argmax(a, cta, col, n_cols, arg_v, arg_i);
+            }
             if (cta == 0 && tid == 0) a.state[0] = col + 1;
         } else {
             const int kind = k == 1 ? 0 : k == 4 ? 1 : k == 6 ? 2 : k == 8 ? 3 : 4;
@@ -855,11 +872,16 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     a.sync_ctr = (unsigned long long*)p->dev_ctr; a.error_flag = device_error_flag();
     a.fht_x = (float*)p->dev_fht_x; a.fht_flags = (int*)p->dev_fht_flags;
     a.trace = (unsigned long long*)p->dev_trace;
+    a.sample_lanes = 0; a.sample_k = 0; a.sample_rnd = nullptr;
     a.stages = stages; a.cs = cs; a.scratch_bytes = scratch; a.attn_bytes = attn_bytes;
     a.ks_qkv = ks_qkv; a.ks_o = ks_o; a.ks_d = ks_d; a.slab_rows = v.max_batch;
     if (!a.error_flag) { mega_destroy(p); return FLEXLLM_ECUDA; }
     *out = p;
     return FLEXLLM_OK;
+}
+
+void mega_set_sampling(MegaPlan* p, int lanes, int top_k, const float* rnd) {
+    p->args.sample_lanes = lanes; p->args.sample_k = top_k; p->args.sample_rnd = rnd;
 }
 
 int mega_reset(MegaPlan* p, cudaStream_t st) {

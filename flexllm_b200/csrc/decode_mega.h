@@ -33,6 +33,8 @@ int mega_create(const MegaModelView& v, MegaPlan** out);
 void mega_destroy(MegaPlan* p);
 // Zeroes the grid-barrier counter (start of a generation, or after an error).
 int mega_reset(MegaPlan* p, cudaStream_t st);
+// Token choice of the following steps: top_k == 0 greedy, else top-k sampling with rnd [n_new][B] (device).
+void mega_set_sampling(MegaPlan* p, int lanes, int top_k, const float* rnd);
 // One decode step for B sequences (one kernel launch).
 int mega_launch(MegaPlan* p, int B, cudaStream_t st);
 

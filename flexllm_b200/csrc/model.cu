@@ -44,6 +44,8 @@ int dequant_residual(const int32_t* acc, const float* s_tok, const float* s_ch, 
 int argmax_pair(const float* logits, int B, long V, int offset, void* pairs, cudaStream_t st);
 int argmax_select(const void* pairs, int g, int B, int32_t* idx, cudaStream_t st);
 int fht_quant_gathered(const float* h, int M, int g, int r, float scale, int8_t* q, float* s, cudaStream_t st);
+int topk_sample(const float* logits, int B, long V, int lanes, int top_k, const float* rnd, const int32_t* col, int32_t* idx,
+                int32_t* top_idx, float* top_val, cudaStream_t st);
 
 // x[t][:] = (float)lm_w[tok[t]][:] * lm_s[tok[t]]
 __global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ lm_w, const float* __restrict__ lm_s,
@@ -122,6 +124,8 @@ struct flexllm_model {
     void *pairs_l = nullptr, *pairs_g = nullptr;
     // persistent decode-step kernel: -1 not tried yet, 0 not usable for this model, 1 ready
     flexllm::MegaPlan* mega = nullptr; int mega_state = -1;
+    // token choice: greedy (sample_k == 0) or the reference's top-k sampling with uniform numbers rnd [n_new][B]
+    int sample_lanes = 0, sample_k = 0; const float* sample_rnd = nullptr;
 };
 
 template <class T> static int dmalloc(flexllm_model* m, T** p, size_t n) {
@@ -271,14 +275,18 @@ extern "C" int flexllm_model_load_head(flexllm_model* m, const int8_t* lm_w, con
 }
 
 // lm_head on the rows of xin [B][D] -> logits, argmax -> m->next
-static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaStream_t st) {
+// col: device pointer to the output column this head call fills (selects the row of sampling numbers), or
+// nullptr for column 0 (the prefill's token)
+static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaStream_t st, const int32_t* col = nullptr) {
     const int D = m->cfg.hidden, V = m->cfg.vocab;
     TRY(flexllm_rmsnorm_quant(xin, m->g_final, B, D, m->cfg.eps, order, nullptr, m->xq, m->xs, st));
     if (m->g == 1) {
         TRY(flexllm_linear_decode_i8(m->xq, m->xs, m->lm_w, m->lm_s, B, V, D, nullptr, m->logits, st));
-        TRY(flexllm_logits_argmax(m->logits, B, V, m->next, st));
+        if (m->sample_k > 0) TRY(topk_sample(m->logits, B, V, m->sample_lanes, m->sample_k, m->sample_rnd, col, m->next, nullptr, nullptr, st));
+        else TRY(flexllm_logits_argmax(m->logits, B, V, m->next, st));
         return FLEXLLM_OK;
     }
+    if (m->sample_k > 0) return FLEXLLM_ENOTSUP;      // sampling needs the whole vocabulary on one GPU
     // vocab-parallel: this rank's rows of the (replicated) lm_head, local argmax, gather, select
     const int Vl = m->Vl, off = m->r * Vl;
     TRY(flexllm_linear_decode_i8(m->xq, m->xs, m->lm_w + (size_t)off * D, m->lm_s + off, B, Vl, D, nullptr, m->logits, st));
@@ -360,7 +368,7 @@ static int mega_prepare(flexllm_model* m) {
     v.ctx = m->ctx; v.next = m->next; v.out_tokens = m->out_tokens; v.state = m->state;
     v.x = m->x; v.xq = m->xq; v.xs = m->xs; v.hq = m->hq; v.att = m->att; v.logits = m->logits;
     const int rc = mega_create(v, &m->mega);
-    if (rc == FLEXLLM_OK) m->mega_state = 1;
+    if (rc == FLEXLLM_OK) { m->mega_state = 1; mega_set_sampling(m->mega, m->sample_lanes, m->sample_k, m->sample_rnd); }
     else if (rc != FLEXLLM_ENOTSUP) return rc;
     return FLEXLLM_OK;
 }
@@ -412,7 +420,7 @@ static int decode_step_body(flexllm_model* m, cudaStream_t st) {
             TRY(dequant_residual(m->acc32, m->xs, L.sd, B, D, m->x, m->x, st));
         }
     }
-    TRY(run_head(m, m->x, B, FLEXLLM_NORM_DECODE8, st));
+    TRY(run_head(m, m->x, B, FLEXLLM_NORM_DECODE8, st, m->state));
     launch_k(step_bookkeeping_kernel, dim3(1), dim3(64), 0, st, (const int32_t*)m->next, B, m->out_tokens, m->state, m->ctx, 1);
     return launch_status();
 }
@@ -487,6 +495,22 @@ extern "C" int flexllm_model_generate_host(flexllm_model* m, const int32_t* toke
     FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(out_host, m->out_tokens, (size_t)B * n_new * 4, cudaMemcpyDeviceToHost, st));
     FLEXLLM_CHECK_CUDA(cudaStreamSynchronize(st));
     return gemm_check_error_flag();
+}
+
+// Token choice for the following prefill / decode calls: top_k == 0 -> greedy argmax (the default); otherwise the
+// reference's top-k sampling (Logits.h:145-279) with `lanes` lanes and the uniform numbers rnd [n_new][B] in device
+// memory (row = output column, i.e. the reference's rand_seeds_mmap per decode step; B = the batch of the
+// following prefill). The pointer must stay valid while it is in use.
+extern "C" int flexllm_model_set_sampling(flexllm_model* m, int lanes, int top_k, const float* rnd) {
+    FLEXLLM_REQUIRE(m && top_k >= 0);
+    if (top_k > 0) {
+        FLEXLLM_REQUIRE(rnd && lanes > 0);
+        if (top_k > 8 || lanes > 64 || m->cfg.vocab % lanes || m->cfg.vocab / lanes < top_k || m->g != 1) return FLEXLLM_ENOTSUP;
+    }
+    m->sample_lanes = top_k > 0 ? lanes : 0; m->sample_k = top_k; m->sample_rnd = top_k > 0 ? rnd : nullptr;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }      // the captured step holds the old choice
+    if (m->mega) mega_set_sampling(m->mega, m->sample_lanes, m->sample_k, m->sample_rnd);
+    return FLEXLLM_OK;
 }
 
 // Device pointers of internal buffers, for tests: 0 = residual stream x, 1 = logits of the last head

@@ -390,6 +390,11 @@ class Model:
             self._h, C.c_void_p(tokens_cpu.data_ptr()), B, S, n_new, C.c_void_p(out.data_ptr()), 1 if use_graph else 0, _stream()))
         return out
 
+    def set_sampling(self, lanes=0, top_k=0, rnd=None):
+        """top_k == 0: greedy. Else top-k sampling with uniform numbers rnd [n_new, B] (CUDA fp32; kept alive here)."""
+        self._rnd = rnd.contiguous() if rnd is not None else None
+        _check("flexllm_model_set_sampling", lib().flexllm_model_set_sampling(self._h, lanes, top_k, _ptr(self._rnd) if self._rnd is not None else None))
+
     def buffer(self, which, shape, dtype):
         p = C.c_void_p()
         _check("flexllm_model_buffer", lib().flexllm_model_buffer(self._h, which, C.byref(p)))

@@ -253,6 +253,12 @@ FLEXLLM_API int flexllm_model_decode(flexllm_model* m, int n_steps, int use_grap
 /* Whole request through HOST buffers: tokens_host [B][S] -> out_host [B][n_new]; synchronises. */
 FLEXLLM_API int flexllm_model_generate_host(flexllm_model* m, const int32_t* tokens_host, int B, int S, int n_new,
                                 int32_t* out_host, int use_graph, void* stream);
+/* Token choice of the following prefill / decode calls. top_k == 0: greedy argmax (default). Otherwise the reference's
+ * top-k sampling (flexllm_topk_sample) with `lanes` lanes and uniform numbers rnd [n_new][B] in DEVICE memory, row c for
+ * output column c -- the reference's rand_seeds_mmap, one number per decode step (SpinQuant_Decoding_mem_opt.h:934-937).
+ * The token feedback stays on the device in both decode paths. Single GPU only. */
+FLEXLLM_API int flexllm_model_set_sampling(flexllm_model* m, int lanes, int top_k, const float* rnd);
+
 /* Device pointers of internal buffers (tests): 0 residual stream, 1 logits, 2 token table, 3 ctx. */
 FLEXLLM_API int flexllm_model_buffer(flexllm_model* m, int which, void** ptr);
 

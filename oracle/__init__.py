@@ -275,11 +275,11 @@ class _OrcModel(C.Structure):
                 [("g_final", C.c_void_p), ("lm_w", C.c_void_p), ("lm_s", C.c_void_p), ("cos_t", C.c_void_p), ("sin_t", C.c_void_p)])
 
 
-def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False):
+def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False, sampling=None):
     """Full-model greedy generation on the CPU. `weights`: dict with per-layer lists under the keys
     wq wk wv wo wg wu wd (int8 [N,K]), sq sk sv so sg su sd g0 g1 a_s (fp32) and g_final, lm_w, lm_s,
-    cos_t, sin_t, plus ints HQ, HKV. tokens [B,S] int32. Returns dict(tokens [B,n_new], hidden, logits_prefill,
-    logits_last)."""
+    cos_t, sin_t, plus ints HQ, HKV. tokens [B,S] int32. sampling: None (greedy) or (lanes, top_k, rnd [n_new,B])
+    for the reference's top-k sampling. Returns dict(tokens [B,n_new], hidden, logits_prefill, logits_last)."""
     tokens = _i32(tokens); B, S = tokens.shape
     L = len(weights["wq"]); D = weights["wq"][0].shape[1]; F = weights["wg"][0].shape[0]; V = weights["lm_w"].shape[0]
     keep = []
@@ -301,7 +301,14 @@ def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False)
     hidden = np.empty((B * S, D), np.float32) if want_hidden else None
     lp = np.empty((B, V), np.float32) if want_logits else None
     ll = np.empty((B, V), np.float32) if (want_logits and n_new > 1) else None
-    _lib.orc_model_generate(C.byref(m), _p(tokens), C.c_int(B), C.c_int(S), C.c_int(n_new), _p(out), _p(hidden), _p(lp), _p(ll))
+    rnd = None
+    if sampling is not None:
+        rnd = _f32(np.asarray(sampling[2]).reshape(max(n_new, 1), B))
+        _lib.orc_set_sampling(C.c_int(sampling[0]), C.c_int(sampling[1]), _p(rnd))
+    try:
+        _lib.orc_model_generate(C.byref(m), _p(tokens), C.c_int(B), C.c_int(S), C.c_int(n_new), _p(out), _p(hidden), _p(lp), _p(ll))
+    finally:
+        _lib.orc_set_sampling(C.c_int(0), C.c_int(0), None)
     return dict(tokens=out[:, :n_new], hidden=hidden, logits_prefill=lp, logits_last=ll)
 
 

@@ -350,6 +350,12 @@ ORC_API int orc_topk_sample(const float* logits, int B, long V, int lanes, int t
     return 0;
 }
 
+// Token choice of orc_model_generate: greedy (top_k 0, the default) or top-k sampling with uniform numbers
+// rnd [n_new][B] (row = output column).
+static int g_sample_lanes = 0, g_sample_k = 0, g_sample_step = 0;
+static const float* g_sample_rnd = nullptr;
+ORC_API void orc_set_sampling(int lanes, int top_k, const float* rnd) { g_sample_lanes = lanes; g_sample_k = top_k; g_sample_rnd = rnd; }
+
 // ----------------------------------------------------------------------------------------------
 // Config 1: one W8A8 linear layer on already-quantised activations.
 // ----------------------------------------------------------------------------------------------
@@ -692,7 +698,8 @@ static void model_head(const OrcModel& m, const float* x, int M, int lanes, floa
     orc_quant_per_token(xn.data(), M, m.D, xq.data(), xs.data());
     if (!logits) { lg.resize((size_t)M * m.V); logits = lg.data(); }
     orc_linear_i8(xq.data(), xs.data(), m.lm_w, m.lm_s, M, m.V, m.D, nullptr, logits);
-    orc_argmax(logits, M, m.V, next);
+    if (g_sample_k > 0) orc_topk_sample(logits, M, m.V, g_sample_lanes, g_sample_k, g_sample_rnd + (size_t)g_sample_step * M, next, nullptr, nullptr, nullptr);
+    else orc_argmax(logits, M, m.V, next);
 }
 
 // tokens [B][S] -> greedy generation of n_new tokens per sequence: out_tokens [B][n_new].
@@ -715,6 +722,7 @@ ORC_API void orc_model_generate(const OrcModel* mp, const int32_t* tokens, int B
     std::vector<float> last((size_t)B * m.D);
     for (int b = 0; b < B; b++) std::memcpy(&last[(size_t)b * m.D], &x[((size_t)b * S + S - 1) * m.D], sizeof(float) * m.D);
     std::vector<int32_t> next(B);
+    g_sample_step = 0;
     if (n_new <= 0) { if (logits_prefill) model_head(m, last.data(), B, 0, logits_prefill, next.data()); return; }
     model_head(m, last.data(), B, 0, logits_prefill, next.data());
     for (int b = 0; b < B; b++) out_tokens[(size_t)b * n_new] = next[b];
@@ -723,6 +731,7 @@ ORC_API void orc_model_generate(const OrcModel* mp, const int32_t* tokens, int B
         for (int b = 0; b < B; b++) { dseq[b] = b; dpos[b] = S + step - 1; }
         model_embed(m, next.data(), B, x);
         for (int l = 0; l < m.L; l++) model_layer(m, l, x, B, dseq.data(), dpos.data(), c, 8);
+        g_sample_step = step;
         model_head(m, x.data(), B, 8, step == n_new - 1 ? logits_last : nullptr, next.data());
         for (int b = 0; b < B; b++) out_tokens[(size_t)b * n_new + step] = next[b];
     }

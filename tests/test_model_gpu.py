@@ -91,3 +91,27 @@ def test_model_kernel_per_operator_decode(F, monkeypatch):
     shapes outside the persistent kernel's range use): same bits."""
     monkeypatch.setenv("FLEXLLM_MEGA", "0")
     run_case(F, layers=2, hidden=512, hq=8, hkv=2, vocab=1000, B=12, S=16, n_new=4, seed=53, use_graph=True)
+
+
+@pytest.mark.parametrize("mega", ["1", "0"])
+def test_model_topk_sampling(F, monkeypatch, mega):
+    """Generation with the reference's top-k sampling (Logits.h:145-279), token feedback on the device: identical
+    token streams on the persistent-kernel path and the kernel-per-operator path."""
+    from flexllm_b200 import synthetic
+    monkeypatch.setenv("FLEXLLM_MEGA", mega)
+    layers, hidden, hq, hkv, vocab, B, S, n_new, seed = 2, 512, 8, 2, 1024, 5, 32, 7, 57
+    W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, S + n_new, seed=seed)
+    tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
+    rnd = np.random.default_rng(seed + 2).random((n_new, B)).astype(np.float32)
+    m = F.Model(layers, hidden, hq, hkv, 8192, vocab, max_batch=B, max_prefill=S, max_ctx=S + n_new)
+    synthetic.load_numpy_weights(m, W)
+    m.set_sampling(lanes=32, top_k=5, rnd=torch.from_numpy(rnd).cuda())
+    out = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=True)
+    ref = oracle.model_generate(W, tokens, n_new, sampling=(32, 5, rnd))
+    greedy = oracle.model_generate(W, tokens, n_new)
+    assert np.array_equal(out.numpy(), ref["tokens"])
+    assert not np.array_equal(ref["tokens"], greedy["tokens"])          # the sampler does pick other ranks here
+    m.set_sampling()                                                     # back to greedy
+    out = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=True)
+    assert np.array_equal(out.numpy(), greedy["tokens"])
+    m.close()
