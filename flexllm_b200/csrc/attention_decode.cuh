@@ -59,6 +59,7 @@ struct DecAttnSmem {
     __align__(16) int8_t q_sm[4][64];
     float q_scale[4], red[4][16], row_max[4], row_rinv[4], part[4][4];
     int pt_sm[160];
+    int last;           // scratch flag for callers (e.g. "this item completed its sequence")
 };
 
 // One call by a group of NT threads per (sequence b, KV head hkv) does the whole step for its GQA group of 4 query

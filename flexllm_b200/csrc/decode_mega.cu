@@ -10,8 +10,7 @@
 //   per layer   A  x += dequant(down partial sums) [embedding for layer 0], RMSNorm, int8 quant
 //               .  fused q|k|v projection          (tcgen05 kind::i8, split-K over the CTAs)
 //               .  attention per (sequence, KV head): dequant, RoPE, FHT-64, quant, cache append,
-//                  scores, ordered softmax, u8 quant, P.V
-//               B  int8 quant of the attention output rows
+//                  scores, ordered softmax, u8 quant, P.V; the item that completes a sequence's row quantises it
 //               .  o projection
 //               C  x += dequant(o partial sums), RMSNorm, int8 quant
 //               .  fused gate|up projection
@@ -57,7 +56,8 @@ constexpr int MG_BAR_FHT = 2;                   // named barrier of the 256 FHT 
 constexpr int MG_BAR_HALF0 = 3, MG_BAR_HALF1 = 4;  // named barriers of the two 256-thread halves (attention)
 constexpr int MG_MAX_KS = 10;                   // most split-K slabs a projection may use
 constexpr int MG_A_TILE = 128 * 128;            // weight tile: 128 channels x 128 bytes of K
-constexpr int MG_PHASES_PER_LAYER = 9;
+// phases of a layer, then of the head
+enum { PH_A = 0, PH_QKV, PH_ATT, PH_O, PH_C, PH_GU, PH_D, PH_DOWN, MG_PHASES_PER_LAYER, PH_E = MG_PHASES_PER_LAYER, PH_LM, PH_TOKEN };
 constexpr int MG_FHT_SCRATCH = (8192 + 256 + 80) * 4;   // padded row + reduction slots
 
 struct MegaLayer {
@@ -80,6 +80,7 @@ struct MegaArgs {
     unsigned long long* sync_ctr; int* error_flag;
     float* fht_x;                 // FHT phase split over 4 CTAs per row: the parts' locally transformed values [max_batch][F]
     int* fht_flags;               // [3][max_batch]: parts published, parts' maxima merged, merged |max| as float bits
+    int* att_cnt;                 // [max_batch]: attention items of the sequence that have finished (self-resetting)
     unsigned long long* trace;    // optional phase timeline [barrier][arrive, leave][CTA] in globaltimer ns (last launch)
     int stages, cs, scratch_bytes;
     int attn_bytes;               // per-half attention scratch: score rows (20 bytes per key) + DecAttnSmem
@@ -256,27 +257,51 @@ __device__ __forceinline__ void mega_row_norm(const MegaArgs& a, int row, const 
     }
 }
 
-// int8 quantiser of one attention output row (Modules/quant.h:349-430)
-__device__ __forceinline__ void mega_row_quant(const MegaArgs& a, int row, float* red, int tid) {
-    constexpr int NT = MG_WORKERS;
-    const int D = a.D, nv = D >> 2, c = tid;
-    const bool active = c < nv;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+// Attention output row b -> int8 (Modules/quant.h:349-430), by the 256 threads of the half whose item arrived
+// last on the sequence's counter. Arrival: acq_rel atomic by one thread after the half's barrier (orders the
+// half's stores before it; the last arriver sees every other item's stores after it).
+__device__ __forceinline__ void mega_att_row_quant(const MegaArgs& a, int b, DecAttnSmem& sm, int t, int bar) {
+    named_sync_id<256>(bar);
+    if (t == 0) {
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(a.att_cnt + b), "r"(1) : "memory");
+        sm.last = old == a.HKV - 1;
+        if (sm.last) a.att_cnt[b] = 0;          // next use: the next layer's attention phase, grid barriers away
+    }
+    named_sync_id<256>(bar);
+    if (!sm.last) return;
+    const int D = a.D, nv = D >> 2;
+    const float4* src = reinterpret_cast<const float4*>(a.att + (long)b * D);
+    float4 v[2];
     float mx = -1e32f, mn = 1e32f;
-    if (active) {
-        v = __ldcg(reinterpret_cast<const float4*>(a.att + (long)row * D) + c);
-        mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-        mn = fminf(fminf(v.x, v.y), fminf(v.z, v.w));
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int c = t + i * 256;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < nv) {
+            v[i] = __ldcg(src + c);
+            mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            mn = fminf(mn, fminf(fminf(v[i].x, v[i].y), fminf(v[i].z, v[i].w)));
+        }
     }
-    group_max_min<MG_BAR_WORK, NT>(mx, mn, red, tid);
+    mx = warp_max(mx); mn = warp_min(mn);
+    if ((t & 31) == 0) { sm.red[0][t >> 5] = mx; sm.red[1][t >> 5] = mn; }
+    named_sync_id<256>(bar);
+#pragma unroll
+    for (int w = 0; w < 8; w++) { mx = fmaxf(mx, sm.red[0][w]); mn = fminf(mn, sm.red[1][w]); }
     const float sc = sym_scale_from(mx, mn);
-    if (tid == 0) a.xs[row] = sc;
-    if (active) {
-        char4 o;
-        o.x = quant_s8(v.x, sc); o.y = quant_s8(v.y, sc); o.z = quant_s8(v.z, sc); o.w = quant_s8(v.w, sc);
-        reinterpret_cast<char4*>(a.xq + (long)row * D)[c] = o;
-        asm volatile("fence.proxy.async.global;" ::: "memory");   // xq is read by other CTAs' TMA (async proxy)
+    if (t == 0) a.xs[b] = sc;
+    char4* qr = reinterpret_cast<char4*>(a.xq + (long)b * D);
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int c = t + i * 256;
+        if (c < nv) {
+            char4 o;
+            o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc); o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+            qr[c] = o;
+        }
     }
+    asm volatile("fence.proxy.async.global;" ::: "memory");   // xq is read by other CTAs' TMA (async proxy)
 }
 
 // dequant(gate|up sums) -> silu(gate)*up -> FHT-8192 / scale -> int8 quant. All 512 threads fetch and
@@ -668,14 +693,14 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
         int l = p / MG_PHASES_PER_LAYER, k = p - MG_PHASES_PER_LAYER * l;
         if (l >= L) { k = MG_PHASES_PER_LAYER + (p - MG_PHASES_PER_LAYER * L); l = L - 1; }
         const MegaLayer& ly = a.layers[l];
-        if (k == 0 || k == 5 || k == 9) {
+        if (k == PH_A || k == PH_C || k == PH_E) {
             if (cta < a.B) {
                 const int32_t* acc; int ks; const float *s_ch, *gamma;
-                if (k == 5) { acc = a.w_o; ks = a.ks_o; s_ch = ly.so; gamma = ly.g1; }
-                else if (k == 9) { acc = a.w_d; ks = a.ks_d; s_ch = ly.sd; gamma = a.g_final; }
+                if (k == PH_C) { acc = a.w_o; ks = a.ks_o; s_ch = ly.so; gamma = ly.g1; }
+                else if (k == PH_E) { acc = a.w_d; ks = a.ks_d; s_ch = ly.sd; gamma = a.g_final; }
                 else { acc = p == 0 ? nullptr : a.w_d; ks = a.ks_d; s_ch = p == 0 ? nullptr : a.layers[l - 1].sd; gamma = ly.g0; }
                 mega_row_norm(a, cta, acc, ks, s_ch, gamma, rowbuf, rowred, tid);
-            } else if ((p == 0 || (k == 5 && l + 1 < L)) && G > a.B) {
+            } else if ((p == 0 || (k == PH_C && l + 1 < L)) && G > a.B) {
                 // CTAs without a row ask L2 for the KV pages an attention phase will read (any CTA can do this
                 // for any item: L2 is shared): the first layer's at the start of the step, and in every phase C
                 // those of the NEXT layer, long before they are needed
@@ -683,7 +708,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
                     dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
             }
-        } else if (k == 2) {
+        } else if (k == PH_ATT) {
             DecAttnIn in;
             in.q = in.k = in.v = nullptr; in.qs = in.ks = in.vs = nullptr; in.qkv_f32 = nullptr;
             in.qkv_acc = a.w_qkv; in.tok_scale = a.xs; in.ch_scale = ly.sqkv;
@@ -693,25 +718,28 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             const int half = tid >> 8;
             uint8_t* dsm = scratch + (size_t)half * a.attn_bytes;
             DecAttnSmem& sm = *reinterpret_cast<DecAttnSmem*>(dsm + a.attn_bytes - sizeof(DecAttnSmem));
-            for (int idx = 2 * cta + half; idx < a.B * a.HKV; idx += 2 * G)
+            for (int idx = 2 * cta + half; idx < a.B * a.HKV; idx += 2 * G) {
+                const int b = idx / a.HKV;
                 dec_attn_fused_body<2, 256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
-                                            a.att, nullptr, idx % a.HKV, idx / a.HKV, dsm, sm, tid & 255, MG_BAR_HALF0 + half);
-        } else if (k == 3) {
-            if (cta < a.B) mega_row_quant(a, cta, rowred, tid);
-        } else if (k == 7) {
+                                            a.att, nullptr, idx % a.HKV, b, dsm, sm, tid & 255, MG_BAR_HALF0 + half);
+                // the item that completes its sequence's attention row (the last of its HKV items to arrive)
+                // quantises the row for the o projection -- no separate phase, no extra grid barrier
+                mega_att_row_quant(a, b, sm, tid & 255, MG_BAR_HALF0 + half);
+            }
+        } else if (k == PH_D) {
             const int parts = 4 * a.B <= G ? 4 : 1;         // CTAs per row
             if (cta < parts * a.B) {
                 if (parts == 4) mega_row_fht4(a, ly, cta >> 2, cta & 3, rowbuf, rowred, tid, abort_flag);
                 else mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
             }
-        } else if (k == 11) {
+        } else if (k == PH_TOKEN) {
             if (cta < a.B) {
                 if (a.sample_k > 0) mega_row_sample(a, cta, col, n_cols, *reinterpret_cast<SampleSmem*>(scratch));
                 else mega_row_argmax(a, cta, col, n_cols, arg_v, arg_i);
             }
             if (cta == 0 && tid == 0) a.state[0] = col + 1;
         } else {
-            const int kind = k == 1 ? 0 : k == 4 ? 1 : k == 6 ? 2 : k == 8 ? 3 : 4;
+            const int kind = k == PH_QKV ? 0 : k == PH_O ? 1 : k == PH_GU ? 2 : k == PH_DOWN ? 3 : 4;
             if (kind == 3 && cta == G - 1 && tid < 3 * a.slab_rows) a.fht_flags[tid] = 0;   // idle until the next FHT phase
             const MegaJob j = mega_job(a, l, kind);
             const MegaJob nj = kind < 3 ? mega_job(a, l, kind + 1) : (p + 1 < MG_PHASES_PER_LAYER * L ? mega_job(a, l + 1, 0) : mega_job(a, 0, 4));
@@ -846,7 +874,7 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     if (e == cudaSuccess) e = cudaMemcpy(p->dev_layers, layers.data(), v.layers * sizeof(MegaLayer), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(p->dev_work, 0, p->work_bytes);
     if (e == cudaSuccess) e = cudaMemset(p->dev_ctr, 0, 256);
-    p->n_flags = 3 * v.max_batch;
+    p->n_flags = 4 * v.max_batch;
     if (e == cudaSuccess) e = cudaMalloc(&p->dev_fht_x, (size_t)v.max_batch * v.F * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&p->dev_fht_flags, p->n_flags * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(p->dev_fht_flags, 0, p->n_flags * sizeof(int));
@@ -870,7 +898,7 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     a.page_table = v.page_table; a.max_pages = v.max_pages;
     a.ctx = v.ctx; a.next = v.next; a.out_tokens = v.out_tokens; a.state = v.state;
     a.sync_ctr = (unsigned long long*)p->dev_ctr; a.error_flag = device_error_flag();
-    a.fht_x = (float*)p->dev_fht_x; a.fht_flags = (int*)p->dev_fht_flags;
+    a.fht_x = (float*)p->dev_fht_x; a.fht_flags = (int*)p->dev_fht_flags; a.att_cnt = a.fht_flags + 3 * v.max_batch;
     a.trace = (unsigned long long*)p->dev_trace;
     a.sample_lanes = 0; a.sample_k = 0; a.sample_rnd = nullptr;
     a.stages = stages; a.cs = cs; a.scratch_bytes = scratch; a.attn_bytes = attn_bytes;
