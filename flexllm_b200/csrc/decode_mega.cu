@@ -14,24 +14,24 @@
 //               .  o projection
 //               C  x += dequant(o partial sums), RMSNorm, int8 quant
 //               .  fused gate|up projection
-//               D  dequant, silu(gate)*up, FHT-8192, int8 quant
+//               D  dequant, silu(gate)*up, FHT-8192, int8 quant (four CTAs per row when the grid allows)
 //               .  down projection
-//   head        E  x += dequant(down partial sums), final RMSNorm, quant;  lm_head;  greedy argmax,
-//                  token feedback, context lengths + 1
+//   head        E  x += dequant(down partial sums), final RMSNorm, quant;  lm_head;  greedy argmax or
+//                  top-k sampling, token feedback, context lengths + 1
 //
 // Projections leave raw int32 sums (split-K: one slab of partial sums per split, plain coalesced
 // stores; the reader adds the slabs -- integers, exact in any order); the row phase that follows
-// applies ((float)acc * s_tok) * s_ch itself, so a
-// projection's result crosses HBM/L2 once. One thread issues both the TMA loads and the MMAs: as
-// soon as it has issued the last MMA of one projection it starts streaming the WEIGHT tiles of the
-// next one into the ring -- weights do not depend on the phases in between -- and only the small
-// activation tiles wait for the grid barrier. Arithmetic is the same device code the stand-alone
-// kernels use (attention_decode.cuh, fht_core.cuh, rmsnorm_core.cuh), hence bit-identical.
+// applies ((float)acc * s_tok) * s_ch itself, so a projection's result crosses HBM/L2 once. One
+// thread (warp 4) issues the TMA loads, one (warp 5) the MMAs, warps 0..3 drain TMEM. As soon as the
+// TMA thread has issued the last loads of one projection it starts streaming the WEIGHT tiles of
+// the next one into the ring -- weights do not depend on the phases in between -- and only the
+// small activation tiles wait for the grid barrier. Arithmetic is the same device code the
+// stand-alone kernels use (attention_decode.cuh, fht_core.cuh, sampling.cuh; the RMSNorm statements of
+// rmsnorm_core.cuh spread over a CTA), hence bit-identical.
 //
 // Every wait (mbarrier, grid barrier) is bounded; on a timeout the CTA raises the global error
 // flag, all CTAs leave through the tear-down and the host sees FLEXLLM_ETIMEDOUT.
 #include <cstdio>
-#include <string>
 #include <cstdlib>
 #include <new>
 #include <vector>

@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const float* __res
     }
     block_max_min(mx, mn, red);
     const float sc = sym_scale_from(mx, mn);
+    const DivBy dsc = div_by(sc);       // one reciprocal per row: every element is then quantised without a full division
     if (threadIdx.x == 0) s[row] = sc;
     char4* qr = reinterpret_cast<char4*>(q + row * K);
 #pragma unroll
@@ -42,8 +43,8 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const float* __res
         int c = threadIdx.x + i * 256;
         if (c < nv) {
             char4 o;
-            o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc);
-            o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+            o.x = (int8_t)(int)roundf(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v[i].y, dsc));
+            o.z = (int8_t)(int)roundf(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v[i].w, dsc));
             qr[c] = o;
         }
     }
@@ -119,6 +120,7 @@ __device__ __forceinline__ void rmsnorm_output_row(const float* __restrict__ xr,
     if (qr8) {
         mx = warp_max(mx); mn = warp_min(mn);
         const float sc = sym_scale_from(mx, mn);
+    const DivBy dsc = div_by(sc);       // one reciprocal per row: every element is then quantised without a full division
         if (lane == 0) *srow = sc;
         char4* qr = reinterpret_cast<char4*>(qr8);
 #pragma unroll
@@ -126,7 +128,7 @@ __device__ __forceinline__ void rmsnorm_output_row(const float* __restrict__ xr,
             int c = lane + i * 32;
             if (c < nv) {
                 char4 w;
-                w.x = quant_s8(o[i].x, sc); w.y = quant_s8(o[i].y, sc); w.z = quant_s8(o[i].z, sc); w.w = quant_s8(o[i].w, sc);
+                w.x = (int8_t)(int)roundf(div_for_rounding(o[i].x, dsc)); w.y = (int8_t)(int)roundf(div_for_rounding(o[i].y, dsc)); w.z = (int8_t)(int)roundf(div_for_rounding(o[i].z, dsc)); w.w = (int8_t)(int)roundf(div_for_rounding(o[i].w, dsc));
                 qr[c] = w;
             }
         }
@@ -144,14 +146,21 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_prefill_kernel(const f
     if (row0 >= M) return;
     const int rr = lane >> 2, j = lane & 3;      // chain (row rr of the group, residue j)
     float ss = 0.0f;
-    for (int p = 0; p < D; p += RMS_PIECE) {
+    // the next piece's loads are in flight while the chains run over the current one
+    float4 nxt[8];
+    auto fetch = [&](int p) {
 #pragma unroll
         for (int r = 0; r < 8; r++) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row0 + r < M) v = *reinterpret_cast<const float4*>(x + (row0 + r) * D + p + lane * 4);
-            *reinterpret_cast<float4*>(&stage[w][r][lane * 4]) = v;
+            nxt[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row0 + r < M) nxt[r] = *reinterpret_cast<const float4*>(x + (row0 + r) * D + p + lane * 4);
         }
+    };
+    fetch(0);
+    for (int p = 0; p < D; p += RMS_PIECE) {
+#pragma unroll
+        for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(&stage[w][r][lane * 4]) = nxt[r];
         __syncwarp();
+        if (p + RMS_PIECE < D) fetch(p + RMS_PIECE);
 #pragma unroll
         for (int k = 0; k < RMS_PIECE / 4; k++) { const float v = stage[w][rr][4 * k + j]; ss += v * v; }
         __syncwarp();

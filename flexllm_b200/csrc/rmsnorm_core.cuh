@@ -54,6 +54,7 @@ __device__ __forceinline__ void rmsnorm_decode_row(float4 (&v)[MAXV], float4 (&g
     if (q_row) {
         mx = warp_max(mx); mn = warp_min(mn);
         const float sc = sym_scale_from(mx, mn);
+    const DivBy dsc = div_by(sc);       // one reciprocal per row: every element is then quantised without a full division
         if (lane == 0) *s_out = sc;
         char4* qr = reinterpret_cast<char4*>(q_row);
 #pragma unroll
@@ -61,7 +62,7 @@ __device__ __forceinline__ void rmsnorm_decode_row(float4 (&v)[MAXV], float4 (&g
             const int c = lane + i * 32;
             if (c < nv) {
                 char4 o;
-                o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc); o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+                o.x = (int8_t)(int)roundf(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v[i].y, dsc)); o.z = (int8_t)(int)roundf(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v[i].w, dsc));
                 qr[c] = o;
             }
         }

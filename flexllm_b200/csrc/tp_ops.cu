@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(256) quant_gathered_kernel(const float* __rest
     }
     block_max_min(mx, mn, red);
     const float sc = sym_scale_from(mx, mn);
+    const DivBy dsc = div_by(sc);       // one reciprocal per row: every element is then quantised without a full division
     if (threadIdx.x == 0) s[row] = sc;
     char4* qr = reinterpret_cast<char4*>(q + row * W);
 #pragma unroll
@@ -35,7 +36,7 @@ __global__ void __launch_bounds__(256) quant_gathered_kernel(const float* __rest
         const int c = threadIdx.x + i * 256;
         if (c < nv && c / wv == r) {
             char4 o;
-            o.x = quant_s8(v[i].x, sc); o.y = quant_s8(v[i].y, sc); o.z = quant_s8(v[i].z, sc); o.w = quant_s8(v[i].w, sc);
+            o.x = (int8_t)(int)roundf(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v[i].y, dsc)); o.z = (int8_t)(int)roundf(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v[i].w, dsc));
             qr[c - r * wv] = o;
         }
     }
