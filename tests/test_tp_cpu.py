@@ -10,7 +10,9 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-CFG = dict(hidden=512, hq=8, hkv=2, ffn=8192, vocab=1024, T=12, seed=70)
+CFGS = {2: dict(hidden=512, hq=8, hkv=2, ffn=8192, vocab=1024, T=12, seed=70),
+        4: dict(hidden=1024, hq=16, hkv=4, ffn=8192, vocab=1024, T=6, seed=71)}
+CFG = dict(CFGS[2])
 
 
 def _free_port():
@@ -58,6 +60,7 @@ def _single(oracle):
 
 
 def _rank(rank, world, port, ret):
+    CFG.clear(); CFG.update(CFGS[world])
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import oracle
@@ -104,13 +107,18 @@ def _rank(rank, world, port, ret):
     dist.barrier(); dist.destroy_process_group()
 
 
-def test_tp_partition_is_bit_exact_on_cpu():
+import pytest
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_partition_is_bit_exact_on_cpu(world):
     import oracle
+    CFG.clear(); CFG.update(CFGS[world])
     with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
         want_out, want_tok = _single(oracle)
     mgr = mp.Manager(); ret = mgr.dict()
-    mp.spawn(_rank, args=(2, _free_port(), ret), nprocs=2, join=True)
-    for rank in (0, 1):
+    mp.spawn(_rank, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for rank in range(world):
         out, tok = ret[rank]
         assert np.array_equal(out.view(np.uint32), want_out.view(np.uint32)), f"rank {rank}: residual stream differs"
         assert np.array_equal(tok, want_tok), f"rank {rank}: greedy tokens differ"

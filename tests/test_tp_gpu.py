@@ -42,16 +42,17 @@ def _worker(rank, world, port, cfg, ret):
     dist.barrier(); dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("cfg", [(2, 512, 8, 2, 1008, 2, 32, 4, 60), (2, 1024, 16, 4, 2000, 12, 48, 4, 61)])
-def test_tp2_matches_oracle(cfg):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world,cfg", [(2, (2, 512, 8, 2, 1008, 2, 32, 4, 60)), (2, (2, 1024, 16, 4, 2000, 12, 48, 4, 61)),
+                                       (4, (2, 1024, 16, 4, 2016, 5, 32, 4, 62))])
+def test_tp_matches_oracle(world, cfg):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     import oracle
     from flexllm_b200 import synthetic
     layers, hidden, hq, hkv, vocab, B, S, n_new, seed = cfg
     mgr = mp.Manager(); ret = mgr.dict()
-    mp.spawn(_worker, args=(2, _free_port(), cfg, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), cfg, ret), nprocs=world, join=True)
     W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, S + n_new, seed=seed)
     tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
     with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
