@@ -562,8 +562,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
         int t, kb, kb0, kb1, n_items, ksplit, num_kb, G;
         __device__ void range() {
             const int split = t % ksplit;
-            kb0 = kb = (int)((long)split * num_kb / ksplit);
-            kb1 = (int)((long)(split + 1) * num_kb / ksplit);
+            kb0 = kb = split * num_kb / ksplit;            // small numbers: 32-bit arithmetic
+            kb1 = (split + 1) * num_kb / ksplit;
         }
         __device__ void init(const MegaJob& j, int cta, int G_) {
             n_items = j.tilesA * j.ksplit; ksplit = j.ksplit; num_kb = j.num_kb; G = G_; t = cta; kb = kb0 = kb1 = 0;
@@ -661,14 +661,20 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                     uint32_t v[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + c * 32, v);
                     tmem_ld_wait();
+                    if (slab) {
+                        // the per-layer path: raw sums, one coalesced store per token (kept apart from the lm_head
+                        // path so that the code walked every layer stays short)
+                        int32_t* dst = slab + rowA + (long)(c * 32) * j.ldo;
+                        const int ntok = a.B - c * 32;
 #pragma unroll
-                    for (int jj = 0; jj < 32; jj++) {
-                        const int tok = c * 32 + jj;
-                        const float st = __shfl_sync(0xffffffffu, c == 0 ? xs0 : xs1, jj);
-                        if (row_ok && tok < a.B) {
-                            const long o = (long)tok * j.ldo + rowA;
-                            if (slab) slab[o] = (int)v[jj];
-                            else a.logits[o] = ((float)(int)v[jj] * st) * sa;
+                        for (int jj = 0; jj < 32; jj++)
+                            if (row_ok && jj < ntok) dst[(long)jj * j.ldo] = (int)v[jj];
+                    } else {
+#pragma unroll
+                        for (int jj = 0; jj < 32; jj++) {
+                            const int tok = c * 32 + jj;
+                            const float st = __shfl_sync(0xffffffffu, c == 0 ? xs0 : xs1, jj);
+                            if (row_ok && tok < a.B) a.logits[(long)tok * j.ldo + rowA] = ((float)(int)v[jj] * st) * sa;
                         }
                     }
                 }
