@@ -417,11 +417,15 @@ def gpu_arm(args):
     main_r = measure(use_tp, args.steps)
     other = None
     if multi and not args.no_extras:
-        o = measure(not use_tp, min(args.steps, 2), with_e2e=False)
-        nb_o = BATCH if not use_tp else BATCH * world
         other = {"parallelism": workload_config(world, "dp" if use_tp else "tp")["parallelism"],
-                 "scaling": "weak" if use_tp else "strong", "value": round(o["value"], 1), "unit": "tokens/s",
-                 "ms_per_step": round(o["ms_dev"] / min(args.steps, 2), 3), "phases": phases(o, nb_o)}
+                 "scaling": "weak" if use_tp else "strong"}
+        try:
+            o = measure(not use_tp, min(args.steps, 2), with_e2e=False)
+            nb_o = BATCH if not use_tp else BATCH * world
+            other.update({"value": round(o["value"], 1), "unit": "tokens/s",
+                          "ms_per_step": round(o["ms_dev"] / min(args.steps, 2), 3), "phases": phases(o, nb_o)})
+        except Exception as e:      # the side measurement must not take the headline line down with it
+            other.update({"value": None, "error": f"{type(e).__name__}: {e}"})
 
     if rank == 0:
         roof = cpu = None
