@@ -93,6 +93,7 @@ def cpu_port_baseline():
     one sequence, 64 prompt tokens + 2 generated."""
     import numpy as np
     import oracle
+    oracle.set_threads(os.cpu_count() or 1)      # a launcher (torchrun) may have exported OMP_NUM_THREADS=1
     from flexllm_b200 import synthetic
     S, n_new = 64, 2
     W = synthetic.numpy_weights(max_ctx=S + n_new, seed=0, **CFG)
@@ -100,7 +101,7 @@ def cpu_port_baseline():
     t0 = time.perf_counter()
     oracle.model_generate(W, tok, n_new)
     dt = time.perf_counter() - t0
-    return {"value": (S + n_new) / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+    return {"value": (S + n_new) / dt, "unit": "tokens/s", "cores": oracle.get_threads(), "kind": "port",
             "sample": f"full 16-layer model, batch 1, {S} prompt + {n_new} generated tokens, {dt:.1f} s"}
 
 
@@ -116,6 +117,7 @@ def reference_arm(args):
     kind = "reference" if R is not None else "port"
     T = 8
     threads = os.cpu_count() or 1
+    oracle.set_threads(threads)                  # a launcher (torchrun) may have exported OMP_NUM_THREADS=1
     W = synthetic.numpy_weights(1, CFG["hidden"], CFG["heads_q"], CFG["heads_kv"], CFG["ffn"], 2048, T + 1, seed=0)
     g = np.random.default_rng(2)
     x = g.standard_normal((T, CFG["hidden"])).astype(np.float32)
@@ -140,10 +142,16 @@ def reference_arm(args):
         xn = O.rmsnorm(x, W["g0"][0], lanes=0) if R is not None else oracle.rmsnorm(x, W["g0"][0])
         qf = linear(xn, W["wq"][0], W["sq"][0]); kf = linear(xn, W["wk"][0], W["sk"][0]); vf = linear(xn, W["wv"][0], W["sv"][0])
         pos = np.arange(T, dtype=np.int32)
-        qr = oracle.fht(oracle.rope(qf.reshape(T, HQ, 64), pos, W["cos_t"], W["sin_t"]), 8.0)
-        kr = oracle.fht(oracle.rope(kf.reshape(T, HKV, 64), pos, W["cos_t"], W["sin_t"]), 8.0)
-        q2, qs2 = oracle.quant_per_token(qr.reshape(T * HQ, 64)); k2, ks2 = oracle.quant_per_token(kr.reshape(T * HKV, 64))
-        v2, vs2 = oracle.quant_per_token(vf.reshape(T * HKV, 64))
+        if R is not None:           # RoPE, 64-point FHT and the per-head quantiser through the reference templates too
+            qr = R.fht(R.rope_prefill(qf.reshape(T, HQ, 64), W["cos_t"], W["sin_t"]), 8.0)
+            kr = R.fht(R.rope_prefill(kf.reshape(T, HKV, 64), W["cos_t"], W["sin_t"]), 8.0)
+            hq_ = lambda x, H: [np.stack(z) for z in zip(*[R.head_quant(x.reshape(T, H, 64)[t]) for t in range(T)])]
+            (q2, qs2), (k2, ks2), (v2, vs2) = hq_(qr, HQ), hq_(kr, HKV), hq_(vf, HKV)
+        else:
+            qr = oracle.fht(oracle.rope(qf.reshape(T, HQ, 64), pos, W["cos_t"], W["sin_t"]), 8.0)
+            kr = oracle.fht(oracle.rope(kf.reshape(T, HKV, 64), pos, W["cos_t"], W["sin_t"]), 8.0)
+            q2, qs2 = oracle.quant_per_token(qr.reshape(T * HQ, 64)); k2, ks2 = oracle.quant_per_token(kr.reshape(T * HKV, 64))
+            v2, vs2 = oracle.quant_per_token(vf.reshape(T * HKV, 64))
         q2 = q2.reshape(T, HQ, 64); k2 = k2.reshape(T, HKV, 64); v2 = v2.reshape(T, HKV, 64)
         qs2 = qs2.reshape(T, HQ); ks2 = ks2.reshape(T, HKV); vs2 = vs2.reshape(T, HKV)
         att = np.zeros((T, HQ * 64), np.float32)
@@ -168,8 +176,9 @@ def reference_arm(args):
             times.append(time.perf_counter() - t0)
     t_layer = sum(times) / len(times)
     tok_s = T / (t_layer * CFG["layers"])
-    sample = (f"one decoder layer (all projections, RoPE, FHT, attention, MLP) on one {T}-token block through the "
-              f"{'reference templates' if R is not None else 'oracle port'}, {t_layer:.2f} s per layer; x{CFG['layers']} layers, lm_head not included")
+    sample = (f"one decoder layer on one {T}-token block, {t_layer:.2f} s per layer, x{CFG['layers']} layers, lm_head not included; "
+              + ("mixed: quantisers, int8 GEMMs, dequant, RMSNorm, RoPE, FHT, SiLU, gate and residual through the reference's own templates, "
+                 "the 8 x 8 attention rows (scores, softmax, P.V) through the plain-C++ port" if R is not None else "everything through the plain-C++ port"))
     line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": t_layer * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "s8", "data": "synthetic", "config": workload_config(),
@@ -239,10 +248,223 @@ def kernel_roofline(F, torch, peaks):
             "achieved": round(achieved, 1), "unit": "GB/s", "per_projection": detail}
 
 
+# ------------------------------------------------------------------------------------ unit configurations
+def unit_configs(F, torch, peaks, with_cpu=True):
+    """The four operator-level configurations of the workload family, each timed on the device with CUDA events
+    through the C ABI and set against its roofline; beside each, the CPU oracle (plain-C++ port, all host threads)
+    on the same or a stated smaller case.
+
+      config1  prefill linear layer 128 x 2048 x 2048 (int32 sums + fp32 dequant)
+      config2  decode MLP block at batch 1 and batch 64 (RMSNorm, quant, gate, up, SiLU*up, FHT-8192, quant, down, +residual)
+      config3  prefill GQA attention, batch 4 x 1024, 32/8 heads
+      config4  decode attention, batch 64, contexts ~ U{512..8192}, 16 layers of paged int8 KV cache
+    Inputs that must come from HBM are cycled through more copies than fit in the 126 MB L2."""
+    import numpy as np
+    lib = F.lib()
+    dev = "cuda"
+    if with_cpu:
+        import oracle
+        oracle.set_threads(os.cpu_count() or 1)  # a launcher (torchrun) may have exported OMP_NUM_THREADS=1
+    hbm = peaks.get("hbm_gbs") or 6650.0
+    i8_proxy = 2.0 * (peaks.get("bf16_tflops") or 1590.0)
+    gen = torch.Generator(device=dev).manual_seed(11)
+    r8 = lambda *sh: torch.randint(-127, 128, sh, dtype=torch.int8, device=dev, generator=gen)
+    ru = lambda lo, hi, *sh: torch.rand(sh, device=dev, generator=gen) * (hi - lo) + lo
+    P = lambda t: t.data_ptr()
+    out = {}
+
+    def graph_time(body, n_iter):
+        """body(i, stream) issues iteration i; n_iter iterations are replayed from one CUDA graph."""
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for i in range(min(3, n_iter)):
+                body(i, side.cuda_stream)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                for i in range(n_iter):
+                    body(i, side.cuda_stream)
+            g.replay(); side.synchronize()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(side); g.replay(); e1.record(side); side.synchronize()
+        return e0.elapsed_time(e1) / n_iter
+
+    def cpu_time(fn, reps=1):
+        if not with_cpu:
+            return None
+        import oracle  # noqa: F401  (the CPU leg is the only user of the oracle here)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        return (time.perf_counter() - t0) / reps * 1e3
+
+    # ---- int8 tensor-core ceiling of this library's own main loop (epilogue stores nothing)
+    M, N, K = 8192, 8192, 2048
+    a = r8(M, K); w = r8(N, K)
+    ms = graph_time(lambda i, st: lib.flexllm_gemm_i8_mainloop_probe(P(a), P(w), M, N, K, st), 10)
+    int8_peak = 2.0 * M * N * K / ms / 1e9
+    out["int8_peak_measured"] = {"tops": round(int8_peak, 1), "how": "tcgen05.mma kind::i8 main loop of the prefill GEMM on 8192 x 8192 x 2048, "
+                                 "accumulators drained, nothing stored", "proxy_2x_bf16_tops": round(i8_proxy, 1)}
+    del a, w
+
+    # ---- config 1
+    M, N, K = 128, 2048, 2048
+    nset = 40                                           # 40 x 4 MB of weights > L2
+    ws = [r8(N, K) for _ in range(nset)]
+    a = r8(M, K); st_ = ru(0.005, 0.05, M); sc = ru(0.001, 0.01, N)
+    acc = torch.empty((M, N), dtype=torch.int32, device=dev); y = torch.empty((M, N), dtype=torch.float32, device=dev)
+    ms = graph_time(lambda i, st: lib.flexllm_linear_prefill_i8(P(a), P(st_), P(ws[i % nset]), P(sc), M, N, K, None, P(y), st), nset)
+    ops, nbytes = 2.0 * M * N * K, 262144 + 4194304 + 512 + 8192 + 1048576
+    c1 = {"ms": round(ms, 5), "tops": round(ops / ms / 1e9, 2), "GB/s": round(nbytes / ms / 1e6, 1),
+          "frac_hbm": round(nbytes / ms / 1e6 / hbm, 4), "frac_int8_proxy": round(ops / ms / 1e9 / i8_proxy, 4),
+          "bound": "hbm + launch latency (16 output tiles on 148 SMs)", "algorithmic_bytes": nbytes, "ops": int(ops)}
+    if with_cpu:
+        import oracle
+        an, wn = a.cpu().numpy(), ws[0].cpu().numpy(); sn, cn = st_.cpu().numpy(), sc.cpu().numpy()
+        c1["cpu_port_ms"] = round(cpu_time(lambda: oracle.linear_i8(an, sn, wn, cn), 3), 2)
+        if oracle.ref is not None:                       # the reference's own systolic-array template, 16 tokens of the 128
+            t = cpu_time(lambda: oracle.ref.gemm_s8s8(an[:16], wn))
+            c1["cpu_reference_ms"] = round(t * (M / 16), 1)
+            c1["cpu_reference_sample"] = "reference template on 16 of the 128 tokens, one thread, scaled x8"
+    out["config1_prefill_linear_128x2048x2048"] = c1
+    del ws
+
+    # ---- config 2
+    D, Fd = 2048, 8192
+    nset = 4                                            # 4 x 50 MB of weights > L2
+    wg = [r8(Fd, D) for _ in range(nset)]; wu = [r8(Fd, D) for _ in range(nset)]; wd = [r8(D, Fd) for _ in range(nset)]
+    sg, su, sd = ru(0.001, 0.01, Fd), ru(0.001, 0.01, Fd), ru(0.001, 0.01, D)
+    gamma = 1 + 0.02 * torch.randn(D, device=dev, generator=gen)
+    c2 = {}
+    for B in (1, 64):
+        h = torch.randn((B, D), device=dev, generator=gen)
+        xq = torch.empty((B, D), dtype=torch.int8, device=dev); xs = torch.empty(B, device=dev)
+        gt = torch.empty((B, Fd), device=dev); up = torch.empty((B, Fd), device=dev)
+        hq = torch.empty((B, Fd), dtype=torch.int8, device=dev); hs = torch.empty(B, device=dev)
+        o = torch.empty((B, D), device=dev)
+
+        def block(i, st, B=B, h=h, xq=xq, xs=xs, gt=gt, up=up, hq=hq, hs=hs, o=o):
+            j = i % nset
+            rc = lib.flexllm_rmsnorm_quant(P(h), P(gamma), B, D, 1e-5, 8, None, P(xq), P(xs), st)
+            rc |= lib.flexllm_linear_decode_i8(P(xq), P(xs), P(wg[j]), P(sg), B, Fd, D, None, P(gt), st)
+            rc |= lib.flexllm_linear_decode_i8(P(xq), P(xs), P(wu[j]), P(su), B, Fd, D, None, P(up), st)
+            rc |= lib.flexllm_swiglu_fht_quant(P(gt), P(up), B, Fd, 90.50966799, P(hq), P(hs), None, st)
+            rc |= lib.flexllm_linear_decode_i8_residual(P(hq), P(hs), P(wd[j]), P(sd), B, D, Fd, P(h), P(o), st)
+            assert rc == 0, rc
+        ms = graph_time(block, 4 * nset)
+        nbytes = 50331648 + 73728 + 8192 + 2 * B * 8192
+        e = {"ms": round(ms, 5), "GB/s": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / hbm, 4),
+             "bound": "hbm (weights)", "algorithmic_bytes": nbytes, "launches_per_block": 5}
+        if with_cpu:
+            import oracle
+            hn = h.cpu().numpy()
+            args = [hn, gamma.cpu().numpy(), wg[0].cpu().numpy(), sg.cpu().numpy(), wu[0].cpu().numpy(), su.cpu().numpy(),
+                    wd[0].cpu().numpy(), sd.cpu().numpy()]
+            e["cpu_port_ms"] = round(cpu_time(lambda: oracle.mlp_block(*args, lanes=8)), 2)
+        c2[f"batch{B}"] = e
+    out["config2_decode_mlp_block"] = c2
+    del wg, wu, wd
+
+    # ---- config 3
+    from flexllm_b200 import synthetic
+    B, S, HQ, HKV = 4, 1024, 32, 8
+    q, k, v = r8(B, S, HQ, 64), r8(B, S, HKV, 64), r8(B, S, HKV, 64)
+    qs, ks, vs = ru(0.005, 0.05, B, S, HQ), ru(0.005, 0.05, B, S, HKV), ru(0.005, 0.05, B, S, HKV)
+    ct, sn_ = synthetic.rope_table(S); ct = torch.from_numpy(ct).to(dev); sn_ = torch.from_numpy(sn_).to(dev)
+    a_s = torch.full((HQ,), 1.0 / 255, device=dev)
+    for _ in range(3):
+        F.MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, ct, sn_, a_s)
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    n = 5
+    e0.record()
+    for _ in range(n):
+        F.MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, ct, sn_, a_s)
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    ops, nbytes = 17196646400.0, 47185920
+    c3 = {"ms": round(ms, 4), "tops": round(ops / ms / 1e9, 2), "frac_int8_proxy": round(ops / ms / 1e9 / i8_proxy, 4),
+          "GB/s": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / hbm, 4),
+          "bound": "CUDA-core softmax arithmetic (exact ordered sums, correctly rounded exp)", "algorithmic_bytes": nbytes, "ops": int(ops),
+          "l2": "working set 47 MB < L2: the operands of consecutive runs may hit L2 (the exp scratch is written and re-read each run)"}
+    if with_cpu:
+        import oracle
+        an = [t.cpu().numpy() for t in (q[:1], qs[:1], k[:1], ks[:1], v[:1], vs[:1])]
+        t = cpu_time(lambda: oracle.mha_prefill(*an, ct.cpu().numpy(), sn_.cpu().numpy(), a_s.cpu().numpy()))
+        c3["cpu_port_ms"] = round(t * B, 1); c3["cpu_port_sample"] = "1 of the 4 sequences, scaled x4"
+    out["config3_prefill_attention_b4_s1024"] = c3
+    del q, k, v
+
+    # ---- config 4
+    B, L, HQ, HKV, PAGE = 64, 16, 32, 8, 64
+    rng = np.random.default_rng(4)
+    ctx = rng.integers(512, 8193, B).astype(np.int32)
+    pages_per_seq = (ctx + 1 + PAGE - 1) // PAGE
+    n_pages = int(pages_per_seq.sum()) + 3
+    max_pages = int(pages_per_seq.max())
+    perm = rng.permutation(n_pages).astype(np.int32)
+    pt = np.zeros((B, max_pages), np.int32); o_ = 0
+    for b in range(B):
+        pt[b, :pages_per_seq[b]] = perm[o_:o_ + pages_per_seq[b]]; o_ += pages_per_seq[b]
+    cache = F.KVCache(L, n_pages, HKV)
+    for l in range(L):
+        kd, ksd, vd, vsd = cache.pools(l)
+        kd.copy_(r8(n_pages, HKV, PAGE, 64)); vd.copy_(r8(n_pages, HKV, 64, PAGE))
+        ksd.copy_(ru(0.005, 0.05, n_pages, HKV, PAGE)); vsd.copy_(ru(0.005, 0.05, n_pages, HKV, PAGE))
+    max_ctx = int(ctx.max()) + 1
+    ct, sn_ = synthetic.rope_table(max_ctx + 1); ct = torch.from_numpy(ct).to(dev); sn_ = torch.from_numpy(sn_).to(dev)
+    q, k, v = r8(B, HQ, 64), r8(B, HKV, 64), r8(B, HKV, 64)
+    qs, ks, vs = ru(0.005, 0.05, B, HQ), ru(0.005, 0.05, B, HKV), ru(0.005, 0.05, B, HKV)
+    ptd = torch.from_numpy(pt).to(dev); ctxd = torch.from_numpy(ctx).to(dev)
+    nb = lib.flexllm_mha_decode_workspace(B, HQ, max_ctx)
+    wsb = torch.empty(nb, dtype=torch.uint8, device=dev); o = torch.empty((B, HQ * 64), device=dev)
+
+    def step(i, st):
+        for l in range(L):
+            rc = lib.flexllm_mha_i8xi8_decode(cache._h, l, P(q), P(qs), P(k), P(ks), P(v), P(vs), P(ct), P(sn_), P(a_s), P(ptd), max_pages,
+                                              P(ctxd), max_ctx, B, HQ, P(o), None, P(wsb), nb, st)
+            assert rc == 0, rc
+    ms = graph_time(step, 3)                           # the step appends at the same slot every time: contents do not matter for time
+    nbytes = 1088 * int((ctx.astype(np.int64) + 1).sum()) * L
+    c4 = {"ms": round(ms, 4), "ms_per_layer": round(ms / L, 4), "GB/s": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / hbm, 4),
+          "bound": "hbm (KV pages)", "algorithmic_bytes": nbytes, "sum_ctx_plus_1": int((ctx.astype(np.int64) + 1).sum())}
+    if with_cpu:
+        import oracle
+        Bc = 8                                          # 8 of the 64 sequences, one layer
+        npg = int(pages_per_seq[:Bc].sum()) + 1
+        pt8 = np.zeros((Bc, max_pages), np.int32); o_ = 0
+        for b in range(Bc):
+            pt8[b, :pages_per_seq[b]] = np.arange(o_, o_ + pages_per_seq[b]); o_ += pages_per_seq[b]
+        kp = rng.integers(-127, 128, (npg, HKV, PAGE, 64), dtype=np.int8); vp = rng.integers(-127, 128, (npg, HKV, PAGE, 64), dtype=np.int8)
+        ksp = rng.uniform(0.005, 0.05, (npg, HKV, PAGE)).astype(np.float32); vsp = ksp.copy()
+        hn = lambda t: t[:Bc].cpu().numpy()
+        t = cpu_time(lambda: oracle.mha_decode(hn(q), hn(qs), hn(k), hn(ks), hn(v), hn(vs), ct.cpu().numpy(), sn_.cpu().numpy(),
+                                               a_s.cpu().numpy(), kp, ksp, vp, vsp, pt8, ctx[:Bc]))
+        share = float((ctx[:Bc].astype(np.int64) + 1).sum()) / float((ctx.astype(np.int64) + 1).sum())
+        c4["cpu_port_ms"] = round(t / share * L, 1); c4["cpu_port_sample"] = "8 of the 64 sequences on one layer, scaled by cached tokens and x16 layers"
+    out["config4_decode_attention_b64"] = c4
+    cache.close()
+    if with_cpu:
+        import oracle
+        out["cpu_threads"] = oracle.get_threads()
+    return out
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch: ncu capture at context 131..136
 # (1.358 GB read + 0.107 GB written, profiles/decode_mega_kernel_batch32_ctx131.md) plus the KV pages the
 # bench's mean context of 1152 adds (16 layers x 1088 B x 32 sequences x 1019 tokens; KV traffic is proportional)
 DRAM_TRAFFIC_PER_LAUNCH = int(1.358e9 + 0.107e9 + 16 * 1088 * 32 * 1019)
+
+
+def prefill_ops(nb):
+    """Integer operations of one prefill of nb sequences: 2 x tokens x weight elements of the 16 layers, the causal
+    attention (4 x heads x 64 x S(S+1)/2 per sequence and layer) and the lm_head on each sequence's last token."""
+    D, Fd, V, L = CFG["hidden"], CFG["ffn"], CFG["vocab"], CFG["layers"]
+    qkv = (CFG["heads_q"] + 2 * CFG["heads_kv"]) * 64
+    per_layer_w = qkv * D + D * D + 2 * Fd * D + D * Fd
+    lin = 2.0 * nb * PREFILL * L * per_layer_w
+    att = L * 4.0 * nb * CFG["heads_q"] * 64 * (PREFILL * (PREFILL + 1) / 2)
+    return lin + att + 2.0 * nb * V * D
 
 
 def decode_step_bytes():
@@ -405,7 +627,7 @@ def gpu_arm(args):
     def phases(r, nb):
         dec_bytes = decode_step_bytes()
         return {"prefill_ms": round(r["t_pre"], 3), "prefill_tokens_per_s": round(nb * PREFILL / r["t_pre"] * 1e3, 1),
-                "prefill_tops": round(6.60e13 * nb / BATCH / r["t_pre"] / 1e9, 1),
+                "prefill_tops": round(prefill_ops(nb) / r["t_pre"] / 1e9, 1),
                 "decode_ms_per_step": round(r["t_dec"] / (NEW - 1), 4),
                 "decode_tokens_per_s": round(nb * (NEW - 1) / r["t_dec"] * 1e3, 1),
                 "decode_hbm_frac_of_measured": round(dec_bytes / (r["t_dec"] / (NEW - 1) / 1e3) / 1e9 / (peaks.get("hbm_gbs") or 6650.0), 4)}
@@ -439,8 +661,13 @@ def gpu_arm(args):
                 "frac": round(nbytes / step_ms / 1e6 / hbm_peak, 4), "traffic": DRAM_TRAFFIC_PER_LAUNCH,
                 "algorithmic_bytes_per_launch": int(nbytes), "us_per_launch": round(step_ms * 1e3, 1),
                 "peak_source": "measured (MEASURED_PEAKS.json)" if peaks.get("hbm_gbs") else "fallback"}
+        units = None
         if not args.no_extras:
             roof["standalone_linear"] = kernel_roofline(F, torch, peaks)
+            try:
+                units = unit_configs(F, torch, peaks)
+            except Exception as e:  # the side measurements must not take the headline line down with them
+                units = {"error": f"{type(e).__name__}: {e}"}
             try:
                 cpu = cpu_port_baseline()
             except Exception as e:  # the CPU figure is a reported baseline only
@@ -458,6 +685,8 @@ def gpu_arm(args):
                 "phases": phases(r, nb)}
         if other is not None:
             line["other_partition"] = other
+        if units is not None:
+            line["unit_configs"] = units
         print(json.dumps(line))
     if tp_comm[0] is not None:
         tp_comm[0].close()

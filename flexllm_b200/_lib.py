@@ -5,7 +5,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflexllm_b200.so")
 
-OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM, ETOOBIG = 0, -1, -2, -3, -4, -5, -6
+OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM, ETOOBIG, EDEVDATA = 0, -1, -2, -3, -4, -5, -6, -7
 
 # name -> argument types, in the order of include/flexllm_b200.h (return type is int unless noted)
 _P, _I, _L, _F, _SZ = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_size_t
@@ -13,6 +13,7 @@ SIGNATURES = {
     "flexllm_version": [],
     "flexllm_last_cuda_error": [],
     "flexllm_launch_count": [],
+    "flexllm_device_status": [],
     "flexllm_linear_prefill_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_linear_decode_i8": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "flexllm_linear_prefill_i8_residual": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
@@ -58,6 +59,8 @@ SIGNATURES = {
     "flexllm_model_generate_host": [_P, _P, _I, _I, _I, _P, _I, _P],
     "flexllm_model_set_sampling": [_P, _I, _I, _P],
     "flexllm_model_buffer": [_P, _I, _P],
+    "flexllm_debug_hook": [_I, C.c_longlong],
+    "flexllm_gemm_i8_mainloop_probe": [_P, _P, _I, _I, _I, _P],
 }
 
 

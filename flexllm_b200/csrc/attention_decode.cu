@@ -26,10 +26,7 @@
 
 namespace flexllm {
 
-}  // namespace flexllm
-
-
-namespace flexllm {
+int* device_error_flag();
 
 static inline KvLayer kv_layer(const flexllm_kv_cache* c, int layer) {
     KvLayer l;
@@ -53,13 +50,14 @@ __global__ void __launch_bounds__(256) dec_append_kernel(const int8_t* __restric
                                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                          KvLayer cache, const int32_t* __restrict__ page_table, int max_pages,
                                                          const int32_t* __restrict__ ctx, int B, int HQ, int HKV,
-                                                         int8_t* __restrict__ q2, float* __restrict__ qs2) {
+                                                         int8_t* __restrict__ q2, float* __restrict__ qs2, int max_pos,
+                                                         int* error_flag) {
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int heads = HQ + 2 * HKV;
     if (w >= B * heads) return;
     const int b = w / heads, h = w % heads;
-    const int pos = ctx[b];
+    const int pos = dec_guarded_pos(ctx, b, max_pos, error_flag);
     const long pg = page_table[(long)b * max_pages + pos / PAGE];
     const int slot = pos % PAGE;
     if (h >= HQ + HKV) {   // value head: into the transposed page
@@ -128,9 +126,9 @@ template <int G>
 __global__ void __launch_bounds__(256) dec_scores_kernel(const int8_t* __restrict__ q2, const float* __restrict__ qs2,
                                                          KvLayer cache, const int32_t* __restrict__ page_table, int max_pages,
                                                          const int32_t* __restrict__ ctx, int HQ, int HKV, int ctx_stride,
-                                                         int nsplit, float* __restrict__ scores, float* __restrict__ smax) {
+                                                         int nsplit, float* __restrict__ scores, float* __restrict__ smax, int max_pos) {
     const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
-    const int nk = ctx[b] + 1;
+    const int nk = dec_guarded_pos(ctx, b, max_pos, nullptr) + 1;
     const int k_begin = split * KEYS_PER_CTA;
     __shared__ int qsm[G][16];
     __shared__ float red[G][8];
@@ -188,13 +186,13 @@ __global__ void __launch_bounds__(256) dec_scores_kernel(const int8_t* __restric
 // shared memory in chunks.
 __global__ void __launch_bounds__(128) dec_softmax_kernel(const int32_t* __restrict__ ctx, int HQ, int ctx_stride, int nsplit,
                                                           float* __restrict__ scores, const float* __restrict__ smax,
-                                                          float* __restrict__ rinv) {
+                                                          float* __restrict__ rinv, int max_pos) {
     constexpr int CH = 2048;
     __shared__ float e_sm[CH];
     __shared__ float part[4];
     const int row = blockIdx.x;
     const int b = row / HQ;
-    const int nk = ctx[b] + 1;
+    const int nk = dec_guarded_pos(ctx, b, max_pos, nullptr) + 1;
     float* x = scores + (long)row * ctx_stride;
     float mx = -1e32f;
     const int used = (nk + KEYS_PER_CTA - 1) / KEYS_PER_CTA;
@@ -227,9 +225,9 @@ template <int G>
 __global__ void __launch_bounds__(64 * G) dec_pv_kernel(KvLayer cache, const int32_t* __restrict__ page_table, int max_pages,
                                                         const int32_t* __restrict__ ctx, int HQ, int HKV, int ctx_stride,
                                                         const float* __restrict__ scores, const float* __restrict__ rinv,
-                                                        const float* __restrict__ a_s, int32_t* __restrict__ oacc) {
+                                                        const float* __restrict__ a_s, int32_t* __restrict__ oacc, int max_pos) {
     const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
-    const int nk = ctx[b] + 1;
+    const int nk = dec_guarded_pos(ctx, b, max_pos, nullptr) + 1;
     const int k_begin = split * KEYS_PER_CTA;
     if (k_begin >= nk) return;
     const int k_end = min(nk, k_begin + KEYS_PER_CTA);
@@ -282,13 +280,15 @@ __global__ void __launch_bounds__(NT) dec_attn_fused_kernel(const int8_t* __rest
                                                              const float* __restrict__ sin_t, const float* __restrict__ a_s,
                                                              KvLayer cache, const int32_t* __restrict__ page_table, int max_pages,
                                                              const int32_t* __restrict__ ctx, int HQ, int HKV, int cs,
-                                                             float* __restrict__ out, int32_t* __restrict__ oacc) {
+                                                             float* __restrict__ out, int32_t* __restrict__ oacc, int max_pos,
+                                                             int* error_flag) {
     extern __shared__ __align__(16) uint8_t dsm[];
     __shared__ DecAttnSmem sm;
     pdl_sync();
     DecAttnIn in;
     in.q = q; in.qs = qs; in.k = k; in.ks = ks; in.v = v; in.vs = vs; in.qkv_f32 = qkv_f32;
     in.qkv_acc = nullptr; in.tok_scale = nullptr; in.ch_scale = nullptr; in.n_slabs = 0; in.slab_stride = 0;
+    in.max_pos = max_pos; in.error_flag = error_flag;
     dec_attn_fused_body<IN_F32 ? 1 : 0, NT>(in, cos_t, sin_t, a_s, cache, page_table, max_pages, ctx, HQ, HKV, cs, out, oacc,
                                                (int)blockIdx.x, (int)blockIdx.y, dsm, sm, (int)threadIdx.x, 0);
 }
@@ -446,6 +446,7 @@ int flexllm::mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, con
     float* rinv = (float*)w; w += align_up((size_t)B * HQ * 4, 256);
     int32_t* acc = (int32_t*)w;
     KvLayer L = kv_layer(c, layer);
+    int* err = device_error_flag();     // raised (and the length clamped) when a ctx[] entry lies beyond max_ctx
 
     // enough (sequence, head) pairs, or short rows: one fused kernel; otherwise the split kernels
     const size_t fused_smem = (size_t)20 * ctx_stride < 4096 ? 4096 : (size_t)20 * ctx_stride;
@@ -455,27 +456,27 @@ int flexllm::mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, con
             auto kern = dec_attn_fused_kernel<true, 512>;
             if (fused_smem > 48 * 1024) FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem));
             launch_k(kern, fg, dim3(512), fused_smem, st, q, qs, k, ks, v, vs, qkv_f32, cos_t, sin_t, a_s, L, page_table, max_pages, ctx,
-                     HQ, HKV, ctx_stride, out, oacc);
+                     HQ, HKV, ctx_stride, out, oacc, max_ctx, err);
         } else {
             auto kern = dec_attn_fused_kernel<false, 512>;
             if (fused_smem > 48 * 1024) FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem));
             launch_k(kern, fg, dim3(512), fused_smem, st, q, qs, k, ks, v, vs, (const float*)nullptr, cos_t, sin_t, a_s, L, page_table,
-                     max_pages, ctx, HQ, HKV, ctx_stride, out, oacc);
+                     max_pages, ctx, HQ, HKV, ctx_stride, out, oacc, max_ctx, err);
         }
         return launch_status(1);
     }
     const int warps = B * (HQ + 2 * HKV);
     if (qkv_f32)
         dec_append_kernel<true><<<(warps + 7) / 8, 256, 0, st>>>(q, qs, k, ks, v, vs, qkv_f32, cos_t, sin_t, L, page_table,
-                                                                 max_pages, ctx, B, HQ, HKV, q2, qs2);
+                                                                 max_pages, ctx, B, HQ, HKV, q2, qs2, max_ctx, err);
     else
         dec_append_kernel<false><<<(warps + 7) / 8, 256, 0, st>>>(q, qs, k, ks, v, vs, nullptr, cos_t, sin_t, L, page_table,
-                                                                  max_pages, ctx, B, HQ, HKV, q2, qs2);
+                                                                  max_pages, ctx, B, HQ, HKV, q2, qs2, max_ctx, err);
     dim3 grid(nsplit, HKV, B);
-    dec_scores_kernel<4><<<grid, 256, 0, st>>>(q2, qs2, L, page_table, max_pages, ctx, HQ, HKV, ctx_stride, nsplit, scores, smax);
-    dec_softmax_kernel<<<B * HQ, 128, 0, st>>>(ctx, HQ, ctx_stride, nsplit, scores, smax, rinv);
+    dec_scores_kernel<4><<<grid, 256, 0, st>>>(q2, qs2, L, page_table, max_pages, ctx, HQ, HKV, ctx_stride, nsplit, scores, smax, max_ctx);
+    dec_softmax_kernel<<<B * HQ, 128, 0, st>>>(ctx, HQ, ctx_stride, nsplit, scores, smax, rinv, max_ctx);
     FLEXLLM_CHECK_CUDA(cudaMemsetAsync(acc, 0, (size_t)B * HQ * 64 * 4, st));
-    dec_pv_kernel<4><<<grid, 256, 0, st>>>(L, page_table, max_pages, ctx, HQ, HKV, ctx_stride, scores, rinv, a_s, acc);
+    dec_pv_kernel<4><<<grid, 256, 0, st>>>(L, page_table, max_pages, ctx, HQ, HKV, ctx_stride, scores, rinv, a_s, acc, max_ctx);
     dec_out_kernel<<<(B * HQ * 64 + 255) / 256, 256, 0, st>>>(acc, a_s, B, HQ, out, oacc);
     return launch_status(5);
 }

@@ -33,13 +33,28 @@ struct DecAttnIn {
     const float* qkv_f32;
     const int32_t* qkv_acc; const float* tok_scale; const float* ch_scale;
     int n_slabs; long slab_stride;     // MODE 2: split-K partial sums, slab s at qkv_acc + s * slab_stride
+    int max_pos;                       // largest context length the tables, the page-table rows and the score rows cover
+    int* error_flag;                   // raised when a sequence's ctx[] lies beyond max_pos (optional)
 };
+
+// Context length of sequence b as the kernels use it: ctx[] is device data the host cannot vet, so a
+// value outside [0, max_pos] is clamped (every index derived from it then stays inside the page-table
+// row, the RoPE tables and the score row) and reported through the error word.
+__device__ __forceinline__ int dec_guarded_pos(const int32_t* __restrict__ ctx, int b, int max_pos, int* error_flag) {
+    int pos = ctx[b];
+    if (pos < 0 || pos > max_pos) {
+        if (error_flag) atomicOr(error_flag, 2);
+        pos = pos < 0 ? 0 : max_pos;
+    }
+    return pos;
+}
 
 // Asks L2 for everything one (sequence, KV head) item will read: its K and V pages (4 KB each) and
 // their scale rows. `n_threads` threads (index `t`) share the work. Pure hint: no data is returned.
 __device__ __forceinline__ void dec_attn_prefetch_l2(const KvLayer& cache, const int32_t* __restrict__ page_table, int max_pages,
                                                      const int32_t* __restrict__ ctx, int HKV, int hkv, int b, int t, int n_threads) {
-    const int npages = (ctx[b] + 1 + PAGE - 1) / PAGE;
+    int npages = (ctx[b] + 1 + PAGE - 1) / PAGE;
+    npages = npages < 0 ? 0 : (npages > max_pages ? max_pages : npages);     // a hint only, but it indexes the page table
     // per page: 32 lines of K, 32 lines of V, 2 lines of K scales, 2 lines of V scales (128 bytes each)
     for (int i = t; i < npages * 68; i += n_threads) {
         const int p = i / 68, j = i - p * 68;
@@ -104,7 +119,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
             a1 += (p1[0] + p1[1]) + (p1[2] + p1[3]);
         }
     }
-    const int pos = ctx[b];
+    const int pos = dec_guarded_pos(ctx, b, in.max_pos, in.error_flag);
     const int nk = pos + 1;
     const int npages_all = (nk + PAGE - 1) / PAGE;
     const bool pt_cached = npages_all <= 160;

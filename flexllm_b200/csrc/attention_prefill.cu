@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
     if (*abort_flag) {
         const unsigned long long t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
-        if (threadIdx.x == 0 && args.error_flag) atomicExch(args.error_flag, 1);
+        if (threadIdx.x == 0 && args.error_flag) atomicOr(args.error_flag, 1);
         __syncthreads();
     }
     if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, ATT_TMEM_COLS); }
@@ -479,10 +479,12 @@ static int mha_prefill_core(const PrefillWs& ws, const float* a_s, int B, int S,
     AttnArgs a;
     a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.a_s = a_s; a.out = out; a.oacc = oacc; a.ecache = ws.ecache;
     a.error_flag = device_error_flag();
-    static bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<bool> attr_set[kMaxDevices];      // the attribute belongs to (function, device)
+    const int dev = current_device();
+    if (dev < 0) return FLEXLLM_ECUDA;
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
         FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
-        attr_set = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     const int n_qt = (S + 127) / 128;
     const long grid = (long)B * HQ * n_qt;

@@ -4,6 +4,9 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <atomic>
+
 #include "../../include/flexllm_b200.h"
 
 namespace flexllm {
@@ -11,8 +14,17 @@ namespace flexllm {
 extern thread_local int g_last_cuda_error;
 // Number of kernels this library has launched in this process (graph replays count the kernels
 // inside the graph). Read through flexllm_launch_count().
-extern unsigned long long g_launch_count;
-inline void note_launches(int n) { g_launch_count += (unsigned long long)n; }
+extern std::atomic<unsigned long long> g_launch_count;
+inline void note_launches(int n) { g_launch_count.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+// Host-side per-device state (function attributes, scratch, error word) is kept in arrays of this size.
+constexpr int kMaxDevices = 64;
+// Index of the current device, or -1 when it cannot be had or does not fit the per-device arrays.
+inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
 
 inline int cuda_status(cudaError_t e) {
     if (e == cudaSuccess) return FLEXLLM_OK;

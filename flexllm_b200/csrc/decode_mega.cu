@@ -31,6 +31,7 @@
 //
 // Every wait (mbarrier, grid barrier) is bounded; on a timeout the CTA raises the global error
 // flag, all CTAs leave through the tear-down and the host sees FLEXLLM_ETIMEDOUT.
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <new>
@@ -82,7 +83,9 @@ struct MegaArgs {
     int* fht_flags;               // [3][max_batch]: parts published, parts' maxima merged, merged |max| as float bits
     int* att_cnt;                 // [max_batch]: attention items of the sequence that have finished (self-resetting)
     unsigned long long* trace;    // optional phase timeline [barrier][arrive, leave][CTA] in globaltimer ns (last launch)
-    int stages, cs, scratch_bytes;
+    int stages, cs, scratch_bytes, max_ctx;
+    unsigned long long wait_limit_ns;   // bound of the grid-barrier and flag waits
+    int test_barrier_extra;             // test aid: arrivals the FIRST grid barrier waits for beyond those the grid delivers
     int attn_bytes;               // per-half attention scratch: score rows (20 bytes per key) + DecAttnSmem
     int ks_qkv, ks_o, ks_d;       // split-K factors (gate|up and lm_head have enough tiles: 1)
     int slab_rows;                // rows (tokens) per split-K slab = max batch
@@ -128,21 +131,22 @@ __device__ __forceinline__ int ld_volatile_s32(const int* p) {
 // Polls the grid-barrier counter until it reaches `target`. Bounded: gives up after the wait
 // limit, or as soon as this CTA (shared flag) or any CTA (global flag) has given up.
 __device__ __noinline__ bool mega_wait_counter(const unsigned long long* ctr, unsigned long long target, volatile int* abort_flag,
-                                               int* error_flag) {
+                                               int* error_flag, unsigned long long limit_ns) {
     if (ld_acquire_u64(ctr) >= target) return true;
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t it = 1;; it++) {
         if (ld_acquire_u64(ctr) >= target) return true;
         if ((it & 63u) == 0) {
             if (*abort_flag) return false;
-            if (ld_volatile_s32(error_flag)) { *abort_flag = 1; return false; }
-            if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
+            if (ld_volatile_s32(error_flag) & 1) { *abort_flag = 1; return false; }
+            if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; atomicOr(error_flag, 1); return false; }
         }
     }
 }
 
 // Polls an int flag until it reaches `target` (bounded like the counter wait).
-__device__ __noinline__ bool mega_wait_flag(const int* flag, int target, volatile int* abort_flag, int* error_flag) {
+__device__ __noinline__ bool mega_wait_flag(const int* flag, int target, volatile int* abort_flag, int* error_flag,
+                                            unsigned long long limit_ns) {
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t it = 1;; it++) {
         int v;
@@ -150,8 +154,8 @@ __device__ __noinline__ bool mega_wait_flag(const int* flag, int target, volatil
         if (v >= target) return true;
         if ((it & 63u) == 0) {
             if (*abort_flag) return false;
-            if (ld_volatile_s32(error_flag)) { *abort_flag = 1; return false; }
-            if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
+            if (ld_volatile_s32(error_flag) & 1) { *abort_flag = 1; return false; }
+            if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; atomicOr(error_flag, 1); return false; }
         }
     }
 }
@@ -159,14 +163,15 @@ __device__ __noinline__ bool mega_wait_flag(const int* flag, int target, volatil
 // Grid-wide barrier of the worker threads: everything the CTA wrote before it is visible to every
 // CTA after it. Returns false when the step is being abandoned.
 __device__ __forceinline__ bool mega_grid_sync(unsigned long long* ctr, unsigned long long target, volatile int* abort_flag,
-                                               volatile int* go_flag, int* error_flag, unsigned long long* trace) {
+                                               volatile int* go_flag, int* error_flag, unsigned long long* trace,
+                                               unsigned long long limit_ns) {
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (threadIdx.x == 0) {
         // release at GPU scope: orders this thread's writes and, through the CTA barrier above, every write of
         // the CTA before the arrival; the acquire loads of the wait plus the CTA barrier below do the reverse
         if (trace) trace[blockIdx.x] = globaltimer_ns();
         asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(ctr), "l"(1ull) : "memory");
-        mega_wait_counter(ctr, target, abort_flag, error_flag);
+        mega_wait_counter(ctr, target, abort_flag, error_flag, limit_ns);
         if (trace) trace[gridDim.x + blockIdx.x] = globaltimer_ns();
         *go_flag = (*abort_flag == 0);      // one verdict for the whole CTA, fixed before anyone reads it
     }
@@ -191,7 +196,8 @@ __device__ __forceinline__ void mega_row_norm(const MegaArgs& a, int row, const 
     if (active) {
         g = __ldg(reinterpret_cast<const float4*>(gamma) + c);
         if (acc == nullptr) {
-            const int id = a.next[row];
+            int id = a.next[row];
+            if (id < 0 || id >= a.V) { if (c == 0) atomicOr(a.error_flag, 2); id = id < 0 ? 0 : a.V - 1; }   // never a wild read
             const float s = a.lm_s[id];
             const char4 t = reinterpret_cast<const char4*>(a.lm_w + (long)id * D)[c];
             v = make_float4((float)t.x * s, (float)t.y * s, (float)t.z * s, (float)t.w * s);
@@ -413,7 +419,7 @@ __device__ __forceinline__ void mega_row_fht4(const MegaArgs& a, const MegaLayer
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (tid == 0) {
         asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(flag_a), "r"(1) : "memory");
-        mega_wait_flag(flag_a, 4, abort_flag, a.error_flag);
+        mega_wait_flag(flag_a, 4, abort_flag, a.error_flag, a.wait_limit_ns);
     }
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (*abort_flag) return;
@@ -439,7 +445,7 @@ __device__ __forceinline__ void mega_row_fht4(const MegaArgs& a, const MegaLayer
         const float am = fmaxf(fabsf(mx), fabsf(mn));
         atomicMax(amax_bits, __float_as_uint(am));
         asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(flag_b), "r"(1) : "memory");
-        mega_wait_flag(flag_b, 4, abort_flag, a.error_flag);
+        mega_wait_flag(flag_b, 4, abort_flag, a.error_flag, a.wait_limit_ns);
     }
     named_sync<MG_BAR_WORK, MG_WORKERS>();
     if (*abort_flag) return;
@@ -719,6 +725,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             in.q = in.k = in.v = nullptr; in.qs = in.ks = in.vs = nullptr; in.qkv_f32 = nullptr;
             in.qkv_acc = a.w_qkv; in.tok_scale = a.xs; in.ch_scale = ly.sqkv;
             in.n_slabs = a.ks_qkv; in.slab_stride = (long)a.slab_rows * (a.HQ + 2 * a.HKV) * 64;
+            in.max_pos = a.max_ctx; in.error_flag = a.error_flag;
             // two (sequence, KV head) items at a time, one per half of the CTA: an item is a chain of
             // global-memory round trips, so two chains side by side nearly double the throughput
             const int half = tid >> 8;
@@ -752,8 +759,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             gemm_phase(j, kind == 4 ? nullptr : &nj);
         }
         if (p + 1 < n_phases) {
-            if (!mega_grid_sync(a.sync_ctr, target_of(p), abort_flag, go_flag, a.error_flag,
-                                a.trace ? a.trace + (size_t)p * 2 * G : nullptr))
+            if (!mega_grid_sync(a.sync_ctr, target_of(p) + (p == 0 ? (unsigned long long)a.test_barrier_extra : 0ull), abort_flag, go_flag,
+                                a.error_flag, a.trace ? a.trace + (size_t)p * 2 * G : nullptr, a.wait_limit_ns))
                 break;
         }
     }
@@ -765,7 +772,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
         // a wait ran out: give copies still in flight time to land before shared memory is released
         const unsigned long long t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
-        if (tid == 0) atomicExch(a.error_flag, 1);
+        if (tid == 0) atomicOr(a.error_flag, 1);
         __syncthreads();
     }
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
@@ -907,7 +914,7 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     a.fht_x = (float*)p->dev_fht_x; a.fht_flags = (int*)p->dev_fht_flags; a.att_cnt = a.fht_flags + 3 * v.max_batch;
     a.trace = (unsigned long long*)p->dev_trace;
     a.sample_lanes = 0; a.sample_k = 0; a.sample_rnd = nullptr;
-    a.stages = stages; a.cs = cs; a.scratch_bytes = scratch; a.attn_bytes = attn_bytes;
+    a.stages = stages; a.cs = cs; a.scratch_bytes = scratch; a.attn_bytes = attn_bytes; a.max_ctx = v.max_ctx;
     a.ks_qkv = ks_qkv; a.ks_o = ks_o; a.ks_d = ks_d; a.slab_rows = v.max_batch;
     if (!a.error_flag) { mega_destroy(p); return FLEXLLM_ECUDA; }
     *out = p;
@@ -924,9 +931,18 @@ int mega_reset(MegaPlan* p, cudaStream_t st) {
     return FLEXLLM_OK;
 }
 
+// Test aids (flexllm_debug_hook): a shorter bound for the kernel's grid-barrier and flag waits, and a one-shot
+// request that the next launch's first grid barrier wait for more arrivals than the grid delivers, so that the
+// bounded wait runs out, every CTA leaves through the tear-down and the error word is raised.
+static std::atomic<long long> g_hook_wait_limit_ns{0};
+static std::atomic<int> g_hook_barrier_extra{0};
+
 int mega_launch(MegaPlan* p, int B, cudaStream_t st) {
     if (B < 1 || B > p->bn) return FLEXLLM_EINVAL;
     p->args.B = B;
+    const long long lim = g_hook_wait_limit_ns.load();
+    p->args.wait_limit_ns = lim > 0 ? (unsigned long long)lim : kWaitLimitNs;
+    p->args.test_barrier_extra = g_hook_barrier_extra.exchange(0);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p->grid); cfg.blockDim = dim3(MG_THREADS); cfg.dynamicSmemBytes = p->smem; cfg.stream = st;
     cudaLaunchAttribute at[1];
@@ -939,3 +955,12 @@ int mega_launch(MegaPlan* p, int B, cudaStream_t st) {
 }
 
 }  // namespace flexllm
+
+// See include/flexllm_b200.h.
+extern "C" int flexllm_debug_hook(int which, long long value) {
+    switch (which) {
+        case 0: flexllm::g_hook_wait_limit_ns.store(value > 0 ? value : 0); return FLEXLLM_OK;
+        case 1: flexllm::g_hook_barrier_extra.store(value > 0 ? 1 : 0); return FLEXLLM_OK;
+        default: return FLEXLLM_EINVAL;
+    }
+}

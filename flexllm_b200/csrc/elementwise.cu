@@ -8,7 +8,7 @@ namespace flexllm {
 
 thread_local int g_last_cuda_error = 0;
 thread_local int g_pdl = 0;
-unsigned long long g_launch_count = 0;
+std::atomic<unsigned long long> g_launch_count{0};
 
 // ---------------------------------------------------------------------------------------------
 // Per-token symmetric int8 quantisation (Modules/quant.h:6-112, symmetric branch).
@@ -341,12 +341,13 @@ extern "C" const char* flexllm_status_string(int st) {
         case FLEXLLM_ENOTSUP: return "unsupported shape";
         case FLEXLLM_ENOMEM: return "out of memory";
         case FLEXLLM_ETOOBIG: return "problem exceeds a fixed built-in buffer";
+        case FLEXLLM_EDEVDATA: return "token id or context length in device memory out of range (clamped)";
         default: return "unknown status";
     }
 }
 
 extern "C" int flexllm_last_cuda_error(void) { return g_last_cuda_error; }
-extern "C" unsigned long long flexllm_launch_count(void) { return g_launch_count; }
+extern "C" unsigned long long flexllm_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 
 extern "C" int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, float* s, void* stream) {
     FLEXLLM_REQUIRE(M >= 0 && K > 0 && (K % 4) == 0 && K <= 8192);

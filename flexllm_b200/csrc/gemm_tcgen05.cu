@@ -19,6 +19,7 @@
 //
 // Replaces pref_Linear_Layer_i4xi4 / dec_Linear_Layer_i4xi4 + the dequant layers
 // (Modules/Linear_Layer.h:293-341, :862-923; Modules/quant.h:115-164, :434-524) at 8-bit precision.
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
@@ -452,7 +453,7 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_tcgen05_kernel(const __grid_co
         // a wait ran out: give copies still in flight time to land before shared memory is released
         const unsigned long long t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
-        if (threadIdx.x == 0 && args.error_flag) atomicExch(args.error_flag, 1);
+        if (threadIdx.x == 0 && args.error_flag) atomicOr(args.error_flag, 1);
         __syncthreads();
     }
     if (warp == 1) {
@@ -491,22 +492,30 @@ static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64
     return FLEXLLM_OK;
 }
 
+// One error word per device: bit 0 is raised by any kernel of the library whose bounded device-side wait ran
+// out, bit 1 by a kernel that found (and clamped) a token id or context length in device memory out of range. It lives in the library's device image (no allocation needed to reach it); its device address
+// is looked up once per device. Process-wide: a time-out raised by a launch from one host thread is
+// seen by a status check from any other.
+static __device__ int g_error_flag;
+struct DevFlag { std::once_flag once; int* p = nullptr; };
+static DevFlag g_dev_flag[kMaxDevices];
+
 int* device_error_flag() {
-    static thread_local int* flag[16] = {nullptr};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
-    if (!flag[dev]) {
-        if (cudaMalloc(&flag[dev], sizeof(int)) != cudaSuccess) return nullptr;
-        cudaMemset(flag[dev], 0, sizeof(int));
-    }
-    return flag[dev];
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    DevFlag& f = g_dev_flag[dev];
+    std::call_once(f.once, [&] {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_error_flag) == cudaSuccess) f.p = p;
+    });
+    return f.p;
 }
 
 static int sm_count() {
-    static int n[16] = {0};
+    static int n[kMaxDevices] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 16) return 148;
+    if (dev < 0 || dev >= kMaxDevices) return 148;
     if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
     return n[dev] > 0 ? n[dev] : 148;
 }
@@ -527,10 +536,13 @@ static int launch_gemm(const int8_t* A, int rowsA, const int8_t* B, int rowsB, i
     g.ldo = ldo; g.acc = acc; g.y = y; g.sA = sA; g.sB = sB; g.error_flag = device_error_flag();
     g.residual = residual; g.work = work; g.counters = counters;
     auto kern = gemm_i8_tcgen05_kernel<BN, SWAP, KCH>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    // the attribute belongs to (function, device): once per device, not once per process
+    static std::atomic<bool> attr_set[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0) return FLEXLLM_ECUDA;
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
         FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     const int total = g.tilesA * g.tilesB * g.ksplit;
     const int grid = total < sm_count() ? total : sm_count();
@@ -572,12 +584,17 @@ int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const f
 #undef FLEXLLM_DEC
 }
 
+// Reads and clears the current device's error word (synchronises the device: the copy is ordered
+// behind all work queued so far).
 int gemm_check_error_flag() {
     int* f = device_error_flag();
     if (!f) return FLEXLLM_ECUDA;
     int h = 0;
     FLEXLLM_CHECK_CUDA(cudaMemcpy(&h, f, sizeof(int), cudaMemcpyDeviceToHost));
-    if (h) { cudaMemset(f, 0, sizeof(int)); return FLEXLLM_ETIMEDOUT; }
+    if (h) {
+        FLEXLLM_CHECK_CUDA(cudaMemset(f, 0, sizeof(int)));
+        return (h & 1) ? FLEXLLM_ETIMEDOUT : FLEXLLM_EDEVDATA;      // bit 0: a wait ran out; bit 1: an index in device memory was clamped
+    }
     return FLEXLLM_OK;
 }
 
@@ -589,9 +606,9 @@ int gemm_sm_count() { return sm_count(); }
 // that loads the library carries these 4 MiB until the process exits.
 constexpr long kNoAllocMaxElems = 64L * 16384L;   // tokens x output channels, int32 each
 static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocMaxElems];
-static __device__ int g_noalloc_error_flag;
 
-struct NoAllocDev { int32_t* scratch = nullptr; int* flag = nullptr; bool ready = false; };
+struct NoAllocDev { std::once_flag once; int32_t* scratch = nullptr; int* flag = nullptr; int rc = FLEXLLM_ECUDA; };
+static NoAllocDev g_noalloc_dev[kMaxDevices];
 
 template <int BN>
 static int launch_gemm_noalloc(const int8_t* w, int N, const int8_t* a, int M, int K, int ksplit, int32_t* acc, int* flag,
@@ -608,7 +625,13 @@ static int launch_gemm_noalloc(const int8_t* w, int N, const int8_t* a, int M, i
     g.ldo = N; g.acc = acc; g.y = nullptr; g.sA = nullptr; g.sB = nullptr; g.error_flag = flag;
     g.residual = nullptr; g.work = nullptr; g.counters = nullptr;
     auto kern = gemm_i8_tcgen05_kernel<BN, true>;
-    FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    static std::atomic<bool> attr_set[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0) return FLEXLLM_ECUDA;
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
+        FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set[dev].store(true, std::memory_order_release);
+    }
     const int total = g.tilesA * g.ksplit;
     const int grid = total < sm_count() ? total : sm_count();
     kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, g);
@@ -618,6 +641,15 @@ static int launch_gemm_noalloc(const int8_t* w, int N, const int8_t* a, int M, i
 }  // namespace flexllm
 
 using namespace flexllm;
+
+// See include/flexllm_b200.h.
+extern "C" int flexllm_device_status(void) { return gemm_check_error_flag(); }
+
+// See include/flexllm_b200.h: the prefill GEMM with nothing to store (the epilogue warps still drain TMEM).
+extern "C" int flexllm_gemm_i8_mainloop_probe(const int8_t* a, const int8_t* w, int M, int N, int K, void* stream) {
+    FLEXLLM_REQUIRE(a && w && M > 0 && N > 128 && K > 0 && (K % 16) == 0 && aligned(a, 16) && aligned(w, 16));
+    return launch_gemm<256, false>(a, M, w, N, K, 1, N, nullptr, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
 
 // See include/flexllm_b200.h. The first call on a device resolves the device addresses of the
 // built-in arrays (cudaGetSymbolAddress: the array's name is only a host-side handle, not a device
@@ -630,16 +662,17 @@ extern "C" int flexllm_linear_decode_i8_noalloc(const int8_t* a, const float* s_
     FLEXLLM_REQUIRE(aligned(a, 16) && aligned(w, 16) && aligned(y, 16) && aligned(s_ch, 16));
     if (M > 64) return FLEXLLM_ENOTSUP;
     if ((long)M * N > kNoAllocMaxElems) return FLEXLLM_ETOOBIG;   // larger than the built-in scratch
-    static NoAllocDev devs[16];
-    int dev = 0;
-    FLEXLLM_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 16) return FLEXLLM_EINVAL;
-    NoAllocDev& d = devs[dev];
-    if (!d.ready) {
-        FLEXLLM_CHECK_CUDA(cudaGetSymbolAddress((void**)&d.scratch, g_noalloc_scratch));
-        FLEXLLM_CHECK_CUDA(cudaGetSymbolAddress((void**)&d.flag, g_noalloc_error_flag));
-        d.ready = true;
-    }
+    const int dev = current_device();
+    if (dev < 0) return FLEXLLM_ECUDA;
+    NoAllocDev& d = g_noalloc_dev[dev];
+    // set-up, once per device, with that device current: the array's name is only a host-side handle,
+    // the kernel needs the address cudaGetSymbolAddress returns. The error word is the library's
+    // per-device one, so a time-out in this path is reported by flexllm_device_status() like any other.
+    std::call_once(d.once, [&] {
+        d.rc = cuda_status(cudaGetSymbolAddress((void**)&d.scratch, g_noalloc_scratch));
+        if (d.rc == FLEXLLM_OK) { d.flag = device_error_flag(); if (!d.flag) d.rc = FLEXLLM_ECUDA; }
+    });
+    if (d.rc != FLEXLLM_OK) return d.rc;
     cudaStream_t st = (cudaStream_t)stream;
     // split-K as in the allocating entry point: enough CTAs to pull the weights at full HBM rate
     const int tiles = (N + 127) / 128, num_kb = (K + 127) / 128;

@@ -1,5 +1,7 @@
 // C-ABI entry points of the W8A8 linear layers: shape checks, choice between the weight-streaming
 // GEMV and the tcgen05 GEMM, split-K bookkeeping for decode.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace flexllm {
@@ -11,28 +13,38 @@ int gemm_i8_decode(const int8_t* a, const float* s_tok, const int8_t* w, const f
                    int ksplit, int32_t* acc, float* y, cudaStream_t st, const float* residual, int32_t* work, int* counters);
 int gemm_sm_count();
 
-// Library-owned split-K scratch, one per device, grown on demand: int32 partial sums followed by the
-// arrival counters. Invariant: all zero between launches (the kernel's last arriver restores it), so
-// launches on one stream can share it without a memset. Launches on different streams must not
-// overlap (they would mix their partial sums).
-struct Scratch { void* p = nullptr; size_t bytes = 0; };
-static Scratch g_scratch[16];
-constexpr size_t kCounterBytes = 16384;   // 4 counters per 128-channel tile, up to 131072 channels
+// Library-owned split-K scratch, one per device: int32 partial sums followed by the arrival counters.
+// It is allocated ONCE per device, at its full size (64 tokens x 131072 output channels), on the
+// first decode linear layer that needs it, and never freed, grown or moved afterwards: CUDA graphs
+// that captured a launch hold it by address. That first call must therefore come outside any stream
+// capture (an allocation is illegal inside one); a capturing call that finds no scratch yet is
+// refused. Invariant: all zero between launches (the kernel's last arriver restores it), so launches
+// on ONE stream share it without a memset. Launches that can overlap on the GPU (different streams)
+// would mix their partial sums: the caller serialises them (stated at the entry point's declaration).
+struct Scratch { std::mutex mu; void* p = nullptr; };
+static Scratch g_scratch[kMaxDevices];
+constexpr size_t kCounterBytes = 16384;                                  // 4 counters per 128-channel tile, up to 131072 channels
+constexpr size_t kScratchBytes = (size_t)64 * 131072 * sizeof(int32_t);  // largest M x N the decode path accepts
 
-int scratch_get(size_t bytes, int32_t** work, int** counters) {
-    int dev = 0;
-    FLEXLLM_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 16) return FLEXLLM_EINVAL;
+int scratch_get(size_t bytes, int32_t** work, int** counters, cudaStream_t st) {
+    const int dev = current_device();
+    if (dev < 0) return FLEXLLM_ECUDA;
+    if (bytes > kScratchBytes) return FLEXLLM_ENOTSUP;
     Scratch& s = g_scratch[dev];
-    if (s.bytes < bytes) {
-        if (s.p) { FLEXLLM_CHECK_CUDA(cudaDeviceSynchronize()); FLEXLLM_CHECK_CUDA(cudaFree(s.p)); s.p = nullptr; s.bytes = 0; }
-        size_t want = bytes < (size_t)(8 << 20) ? (size_t)(8 << 20) : bytes;
-        FLEXLLM_CHECK_CUDA(cudaMalloc(&s.p, want + kCounterBytes));
-        FLEXLLM_CHECK_CUDA(cudaMemset(s.p, 0, want + kCounterBytes));
-        s.bytes = want;
+    std::lock_guard<std::mutex> lk(s.mu);
+    if (!s.p) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        FLEXLLM_CHECK_CUDA(cudaStreamIsCapturing(st, &cap));
+        if (cap != cudaStreamCaptureStatusNone) return FLEXLLM_EINVAL;   // make the first call outside the capture
+        void* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, kScratchBytes + kCounterBytes);
+        if (e != cudaSuccess) { g_last_cuda_error = (int)e; return e == cudaErrorMemoryAllocation ? FLEXLLM_ENOMEM : FLEXLLM_ECUDA; }
+        e = cudaMemset(p, 0, kScratchBytes + kCounterBytes);
+        if (e != cudaSuccess) { cudaFree(p); return cuda_status(e); }
+        s.p = p;
     }
     *work = (int32_t*)s.p;
-    *counters = (int*)((char*)s.p + s.bytes);
+    *counters = (int*)((char*)s.p + kScratchBytes);
     return FLEXLLM_OK;
 }
 
@@ -81,7 +93,7 @@ static int linear_decode(const int8_t* a, const float* s_tok, const int8_t* w, c
     if (ks == 1) return gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, 1, acc, y, st, residual, nullptr, nullptr);
     if ((size_t)((N + 127) / 128) * 16 > kCounterBytes) return FLEXLLM_ENOTSUP;
     int32_t* work = nullptr; int* counters = nullptr;
-    rc = scratch_get((size_t)M * N * sizeof(int32_t), &work, &counters);
+    rc = scratch_get((size_t)M * N * sizeof(int32_t), &work, &counters, st);
     if (rc != FLEXLLM_OK) return rc;
     return gemm_i8_decode(a, s_tok, w, s_ch, M, N, K, ks, acc, y, st, residual, work, counters);
 }

@@ -37,6 +37,7 @@ int mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float*
                    const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, int HQ,
                    float* out, int32_t* oacc, void* workspace, cudaStream_t st);
 int gemm_check_error_flag();
+int* device_error_flag();
 int quant_gathered(const float* x, int M, int W, int g, int r, int8_t* q, float* s, cudaStream_t st);
 int swiglu_slice(const float* gu, long M, int W, float* h, cudaStream_t st);
 int dequant_residual(const int32_t* acc, const float* s_tok, const float* s_ch, long M, int N, const float* residual, float* y,
@@ -48,11 +49,17 @@ int topk_sample(const float* logits, int B, long V, int lanes, int top_k, const 
                 int32_t* top_idx, float* top_val, cudaStream_t st);
 
 // x[t][:] = (float)lm_w[tok[t]][:] * lm_s[tok[t]]
+// An id outside [0, V) (device data the host has not seen, e.g. fed back by a sampler) is clamped so that
+// it cannot become a wild read, and reported through the error word.
 __global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ lm_w, const float* __restrict__ lm_s,
-                             int D, float* __restrict__ x) {
+                             int D, int V, float* __restrict__ x, int* error_flag) {
     pdl_sync();
     const int t = blockIdx.x;
-    const int id = tok[t];
+    int id = tok[t];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0 && error_flag) atomicOr(error_flag, 2);
+        id = id < 0 ? 0 : V - 1;
+    }
     const float s = lm_s[id];
     const char4* w = reinterpret_cast<const char4*>(lm_w + (long)id * D);
     float4* o = reinterpret_cast<float4*>(x + (long)t * D);
@@ -114,6 +121,7 @@ struct flexllm_model {
     size_t attn_ws_bytes = 0, dec_ws_bytes = 0;
     // decode state
     int B = 0, S = 0;
+    int pos = 0;                                // context length of the batch = position the next decode step writes
     cudaGraphExec_t graph = nullptr; int graph_B = 0; int graph_kernels = 0;
     std::vector<void*> owned;
     // tensor parallelism: g ranks, this one is r; *l = local (per-rank) sizes
@@ -304,7 +312,7 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
     const int QKV = (HQ + 2 * HKV) * 64;
     const int M = B * S;
     const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
-    embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->x);
+    embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag());
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
@@ -343,7 +351,7 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
     fill_ctx_kernel<<<1, 64, 0, st>>>(m->ctx, B, S);
     TRY(launch_status());
     if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
-    m->B = B; m->S = S;
+    m->B = B; m->S = S; m->pos = S;
     return FLEXLLM_OK;
 }
 
@@ -389,7 +397,8 @@ static int decode_step_body(flexllm_model* m, cudaStream_t st) {
     const int QKV = (HQ + 2 * HKV) * 64;
     const int B = m->B;
     const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
-    launch_k(embed_kernel, dim3(B), dim3(256), 0, st, (const int32_t*)m->next, (const int8_t*)m->lm_w, (const float*)m->lm_s, D, m->x);
+    launch_k(embed_kernel, dim3(B), dim3(256), 0, st, (const int32_t*)m->next, (const int8_t*)m->lm_w, (const float*)m->lm_s, D, m->cfg.vocab, m->x,
+             device_error_flag());
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
@@ -435,10 +444,11 @@ static int build_graph(flexllm_model* m) {
     cudaError_t e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal);
     int rc = FLEXLLM_OK;
     if (e == cudaSuccess) {
-        const unsigned long long before = g_launch_count;
+        const unsigned long long before = g_launch_count.load();
         rc = decode_step(m, cap);
-        m->graph_kernels = (int)(g_launch_count - before);   // kernels recorded, not executed
-        g_launch_count = before;
+        const unsigned long long recorded = g_launch_count.load() - before;   // kernels recorded, not executed
+        m->graph_kernels = (int)recorded;
+        g_launch_count.fetch_sub(recorded);
         cudaError_t e2 = cudaStreamEndCapture(cap, &g);
         if (e == cudaSuccess) e = e2;
     }
@@ -453,6 +463,10 @@ static int build_graph(flexllm_model* m) {
 
 extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph, void* stream) {
     FLEXLLM_REQUIRE(m && m->B > 0 && n_steps >= 0);
+    // step i appends at position pos + i, and the page-table rows, the RoPE tables and the attention
+    // score rows end at max_ctx: refuse, before anything is launched, steps that would run past it
+    FLEXLLM_REQUIRE(n_steps == 0 || (long)m->pos + n_steps - 1 <= (long)m->cfg.max_ctx);
+    m->pos += n_steps;
     cudaStream_t st = (cudaStream_t)stream;
     int done = 0;
     if (use_graph && n_steps > 0 && (!m->graph || m->graph_B != m->B)) {
@@ -487,6 +501,7 @@ extern "C" int flexllm_model_generate_host(flexllm_model* m, const int32_t* toke
                                            int32_t* out_host, int use_graph, void* stream) {
     FLEXLLM_REQUIRE(m && tokens_host && out_host && n_new >= 1);
     FLEXLLM_REQUIRE(B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill && S + n_new - 1 <= m->cfg.max_ctx);
+    for (size_t i = 0; i < (size_t)B * S; i++) FLEXLLM_REQUIRE(tokens_host[i] >= 0 && tokens_host[i] < m->cfg.vocab);
     cudaStream_t st = (cudaStream_t)stream;
     FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(m->tokens, tokens_host, (size_t)B * S * 4, cudaMemcpyHostToDevice, st));
     TRY(flexllm_model_prefill(m, m->tokens, B, S, nullptr, st));

@@ -39,6 +39,7 @@ extern "C" {
 #define FLEXLLM_ENOTSUP (-4)   /* shape outside what the kernels were built for */
 #define FLEXLLM_ENOMEM (-5)
 #define FLEXLLM_ETOOBIG (-6)   /* problem larger than a fixed built-in buffer */
+#define FLEXLLM_EDEVDATA (-7)  /* a token id or context length in DEVICE memory was out of range (clamped) */
 
 /* RMSNorm summation orders (Modules/LayerNorm.h:82-130 prefill, :263-321 decode). */
 #define FLEXLLM_NORM_PREFILL 0 /* 4 interleaved partial sums over the whole row          */
@@ -51,6 +52,16 @@ FLEXLLM_API const char* flexllm_status_string(int status);
 FLEXLLM_API int flexllm_last_cuda_error(void);
 /* Kernels launched by this library in this process so far (a graph replay counts its kernel nodes). */
 FLEXLLM_API unsigned long long flexllm_launch_count(void);
+/* Device-side waits (TMA / MMA pipeline barriers, the grid barrier of the persistent decode kernel) are
+ * bounded: a wait that runs out makes the kernel leave through its tear-down, possibly with partial
+ * results, and raise one error word per device. Calls are asynchronous, so they cannot report that
+ * themselves; this call synchronises the current device, returns FLEXLLM_ETIMEDOUT if any kernel of
+ * the library has raised the word since the last check (from any host thread) and clears it, else
+ * FLEXLLM_OK. The same word reports FLEXLLM_EDEVDATA: a kernel met a token id outside [0, vocab) or a
+ * context length outside [0, max_ctx] in device memory (values the host never sees, e.g. ids fed back by
+ * a sampler); such a value is clamped so that it can never become an out-of-bounds access. flexllm_model_generate_host performs this check itself. The reference has no
+ * counterpart: a mis-sized stream there simply deadlocks the simulation. */
+FLEXLLM_API int flexllm_device_status(void);
 
 /* ---------------------------------------------------------------------------------------------
  * Linear layers.   acc[m][n] = sum_k a[m][k]*w[n][k]  (exact int32);
@@ -66,6 +77,10 @@ FLEXLLM_API int flexllm_linear_prefill_i8(const int8_t* a, const float* s_tok, c
                               int M, int N, int K, int32_t* acc, float* y, void* stream);
 FLEXLLM_API int flexllm_linear_decode_i8(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
                              int M, int N, int K, int32_t* acc, float* y, void* stream);
+/* Library-owned state of the decode layer (9..64 tokens): its split-K partial sums go through ONE scratch
+ * buffer per device (32 MiB, allocated by the first such call on the device and kept until the process
+ * exits -- make that call outside any stream capture). Calls on one stream share it safely; calls that can
+ * overlap on the GPU (different streams of one device) would mix their partial sums: serialise them. */
 
 /* The same two layers fused with the residual add that follows them in the model
  * (pref_Residual_Layer / dec_Residual_Layer, Residual_Layer.h:46-87): y = residual + dequant(acc).
@@ -87,7 +102,9 @@ FLEXLLM_API int flexllm_linear_decode_i8_residual(const int8_t* a, const float* 
  *  - the first call on each device looks up the array's device address; make it before any CUDA
  *    stream capture begins;
  *  - all calls share the one array (it is cleared at the start of every call): two calls that can
- *    run concurrently on the GPU, e.g. on different streams, race -- serialise them. */
+ *    run concurrently on the GPU, e.g. on different streams, race -- serialise them;
+ *  - a device-side wait that runs out is reported by flexllm_device_status(), as for every other
+ *    entry point. */
 FLEXLLM_API int flexllm_linear_decode_i8_noalloc(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch,
                                      int M, int N, int K, float* y, void* stream);
 
@@ -258,6 +275,19 @@ FLEXLLM_API int flexllm_model_generate_host(flexllm_model* m, const int32_t* tok
  * output column c -- the reference's rand_seeds_mmap, one number per decode step (SpinQuant_Decoding_mem_opt.h:934-937).
  * The token feedback stays on the device in both decode paths. Single GPU only. */
 FLEXLLM_API int flexllm_model_set_sampling(flexllm_model* m, int lanes, int top_k, const float* rnd);
+
+/* Measurement aid: the prefill GEMM's TMA -> shared memory -> tcgen05.mma kind::i8 -> TMEM pipeline on
+ * a [M][K] x [N][K] problem with an epilogue that reads the accumulators and stores nothing. Its rate is
+ * the int8 tensor-core ceiling this library's main loop reaches on the device (N > 128). */
+FLEXLLM_API int flexllm_gemm_i8_mainloop_probe(const int8_t* a, const int8_t* w, int M, int N, int K, void* stream);
+
+/* Test aids for the failure path of the persistent decode-step kernel (no counterpart in the reference).
+ * which = 0: bound, in nanoseconds, of that kernel's grid-barrier and flag waits (0 restores the default
+ * of 2 s). which = 1, value != 0: the NEXT decode step's first grid barrier waits for one arrival more than
+ * the grid delivers, so the wait runs out, the kernel returns through its tear-down, and
+ * flexllm_device_status() reports FLEXLLM_ETIMEDOUT (one-shot). A generation that timed out is void: start
+ * again from flexllm_model_prefill / flexllm_model_begin, which also re-arm the barrier counter. */
+FLEXLLM_API int flexllm_debug_hook(int which, long long value);
 
 /* Device pointers of internal buffers (tests): 0 residual stream, 1 logits, 2 token table, 3 ctx. */
 FLEXLLM_API int flexllm_model_buffer(flexllm_model* m, int which, void** ptr);

@@ -71,6 +71,15 @@ def set_exp_mode(mode):
     _lib.orc_set_exp_mode(C.c_int(mode))
 
 
+def set_threads(n):
+    """Number of threads of the oracle's OpenMP loops (overrides an inherited OMP_NUM_THREADS)."""
+    _lib.orc_set_threads(C.c_int(int(n)))
+
+
+def get_threads():
+    return int(_lib.orc_get_threads())
+
+
 def get_exp_mode():
     return _lib.orc_get_exp_mode()
 

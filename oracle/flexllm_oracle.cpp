@@ -16,6 +16,7 @@
 // Conventions: all tensors row-major, weights [N][K] with K contiguous. `rnd` is
 // std::round (half away from zero). (float)int32 is round-to-nearest-even.
 
+#include <omp.h>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -31,6 +32,9 @@
 // the CUDA kernels reproduce bit for bit.
 static int g_exp_mode = 0;
 ORC_API void orc_set_exp_mode(int mode) { g_exp_mode = mode; }
+// Threads of the OpenMP loops below (a launcher may have exported OMP_NUM_THREADS=1 before this library was loaded).
+ORC_API void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+ORC_API int orc_get_threads(void) { return omp_get_max_threads(); }
 ORC_API int orc_get_exp_mode() { return g_exp_mode; }
 
 namespace {
