@@ -48,6 +48,9 @@ SIGNATURES = {
     "flexllm_tp_size": [_P],
     "flexllm_tp_allreduce_s32": [_P, _P, _SZ, _P],
     "flexllm_tp_allgather": [_P, _P, _P, _SZ, _P],
+    "flexllm_tp_reduce_scatter_s32": [_P, _P, _P, _SZ, _P],
+    "flexllm_tp_allreduce_max_f32": [_P, _P, _SZ, _P],
+    "flexllm_tp_alltoall": [_P, _P, _P, _SZ, _P],
     "flexllm_model_create": [_P, _P],
     "flexllm_model_create_tp": [_P, _P, _P],
     "flexllm_model_destroy": [_P],

@@ -19,6 +19,15 @@ __device__ __forceinline__ int dp4a_u8s8(unsigned a, int b, int c) {
     return d;
 }
 
+// Development aid (compiled in only with -DFLEXLLM_ATT_TRACE): thread 0 of the item (sequence 0, KV head 0)
+// stamps the global timer at the boundaries of the fused attention step; read back with flexllm_att_trace().
+#ifdef FLEXLLM_ATT_TRACE
+static __device__ unsigned long long g_att_ts[32];
+#define ATT_TS(i) do { if (b == 0 && hkv == 0 && tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_att_ts[i] = t_; } } while (0)
+#else
+#define ATT_TS(i) do { } while (0)
+#endif
+
 constexpr int PAGE = 64;
 constexpr int KEYS_PER_CTA = 512;   // 8 pages per CTA in the score and P.V kernels
 
@@ -98,6 +107,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
     float (*part)[4] = sm.part;
     int* pt_sm = sm.pt_sm;                                            // this sequence's page-table row
     named_sync_id<NT>(bar);   // a CTA may run several (sequence, head) items back to back
+    ATT_TS(0);
     const int w = tid >> 5, lane = tid & 31;
     const int heads = HQ + 2 * HKV;
     // MODE 2: the split-K partial sums of this warp's head do not depend on the context length, so
@@ -134,6 +144,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
     }
 
+    ATT_TS(1);
     // ---- A. prepare: warps 0..3 the query heads, warp 4 the key head, warp 5 the value head
     if (w < 6) {
         const long pg = page_table[(long)b * max_pages + pos / PAGE];
@@ -198,6 +209,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         }
     }
     named_sync_id<NT>(bar);
+    ATT_TS(2);
 
     // ---- B. scores: four lanes share one key (16 bytes of its row each), NT/4 keys per iteration
     const int l4 = tid & 3, slot = tid >> 2;
@@ -245,6 +257,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
             }
         }
     }
+    ATT_TS(3);
     // maximum over the lanes with the same l4 (xor 4, 8, 16), then over the warps
     mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 4));
     mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 8));
@@ -270,12 +283,14 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
             vsc_pre[u] = cache.vs[(pg * HKV + hkv) * PAGE + (key % PAGE)];
         }
     }
+    ATT_TS(4);
     // ---- D. e = exp(x - max), in place
     for (int g = 0; g < G; g++) {
         const float m = row_max[g];
         for (int key = tid; key < nk; key += NT) sc[g * cs + key] = ref_expf(sc[g * cs + key] - m);
     }
     named_sync_id<NT>(bar);
+    ATT_TS(5);
     // ---- E. the four ordered chains of each row (Softmax.h:514-553): one thread per chain
     if (tid < 4 * G) {
         const int g = tid >> 2, j = tid & 3;
@@ -288,6 +303,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
     named_sync_id<NT>(bar);
     if (tid < G) row_rinv[tid] = 1.0f / ((part[tid][0] + part[tid][1]) + (part[tid][2] + part[tid][3]));
     named_sync_id<NT>(bar);
+    ATT_TS(6);
     // ---- F. u8 probabilities (zero beyond the last key up to the page boundary)
     const int nk_pad = (nk + PAGE - 1) / PAGE * PAGE;
     {
@@ -324,6 +340,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         }
     }
     named_sync_id<NT>(bar);
+    ATT_TS(7);
     // ---- G. P.V: four lanes share one V^T row (16 keys of the page each); thread = (page slot, d, quarter)
     {
         const int d = (tid >> 2) & 63, ps = tid >> 8;     // ps: which of the NT/256 pages of an iteration
@@ -342,6 +359,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
                 acc[g] = a;
             }
         }
+        ATT_TS(8);
         int mine = 0;
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -363,6 +381,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
             out[o] = (float)tot * a_s[hq];
             if (oacc) oacc[o] = tot;
         }
+        ATT_TS(9);
     }
 }
 

@@ -956,6 +956,13 @@ int mega_launch(MegaPlan* p, int B, cudaStream_t st) {
 
 }  // namespace flexllm
 
+#ifdef FLEXLLM_ATT_TRACE
+// development builds only: the time stamps of the traced attention item (see attention_decode.cuh)
+extern "C" __attribute__((visibility("default"))) int flexllm_att_trace(unsigned long long* out32) {
+    return flexllm::cuda_status(cudaMemcpyFromSymbol(out32, flexllm::g_att_ts, 32 * sizeof(unsigned long long)));
+}
+#endif
+
 // See include/flexllm_b200.h.
 extern "C" int flexllm_debug_hook(int which, long long value) {
     switch (which) {

@@ -13,13 +13,14 @@
 // uses the decode order, the weight-streaming linear layers and the paged attention, and is replayed
 // from a CUDA graph (the token feedback stays on the device, as in the reference's decode graph).
 #include <cstdlib>
+#include <cstring>
 #include <new>
 #include <vector>
 
+#include "attention_decode.cuh"     // layout of the paged KV cache (for the hand-over between partitions)
 #include "common.cuh"
 #include "decode_mega.h"
 
-struct flexllm_kv_cache;
 struct flexllm_tp;
 
 namespace flexllm {
@@ -45,6 +46,11 @@ int dequant_residual(const int32_t* acc, const float* s_tok, const float* s_ch, 
 int argmax_pair(const float* logits, int B, long V, int offset, void* pairs, cudaStream_t st);
 int argmax_select(const void* pairs, int g, int B, int32_t* idx, cudaStream_t st);
 int fht_quant_gathered(const float* h, int M, int g, int r, float scale, int8_t* q, float* s, cudaStream_t st);
+int row_absmax(const float* x, long M, int W, float* amax, cudaStream_t st);
+int quant_given_amax(const float* x, long M, int W, const float* amax, int8_t* q, float* s_out, cudaStream_t st);
+int swiglu_fht_local(const float* gu, long M, int Fl, int g, float* send, cudaStream_t st);
+int fht_cross(const float* recv, long M, int W, int g, float scale, float* hf, float* amax, cudaStream_t st);
+int kv_regroup(const void* stage, int n_pages, int g, int hl, int elem_bytes, void* dst, cudaStream_t st);
 int topk_sample(const float* logits, int B, long V, int lanes, int top_k, const float* rnd, const int32_t* col, int32_t* idx,
                 int32_t* top_idx, float* top_val, cudaStream_t st);
 
@@ -102,6 +108,7 @@ using namespace flexllm;
 
 struct LayerW {
     int8_t *wqkv, *wo, *wgu, *wd;
+    int8_t* wd_x = nullptr;     // token-row partition: this rank's down_proj columns in the order the FHT exchange leaves them
     float *sqkv, *so, *sgu, *sd, *g0, *g1, *a_s;
 };
 
@@ -121,6 +128,7 @@ struct flexllm_model {
     size_t attn_ws_bytes = 0, dec_ws_bytes = 0;
     // decode state
     int B = 0, S = 0;
+    int n_new = 0;                              // columns of the token table of the running generation
     int pos = 0;                                // context length of the batch = position the next decode step writes
     cudaGraphExec_t graph = nullptr; int graph_B = 0; int graph_kernels = 0;
     std::vector<void*> owned;
@@ -128,6 +136,12 @@ struct flexllm_model {
     flexllm_tp* tp = nullptr;
     int g = 1, r = 0, HQl = 0, HKVl = 0, Fl = 0, Dl = 0, Vl = 0;
     float *gath = nullptr, *hloc = nullptr;     // all-gather target / local silu(gate)*up slice
+    // token-row partition of the prefill + batch-parallel decode (see flexllm_model_prefill)
+    flexllm_model* dm = nullptr;                // single-GPU model of this rank's sequences: full weights, all KV heads
+    float *amax = nullptr, *xs2 = nullptr;      // per-token largest magnitudes / scales of the row-parallel inputs
+    int8_t* aq = nullptr;                       // quantised attention output, this rank's columns
+    uint8_t *kv_stage = nullptr, *kvs_stage = nullptr;   // KV hand-over: pages / scale rows as received
+    bool rows_mode = false;                     // the last prefill used the token-row partition
     int32_t* acc32 = nullptr;                   // row-parallel partial sums
     void *pairs_l = nullptr, *pairs_g = nullptr;
     // persistent decode-step kernel: -1 not tried yet, 0 not usable for this model, 1 ready
@@ -211,6 +225,21 @@ extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_
         uint8_t *pl = nullptr, *pg = nullptr;
         if ((rc = dmalloc(m, &pl, (size_t)64 * 8)) || (rc = dmalloc(m, &pg, (size_t)64 * 8 * g))) return fail(rc);
         m->pairs_l = pl; m->pairs_g = pg;
+        // Token-row partition + batch-parallel decode: needs the batch to split evenly over the ranks.
+        // FLEXLLM_TP_MODE=allgather keeps every call on the all-gather partition instead.
+        const char* mode = getenv("FLEXLLM_TP_MODE");
+        if (c->max_batch % g == 0 && !(mode && !strcmp(mode, "allgather"))) {
+            flexllm_model_config dc = *c;
+            dc.max_batch = c->max_batch / g;
+            dc.max_prefill = 16;                    // the decode model never prefills; its row buffers serve the head
+            if ((rc = flexllm_model_create(&m->dm, &dc))) return fail(rc);
+            for (int l = 0; l < NL; l++)
+                if ((rc = dmalloc(m, &m->L[l].wd_x, (size_t)D * m->Fl))) return fail(rc);
+            const size_t pages_l = (size_t)dc.max_batch * m->max_pages;
+            if ((rc = dmalloc(m, &m->amax, Mmax)) || (rc = dmalloc(m, &m->xs2, Mmax)) || (rc = dmalloc(m, &m->aq, Mmax * m->Dl)) ||
+                (rc = dmalloc(m, &m->kv_stage, pages_l * c->heads_kv * 4096)) || (rc = dmalloc(m, &m->kvs_stage, pages_l * c->heads_kv * 256)))
+                return fail(rc);
+        }
     }
     m->attn_ws_bytes = mha_prefill_ws_bytes(c->max_batch, c->max_prefill, HQ, HKV);
     m->dec_ws_bytes = flexllm_mha_decode_workspace(c->max_batch, HQ, c->max_ctx);
@@ -224,6 +253,7 @@ extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_
 extern "C" int flexllm_model_destroy(flexllm_model* m) {
     if (!m) return FLEXLLM_OK;
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    if (m->dm) flexllm_model_destroy(m->dm);
     mega_destroy(m->mega);
     if (m->cache) flexllm_kv_cache_destroy(m->cache);
     for (void* p : m->owned) cudaFree(p);
@@ -267,6 +297,14 @@ extern "C" int flexllm_model_load_layer(flexllm_model* m, int layer, const flexl
     TRY(copy_any(L.g0, w->gamma0, (size_t)D * 4, st));
     TRY(copy_any(L.g1, w->gamma1, (size_t)D * 4, st));
     TRY(copy_any(L.a_s, w->a_s + r * m->HQl, (size_t)m->HQl * 4, st));
+    if (m->dm) {
+        // K order of the token-row partition's down_proj: after the FHT exchange rank r holds, from every rank s,
+        // the window [r * W, (r + 1) * W) of s's Fl channels, i.e. original columns s * Fl + r * W + j at position s * W + j
+        const size_t W = Fl / m->g;
+        for (int s = 0; s < m->g; s++)
+            FLEXLLM_CHECK_CUDA(cudaMemcpy2DAsync(L.wd_x + s * W, Fl, w->wd + s * Fl + r * W, F, W, D, cudaMemcpyDefault, st));
+        TRY(flexllm_model_load_layer(m->dm, layer, w, stream));
+    }
     return FLEXLLM_OK;
 }
 
@@ -279,6 +317,7 @@ extern "C" int flexllm_model_load_head(flexllm_model* m, const int8_t* lm_w, con
     TRY(copy_any(m->g_final, gamma_final, (size_t)m->cfg.hidden * 4, st));
     TRY(copy_any(m->cos_t, cos_t, (size_t)m->table_len * 32 * 4, st));
     TRY(copy_any(m->sin_t, sin_t, (size_t)m->table_len * 32 * 4, st));
+    if (m->dm) TRY(flexllm_model_load_head(m->dm, lm_w, lm_s, gamma_final, cos_t, sin_t, table_len, stream));
     return FLEXLLM_OK;
 }
 
@@ -304,10 +343,101 @@ static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaSt
     return FLEXLLM_OK;
 }
 
+// Tensor-parallel prefill in the token-row partition, then hand-over to batch-parallel decode.
+//
+// Between the projections every rank owns a block of M / g token rows (= B / g whole sequences) of the residual
+// stream: RMSNorm and the residual adds run on those rows only. Around them, per layer:
+//   all-gather   int8 rows + scales of the normalised input          -> column-parallel q|k|v (local heads), gate|up
+//   all-reduce   max over the ranks of the per-token largest magnitude of the attention output / FHT output, so that
+//                each rank quantises ITS columns with the whole row's scale (no row ever leaves the rank in fp32)
+//   reduce-scatter  int32 partial sums of the row-parallel o / down projections (exact, order-free) -> dequant +
+//                residual on the rank's rows
+//   all-to-all   between the local stages (index bits 1 .. log2(Fl)-1) and the cross-rank stages + bit 0 of the
+//                8192-point Hadamard transform: the reference's stage order, hence the single-GPU bits
+// Every exchanged quantity is either an integer sum or a maximum, or moves values unchanged, so the results equal the
+// single-GPU model's bit for bit. Afterwards the KV cache (sharded by KV head during the prefill) is regrouped by
+// sequence, and each rank decodes its B / g sequences with the full (replicated, 1.2 GB) weights on the persistent
+// decode kernel: independent batch-parallel decode streams, no collective inside a decode step.
+static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, cudaStream_t st) {
+    const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl;
+    const int QKV = (HQ + 2 * HKV) * 64;
+    const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl, W = Fl / g;
+    const long M = (long)B * S, Mr = M / g;
+    const int Bl = B / g;
+    flexllm_model* dm = m->dm;
+    int8_t* xq_mine = m->xq + (size_t)r * Mr * D;
+    float* xs_mine = m->xs + (size_t)r * Mr;
+    int32_t* acc_mine = m->acc32 + (size_t)r * Mr * D;
+    embed_kernel<<<(unsigned)Mr, 256, 0, st>>>(tokens + (size_t)r * Mr, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag());
+    note_launches(1);
+    auto norm_and_gather = [&](const float* gamma) {
+        TRY(flexllm_rmsnorm_quant(m->x, gamma, (int)Mr, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, xq_mine, xs_mine, st));
+        TRY(flexllm_tp_allgather(m->tp, xq_mine, m->xq, (size_t)Mr * D, st));             // in place: block r is already there
+        TRY(flexllm_tp_allgather(m->tp, xs_mine, m->xs, (size_t)Mr * 4, st));
+        return FLEXLLM_OK;
+    };
+    for (int l = 0; l < m->cfg.layers; l++) {
+        const LayerW& L = m->L[l];
+        TRY(norm_and_gather(L.g0));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, (int)M, QKV, D, nullptr, m->qkv, st, nullptr));
+        const int8_t *k2, *vT; const float *ks2, *vsT;
+        TRY(mha_prefill_f32(m->qkv, m->cos_t, m->sin_t, L.a_s, B, S, HQ, HKV, m->att, m->attn_ws, st, &k2, &ks2, &vT, &vsT));
+        TRY(kv_pack(m->cache, l, k2, ks2, vT, vsT, m->page_table, m->max_pages, B, S, st));
+        // o projection, row-parallel over this rank's heads
+        TRY(row_absmax(m->att, M, Dl, m->amax, st));
+        TRY(flexllm_tp_allreduce_max_f32(m->tp, m->amax, (size_t)M, st));
+        TRY(quant_given_amax(m->att, M, Dl, m->amax, m->aq, m->xs2, st));
+        TRY(gemm_i8_prefill(m->aq, nullptr, L.wo, nullptr, (int)M, D, Dl, m->acc32, nullptr, st, nullptr));
+        TRY(flexllm_tp_reduce_scatter_s32(m->tp, m->acc32, acc_mine, (size_t)Mr * D, st));
+        TRY(dequant_residual(acc_mine, m->xs2 + (size_t)r * Mr, L.so, Mr, D, m->x, m->x, st));
+        // MLP
+        TRY(norm_and_gather(L.g1));
+        TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, (int)M, 2 * Fl, D, nullptr, m->gu, st, nullptr));
+        TRY(swiglu_fht_local(m->gu, M, Fl, g, m->hloc, st));
+        TRY(flexllm_tp_alltoall(m->tp, m->hloc, m->gath, (size_t)M * W * 4, st));
+        TRY(fht_cross(m->gath, M, W, g, m->cfg.fht_scale, m->hloc, m->amax, st));
+        TRY(flexllm_tp_allreduce_max_f32(m->tp, m->amax, (size_t)M, st));
+        TRY(quant_given_amax(m->hloc, M, Fl, m->amax, m->hq, m->xs2, st));
+        TRY(gemm_i8_prefill(m->hq, nullptr, L.wd_x, nullptr, (int)M, D, Fl, m->acc32, nullptr, st, nullptr));
+        TRY(flexllm_tp_reduce_scatter_s32(m->tp, m->acc32, acc_mine, (size_t)Mr * D, st));
+        TRY(dequant_residual(acc_mine, m->xs2 + (size_t)r * Mr, L.sd, Mr, D, m->x, m->x, st));
+    }
+    // ---- hand-over: this rank's sequences [r * Bl, (r + 1) * Bl) with all KV heads go to its decode model
+    {
+        flexllm_kv_cache* src = m->cache; flexllm_kv_cache* dst = dm->cache;
+        const int n_pg = Bl * m->max_pages;                       // pages of one rank's sequences (identity page tables on both sides)
+        const size_t pg_bytes = (size_t)n_pg * HKV * 4096, sc_bytes = (size_t)n_pg * HKV * 256;
+        for (int l = 0; l < m->cfg.layers; l++) {
+            const size_t so = (size_t)l * src->page_bytes, ss = (size_t)l * (src->scale_bytes / 4);
+            const size_t d_o = (size_t)l * dst->page_bytes, ds = (size_t)l * (dst->scale_bytes / 4);
+            TRY(flexllm_tp_alltoall(m->tp, src->k + so, m->kv_stage, pg_bytes, st));
+            TRY(kv_regroup(m->kv_stage, n_pg, g, HKV, 4096, dst->k + d_o, st));
+            TRY(flexllm_tp_alltoall(m->tp, src->v + so, m->kv_stage, pg_bytes, st));
+            TRY(kv_regroup(m->kv_stage, n_pg, g, HKV, 4096, dst->v + d_o, st));
+            TRY(flexllm_tp_alltoall(m->tp, src->ks + ss, m->kvs_stage, sc_bytes, st));
+            TRY(kv_regroup(m->kvs_stage, n_pg, g, HKV, 256, dst->ks + ds, st));
+            TRY(flexllm_tp_alltoall(m->tp, src->vs + ss, m->kvs_stage, sc_bytes, st));
+            TRY(kv_regroup(m->kvs_stage, n_pg, g, HKV, 256, dst->vs + ds, st));
+        }
+    }
+    gather_last_kernel<<<Bl, 256, 0, st>>>(m->x, S, D, dm->xlast);
+    note_launches(1);
+    TRY(run_head(dm, dm->xlast, Bl, FLEXLLM_NORM_PREFILL, st));
+    fill_ctx_kernel<<<1, 64, 0, st>>>(dm->ctx, Bl, S);
+    TRY(launch_status());
+    dm->B = Bl; dm->S = S; dm->pos = S;
+    TRY(flexllm_tp_allgather(m->tp, dm->next, m->next, (size_t)Bl * 4, st));
+    if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
+    m->B = B; m->S = S; m->pos = S; m->rows_mode = true;
+    return FLEXLLM_OK;
+}
+
 extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, void* stream) {
     FLEXLLM_REQUIRE(m && tokens && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill);
     if (S % 16 != 0) return FLEXLLM_ENOTSUP;
     cudaStream_t st = (cudaStream_t)stream;
+    if (m->dm && B % m->g == 0) return prefill_rows(m, tokens, B, S, next_out, st);
+    m->rows_mode = false;
     const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl, F = m->cfg.ffn;
     const int QKV = (HQ + 2 * HKV) * 64;
     const int M = B * S;
@@ -463,6 +593,7 @@ static int build_graph(flexllm_model* m) {
 
 extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph, void* stream) {
     FLEXLLM_REQUIRE(m && m->B > 0 && n_steps >= 0);
+    if (m->rows_mode) return flexllm_model_decode(m->dm, n_steps, use_graph, stream);   // this rank's sequences, no collective
     // step i appends at position pos + i, and the page-table rows, the RoPE tables and the attention
     // score rows end at max_ctx: refuse, before anything is launched, steps that would run past it
     FLEXLLM_REQUIRE(n_steps == 0 || (long)m->pos + n_steps - 1 <= (long)m->cfg.max_ctx);
@@ -487,6 +618,8 @@ extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph
 extern "C" int flexllm_model_begin(flexllm_model* m, int n_new, void* stream) {
     FLEXLLM_REQUIRE(m && m->B > 0 && n_new >= 1 && (size_t)m->B * n_new <= m->out_capacity);
     FLEXLLM_REQUIRE(m->S + n_new - 1 <= m->cfg.max_ctx);
+    m->n_new = n_new;
+    if (m->rows_mode) return flexllm_model_begin(m->dm, n_new, stream);
     cudaStream_t st = (cudaStream_t)stream;
     set_state_kernel<<<1, 1, 0, st>>>(m->state, 0, n_new);
     step_bookkeeping_kernel<<<1, 64, 0, st>>>(m->next, m->B, m->out_tokens, m->state, m->ctx, 0);
@@ -507,6 +640,8 @@ extern "C" int flexllm_model_generate_host(flexllm_model* m, const int32_t* toke
     TRY(flexllm_model_prefill(m, m->tokens, B, S, nullptr, st));
     TRY(flexllm_model_begin(m, n_new, st));
     TRY(flexllm_model_decode(m, n_new - 1, use_graph, st));
+    if (m->rows_mode)      // every rank returns all B sequences: rank blocks of [B / g][n_new] in rank order = sequence order
+        TRY(flexllm_tp_allgather(m->tp, m->dm->out_tokens, m->out_tokens, (size_t)(B / m->g) * n_new * 4, st));
     FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(out_host, m->out_tokens, (size_t)B * n_new * 4, cudaMemcpyDeviceToHost, st));
     FLEXLLM_CHECK_CUDA(cudaStreamSynchronize(st));
     return gemm_check_error_flag();
@@ -532,6 +667,22 @@ extern "C" int flexllm_model_set_sampling(flexllm_model* m, int lanes, int top_k
 // call, 2 = generated tokens table, 3 = context lengths.
 extern "C" int flexllm_model_buffer(flexllm_model* m, int which, void** ptr) {
     FLEXLLM_REQUIRE(m && ptr);
+    if (m->rows_mode) {
+        // token-row partition: the residual stream is spread over the ranks by rows, logits / tokens / lengths belong to
+        // the rank's own sequences. which == 0 gathers the rows (a COLLECTIVE: call it on every rank).
+        switch (which) {
+            case 0: {
+                const size_t n = (size_t)m->B * m->S / m->g * m->cfg.hidden;
+                TRY(flexllm_tp_allgather(m->tp, m->x, m->gath, n * 4, nullptr));
+                FLEXLLM_CHECK_CUDA(cudaStreamSynchronize(nullptr));
+                *ptr = m->gath; return FLEXLLM_OK;
+            }
+            case 1: *ptr = m->dm->logits; return FLEXLLM_OK;
+            case 2: *ptr = m->dm->out_tokens; return FLEXLLM_OK;
+            case 3: *ptr = m->dm->ctx; return FLEXLLM_OK;
+            default: return FLEXLLM_EINVAL;
+        }
+    }
     switch (which) {
         case 0: *ptr = m->x; break;
         case 1: *ptr = m->logits; break;

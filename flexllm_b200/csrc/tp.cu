@@ -3,9 +3,15 @@
 //   all-reduce (sum, int32)  partial accumulators of the row-parallel o_proj / down_proj --
 //                            integer addition is exact and order-free, so every rank ends up
 //                            with the bits a single GPU would have computed
-//   all-gather (bytes)       fp32 activations of the column-parallel stages (attention output,
-//                            silu(gate)*up) before the per-token quantisers that need whole rows,
-//                            and the (value, index) pairs of the vocab-parallel argmax
+//   reduce-scatter (sum, int32)  the same partial sums when every rank keeps only its block of token rows
+//   all-reduce (max, fp32)   per-token largest magnitudes, so that each rank can quantise its own column
+//                            slice of a row with the scale of the whole row
+//   all-gather (bytes)       int8 rows + scales of the token-row blocks, fp32 activations of the
+//                            column-parallel stages in the all-gather partition, and the (value, index)
+//                            pairs of the vocab-parallel argmax
+//   all-to-all (bytes)       the exchange between the local and the cross-rank stages of the 8192-point
+//                            Hadamard transform, and the hand-over of the KV cache from the head-sharded
+//                            prefill to the sequence-sharded decode
 // NCCL is loaded at run time from the library the process already uses (torch's bundled
 // libnccl.so.2), so libflexllm_b200.so itself carries no link-time dependency on it.
 #include <dlfcn.h>
@@ -25,6 +31,11 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 static NcclApi g_nccl;
@@ -43,7 +54,14 @@ static int nccl_load(const char* libpath) {
     a.AllReduce = (decltype(a.AllReduce))dlsym(h, "ncclAllReduce");
     a.AllGather = (decltype(a.AllGather))dlsym(h, "ncclAllGather");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(h, "ncclGetErrorString");
-    if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce || !a.AllGather) return FLEXLLM_ENOTSUP;
+    a.ReduceScatter = (decltype(a.ReduceScatter))dlsym(h, "ncclReduceScatter");
+    a.Send = (decltype(a.Send))dlsym(h, "ncclSend");
+    a.Recv = (decltype(a.Recv))dlsym(h, "ncclRecv");
+    a.GroupStart = (decltype(a.GroupStart))dlsym(h, "ncclGroupStart");
+    a.GroupEnd = (decltype(a.GroupEnd))dlsym(h, "ncclGroupEnd");
+    if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce || !a.AllGather || !a.ReduceScatter || !a.Send || !a.Recv ||
+        !a.GroupStart || !a.GroupEnd)
+        return FLEXLLM_ENOTSUP;
     g_nccl = a;
     return FLEXLLM_OK;
 }
@@ -114,4 +132,40 @@ extern "C" int flexllm_tp_allgather(flexllm_tp* t, const void* send, void* recv,
         return FLEXLLM_OK;
     }
     return nccl_status(g_nccl.AllGather(send, recv, bytes_per_rank, ncclInt8, t->comm, (cudaStream_t)stream));
+}
+
+extern "C" int flexllm_tp_reduce_scatter_s32(flexllm_tp* t, const int32_t* send, int32_t* recv, size_t count_per_rank, void* stream) {
+    FLEXLLM_REQUIRE((send && recv) || count_per_rank == 0);
+    if (count_per_rank == 0) return FLEXLLM_OK;
+    if (!t || t->size == 1) {
+        if (send != recv) FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(recv, send, count_per_rank * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+        return FLEXLLM_OK;
+    }
+    return nccl_status(g_nccl.ReduceScatter(send, recv, count_per_rank, ncclInt32, ncclSum, t->comm, (cudaStream_t)stream));
+}
+
+extern "C" int flexllm_tp_allreduce_max_f32(flexllm_tp* t, float* buf, size_t count, void* stream) {
+    FLEXLLM_REQUIRE(buf || count == 0);
+    if (!t || t->size == 1 || count == 0) return FLEXLLM_OK;
+    return nccl_status(g_nccl.AllReduce(buf, buf, count, ncclFloat32, ncclMax, t->comm, (cudaStream_t)stream));
+}
+
+// Rank r sends bytes [p * bytes_per_pair, (p + 1) * bytes_per_pair) of `send` to rank p and receives rank p's block
+// for r at the same offset of `recv`.
+extern "C" int flexllm_tp_alltoall(flexllm_tp* t, const void* send, void* recv, size_t bytes_per_pair, void* stream) {
+    FLEXLLM_REQUIRE((send && recv) || bytes_per_pair == 0);
+    if (bytes_per_pair == 0) return FLEXLLM_OK;
+    if (!t || t->size == 1) {
+        if (send != recv) FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(recv, send, bytes_per_pair, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+        return FLEXLLM_OK;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = nccl_status(g_nccl.GroupStart());
+    if (rc != FLEXLLM_OK) return rc;
+    for (int p = 0; p < t->size && rc == FLEXLLM_OK; p++) {
+        rc = nccl_status(g_nccl.Send((const char*)send + (size_t)p * bytes_per_pair, bytes_per_pair, ncclInt8, p, t->comm, st));
+        if (rc == FLEXLLM_OK) rc = nccl_status(g_nccl.Recv((char*)recv + (size_t)p * bytes_per_pair, bytes_per_pair, ncclInt8, p, t->comm, st));
+    }
+    const int rc2 = nccl_status(g_nccl.GroupEnd());
+    return rc != FLEXLLM_OK ? rc : rc2;
 }

@@ -231,6 +231,11 @@ FLEXLLM_API int flexllm_tp_rank(const flexllm_tp* t);
 FLEXLLM_API int flexllm_tp_size(const flexllm_tp* t);
 FLEXLLM_API int flexllm_tp_allreduce_s32(flexllm_tp* t, int32_t* buf, size_t count, void* stream);
 FLEXLLM_API int flexllm_tp_allgather(flexllm_tp* t, const void* send, void* recv, size_t bytes_per_rank, void* stream);
+/* sum of the ranks' int32 buffers [size][count_per_rank]; rank r receives block r */
+FLEXLLM_API int flexllm_tp_reduce_scatter_s32(flexllm_tp* t, const int32_t* send, int32_t* recv, size_t count_per_rank, void* stream);
+FLEXLLM_API int flexllm_tp_allreduce_max_f32(flexllm_tp* t, float* buf, size_t count, void* stream);
+/* block p of `send` goes to rank p; block p of `recv` comes from rank p */
+FLEXLLM_API int flexllm_tp_alltoall(flexllm_tp* t, const void* send, void* recv, size_t bytes_per_pair, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Whole-model runner: the two top-level graphs of the reference, SpinQuant_Prefilling

@@ -107,7 +107,109 @@ def _rank(rank, world, port, ret):
     dist.barrier(); dist.destroy_process_group()
 
 
+def _fht_bits(x, bits):
+    """In-place-equivalent Walsh-Hadamard butterflies (lo, hi) <- (lo + hi, lo - hi) on the given index bits of the
+    last axis, in the given order, in fp32 (the reference's stage order is bits 1, 2, ..., log2(N)-1, then 0;
+    Modules/FHT.h:31-53)."""
+    x = np.array(x, dtype=np.float32, copy=True)
+    n = x.shape[-1]
+    idx = np.arange(n)
+    for b in bits:
+        lo = idx[(idx >> b) & 1 == 0]; hi = lo | (1 << b)
+        a, c = x[..., lo].copy(), x[..., hi].copy()
+        x[..., lo] = a + c; x[..., hi] = a - c
+    return x
+
+
+def _rank_rows(rank, world, port, ret):
+    """The token-row partition of the GPU runner's tensor-parallel prefill: each rank owns T / g rows of the residual
+    stream; int8 rows are all-gathered for the column-parallel projections; the row-parallel projections quantise
+    their input slice with the all-reduced (max) row magnitude and reduce-scatter their int32 partial sums; the
+    8192-point FHT runs its local stages, one all-to-all, then the cross-rank stages and bit 0."""
+    CFG.clear(); CFG.update(CFGS_ROWS[world])
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    oracle.set_exp_mode(oracle.EXP_CORRECTLY_ROUNDED)
+    c = CFG; W, x_all = _layer_inputs(); T, D, F = c["T"], c["hidden"], c["ffn"]
+    g, r = world, rank
+    HQl, HKVl, Dl, Fl, Tr = c["hq"] // g, c["hkv"] // g, D // g, F // g, T // g
+    Wn = Fl // g
+    lb = Fl.bit_length() - 1
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    rows = lambda w, n: w[r * n:(r + 1) * n]
+
+    def allgather_rows(a):
+        parts = [torch.empty_like(t(a)) for _ in range(g)]
+        dist.all_gather(parts, t(a))
+        return np.concatenate([p.numpy() for p in parts], axis=0)
+
+    def allreduce_max(a):
+        v = t(a); dist.all_reduce(v, op=dist.ReduceOp.MAX); return v.numpy()
+
+    def reduce_scatter(acc):               # int32 [T][D] partial sums -> this rank's rows of the total
+        v = t(acc); dist.all_reduce(v); return v.numpy()[r * Tr:(r + 1) * Tr]
+
+    def alltoall(blocks):                   # blocks[p] goes to rank p; returns the list received (index = source)
+        every = [None] * g                  # gloo has no all_to_all: gather everything, pick what is addressed to this rank
+        dist.all_gather_object(every, [np.ascontiguousarray(b) for b in blocks])
+        return [every[s][r] for s in range(g)]
+
+    def quant_with(amax, v):                # the per-token quantiser given the row's largest magnitude (quant.h:84-109)
+        s = (amax / np.float32(127.0)).astype(np.float32); s[s == 0] = 1
+        return _round_half_away(v / s[:, None]).astype(np.int8), s
+
+    x = x_all[r * Tr:(r + 1) * Tr]          # this rank's rows
+    xq_l, xs_l = oracle.quant_per_token(oracle.rmsnorm(x, W["g0"][0]))
+    xq, xs = allgather_rows(xq_l), allgather_rows(xs_l)
+    lin = lambda w, s, n: oracle.linear_i8(xq, xs, rows(w, n), rows(s, n))[1]
+    att_l = _attention(oracle, W, lin(W["wq"][0], W["sq"][0], HQl * 64), lin(W["wk"][0], W["sk"][0], HKVl * 64),
+                       lin(W["wv"][0], W["sv"][0], HKVl * 64), HQl, HKVl, W["a_s"][0][r * HQl:(r + 1) * HQl], T)
+    amax = allreduce_max(np.abs(att_l).max(axis=1).astype(np.float32))
+    aq, as_ = quant_with(amax, att_l)
+    acc = reduce_scatter(oracle.gemm_s8s8(aq, np.ascontiguousarray(W["wo"][0][:, r * Dl:(r + 1) * Dl])))
+    x1 = oracle.residual(x, oracle.dequant(acc, as_[r * Tr:(r + 1) * Tr], W["so"][0]))
+    xq_l, xs_l = oracle.quant_per_token(oracle.rmsnorm(x1, W["g1"][0]))
+    xq, xs = allgather_rows(xq_l), allgather_rows(xs_l)
+    gt = oracle.linear_i8(xq, xs, rows(W["wg"][0], Fl), rows(W["sg"][0], Fl))[1]
+    up = oracle.linear_i8(xq, xs, rows(W["wu"][0], Fl), rows(W["su"][0], Fl))[1]
+    h = _fht_bits(oracle.silu_mul(gt, up), range(1, lb))                          # local stages: bits 1 .. lb-1
+    got = alltoall([h[:, p * Wn:(p + 1) * Wn] for p in range(g)])                # window r of every rank
+    z = np.stack(got, axis=1)                                                    # [T][src][Wn]
+    z = _fht_bits(z.transpose(0, 2, 1), range(0, g.bit_length() - 1)).transpose(0, 2, 1)   # rank-index bits = index bits lb, lb+1, ...
+    z = _fht_bits(z, [0])                                                        # bit 0 inside the window
+    hf = (z.reshape(T, g * Wn) / np.float32(np.sqrt(8192))).astype(np.float32)
+    amax = allreduce_max(np.abs(hf).max(axis=1).astype(np.float32))
+    hq, hs = quant_with(amax, hf)
+    cols = np.concatenate([np.arange(s_ * Fl + r * Wn, s_ * Fl + (r + 1) * Wn) for s_ in range(g)])     # K order of this rank's slice
+    acc = reduce_scatter(oracle.gemm_s8s8(hq, np.ascontiguousarray(W["wd"][0][:, cols])))
+    out_l = oracle.residual(x1, oracle.dequant(acc, hs[r * Tr:(r + 1) * Tr], W["sd"][0]))
+    ret[rank] = (allgather_rows(out_l), None)
+    dist.barrier(); dist.destroy_process_group()
+
+
+def _round_half_away(x):
+    """std::round on fp32 values (half away from zero)."""
+    x = np.asarray(x, np.float32)
+    return np.where(x >= 0, np.floor(x + np.float32(0.5)), np.ceil(x - np.float32(0.5))).astype(np.float32)
+
+
+CFGS_ROWS = {2: dict(hidden=512, hq=8, hkv=2, ffn=8192, vocab=1024, T=12, seed=72),
+             4: dict(hidden=1024, hq=16, hkv=4, ffn=8192, vocab=1024, T=8, seed=73)}
+
 import pytest
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_token_row_partition_is_bit_exact_on_cpu(world):
+    import oracle
+    CFG.clear(); CFG.update(CFGS_ROWS[world])
+    with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
+        want_out, _ = _single(oracle)
+    mgr = mp.Manager(); ret = mgr.dict()
+    mp.spawn(_rank_rows, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for rank in range(world):
+        assert np.array_equal(ret[rank][0].view(np.uint32), want_out.view(np.uint32)), f"rank {rank}: residual stream differs"
 
 
 @pytest.mark.parametrize("world", [2, 4])

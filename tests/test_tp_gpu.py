@@ -1,6 +1,8 @@
-"""Tensor-parallel model on 2 GPUs (one process per GPU, NCCL): identical greedy tokens and a
-bit-identical residual stream / logits against the CPU oracle's single-device forward. Skipped on
-boxes with fewer than two GPUs."""
+"""Tensor-parallel model on 2, 4 and 8 GPUs (one process per GPU, NCCL): identical greedy tokens on every rank and a
+bit-identical residual stream against the CPU oracle's single-device forward. Both partitions are covered: the
+token-row partition with batch-parallel decode (batch divisible by the number of ranks; the 8-rank case leaves one KV
+head per rank) and the all-gather partition (any batch, or FLEXLLM_TP_MODE=allgather). Cases that need more GPUs than
+the box has are skipped."""
 import os
 import socket
 
@@ -16,9 +18,11 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, cfg, ret):
+def _worker(rank, world, port, cfg, mode, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    if mode:
+        os.environ["FLEXLLM_TP_MODE"] = mode
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)      # only to hand the NCCL id around
     import flexllm_b200 as F
@@ -34,17 +38,24 @@ def _worker(rank, world, port, cfg, ret):
     out = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=True)
     m.prefill(torch.from_numpy(tokens).cuda()); torch.cuda.synchronize()
     hidden_gpu = m.buffer(0, (B * S, hidden), torch.float32).cpu().numpy()
+    ret[f"tokens{rank}"] = out.numpy().copy()
+    ret[f"status{rank}"] = F.lib().flexllm_device_status()
     if rank == 0:
-        ret["tokens"] = out.numpy().copy(); ret["hidden"] = hidden_gpu
-    else:
-        ret["tokens1"] = out.numpy().copy()
+        ret["hidden"] = hidden_gpu
     m.close(); tp.close()
     dist.barrier(); dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,cfg", [(2, (2, 512, 8, 2, 1008, 2, 32, 4, 60)), (2, (2, 1024, 16, 4, 2000, 12, 48, 4, 61)),
-                                       (4, (2, 1024, 16, 4, 2016, 5, 32, 4, 62))])
-def test_tp_matches_oracle(world, cfg):
+# cfg = (layers, hidden, heads_q, heads_kv, vocab, batch, prompt, generated, seed)
+@pytest.mark.parametrize("world,cfg,mode", [
+    (2, (2, 512, 8, 2, 1008, 2, 32, 4, 60), None),              # token rows, one sequence per rank
+    (2, (2, 1024, 16, 4, 2000, 12, 48, 4, 61), None),           # token rows, six sequences per rank
+    (2, (2, 1024, 16, 4, 2000, 12, 48, 4, 61), "allgather"),    # the same model on the all-gather partition
+    (4, (2, 1024, 16, 4, 2016, 5, 32, 4, 62), None),            # batch 5 on 4 ranks: falls back to the all-gather partition
+    (4, (2, 1024, 16, 4, 2016, 8, 32, 4, 64), None),            # token rows on 4 ranks
+    (8, (1, 2048, 32, 8, 2048, 8, 32, 3, 63), None),            # 8 ranks: one KV head, four query heads, 1024 FFN channels each
+])
+def test_tp_matches_oracle(world, cfg, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -52,10 +63,12 @@ def test_tp_matches_oracle(world, cfg):
     from flexllm_b200 import synthetic
     layers, hidden, hq, hkv, vocab, B, S, n_new, seed = cfg
     mgr = mp.Manager(); ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), cfg, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), cfg, mode, ret), nprocs=world, join=True)
     W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, S + n_new, seed=seed)
     tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
     with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
         ref = oracle.model_generate(W, tokens, n_new, want_hidden=True)
-    assert np.array_equal(ret["tokens"], ref["tokens"]) and np.array_equal(ret["tokens1"], ref["tokens"])
+    for rank in range(world):
+        assert ret[f"status{rank}"] == 0
+        assert np.array_equal(ret[f"tokens{rank}"], ref["tokens"]), f"rank {rank}: tokens differ"
     assert np.array_equal(ret["hidden"].view(np.uint32), ref["hidden"].view(np.uint32))
