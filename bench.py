@@ -619,9 +619,25 @@ def gpu_arm(args):
         r["t_pre"], r["t_dec"] = float(tt[0]), float(tt[1])
         r["units"] = BATCH * (PREFILL + NEW) * (1 if use_tp else world)
         r["value"] = r["units"] * steps / (r["ms_dev"] / 1e3)
+        if use_tp:
+            # parity carried by the bench itself: the tokens of the partitioned run against ONE GPU running the whole
+            # model on the same seed (rank 0 only; the other ranks wait)
+            tp_out = m.generate_host(tok_host, NEW, True).clone()
         m.close()
         del m
         torch.cuda.empty_cache()
+        if use_tp:
+            match = torch.ones(1, device="cuda")
+            if rank == 0:
+                one = F.Model(max_batch=BATCH, max_prefill=PREFILL, max_ctx=PREFILL + NEW, **CFG)
+                synthetic.load_random_weights(one, max_ctx=PREFILL + NEW, seed=seed, **CFG)
+                want = one.generate_host(tok_host, NEW, True)
+                match[0] = float(torch.equal(want, tp_out))
+                one.close()
+                del one
+                torch.cuda.empty_cache()
+            dist.broadcast(match, src=0)
+            r["tp_tokens_match"] = bool(match.item() == 1.0)
         return r
 
     def phases(r, nb):
@@ -646,6 +662,8 @@ def gpu_arm(args):
             nb_o = BATCH if not use_tp else BATCH * world
             other.update({"value": round(o["value"], 1), "unit": "tokens/s",
                           "ms_per_step": round(o["ms_dev"] / min(args.steps, 2), 3), "phases": phases(o, nb_o)})
+            if "tp_tokens_match" in o:
+                other["tp_tokens_match"] = o["tp_tokens_match"]
         except Exception as e:      # the side measurement must not take the headline line down with it
             other.update({"value": None, "error": f"{type(e).__name__}: {e}"})
 
@@ -683,6 +701,8 @@ def gpu_arm(args):
                         "d2h_bytes_per_step": BATCH * NEW * 4, "ms_per_step": round(r["ms_e2e"] / args.steps, 3)},
                 "gpu_launches": int(r["launches"]), "clocks": r["clocks"], "roofline": roof, "cpu_baseline": cpu,
                 "phases": phases(r, nb)}
+        if "tp_tokens_match" in r:
+            line["tp_tokens_match"] = r["tp_tokens_match"]
         if other is not None:
             line["other_partition"] = other
         if units is not None:

@@ -2,6 +2,7 @@
 // paged KV-cache view and the fused per-(sequence, KV head) attention step.
 #pragma once
 #include "common.cuh"
+#include "tc_common.cuh"
 
 // Paged int8 KV cache, all layers (layout at the top of attention_decode.cu).
 struct flexllm_kv_cache {
@@ -383,6 +384,368 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         }
         ATT_TS(9);
     }
+}
+
+
+// ---- staged variant (persistent decode kernel) ---------------------------------------------------------
+// The same step with the K pages, and after them the V pages, of the item brought into shared memory by bulk
+// asynchronous copies (one 4 KB copy per page, all in flight at once, completion on an mbarrier) instead of
+// per-thread global loads in dependent batches: the copies are issued before the new token is prepared, so the
+// scores start from shared memory as soon as the query is ready, and the V pages arrive while the softmax runs.
+// Needs (ctx + 1) keys <= cap_pages * 64; the caller falls back to dec_attn_fused_body otherwise. Same arithmetic
+// in the same order, hence the same bits.
+struct DecAttnStage {
+    uint8_t* kv;              // cap_pages * 4096 bytes of shared memory (128-byte aligned): K pages, later V^T pages
+    uint32_t bar_k, bar_v;    // shared-memory addresses of two mbarriers (arrival count 1)
+    uint32_t parity;          // their phase parity for this item (each is used once per item)
+    int cap_pages;
+    volatile int* abort_flag; // the CTA's "a bounded wait ran out" flag
+};
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Warp-level integer tensor-core product D (16 x 8, s32) += A (16 x 32, row-major) * B (32 x 8, column-major).
+// Fragments (lane = 4 * g + t): a0 = A[g][4t..4t+3], a1 = A[g+8][4t..], a2 = A[g][16+4t..], a3 = A[g+8][16+4t..];
+// b0 = B[4t..4t+3][g], b1 = B[16+4t..][g]; d0 = D[g][2t], d1 = D[g][2t+1], d2 = D[g+8][2t], d3 = D[g+8][2t+1].
+// Integer accumulation: exact, the same sums as the dp4a path in any order.
+__device__ __forceinline__ void mma_s8s8(int (&d)[4], const int (&a)[4], const int (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// the same with unsigned B (u8 probabilities against s8 values)
+__device__ __forceinline__ void mma_s8u8(int (&d)[4], const int (&a)[4], const int (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// round to nearest, halves away from zero (std::round), for the u8 quantiser: t >= 0 in every legitimate call
+// (probabilities, scales and a_s are positive), where floor(t + 0.5) with the sum rounded DOWN is exact
+__device__ __forceinline__ int round_half_away_to_int(float t) {
+    return t >= 0.0f ? __float2int_rz(__fadd_rd(t, 0.5f)) : (int)roundf(t);
+}
+
+// Returns false when a bounded wait ran out (the same verdict for all NT threads).
+template <int NT>
+__device__ __forceinline__ bool dec_attn_staged_body(const DecAttnIn& in, const float* __restrict__ cos_t,
+                                                     const float* __restrict__ sin_t, const float* __restrict__ a_s,
+                                                     const KvLayer& cache, const int32_t* __restrict__ page_table, int max_pages,
+                                                     int HQ, int HKV, int cs, float* __restrict__ out, const int hkv, const int b,
+                                                     const int pos, uint8_t* dsm, DecAttnSmem& sm, const DecAttnStage& st,
+                                                     const int tid, const int bar) {
+    constexpr int G = 4;
+    float* sc = reinterpret_cast<float*>(dsm);                       // [G][cs]
+    uint8_t* u_sm = dsm + (size_t)G * cs * 4;                        // [G][cs]
+    int8_t (*q_sm)[64] = sm.q_sm;
+    float* q_scale = sm.q_scale; float (*red)[16] = sm.red; float* row_max = sm.row_max; float* row_rinv = sm.row_rinv;
+    float (*part)[4] = sm.part;
+    int* pt_sm = sm.pt_sm;
+    named_sync_id<NT>(bar);   // the previous item of this group is done with the staging area and the score rows
+    ATT_TS(0);
+    const int w = tid >> 5, lane = tid & 31;
+    const int heads = HQ + 2 * HKV;
+    const int nk = pos + 1;
+    const int npages = (nk + PAGE - 1) / PAGE;
+    const uint32_t stage_addr = tc::smem_u32(st.kv);
+    // warp 7: one bulk copy per K page, all in flight
+    if (w == NT / 32 - 1) {
+        if (lane == 0) tc::mbar_expect_tx(st.bar_k, (uint32_t)npages * 4096u);
+        __syncwarp();
+        for (int p = lane; p < npages; p += 32) {
+            const long pg = page_table[(long)b * max_pages + p];
+            bulk_g2s(stage_addr + p * 4096, cache.k + (pg * HKV + hkv) * (long)(64 * PAGE), 4096u, st.bar_k);
+        }
+    }
+    // split-K partial sums of this warp's head (independent of the context): loads first
+    int a0 = 0, a1 = 0;
+    if (w < 6) {
+        const int h = w < 4 ? hkv * G + w : (w == 4 ? HQ + hkv : HQ + HKV + hkv);
+        const int32_t* src = in.qkv_acc + (long)b * heads * 64 + (long)h * 64 + lane;
+#pragma unroll 1
+        for (int sl = 0; sl < in.n_slabs; sl += 4) {
+            int p0[4], p1[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const bool on = sl + i < in.n_slabs;
+                p0[i] = on ? __ldcg(src + (sl + i) * in.slab_stride) : 0;
+                p1[i] = on ? __ldcg(src + (sl + i) * in.slab_stride + 32) : 0;
+            }
+            a0 += (p0[0] + p0[1]) + (p0[2] + p0[3]);
+            a1 += (p1[0] + p1[1]) + (p1[2] + p1[3]);
+        }
+    }
+    for (int i = tid; i < npages; i += NT) pt_sm[i] = page_table[(long)b * max_pages + i];
+    // K scales of this thread's keys (tid + u * NT) into registers; the new token's own scale comes from its preparation
+    constexpr int UK = 5;                                             // 5 * 256 keys = the staging capacity
+    float ks_pre[UK];
+#pragma unroll
+    for (int u = 0; u < UK; u++) {
+        const int key = tid + u * NT;
+        ks_pre[u] = 0.0f;
+        if (key < pos) {
+            const long pg = page_table[(long)b * max_pages + key / PAGE];
+            ks_pre[u] = cache.ks[(pg * HKV + hkv) * PAGE + (key % PAGE)];
+        }
+    }
+    ATT_TS(1);
+    // ---- A. prepare: warps 0..3 the query heads, warp 4 the key head, warp 5 the value head
+    int8_t new_a = 0, new_b = 0; float new_s = 0.0f;                  // warps 4 / 5: the new token's quantised head, for the staging patch
+    if (w < 6) {
+        const long pg = page_table[(long)b * max_pages + pos / PAGE];
+        const int slot = pos % PAGE;
+        const int h = w < 4 ? hkv * G + w : (w == 4 ? HQ + hkv : HQ + HKV + hkv);
+        const float stk = __ldcg(in.tok_scale + b);
+        const float x0 = ((float)a0 * stk) * in.ch_scale[h * 64 + lane];
+        const float x1 = ((float)a1 * stk) * in.ch_scale[h * 64 + lane + 32];
+        float a = x0, bb = x1;
+        if (w < 5) {
+            const float c = cos_t[(long)pos * 32 + lane], sn = sin_t[(long)pos * 32 + lane];
+            a = x0 * c - x1 * sn;
+            bb = x0 * sn + x1 * c;
+            auto lane_stage = [&](int bit) {
+                float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
+                float pb = __shfl_xor_sync(0xffffffffu, bb, 1 << bit);
+                if (lane & (1 << bit)) { a = pa - a; bb = pb - bb; }
+                else { a = a + pa; bb = bb + pb; }
+            };
+            lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
+            { float lo = a, hi = bb; a = lo + hi; bb = lo - hi; }
+            lane_stage(0);
+            a = a / 8.0f;
+            bb = bb / 8.0f;
+        }
+        const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
+        const float s2 = sym_scale_from(mx, mn);
+        const int8_t qa = quant_s8(a, s2), qb = quant_s8(bb, s2);
+        new_a = qa; new_b = qb; new_s = s2;
+        if (w < 4) {
+            q_sm[w][lane] = qa; q_sm[w][lane + 32] = qb;
+            if (lane == 0) q_scale[w] = s2;
+        } else if (w == 4) {
+            int8_t* dst = cache.k + ((pg * HKV + hkv) * PAGE + slot) * 64L;
+            dst[lane] = qa; dst[lane + 32] = qb;
+            if (lane == 0) cache.ks[(pg * HKV + hkv) * PAGE + slot] = s2;
+        } else {
+            int8_t* dst = cache.v + (pg * HKV + hkv) * (long)(64 * PAGE);
+            dst[(long)lane * PAGE + slot] = qa;
+            dst[(long)(lane + 32) * PAGE + slot] = qb;
+            if (lane == 0) cache.vs[(pg * HKV + hkv) * PAGE + slot] = s2;
+        }
+    }
+    // K scales into row 0 of the score buffer (each is read by its key's four lanes right before lane 0 overwrites it)
+#pragma unroll
+    for (int u = 0; u < UK; u++) {
+        const int key = tid + u * NT;
+        if (key < pos) sc[key] = ks_pre[u];
+    }
+    // warp 4 waits for the K pages, then puts the new token's row (the copy may or may not have seen the append) and scale in place
+    if (w == 4) {
+        int ok = lane == 0 ? (tc::mbar_wait(st.bar_k, st.parity, st.abort_flag) ? 1 : 0) : 1;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) {
+            int8_t* row = reinterpret_cast<int8_t*>(st.kv) + (size_t)pos * 64;
+            row[lane] = new_a; row[lane + 32] = new_b;
+            if (lane == 0) sc[pos] = new_s;
+        }
+        if (lane == 0) sm.last = ok;
+    }
+    named_sync_id<NT>(bar);
+    if (!sm.last) return false;
+    ATT_TS(2);
+
+    // ---- B. scores on the tensor cores: a warp takes blocks of 16 keys; A = 16 key rows x 32 dims from the staging area,
+    //         B = 32 dims x the 4 query heads (columns 4..7 are zero), two steps for the 64 dims
+    const int gi = lane >> 2, ti = lane & 3;
+    int bq[2][2];
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++) {
+        bq[ks][0] = gi < G ? *reinterpret_cast<const int*>(&q_sm[gi][ks * 32 + ti * 4]) : 0;
+        bq[ks][1] = gi < G ? *reinterpret_cast<const int*>(&q_sm[gi][ks * 32 + 16 + ti * 4]) : 0;
+    }
+    // lanes ti < 2 receive the sums of heads 2 ti and 2 ti + 1 for the keys gi and gi + 8 of the block
+    const float qs0 = q_scale[(2 * ti) & 3], qs1 = q_scale[(2 * ti + 1) & 3];
+    float mx0 = -1e32f, mx1 = -1e32f;
+    const int nblk = (nk + 15) >> 4;
+    for (int blk = w; blk < nblk; blk += NT / 32) {
+        const uint8_t* rows = st.kv + (size_t)(blk * 16 + gi) * 64 + ti * 4;
+        int d[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            int af[4];
+            af[0] = *reinterpret_cast<const int*>(rows + ks * 32);
+            af[1] = *reinterpret_cast<const int*>(rows + 8 * 64 + ks * 32);
+            af[2] = *reinterpret_cast<const int*>(rows + ks * 32 + 16);
+            af[3] = *reinterpret_cast<const int*>(rows + 8 * 64 + ks * 32 + 16);
+            mma_s8s8(d, af, bq[ks]);
+        }
+        const int kA = blk * 16 + gi, kB = kA + 8;
+        const float ksA = sc[kA < nk ? kA : nk - 1], ksB = sc[kB < nk ? kB : nk - 1];
+        __syncwarp();                            // every lane has read its keys' scales before row 0 is overwritten below
+        if (ti < 2) {
+            const int h0 = 2 * ti, h1 = h0 + 1;
+            if (kA < nk) {
+                const float x0 = (((float)d[0] * qs0) * ksA) * 0.125f, x1 = (((float)d[1] * qs1) * ksA) * 0.125f;
+                sc[h0 * cs + kA] = x0; sc[h1 * cs + kA] = x1;
+                mx0 = x0 > mx0 ? x0 : mx0; mx1 = x1 > mx1 ? x1 : mx1;
+            }
+            if (kB < nk) {
+                const float x0 = (((float)d[2] * qs0) * ksB) * 0.125f, x1 = (((float)d[3] * qs1) * ksB) * 0.125f;
+                sc[h0 * cs + kB] = x0; sc[h1 * cs + kB] = x1;
+                mx0 = x0 > mx0 ? x0 : mx0; mx1 = x1 > mx1 ? x1 : mx1;
+            }
+        }
+    }
+    ATT_TS(3);
+    // maximum over the lanes with the same ti (xor 4, 8, 16): lanes 0 and 1 then hold heads (0, 1) and (2, 3) of this warp
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    if (lane < 2) { red[2 * lane][w] = mx0; red[2 * lane + 1][w] = mx1; }
+    tc::fence_proxy_async_smem();               // this thread's reads / writes of the staging area, before the V copies overwrite it
+    named_sync_id<NT>(bar);
+    // warp 7: the V^T pages into the staging area
+    if (w == NT / 32 - 1) {
+        if (lane == 0) tc::mbar_expect_tx(st.bar_v, (uint32_t)npages * 4096u);
+        __syncwarp();
+        for (int p = lane; p < npages; p += 32)
+            bulk_g2s(stage_addr + p * 4096, cache.v + ((long)pt_sm[p] * HKV + hkv) * (long)(64 * PAGE), 4096u, st.bar_v);
+    }
+    if (tid < G) {
+        float m = red[tid][0];
+        for (int i = 1; i < NT / 32; i++) m = fmaxf(m, red[tid][i]);
+        row_max[tid] = m;
+    }
+    // V scales of this thread's keys (step F): requested now, used after the exponentials and the ordered sums
+    constexpr int UF = UK;
+    float vsc_pre[UF];
+#pragma unroll
+    for (int u = 0; u < UF; u++) {
+        const int key = tid + u * NT;
+        vsc_pre[u] = 0.0f;
+        if (key < nk) vsc_pre[u] = cache.vs[((long)pt_sm[key / PAGE] * HKV + hkv) * PAGE + (key % PAGE)];
+    }
+    named_sync_id<NT>(bar);
+    ATT_TS(4);
+    // ---- D. e = exp(x - max), in place
+    for (int g = 0; g < G; g++) {
+        const float m = row_max[g];
+        for (int key = tid; key < nk; key += NT) sc[g * cs + key] = ref_expf(sc[g * cs + key] - m);
+    }
+    named_sync_id<NT>(bar);
+    ATT_TS(5);
+    // ---- E. the four ordered chains of each row (Softmax.h:514-553): one thread per chain; the next eight terms are
+    //         fetched while the current eight are added (the adds are one dependent chain, the loads are not)
+    if (tid < 4 * G) {
+        const int g = tid >> 2, j = tid & 3;
+        const float* e = sc + g * cs + j;
+        const int n = (nk - j + 3) >> 2;                 // terms of this chain: keys j, j + 4, ...
+        float ps = 0.0f;
+        float cur[8], nxt[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) cur[i] = i < n ? e[4 * i] : 0.0f;
+        int i0 = 0;
+        for (; i0 + 8 < n; i0 += 8) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) nxt[i] = i0 + 8 + i < n ? e[4 * (i0 + 8 + i)] : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) ps += cur[i];
+#pragma unroll
+            for (int i = 0; i < 8; i++) cur[i] = nxt[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) if (i0 + i < n) ps += cur[i];
+        part[g][j] = ps;
+    }
+    named_sync_id<NT>(bar);
+    if (tid < G) row_rinv[tid] = 1.0f / ((part[tid][0] + part[tid][1]) + (part[tid][2] + part[tid][3]));
+    named_sync_id<NT>(bar);
+    ATT_TS(6);
+    // ---- F. u8 probabilities (zero beyond the last key up to the page boundary)
+    const int nk_pad = npages * PAGE;
+    {
+        float rinv_g[G];
+        DivBy as_g[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) { rinv_g[g] = row_rinv[g]; as_g[g] = div_by(a_s[hkv * G + g]); }
+#pragma unroll
+        for (int u = 0; u < UF; u++) {
+            const int key = tid + u * NT;
+            if (key < nk_pad) {
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    int r = 0;
+                    if (key < nk) {
+                        const float p = sc[g * cs + key] * rinv_g[g];
+                        r = round_half_away_to_int(div_for_rounding(p * vsc_pre[u], as_g[g]));
+                        r = r > 255 ? 255 : r;
+                    }
+                    u_sm[g * cs + key] = (uint8_t)r;
+                }
+            }
+        }
+    }
+    // warp 5 waits for the V pages and puts the new token's column in place
+    if (w == 5) {
+        int ok = lane == 0 ? (tc::mbar_wait(st.bar_v, st.parity, st.abort_flag) ? 1 : 0) : 1;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) {
+            int8_t* pg = reinterpret_cast<int8_t*>(st.kv) + (size_t)(pos / PAGE) * 4096 + (pos % PAGE);
+            pg[lane * PAGE] = new_a; pg[(lane + 32) * PAGE] = new_b;
+        }
+        if (lane == 0) sm.last = ok;
+    }
+    named_sync_id<NT>(bar);
+    if (!sm.last) return false;
+    ATT_TS(7);
+    // ---- G. P.V on the tensor cores: A = 16 dims x 32 keys of the V^T page, B = 32 keys x the 4 heads' u8 probabilities.
+    //         Warp w: dims 16 (w & 3) .. +15, pages (w >> 2), (w >> 2) + 2, ...; the two partial sums per dim block are
+    //         added through shared memory (integers: exact)
+    {
+        static_assert(NT == 256, "eight warps: four dim blocks x two page sets");
+        const int dblk = w & 3, pset = w >> 2;
+        int d[4] = {0, 0, 0, 0};
+        for (int p = pset; p < npages; p += 2) {
+            const uint8_t* rows = st.kv + (size_t)p * 4096 + (size_t)(dblk * 16 + gi) * PAGE + ti * 4;
+            const uint8_t* ucol = u_sm + (gi & 3) * cs + p * PAGE + ti * 4;
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                int af[4], bu[2];
+                af[0] = *reinterpret_cast<const int*>(rows + ks * 32);
+                af[1] = *reinterpret_cast<const int*>(rows + 8 * PAGE + ks * 32);
+                af[2] = *reinterpret_cast<const int*>(rows + ks * 32 + 16);
+                af[3] = *reinterpret_cast<const int*>(rows + 8 * PAGE + ks * 32 + 16);
+                bu[0] = gi < G ? *reinterpret_cast<const int*>(ucol + ks * 32) : 0;
+                bu[1] = gi < G ? *reinterpret_cast<const int*>(ucol + ks * 32 + 16) : 0;
+                mma_s8u8(d, af, bu);
+            }
+        }
+        ATT_TS(8);
+        int* pv_sm = reinterpret_cast<int*>(sc);          // the exponentials are no longer needed: [G][64] sums of page set 1
+        named_sync_id<NT>(bar);
+        if (pset == 1 && ti < 2) {
+            pv_sm[(2 * ti) * 64 + dblk * 16 + gi] = d[0]; pv_sm[(2 * ti + 1) * 64 + dblk * 16 + gi] = d[1];
+            pv_sm[(2 * ti) * 64 + dblk * 16 + gi + 8] = d[2]; pv_sm[(2 * ti + 1) * 64 + dblk * 16 + gi + 8] = d[3];
+        }
+        named_sync_id<NT>(bar);
+        if (pset == 0 && ti < 2) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int hd = 2 * ti + (i & 1), dim = dblk * 16 + gi + (i >> 1) * 8;
+                const int tot = d[i] + pv_sm[hd * 64 + dim];
+                const int hq = hkv * G + hd;
+                out[((long)b * HQ + hq) * 64 + dim] = (float)tot * a_s[hq];
+            }
+        }
+        ATT_TS(9);
+    }
+    tc::fence_proxy_async_smem();               // reads of the staging area, before the next item's (or a projection's) copies overwrite it
+    return true;
 }
 
 }  // namespace flexllm

@@ -525,7 +525,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     const uint32_t bar_empty = bar_full + 8 * MG_MAX_STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * MG_MAX_STAGES;
     const uint32_t bar_tempty = bar_tfull + 16;
-    unsigned long long* base_slot = reinterpret_cast<unsigned long long*>(bars + 2 * MG_MAX_STAGES + 4);
+    const uint32_t bar_att = bar_tempty + 16;            // attention staging: (K pages, V pages) of each half of the CTA
+    unsigned long long* base_slot = reinterpret_cast<unsigned long long*>(bars + 2 * MG_MAX_STAGES + 8);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_slot + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* go_flag = abort_flag + 1;
@@ -541,6 +542,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     if (tid == 0) {
         for (int s = 0; s < MG_MAX_STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
         for (int s = 0; s < 2; s++) { mbar_init(bar_tfull + 8 * s, 1); mbar_init(bar_tempty + 8 * s, 4); }
+        for (int s = 0; s < 4; s++) mbar_init(bar_att + 8 * s, 1);
         *abort_flag = 0;
         // every launch adds exactly n_barriers * G arrivals, so the launch's base is the counter rounded
         // down to a multiple of that (no CTA can be a whole launch ahead of another)
@@ -561,6 +563,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     int early_n = 0, early_stage0 = 0;           // TMA thread: weight tiles of the NEXT projection already in flight
     int cstage = 0; uint32_t cphase = 0;         // MMA thread: position in the ring
     int item_base = 0;                           // items (tile, split) this CTA has processed so far
+    uint32_t att_uses = 0;                       // attention items this half of the CTA has run on the staged path (mbarrier parity)
     const bool is_tma = (warp == 4 && lane == 0), is_mma = (warp == 5 && lane == 0);
 
     // k blocks of this CTA in a projection, in issue order: items t = cta, cta + G, ...; inside an item kb0..kb1-1
@@ -593,6 +596,12 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             early_n++;
             it.next();
         }
+    };
+    // The same tiles asked into L2 only (the ring is in use by the attention phase). TMA thread only.
+    auto prefetch_weights_l2 = [&](const MegaJob& j) {
+        KbIter it; it.init(j, cta, G);
+        tma_prefetch_desc(j.tmA);
+        for (int n = 0; n < STAGES && it.valid(); n++, it.next()) tma_prefetch_l2_2d(j.tmA, it.kb * 128, (it.t / j.ksplit) * 128);
     };
     // One projection. Roles: warp 4 lane 0 TMA, warp 5 lane 0 MMA, warps 0..3 epilogue.
     auto gemm_phase = [&](const MegaJob& j, const MegaJob* next_job) {
@@ -715,7 +724,9 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             } else if ((p == 0 || (k == PH_C && l + 1 < L)) && G > a.B) {
                 // CTAs without a row ask L2 for the KV pages an attention phase will read (any CTA can do this
                 // for any item: L2 is shared): the first layer's at the start of the step, and in every phase C
-                // those of the NEXT layer, long before they are needed
+                // those of the NEXT layer, long before they are needed. (Tried and slower: the same requests from the
+                // idle CTAs of the FHT phase, or from all CTAs at its start -- the page-table look-ups are a chain of
+                // latencies that then sits on that phase's critical path.)
                 const MegaLayer& nx = a.layers[p == 0 ? 0 : l + 1];
                 for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
                     dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
@@ -731,14 +742,34 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             const int half = tid >> 8;
             uint8_t* dsm = scratch + (size_t)half * a.attn_bytes;
             DecAttnSmem& sm = *reinterpret_cast<DecAttnSmem*>(dsm + a.attn_bytes - sizeof(DecAttnSmem));
+            // the operand ring is idle during this phase (the next projection's weights are only asked into L2): each half
+            // of the CTA stages its item's K pages, then V pages, in its half of the ring
+            const int half_bytes = ((STAGES * STAGE_BYTES) >> 1) & ~127;
+            DecAttnStage stg;
+            stg.kv = ring_ptr + (size_t)half * half_bytes;
+            stg.bar_k = bar_att + 16 * half; stg.bar_v = stg.bar_k + 8;
+            stg.cap_pages = half_bytes / 4096 < 20 ? half_bytes / 4096 : 20;
+            stg.abort_flag = abort_flag;
+            if (is_tma) prefetch_weights_l2(mega_job(a, l, 1));
             for (int idx = 2 * cta + half; idx < a.B * a.HKV; idx += 2 * G) {
                 const int b = idx / a.HKV;
+                const int pos = dec_guarded_pos(a.ctx, b, a.max_ctx, a.error_flag);
+                if (pos / PAGE + 1 <= stg.cap_pages) {
+                    stg.parity = att_uses & 1u;
+                    att_uses++;
+                    if (!dec_attn_staged_body<256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.HQ, a.HKV, a.cs, a.att,
+                                                   idx % a.HKV, b, pos, dsm, sm, stg, tid & 255, MG_BAR_HALF0 + half))
+                        break;
+                } else     // contexts beyond the staging area: per-thread global loads
                 dec_attn_fused_body<2, 256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
                                             a.att, nullptr, idx % a.HKV, b, dsm, sm, tid & 255, MG_BAR_HALF0 + half);
                 // the item that completes its sequence's attention row (the last of its HKV items to arrive)
                 // quantises the row for the o projection -- no separate phase, no extra grid barrier
                 mega_att_row_quant(a, b, sm, tid & 255, MG_BAR_HALF0 + half);
             }
+            // both halves are done with the ring (each thread has fenced its accesses): the o projection's weights may come in
+            named_sync<MG_BAR_WORK, MG_WORKERS>();
+            if (is_tma && !*abort_flag) prefetch_weights(mega_job(a, l, 1));
         } else if (k == PH_D) {
             const int parts = 4 * a.B <= G ? 4 : 1;         // CTAs per row
             if (cta < parts * a.B) {
@@ -756,7 +787,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             if (kind == 3 && cta == G - 1 && tid < 3 * a.slab_rows) a.fht_flags[tid] = 0;   // idle until the next FHT phase
             const MegaJob j = mega_job(a, l, kind);
             const MegaJob nj = kind < 3 ? mega_job(a, l, kind + 1) : (p + 1 < MG_PHASES_PER_LAYER * L ? mega_job(a, l + 1, 0) : mega_job(a, 0, 4));
-            gemm_phase(j, kind == 4 ? nullptr : &nj);
+            gemm_phase(j, (kind == 4 || kind == 0) ? nullptr : &nj);      // after q|k|v comes the attention phase, which uses the ring itself
         }
         if (p + 1 < n_phases) {
             if (!mega_grid_sync(a.sync_ctr, target_of(p) + (p == 0 ? (unsigned long long)a.test_barrier_extra : 0ull), abort_flag, go_flag,
