@@ -39,6 +39,7 @@ SIGNATURES = {
     "flexllm_kv_cache_destroy": [_P],
     "flexllm_kv_cache_reset": [_P, _P],
     "flexllm_kv_cache_pools": [_P, _I, _P, _P, _P, _P],
+    "flexllm_kv_append": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P],
     "flexllm_mha_decode_workspace": [_I, _I, _I],
     "flexllm_mha_i8xi8_decode": [_P, _I] + [_P] * 10 + [_I, _P, _I, _I, _I, _P, _P, _P, _SZ, _P],
     "flexllm_tp_unique_id": [_P, C.c_char_p],

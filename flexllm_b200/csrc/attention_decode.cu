@@ -119,6 +119,34 @@ __global__ void __launch_bounds__(256) dec_append_kernel(const int8_t* __restric
     dst[lane + 32] = quant_s8(bb, sc);
 }
 
+// Append only: the int8 K and V heads of one new token per sequence (already rotated / quantised by the caller) go to
+// slot ctx[b] of the sequence's current page. One warp per (sequence, K or V head).
+__global__ void __launch_bounds__(256) kv_append_kernel(const int8_t* __restrict__ k, const float* __restrict__ ks,
+                                                        const int8_t* __restrict__ v, const float* __restrict__ vs, KvLayer cache,
+                                                        const int32_t* __restrict__ page_table, int max_pages,
+                                                        const int32_t* __restrict__ ctx, int B, int HKV, int max_pos, int* error_flag) {
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= B * 2 * HKV) return;
+    const int b = w / (2 * HKV), h = w % (2 * HKV);
+    const int pos = dec_guarded_pos(ctx, b, max_pos, error_flag);
+    const long pg = page_table[(long)b * max_pages + pos / PAGE];
+    const int slot = pos % PAGE;
+    if (h < HKV) {
+        const int8_t* src = k + ((long)b * HKV + h) * 64;
+        int8_t* dst = cache.k + ((pg * HKV + h) * PAGE + slot) * 64L;
+        dst[lane] = src[lane]; dst[lane + 32] = src[lane + 32];
+        if (lane == 0) cache.ks[(pg * HKV + h) * PAGE + slot] = ks[(long)b * HKV + h];
+    } else {
+        const int hv = h - HKV;
+        const int8_t* src = v + ((long)b * HKV + hv) * 64;
+        int8_t* dst = cache.v + (pg * HKV + hv) * (long)(64 * PAGE);
+        dst[(long)lane * PAGE + slot] = src[lane];
+        dst[(long)(lane + 32) * PAGE + slot] = src[lane + 32];
+        if (lane == 0) cache.vs[(pg * HKV + hv) * PAGE + slot] = vs[(long)b * HKV + hv];
+    }
+}
+
 // ---- 2. scores ---------------------------------------------------------------------------------
 // grid (splits, HKV, B), 256 threads: one key per thread per iteration (4 pages at a time),
 // the G = HQ/HKV query heads of the group against each key.
@@ -380,39 +408,21 @@ int mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float*
                    const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, int HQ,
                    float* out, int32_t* oacc, void* workspace, cudaStream_t st);
 
-// K/V of a prefilled batch -> cache pages. k2 [B][HKV][S][64], ks2 [B][HKV][S], vT [B][HKV][64][S],
-// vsT [B][HKV][S] (the prefill attention's workspace layouts); sequence b occupies positions 0..S-1.
-__global__ void __launch_bounds__(256) kv_pack_kernel(const int8_t* __restrict__ k2, const float* __restrict__ ks2,
-                                                      const int8_t* __restrict__ vT, const float* __restrict__ vsT, KvLayer cache,
-                                                      const int32_t* __restrict__ page_table, int max_pages, int S, int HKV) {
-    const int p = blockIdx.x, h = blockIdx.y, b = blockIdx.z;      // page index within the sequence
-    const long pg = page_table[(long)b * max_pages + p];
-    const int t0 = p * PAGE;
-    const int n = min(PAGE, S - t0);
-    const long prow = (pg * HKV + h) * PAGE;
-    const long src_row = ((long)b * HKV + h) * S + t0;
-    // K rows: n x 64 bytes contiguous on both sides
-    for (int i = threadIdx.x; i < n * 16; i += 256)
-        reinterpret_cast<int*>(cache.k + prow * 64)[i] = reinterpret_cast<const int*>(k2 + src_row * 64)[i];
-    for (int i = threadIdx.x; i < n; i += 256) {
-        cache.ks[prow + i] = ks2[src_row + i];
-        cache.vs[prow + i] = vsT[src_row + i];
-    }
-    // V^T: for each dim, n contiguous tokens
-    for (int i = threadIdx.x; i < 64 * PAGE; i += 256) {
-        const int d = i / PAGE, t = i % PAGE;
-        if (t < n) cache.v[prow * 64 + (long)d * PAGE + t] = vT[(((long)b * HKV + h) * 64 + d) * S + t0 + t];
-    }
-}
+}  // namespace flexllm
 
-int kv_pack(flexllm_kv_cache* c, int layer, const int8_t* k2, const float* ks2, const int8_t* vT, const float* vsT,
-            const int32_t* page_table, int max_pages, int B, int S, cudaStream_t st) {
-    KvLayer L = kv_layer(c, layer);
-    dim3 g((S + PAGE - 1) / PAGE, c->hkv, B);
-    kv_pack_kernel<<<g, 256, 0, st>>>(k2, ks2, vT, vsT, L, page_table, max_pages, S, c->hkv);
+// The cache managers' append on its own (dec_K_cache_manager_template / dec_V_cache_manager_template,
+// Modules/MHA.h:484-513, :773-801): store the new token's K and V heads at position ctx[b], nothing else.
+extern "C" int flexllm_kv_append(flexllm_kv_cache* c, int layer, const int8_t* k, const float* ks, const int8_t* v, const float* vs,
+                                 const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, void* stream) {
+    FLEXLLM_REQUIRE(c && layer >= 0 && layer < c->layers && B >= 0 && max_ctx >= 0 && max_pages > 0);
+    if (B == 0) return FLEXLLM_OK;
+    FLEXLLM_REQUIRE(k && ks && v && vs && page_table && ctx);
+    FLEXLLM_REQUIRE((long)max_pages * PAGE > max_ctx);
+    const int warps = B * 2 * c->hkv;
+    kv_append_kernel<<<(warps + 7) / 8, 256, 0, (cudaStream_t)stream>>>(k, ks, v, vs, kv_layer(c, layer), page_table, max_pages, ctx, B, c->hkv,
+                                                                         max_ctx, device_error_flag());
     return launch_status();
 }
-}  // namespace flexllm
 
 extern "C" int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs,
                                         const int8_t* k, const float* ks, const int8_t* v, const float* vs,

@@ -23,6 +23,7 @@
 // order. One CTA = 128 queries of one (batch, query head) against 64-key tiles; 4 softmax warps +
 // TMA warp + MMA warp; TMEM: S (64 columns) + O (64 columns) = 128 columns, so four CTAs share an SM
 // and their 16 softmax warps hide each other's latencies.
+#include "attention_decode.cuh"     // layout of the paged KV cache
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -93,12 +94,16 @@ __global__ void __launch_bounds__(256) attn_v_transpose_kernel(const int8_t* __r
 
 // ------------------------------------------------------------------ main kernel
 struct AttnArgs {
-    int B, S, HQ, HKV;
-    const float* qs;    // [B][HQ][S]
-    const float* ks;    // [B][HKV][S]
-    const float* vs;    // [B][HKV][S]
+    int B, HQ, HKV;
+    int Sq;             // queries per sequence in this call (positions q_off .. q_off + Sq - 1)
+    int q_off;          // position of the first query, a multiple of 128; the keys are positions 0 .. q_off + Sq - 1
+    int Sk;             // contiguous K/V: rows per (batch, KV head) of the K, V^T and scale buffers
+    const float* qs;    // [B][HQ][Sq]
+    const float* ks;    // contiguous: [B][HKV][Sk]; paged: the cache's K scale pool [page][HKV][64]
+    const float* vs;    // likewise
+    const int32_t* page_table; int max_pages;   // non-null: K / V^T tiles are pages of the KV cache (one 64-key tile = one page)
     const float* a_s;   // [HQ]
-    float* out;         // [B][S][HQ*64]
+    float* out;         // [B][Sq][HQ*64]
     int32_t* oacc;      // optional, same shape
     uint8_t* ecache;    // exp values of sweep 1 kept for sweep 2 (attn_ecache_head_bytes per (batch, head))
     int* error_flag;
@@ -124,11 +129,11 @@ constexpr int ATT_P_BYTES = 128 * 64;         // U tile [128 queries][64 keys] u
 constexpr int ATT_SMEM = ATT_Q_BYTES + ATT_SLOTS * ATT_TILE_BYTES + 2 * ATT_P_BYTES + 1024 + 256;
 constexpr int ATT_TMEM_COLS = 128;
 
-// Bytes of exp-cache one (batch, query head) needs: for every 128-query tile qt its 2*(qt+1) key
-// tiles of 128 x 64 fp32.
-__host__ __device__ inline size_t attn_ecache_head_bytes(int S) {
-    const size_t n_qt = (S + 127) / 128;
-    return n_qt * (n_qt + 1) * (size_t)(128 * ATT_KT * 4);   // sum_{qt} 2*(qt+1) tiles
+// Bytes of exp-cache one (batch, query head) needs: for every 128-query tile qt = q_off/128 + t (t < n_qt) its
+// 2*(qt+1) key tiles of 128 x 64 fp32.
+__host__ __device__ inline size_t attn_ecache_head_bytes(int q_off, int Sq) {
+    const size_t n_qt = (Sq + 127) / 128, qt0 = q_off / 128;
+    return n_qt * (2 * qt0 + n_qt + 1) * (size_t)(128 * ATT_KT * 4);   // sum_{t < n_qt} 2*(qt0+t+1) tiles
 }
 
 __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmapQ,
@@ -157,15 +162,20 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_qt = (args.S + 127) >> 7;
-    const int qt = n_qt - 1 - (int)(blockIdx.x % n_qt);            // heavy tiles (late queries) first
+    const int S = args.q_off + args.Sq;                            // keys (positions 0 .. S-1)
+    const int n_qt = (args.Sq + 127) >> 7;
+    const int qt_l = n_qt - 1 - (int)(blockIdx.x % n_qt);          // query tile within the call: heavy tiles (late queries) first
+    const int qt0 = args.q_off >> 7, qt = qt0 + qt_l;              // ... and within the sequence
     const int hq = (int)((blockIdx.x / n_qt) % args.HQ);
     const int b = (int)(blockIdx.x / ((long)n_qt * args.HQ));
     const int hkv = hq / (args.HQ / args.HKV);
-    const int n_kt = 2 * (qt + 1);                                 // causal: 64-key tiles 0 .. 2*qt+1
+    const int n_kt_all = (S + ATT_KT - 1) / ATT_KT;
+    const int n_kt = 2 * (qt + 1) < n_kt_all ? 2 * (qt + 1) : n_kt_all;   // causal: 64-key tiles 0 .. 2*qt+1 (those that hold keys)
+    const bool paged = args.page_table != nullptr;
+    const int32_t* pt = paged ? args.page_table + (long)b * args.max_pages : nullptr;
     // this CTA's slice of the exp cache: [n_kt][16 float4 chunks][128 rows] float4
-    float4* ecache = reinterpret_cast<float4*>(args.ecache + ((size_t)b * args.HQ + hq) * attn_ecache_head_bytes(args.S) +
-                                               (size_t)qt * (qt + 1) * (size_t)(128 * ATT_KT * 4));
+    float4* ecache = reinterpret_cast<float4*>(args.ecache + ((size_t)b * args.HQ + hq) * attn_ecache_head_bytes(args.q_off, args.Sq) +
+                                               ((size_t)2 * qt_l * qt0 + (size_t)qt_l * (qt_l + 1)) * (size_t)(128 * ATT_KT * 4));
 
     if (threadIdx.x == 0) {
         mbar_init(bar_qfull, 1);
@@ -189,7 +199,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
         if (lane == 0) {
             tma_prefetch_desc(&tmapQ); tma_prefetch_desc(&tmapK); tma_prefetch_desc(&tmapV);
             mbar_expect_tx(bar_qfull, ATT_Q_BYTES);
-            tma_load_2d(sQ, &tmapQ, bar_qfull, 0, ((b * args.HQ + hq) * args.S) + qt * 128);
+            tma_load_2d(sQ, &tmapQ, bar_qfull, 0, ((b * args.HQ + hq) * args.Sq) + qt_l * 128);
             int slot = 0; uint32_t phase = 0;
             for (int it = 0; it < 3 * n_kt; it++) {
                 const int sweep = it / n_kt, j = it - sweep * n_kt;
@@ -197,7 +207,10 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
                 const uint32_t full = bar_tfull + 8 * slot;
                 const uint32_t dst = sT + slot * ATT_TILE_BYTES;
                 mbar_expect_tx(full, ATT_TILE_BYTES);
-                if (sweep < 2) tma_load_2d(dst, &tmapK, full, 0, ((b * args.HKV + hkv) * args.S) + j * ATT_KT);
+                if (paged) {        // one tile = one page of the cache: K rows [64 keys][64 B], V^T rows [64 dims][64 keys]
+                    const int row = (__ldg(pt + j) * args.HKV + hkv) * 64;
+                    tma_load_2d(dst, sweep < 2 ? &tmapK : &tmapV, full, 0, row);
+                } else if (sweep < 2) tma_load_2d(dst, &tmapK, full, 0, ((b * args.HKV + hkv) * args.Sk) + j * ATT_KT);
                 else tma_load_2d(dst, &tmapV, full, j * ATT_KT, (b * args.HKV + hkv) * 64);
                 if (++slot == ATT_SLOTS) { slot = 0; phase ^= 1u; }
             }
@@ -242,11 +255,11 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
         // ------------------------------------------------------------ softmax warps 0..3
         const int row_in_tile = warp * 32 + lane;
         const int qpos = qt * 128 + row_in_tile;               // position of this thread's query
-        const bool q_ok = qpos < args.S;
+        const bool q_ok = qpos < S;
         const int qlim = q_ok ? qpos : -1;                     // keys 0..qlim are visible to this row
-        const float qscale = q_ok ? args.qs[((long)b * args.HQ + hq) * args.S + qpos] : 0.0f;
-        const float* ksp = args.ks + ((long)b * args.HKV + hkv) * args.S;
-        const float* vsp = args.vs + ((long)b * args.HKV + hkv) * args.S;
+        const float qscale = q_ok ? args.qs[((long)b * args.HQ + hq) * args.Sq + (qpos - args.q_off)] : 0.0f;
+        const float* ksp = args.ks + ((long)b * args.HKV + hkv) * args.Sk;      // contiguous layout
+        const float* vsp = args.vs + ((long)b * args.HKV + hkv) * args.Sk;
         const float a_s = args.a_s[hq];
         const DivBy d_as = div_by(a_s);
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
@@ -261,6 +274,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
             if (!got) { ok = false; break; }
             tc_fence_after();
             const int k0 = j * ATT_KT;
+            const float* kst = paged ? args.ks + ((long)__ldg(pt + j) * args.HKV + hkv) * 64 : ksp + k0;   // this tile's key scales
 #pragma unroll 1
             for (int c = 0; c < ATT_KT / 16; c++) {
                 uint32_t v[16];
@@ -270,7 +284,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
                 float ksv[16];
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
-                    const float4 t = (kc + i < args.S) ? *reinterpret_cast<const float4*>(ksp + kc + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 t = (kc + i < S) ? *reinterpret_cast<const float4*>(kst + c * 16 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
                     ksv[i] = t.x; ksv[i + 1] = t.y; ksv[i + 2] = t.z; ksv[i + 3] = t.w;
                 }
                 tmem_ld_wait();
@@ -313,6 +327,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
             got = __shfl_sync(0xffffffffu, got, 0);
             if (!got) { ok = false; break; }
             const int k0 = j * ATT_KT;
+            const float* vst = paged ? args.vs + ((long)__ldg(pt + j) * args.HKV + hkv) * 64 : vsp + k0;   // this tile's value scales
             uint8_t* prow = sP_ptr + pb * ATT_P_BYTES + row_in_tile * 64;
 #pragma unroll
             for (int c = 0; c < 4; c++) {          // 16 keys = one 16-byte chunk of the U row
@@ -324,7 +339,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
 #pragma unroll
                 for (int i4 = 0; i4 < 4; i4++) {
                     const int kk = k0 + c * 16 + i4 * 4;
-                    const float4 vs4 = (kk < args.S) ? *reinterpret_cast<const float4*>(vsp + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 vs4 = (kk < S) ? *reinterpret_cast<const float4*>(vst + c * 16 + i4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
                     const float4 e4 = ev[(c & 1) * 4 + i4];
                     const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
                     const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
@@ -359,7 +374,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
                     tmem_ld_32x16(tmem_O + lane_addr + c * 16, v);
                     tmem_ld_wait();
                     if (q_ok) {
-                        const long o = (((long)b * args.S + qpos) * args.HQ + hq) * 64 + c * 16;
+                        const long o = (((long)b * args.Sq + (qpos - args.q_off)) * args.HQ + hq) * 64 + c * 16;
 #pragma unroll
                         for (int i = 0; i < 16; i += 4) {
                             float4 r;
@@ -388,28 +403,32 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
 
 int* device_error_flag();
 
-// fp32 front end used by the model: qkv [B*S][(HQ+2*HKV)*64] fp32 as the fused q/k/v projection
-// writes it. Query and key heads: RoPE -> FHT-64/8 -> per-head int8 (head-major outputs); value
-// heads: per-head int8 quant (quant.h:527-650) written token-major for the transpose kernel.
+// fp32 front end used by the model: qkv [B*Sq][(HQ+2*HKV)*64] fp32 as the fused q/k/v projection writes it, tokens at
+// positions q_off .. q_off + Sq - 1. Query heads: RoPE -> FHT-64/8 -> per-head int8, head-major [B][HQ][Sq][64] for the
+// attention kernel's Q tiles. Key heads: the same arithmetic, written straight into the KV cache's pages (row = token).
+// Value heads: per-head int8 quant (quant.h:527-650), token-major into a scratch that attn_v_to_pages_kernel transposes
+// into the cache's V^T pages.
 __global__ void __launch_bounds__(256) attn_qkv_prepare_f32_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
-                                                                   const float* __restrict__ sin_t, int B, int S, int HQ, int HKV,
+                                                                   const float* __restrict__ sin_t, int B, int Sq, int q_off, int HQ, int HKV,
                                                                    int8_t* __restrict__ q2, float* __restrict__ qs2,
-                                                                   int8_t* __restrict__ k2, float* __restrict__ ks2,
+                                                                   int8_t* __restrict__ k_pool, float* __restrict__ ks_pool,
+                                                                   const int32_t* __restrict__ page_table, int max_pages,
                                                                    int8_t* __restrict__ v2, float* __restrict__ vs2) {
     const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int heads = HQ + 2 * HKV;
-    if (w >= (long)B * S * heads) return;
+    if (w >= (long)B * Sq * heads) return;
     const int h = (int)(w % heads);
     const long bt = w / heads;
-    const int t = (int)(bt % S);
-    const int b = (int)(bt / S);
+    const int t = (int)(bt % Sq);
+    const int b = (int)(bt / Sq);
+    const int pos = q_off + t;
     const float* src = qkv + bt * (long)heads * 64 + (long)h * 64;
     const float x0 = src[lane], x1 = src[lane + 32];
     float a, bb;
     const bool rotate = h < HQ + HKV;
     if (rotate) {
-        const float c = cos_t[(long)t * 32 + lane], sn = sin_t[(long)t * 32 + lane];
+        const float c = cos_t[(long)pos * 32 + lane], sn = sin_t[(long)pos * 32 + lane];
         a = x0 * c - x1 * sn;
         bb = x0 * sn + x1 * c;
         auto lane_stage = [&](int bit) {
@@ -429,17 +448,41 @@ __global__ void __launch_bounds__(256) attn_qkv_prepare_f32_kernel(const float* 
     const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
     const float sc = sym_scale_from(mx, mn);
     int8_t* dst; float* sdst;
-    if (h < HQ) { const long o = ((long)b * HQ + h) * S + t; dst = q2 + o * 64; sdst = qs2 + o; }
-    else if (h < HQ + HKV) { const long o = ((long)b * HKV + (h - HQ)) * S + t; dst = k2 + o * 64; sdst = ks2 + o; }
-    else { const long o = ((long)b * S + t) * HKV + (h - HQ - HKV); dst = v2 + o * 64; sdst = vs2 + o; }
+    if (h < HQ) { const long o = ((long)b * HQ + h) * Sq + t; dst = q2 + o * 64; sdst = qs2 + o; }
+    else if (h < HQ + HKV) {
+        const long row = ((long)page_table[(long)b * max_pages + pos / 64] * HKV + (h - HQ)) * 64 + (pos & 63);
+        dst = k_pool + row * 64; sdst = ks_pool + row;
+    } else { const long o = ((long)b * Sq + t) * HKV + (h - HQ - HKV); dst = v2 + o * 64; sdst = vs2 + o; }
     if (lane == 0) *sdst = sc;
     dst[lane] = quant_s8(a, sc);
     dst[lane + 32] = quant_s8(bb, sc);
 }
 
+// V [B][Sq][HKV][64] (token-major scratch) -> the cache's V^T pages [page][HKV][64 dims][64 tokens] and scale pages,
+// for the tokens at positions q_off .. q_off + Sq - 1 (q_off a multiple of 64: one 64-token tile = one page).
+__global__ void __launch_bounds__(256) attn_v_to_pages_kernel(const int8_t* __restrict__ v, const float* __restrict__ vs, int Sq, int q_off,
+                                                              int HKV, const int32_t* __restrict__ page_table, int max_pages,
+                                                              int8_t* __restrict__ v_pool, float* __restrict__ vs_pool) {
+    __shared__ int8_t tile[64][64 + 4];
+    const int s0 = blockIdx.x * 64, h = blockIdx.y, b = blockIdx.z;
+    const long prow = ((long)page_table[(long)b * max_pages + (q_off + s0) / 64] * HKV + h) * 64;
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+        const int r = i >> 4, c4 = i & 15;   // r: token in tile, c4: group of 4 dims
+        int val = 0;
+        if (s0 + r < Sq) val = *reinterpret_cast<const int*>(v + (((long)b * Sq + s0 + r) * HKV + h) * 64 + c4 * 4);
+        *reinterpret_cast<int*>(&tile[r][c4 * 4]) = val;
+    }
+    if (threadIdx.x < 64 && s0 + threadIdx.x < Sq) vs_pool[prow + threadIdx.x] = vs[((long)b * Sq + s0 + threadIdx.x) * HKV + h];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int d = i >> 6, r = i & 63;
+        if (s0 + r < Sq) v_pool[(prow + d) * 64 + r] = tile[r][d];
+    }
+}
+
 static size_t align_up_(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// Workspace carve-up shared by both front ends.
+// Workspace of the stand-alone operator (contiguous head-major K, V^T).
 struct PrefillWs {
     int8_t *q2, *k2, *vT, *v2;
     float *qs2, *ks2, *vsT, *vs2;
@@ -450,7 +493,7 @@ struct PrefillWs {
         n += 3 * align_up_((size_t)B * HKV * S * 64, 1024);
         n += align_up_((size_t)B * HQ * S * 4, 1024);
         n += 3 * align_up_((size_t)B * HKV * S * 4, 1024);
-        n += align_up_((size_t)B * HQ * attn_ecache_head_bytes(S), 1024);
+        n += align_up_((size_t)B * HQ * attn_ecache_head_bytes(0, S), 1024);
         return n + 1024;
     }
     PrefillWs(void* ws, int B, int S, int HQ, int HKV) {
@@ -467,17 +510,35 @@ struct PrefillWs {
     }
 };
 
-static int mha_prefill_core(const PrefillWs& ws, const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
-                            cudaStream_t st) {
+// Workspace of the model path (K and V live in the KV cache): head-major Q, token-major V scratch, exp cache.
+struct PagedWs {
+    int8_t *q2, *v2; float *qs2, *vs2; uint8_t* ecache;
+    static size_t bytes(int B, int Sq_max, int HQ, int HKV, size_t ecache_head_bytes) {
+        return align_up_((size_t)B * HQ * Sq_max * 64, 1024) + align_up_((size_t)B * HKV * Sq_max * 64, 1024) +
+               align_up_((size_t)B * HQ * Sq_max * 4, 1024) + align_up_((size_t)B * HKV * Sq_max * 4, 1024) +
+               align_up_((size_t)B * HQ * ecache_head_bytes, 1024) + 1024;
+    }
+    PagedWs(void* ws, int B, int Sq_max, int HQ, int HKV) {
+        uint8_t* w = (uint8_t*)align_up_((size_t)ws, 1024);
+        q2 = (int8_t*)w; w += align_up_((size_t)B * HQ * Sq_max * 64, 1024);
+        v2 = (int8_t*)w; w += align_up_((size_t)B * HKV * Sq_max * 64, 1024);
+        qs2 = (float*)w; w += align_up_((size_t)B * HQ * Sq_max * 4, 1024);
+        vs2 = (float*)w; w += align_up_((size_t)B * HKV * Sq_max * 4, 1024);
+        ecache = w;
+    }
+};
+
+// a: everything but the error flag filled in. k_rows / v_rows: rows of the [rows][64 B] (K; paged V^T) or
+// [rows][v_row_bytes] (contiguous V^T) matrices the tensor maps describe.
+static int mha_prefill_core(AttnArgs a, const int8_t* q2, const int8_t* kmat, uint64_t k_rows, const int8_t* vmat, uint64_t v_rows,
+                            uint64_t v_row_bytes, cudaStream_t st) {
     CUtensorMap tq, tk, tv;
-    int rc = make_tmap_2d_u8_box(&tq, ws.q2, (uint64_t)B * HQ * S, 64, 64, 128, 64);
+    int rc = make_tmap_2d_u8_box(&tq, q2, (uint64_t)a.B * a.HQ * a.Sq, 64, 64, 128, 64);
     if (rc != FLEXLLM_OK) return rc;
-    rc = make_tmap_2d_u8_box(&tk, ws.k2, (uint64_t)B * HKV * S, 64, 64, ATT_KT, 64);
+    rc = make_tmap_2d_u8_box(&tk, kmat, k_rows, 64, 64, ATT_KT, 64);
     if (rc != FLEXLLM_OK) return rc;
-    rc = make_tmap_2d_u8_box(&tv, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, ATT_KT, 64, 64);
+    rc = make_tmap_2d_u8_box(&tv, vmat, v_rows, v_row_bytes, ATT_KT, 64, 64);
     if (rc != FLEXLLM_OK) return rc;
-    AttnArgs a;
-    a.B = B; a.S = S; a.HQ = HQ; a.HKV = HKV; a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.a_s = a_s; a.out = out; a.oacc = oacc; a.ecache = ws.ecache;
     a.error_flag = device_error_flag();
     static std::atomic<bool> attr_set[kMaxDevices];      // the attribute belongs to (function, device)
     const int dev = current_device();
@@ -486,33 +547,52 @@ static int mha_prefill_core(const PrefillWs& ws, const float* a_s, int B, int S,
         FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
         attr_set[dev].store(true, std::memory_order_release);
     }
-    const int n_qt = (S + 127) / 128;
-    const long grid = (long)B * HQ * n_qt;
+    const int n_qt = (a.Sq + 127) / 128;
+    const long grid = (long)a.B * a.HQ * n_qt;
     attn_prefill_kernel<<<(unsigned)grid, 192, ATT_SMEM, st>>>(tq, tk, tv, a);
     return launch_status();
 }
 
-size_t mha_prefill_ws_bytes(int B, int S, int HQ, int HKV) { return PrefillWs::bytes(B, S, HQ, HKV); }
+// Exp-cache bytes per (batch, query head) that a model with these limits can need: prompts are processed in chunks of
+// max_prefill tokens starting at multiples of it.
+static size_t paged_ecache_head_bytes(int max_prefill, int max_ctx) {
+    size_t worst = 0;
+    for (long c0 = 0; c0 < max_ctx; c0 += max_prefill) {
+        const int sc = (int)(max_ctx - c0 < max_prefill ? max_ctx - c0 : max_prefill);
+        const size_t n = attn_ecache_head_bytes((int)c0, sc);
+        if (n > worst) worst = n;
+    }
+    return worst;
+}
 
-// Model path: attention from the fp32 output of the fused q/k/v projection. Leaves the prepared
-// K (head-major int8 + scales) and V^T in the workspace for the KV-cache pack that follows.
-int mha_prefill_f32(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int S, int HQ, int HKV,
-                    float* out, void* workspace, cudaStream_t st, const int8_t** k2, const float** ks2, const int8_t** vT,
-                    const float** vsT) {
-    if (S % 16 != 0) return FLEXLLM_ENOTSUP;
-    PrefillWs ws(workspace, B, S, HQ, HKV);
-    const long warps = (long)B * S * (HQ + 2 * HKV);
-    attn_qkv_prepare_f32_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(qkv, cos_t, sin_t, B, S, HQ, HKV, ws.q2, ws.qs2,
-                                                                            ws.k2, ws.ks2, ws.v2, ws.vs2);
-    dim3 g((S + 63) / 64, HKV, B);
-    attn_v_transpose_kernel<<<g, 256, 0, st>>>(ws.v2, ws.vs2, B, S, HKV, ws.vT, ws.vsT);
+size_t mha_prefill_ws_bytes(int B, int max_prefill, int max_ctx, int HQ, int HKV) {
+    return PagedWs::bytes(B, max_prefill, HQ, HKV, paged_ecache_head_bytes(max_prefill, max_ctx));
+}
+
+// Model path: attention of the Sq tokens at positions q_off .. q_off + Sq - 1 of every sequence, from the fp32 output of
+// the fused q/k/v projection, over the paged KV cache: the new keys and values are written into the cache first (which
+// is the hand-over to decode: nothing is repacked afterwards), then every query attends to cache positions 0 .. its own.
+// q_off is a multiple of 128 (0 for a prompt that fits one call). max_prefill: the Sq the workspace was sized for.
+int mha_prefill_paged(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int Sq, int q_off, int HQ, int HKV,
+                      int max_prefill, flexllm_kv_cache* c, int layer, const int32_t* page_table, int max_pages, float* out,
+                      void* workspace, cudaStream_t st) {
+    if (Sq % 16 != 0 || q_off % 128 != 0 || Sq > max_prefill || c->hkv != HKV) return FLEXLLM_ENOTSUP;
+    PagedWs ws(workspace, B, max_prefill, HQ, HKV);
+    int8_t* k_pool = c->k + (size_t)layer * c->page_bytes; int8_t* v_pool = c->v + (size_t)layer * c->page_bytes;
+    float* ks_pool = c->ks + (size_t)layer * (c->scale_bytes / 4); float* vs_pool = c->vs + (size_t)layer * (c->scale_bytes / 4);
+    const long warps = (long)B * Sq * (HQ + 2 * HKV);
+    attn_qkv_prepare_f32_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(qkv, cos_t, sin_t, B, Sq, q_off, HQ, HKV, ws.q2, ws.qs2, k_pool,
+                                                                            ks_pool, page_table, max_pages, ws.v2, ws.vs2);
+    dim3 g((Sq + 63) / 64, HKV, B);
+    attn_v_to_pages_kernel<<<g, 256, 0, st>>>(ws.v2, ws.vs2, Sq, q_off, HKV, page_table, max_pages, v_pool, vs_pool);
     int rc = launch_status(2);
     if (rc != FLEXLLM_OK) return rc;
-    if (k2) *k2 = ws.k2;
-    if (ks2) *ks2 = ws.ks2;
-    if (vT) *vT = ws.vT;
-    if (vsT) *vsT = ws.vsT;
-    return mha_prefill_core(ws, a_s, B, S, HQ, HKV, out, nullptr, st);
+    AttnArgs a;
+    a.B = B; a.HQ = HQ; a.HKV = HKV; a.Sq = Sq; a.q_off = q_off; a.Sk = 0;
+    a.qs = ws.qs2; a.ks = ks_pool; a.vs = vs_pool; a.page_table = page_table; a.max_pages = max_pages;
+    a.a_s = a_s; a.out = out; a.oacc = nullptr; a.ecache = ws.ecache;
+    const uint64_t rows = (uint64_t)c->n_pages * HKV * 64;
+    return mha_prefill_core(a, ws.q2, k_pool, rows, v_pool, rows, 64, st);
 }
 
 }  // namespace flexllm
@@ -543,5 +623,9 @@ extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const
     attn_v_transpose_kernel<<<g, 256, 0, st>>>(v, vs, B, S, HKV, ws.vT, ws.vsT);
     int rc = launch_status(3);
     if (rc != FLEXLLM_OK) return rc;
-    return mha_prefill_core(ws, a_s, B, S, HQ, HKV, out, oacc, st);
+    AttnArgs a;
+    a.B = B; a.HQ = HQ; a.HKV = HKV; a.Sq = S; a.q_off = 0; a.Sk = S;
+    a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.page_table = nullptr; a.max_pages = 0;
+    a.a_s = a_s; a.out = out; a.oacc = oacc; a.ecache = ws.ecache;
+    return mha_prefill_core(a, ws.q2, ws.k2, (uint64_t)B * HKV * S, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, st);
 }

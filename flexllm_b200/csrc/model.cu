@@ -27,12 +27,10 @@ namespace flexllm {
 int gemm_i8_prefill(const int8_t* a, const float* s_tok, const int8_t* w, const float* s_ch, int M, int N, int K,
                     int32_t* acc, float* y, cudaStream_t st, const float* residual);
 int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st);
-size_t mha_prefill_ws_bytes(int B, int S, int HQ, int HKV);
-int mha_prefill_f32(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int S, int HQ, int HKV,
-                    float* out, void* workspace, cudaStream_t st, const int8_t** k2, const float** ks2, const int8_t** vT,
-                    const float** vsT);
-int kv_pack(flexllm_kv_cache* c, int layer, const int8_t* k2, const float* ks2, const int8_t* vT, const float* vsT,
-            const int32_t* page_table, int max_pages, int B, int S, cudaStream_t st);
+size_t mha_prefill_ws_bytes(int B, int max_prefill, int max_ctx, int HQ, int HKV);
+int mha_prefill_paged(const float* qkv, const float* cos_t, const float* sin_t, const float* a_s, int B, int Sq, int q_off, int HQ, int HKV,
+                      int max_prefill, flexllm_kv_cache* c, int layer, const int32_t* page_table, int max_pages, float* out,
+                      void* workspace, cudaStream_t st);
 int mha_decode_run(flexllm_kv_cache* c, int layer, const int8_t* q, const float* qs, const int8_t* k, const float* ks,
                    const int8_t* v, const float* vs, const float* qkv_f32, const float* cos_t, const float* sin_t,
                    const float* a_s, const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, int HQ,
@@ -57,11 +55,14 @@ int topk_sample(const float* logits, int B, long V, int lanes, int top_k, const 
 // x[t][:] = (float)lm_w[tok[t]][:] * lm_s[tok[t]]
 // An id outside [0, V) (device data the host has not seen, e.g. fed back by a sampler) is clamped so that
 // it cannot become a wild read, and reported through the error word.
+// Row t of x is token (t0 + t) of the call: sequence b = (t0 + t) / Sc, position c0 + (t0 + t) % Sc of tok [B][S]
+// (a decode step passes S = Sc = 1, c0 = t0 = 0: row t = tok[t]).
 __global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __restrict__ lm_w, const float* __restrict__ lm_s,
-                             int D, int V, float* __restrict__ x, int* error_flag) {
+                             int D, int V, float* __restrict__ x, int* error_flag, int S, int c0, int Sc, long t0) {
     pdl_sync();
     const int t = blockIdx.x;
-    int id = tok[t];
+    const long tg = t0 + t;
+    int id = tok[(tg / Sc) * S + c0 + tg % Sc];
     if (id < 0 || id >= V) {
         if (threadIdx.x == 0 && error_flag) atomicOr(error_flag, 2);
         id = id < 0 ? 0 : V - 1;
@@ -128,6 +129,7 @@ struct flexllm_model {
     size_t attn_ws_bytes = 0, dec_ws_bytes = 0;
     // decode state
     int B = 0, S = 0;
+    int last_chunk = 0;                         // rows per sequence the residual stream x holds after the last prefill
     int n_new = 0;                              // columns of the token table of the running generation
     int pos = 0;                                // context length of the batch = position the next decode step writes
     cudaGraphExec_t graph = nullptr; int graph_B = 0; int graph_kernels = 0;
@@ -205,7 +207,7 @@ extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_
     const int n_pages = m->max_pages * c->max_batch;
     if ((rc = flexllm_kv_cache_create(&m->cache, NL, n_pages, HKV, 64))) return fail(rc);
     if ((rc = dmalloc(m, &m->page_table, (size_t)c->max_batch * m->max_pages)) || (rc = dmalloc(m, &m->ctx, 64)) ||
-        (rc = dmalloc(m, &m->next, 64)) || (rc = dmalloc(m, &m->state, 4)) || (rc = dmalloc(m, &m->tokens, Mmax)))
+        (rc = dmalloc(m, &m->next, 64)) || (rc = dmalloc(m, &m->state, 4)) || (rc = dmalloc(m, &m->tokens, (size_t)c->max_batch * c->max_ctx)))
         return fail(rc);
     m->out_capacity = (size_t)c->max_batch * (c->max_ctx + 1);
     if ((rc = dmalloc(m, &m->out_tokens, m->out_capacity))) return fail(rc);
@@ -241,7 +243,7 @@ extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_
                 return fail(rc);
         }
     }
-    m->attn_ws_bytes = mha_prefill_ws_bytes(c->max_batch, c->max_prefill, HQ, HKV);
+    m->attn_ws_bytes = mha_prefill_ws_bytes(c->max_batch, c->max_prefill, c->max_ctx, HQ, HKV);
     m->dec_ws_bytes = flexllm_mha_decode_workspace(c->max_batch, HQ, c->max_ctx);
     uint8_t *a = nullptr, *d = nullptr;
     if ((rc = dmalloc(m, &a, m->attn_ws_bytes)) || (rc = dmalloc(m, &d, m->dec_ws_bytes))) return fail(rc);
@@ -358,17 +360,16 @@ static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaSt
 // single-GPU model's bit for bit. Afterwards the KV cache (sharded by KV head during the prefill) is regrouped by
 // sequence, and each rank decodes its B / g sequences with the full (replicated, 1.2 GB) weights on the persistent
 // decode kernel: independent batch-parallel decode streams, no collective inside a decode step.
-static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, cudaStream_t st) {
+// One chunk of the prompt (tokens at positions c0 .. c0 + Sc - 1 of every sequence) through all layers.
+static int prefill_rows_chunk(flexllm_model* m, const int32_t* tokens, int B, int S, int c0, int Sc, cudaStream_t st) {
     const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl;
     const int QKV = (HQ + 2 * HKV) * 64;
     const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl, W = Fl / g;
-    const long M = (long)B * S, Mr = M / g;
-    const int Bl = B / g;
-    flexllm_model* dm = m->dm;
+    const long M = (long)B * Sc, Mr = M / g;
     int8_t* xq_mine = m->xq + (size_t)r * Mr * D;
     float* xs_mine = m->xs + (size_t)r * Mr;
     int32_t* acc_mine = m->acc32 + (size_t)r * Mr * D;
-    embed_kernel<<<(unsigned)Mr, 256, 0, st>>>(tokens + (size_t)r * Mr, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag());
+    embed_kernel<<<(unsigned)Mr, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag(), S, c0, Sc, (long)r * Mr);
     note_launches(1);
     auto norm_and_gather = [&](const float* gamma) {
         TRY(flexllm_rmsnorm_quant(m->x, gamma, (int)Mr, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, xq_mine, xs_mine, st));
@@ -380,9 +381,8 @@ static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, i
         const LayerW& L = m->L[l];
         TRY(norm_and_gather(L.g0));
         TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, (int)M, QKV, D, nullptr, m->qkv, st, nullptr));
-        const int8_t *k2, *vT; const float *ks2, *vsT;
-        TRY(mha_prefill_f32(m->qkv, m->cos_t, m->sin_t, L.a_s, B, S, HQ, HKV, m->att, m->attn_ws, st, &k2, &ks2, &vT, &vsT));
-        TRY(kv_pack(m->cache, l, k2, ks2, vT, vsT, m->page_table, m->max_pages, B, S, st));
+        TRY(mha_prefill_paged(m->qkv, m->cos_t, m->sin_t, L.a_s, B, Sc, c0, HQ, HKV, m->cfg.max_prefill, m->cache, l, m->page_table,
+                              m->max_pages, m->att, m->attn_ws, st));
         // o projection, row-parallel over this rank's heads
         TRY(row_absmax(m->att, M, Dl, m->amax, st));
         TRY(flexllm_tp_allreduce_max_f32(m->tp, m->amax, (size_t)M, st));
@@ -402,6 +402,19 @@ static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, i
         TRY(flexllm_tp_reduce_scatter_s32(m->tp, m->acc32, acc_mine, (size_t)Mr * D, st));
         TRY(dequant_residual(acc_mine, m->xs2 + (size_t)r * Mr, L.sd, Mr, D, m->x, m->x, st));
     }
+    return FLEXLLM_OK;
+}
+
+static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, cudaStream_t st) {
+    const int D = m->cfg.hidden, HKV = m->HKVl;
+    const int g = m->g;
+    const int Bl = B / g;
+    flexllm_model* dm = m->dm;
+    int Sc = S;
+    for (int c0 = 0; c0 < S; c0 += m->cfg.max_prefill) {
+        Sc = S - c0 < m->cfg.max_prefill ? S - c0 : m->cfg.max_prefill;
+        TRY(prefill_rows_chunk(m, tokens, B, S, c0, Sc, st));
+    }
     // ---- hand-over: this rank's sequences [r * Bl, (r + 1) * Bl) with all KV heads go to its decode model
     {
         flexllm_kv_cache* src = m->cache; flexllm_kv_cache* dst = dm->cache;
@@ -420,7 +433,7 @@ static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, i
             TRY(kv_regroup(m->kvs_stage, n_pg, g, HKV, 256, dst->vs + ds, st));
         }
     }
-    gather_last_kernel<<<Bl, 256, 0, st>>>(m->x, S, D, dm->xlast);
+    gather_last_kernel<<<Bl, 256, 0, st>>>(m->x, Sc, D, dm->xlast);          // the last chunk's rows are in x
     note_launches(1);
     TRY(run_head(dm, dm->xlast, Bl, FLEXLLM_NORM_PREFILL, st));
     fill_ctx_kernel<<<1, 64, 0, st>>>(dm->ctx, Bl, S);
@@ -428,29 +441,26 @@ static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, i
     dm->B = Bl; dm->S = S; dm->pos = S;
     TRY(flexllm_tp_allgather(m->tp, dm->next, m->next, (size_t)Bl * 4, st));
     if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
-    m->B = B; m->S = S; m->pos = S; m->rows_mode = true;
+    m->B = B; m->S = S; m->pos = S; m->rows_mode = true; m->last_chunk = Sc;
     return FLEXLLM_OK;
 }
 
-extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, void* stream) {
-    FLEXLLM_REQUIRE(m && tokens && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill);
-    if (S % 16 != 0) return FLEXLLM_ENOTSUP;
-    cudaStream_t st = (cudaStream_t)stream;
-    if (m->dm && B % m->g == 0) return prefill_rows(m, tokens, B, S, next_out, st);
-    m->rows_mode = false;
+// One chunk of the prompt (positions c0 .. c0 + Sc - 1 of every sequence) through all layers: single GPU, or the
+// all-gather partition of the tensor-parallel model.
+static int prefill_chunk(flexllm_model* m, const int32_t* tokens, int B, int S, int c0, int Sc, cudaStream_t st) {
     const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl, F = m->cfg.ffn;
     const int QKV = (HQ + 2 * HKV) * 64;
-    const int M = B * S;
+    const int M = B * Sc;
     const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
-    embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag());
+    embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag(), S, c0, Sc, 0L);
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
         TRY(flexllm_rmsnorm_quant(m->x, L.g0, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
         TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, M, QKV, D, nullptr, m->qkv, st, nullptr));
-        const int8_t *k2, *vT; const float *ks2, *vsT;
-        TRY(mha_prefill_f32(m->qkv, m->cos_t, m->sin_t, L.a_s, B, S, HQ, HKV, m->att, m->attn_ws, st, &k2, &ks2, &vT, &vsT));
-        TRY(kv_pack(m->cache, l, k2, ks2, vT, vsT, m->page_table, m->max_pages, B, S, st));
+        // the new keys / values go straight into the paged cache, and the chunk's queries attend to the cache
+        TRY(mha_prefill_paged(m->qkv, m->cos_t, m->sin_t, L.a_s, B, Sc, c0, HQ, HKV, m->cfg.max_prefill, m->cache, l, m->page_table,
+                              m->max_pages, m->att, m->attn_ws, st));
         if (g == 1) {
             TRY(flexllm_quant_per_token(m->att, M, D, m->xq, m->xs, st));
             TRY(gemm_i8_prefill(m->xq, m->xs, L.wo, L.so, M, D, D, nullptr, m->x, st, m->x));       // x += o_proj
@@ -475,13 +485,34 @@ extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, in
             TRY(dequant_residual(m->acc32, m->xs, L.sd, M, D, m->x, m->x, st));
         }
     }
-    gather_last_kernel<<<B, 256, 0, st>>>(m->x, S, D, m->xlast);
+    return FLEXLLM_OK;
+}
+
+// Prompts longer than max_prefill are processed in chunks of max_prefill tokens (the activation buffers are sized for
+// one chunk): chunk after chunk through all layers, each chunk's attention reading the keys and values of the chunks
+// before it from the paged KV cache. The reference's host program has one fixed prefill length and repacks the cache
+// between its two launches (SpinQuant_Prefilling_Decoding_mem_opt_demo.cpp:947-970); here prefill and decode share one
+// paged cache, so there is nothing to repack and no limit but max_ctx.
+extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, void* stream) {
+    FLEXLLM_REQUIRE(m && tokens && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_ctx);
+    if (S % 16 != 0) return FLEXLLM_ENOTSUP;
+    if (S > m->cfg.max_prefill && m->cfg.max_prefill % 128 != 0) return FLEXLLM_ENOTSUP;     // chunks start at multiples of 128
+    cudaStream_t st = (cudaStream_t)stream;
+    if (m->dm && B % m->g == 0) return prefill_rows(m, tokens, B, S, next_out, st);
+    m->rows_mode = false;
+    const int D = m->cfg.hidden;
+    int Sc = S;
+    for (int c0 = 0; c0 < S; c0 += m->cfg.max_prefill) {
+        Sc = S - c0 < m->cfg.max_prefill ? S - c0 : m->cfg.max_prefill;
+        TRY(prefill_chunk(m, tokens, B, S, c0, Sc, st));
+    }
+    gather_last_kernel<<<B, 256, 0, st>>>(m->x, Sc, D, m->xlast);             // the last chunk's rows are in x
     note_launches(1);
     TRY(run_head(m, m->xlast, B, FLEXLLM_NORM_PREFILL, st));
     fill_ctx_kernel<<<1, 64, 0, st>>>(m->ctx, B, S);
     TRY(launch_status());
     if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
-    m->B = B; m->S = S; m->pos = S;
+    m->B = B; m->S = S; m->pos = S; m->last_chunk = Sc;
     return FLEXLLM_OK;
 }
 
@@ -528,7 +559,7 @@ static int decode_step_body(flexllm_model* m, cudaStream_t st) {
     const int B = m->B;
     const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
     launch_k(embed_kernel, dim3(B), dim3(256), 0, st, (const int32_t*)m->next, (const int8_t*)m->lm_w, (const float*)m->lm_s, D, m->cfg.vocab, m->x,
-             device_error_flag());
+             device_error_flag(), 1, 0, 1, 0L);
     note_launches(1);
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
@@ -633,7 +664,7 @@ extern "C" int flexllm_model_begin(flexllm_model* m, int n_new, void* stream) {
 extern "C" int flexllm_model_generate_host(flexllm_model* m, const int32_t* tokens_host, int B, int S, int n_new,
                                            int32_t* out_host, int use_graph, void* stream) {
     FLEXLLM_REQUIRE(m && tokens_host && out_host && n_new >= 1);
-    FLEXLLM_REQUIRE(B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_prefill && S + n_new - 1 <= m->cfg.max_ctx);
+    FLEXLLM_REQUIRE(B > 0 && B <= m->cfg.max_batch && S > 0 && S + n_new - 1 <= m->cfg.max_ctx);
     for (size_t i = 0; i < (size_t)B * S; i++) FLEXLLM_REQUIRE(tokens_host[i] >= 0 && tokens_host[i] < m->cfg.vocab);
     cudaStream_t st = (cudaStream_t)stream;
     FLEXLLM_CHECK_CUDA(cudaMemcpyAsync(m->tokens, tokens_host, (size_t)B * S * 4, cudaMemcpyHostToDevice, st));
@@ -672,7 +703,7 @@ extern "C" int flexllm_model_buffer(flexllm_model* m, int which, void** ptr) {
         // the rank's own sequences. which == 0 gathers the rows (a COLLECTIVE: call it on every rank).
         switch (which) {
             case 0: {
-                const size_t n = (size_t)m->B * m->S / m->g * m->cfg.hidden;
+                const size_t n = (size_t)m->B * m->last_chunk / m->g * m->cfg.hidden;      // rows of the last chunk
                 TRY(flexllm_tp_allgather(m->tp, m->x, m->gath, n * 4, nullptr));
                 FLEXLLM_CHECK_CUDA(cudaStreamSynchronize(nullptr));
                 *ptr = m->gath; return FLEXLLM_OK;

@@ -280,6 +280,14 @@ class KVCache:
                 self._view(v.value, (P, H, 64, T), torch.int8), self._view(vs.value, (P, H, T), torch.float32))
 
 
+def dec_KV_cache_append(cache, layer, k, ks, v, vs, page_table, ctx, max_ctx):
+    """Stores k,v [B,HKV,64] int8 with scales ks,vs [B,HKV] at position ctx[b] of each sequence (the cache managers'
+    append, Modules/MHA.h:484-513, :773-801)."""
+    B = k.shape[0]
+    _check("flexllm_kv_append", lib().flexllm_kv_append(cache._h, layer, _ptr(k), _ptr(ks), _ptr(v), _ptr(vs), _ptr(page_table),
+                                                         page_table.shape[1], _ptr(ctx), max_ctx, B, _stream()))
+
+
 def MHA_i8xi8_Decoding(cache, layer, q, qs, k, ks, v, vs, cos_t, sin_t, a_s, page_table, ctx, max_ctx, want_oacc=False):
     """One decode step of attention on `layer`. q [B,HQ,64] s8, qs [B,HQ]; k,v [B,HKV,64], ks,vs [B,HKV];
     page_table [B,max_pages] int32; ctx [B] int32 (tokens already cached, device); max_ctx >= max(ctx).

@@ -27,6 +27,11 @@ class KVCache {
   private:
     flexllm_kv_cache* h_ = nullptr;
 };
+// the managers' append alone (MHA.h:493-513, :782-801): k,v [B][HKV][64] with scales stored at position ctx[b]
+inline int dec_KV_cache_append(KVCache& cache, int layer, const int8_t* k, const float* ks, const int8_t* v, const float* vs,
+                               const int32_t* page_table, int max_pages, const int32_t* ctx, int max_ctx, int B, stream_t st = nullptr) {
+    return flexllm_kv_append(cache.handle(), layer, k, ks, v, vs, page_table, max_pages, ctx, max_ctx, B, st);
+}
 // MHA_i8xi8_decoding_tb (MHA_i8xi8.h:1027-1114)
 inline size_t MHA_i8xi8_Decoding_workspace(int B, int HQ, int max_ctx) { return flexllm_mha_decode_workspace(B, HQ, max_ctx); }
 inline int MHA_i8xi8_Decoding(KVCache& cache, int layer, const int8_t* q, const float* qs, const int8_t* k, const float* ks,

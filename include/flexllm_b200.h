@@ -203,6 +203,13 @@ FLEXLLM_API int flexllm_kv_cache_reset(flexllm_kv_cache* c, void* stream);
 /* raw device pointers of one layer's pools (for tests and zero-copy hand-off) */
 FLEXLLM_API int flexllm_kv_cache_pools(flexllm_kv_cache* c, int layer, int8_t** k, float** ks, int8_t** v, float** vs);
 
+/* Append alone: the new token's int8 K and V heads k,v [B][HKV][64] with scales ks,vs [B][HKV] are stored at
+ * position ctx[b] of each sequence (replaces dec_K_cache_manager_template / dec_V_cache_manager_template,
+ * Modules/MHA.h:484-513, :773-801, without the read-back). No RoPE, no quantisation: bytes are stored as given. */
+FLEXLLM_API int flexllm_kv_append(flexllm_kv_cache* c, int layer, const int8_t* k, const float* ks, const int8_t* v,
+                                  const float* vs, const int32_t* page_table, int max_pages, const int32_t* ctx,
+                                  int max_ctx, int B, void* stream);
+
 /* One decode step of attention for B sequences on one layer (replaces the graph
  * MHA_i8xi8_decoding_tb, MHA_i8xi8.h:1027-1114): qk_prepare of the new q,k at position ctx[b];
  * append k,v to the cache; attention over ctx[b]+1 keys; out fp32 [B][HQ*64].

@@ -154,3 +154,35 @@ def test_decode_config4_slice(F):
 
 def test_decode_max_context(F):
     decode_case(F, 2, [8192, 8191], seed=43)
+
+
+def test_kv_append_alone(F):
+    """The cache managers' append on its own: the new token's K row, transposed V column and both scales land at
+    position ctx[b] of the right page; everything else in the pools is untouched."""
+    g = np.random.default_rng(45)
+    B, HKV, PAGE = 5, 8, 64
+    ctx = np.array([0, 63, 64, 200, 777], np.int32)
+    pages = (ctx + 1 + PAGE - 1) // PAGE
+    max_pages = int(pages.max()); n_pages = int(pages.sum()) + 2
+    perm = g.permutation(n_pages).astype(np.int32)
+    pt = np.zeros((B, max_pages), np.int32); o = 0
+    for b in range(B):
+        pt[b, :pages[b]] = perm[o:o + pages[b]]; o += pages[b]
+    cache = F.KVCache(2, n_pages, HKV)
+    layer = 1
+    kd, ksd, vd, vsd = cache.pools(layer)
+    k_pool = g.integers(-127, 128, (n_pages, HKV, PAGE, 64), dtype=np.int8); v_pool = g.integers(-127, 128, (n_pages, HKV, 64, PAGE), dtype=np.int8)
+    ks_pool = g.uniform(0.005, 0.05, (n_pages, HKV, PAGE)).astype(np.float32); vs_pool = g.uniform(0.005, 0.05, (n_pages, HKV, PAGE)).astype(np.float32)
+    kd.copy_(dev(k_pool)); vd.copy_(dev(v_pool)); ksd.copy_(dev(ks_pool)); vsd.copy_(dev(vs_pool))
+    k = g.integers(-127, 128, (B, HKV, 64), dtype=np.int8); v = g.integers(-127, 128, (B, HKV, 64), dtype=np.int8)
+    ks = g.uniform(0.005, 0.05, (B, HKV)).astype(np.float32); vs = g.uniform(0.005, 0.05, (B, HKV)).astype(np.float32)
+    F.dec_KV_cache_append(cache, layer, dev(k), dev(ks), dev(v), dev(vs), dev(pt), dev(ctx), int(ctx.max()))
+    torch.cuda.synchronize()
+    for b in range(B):
+        pg, slot = pt[b, ctx[b] // PAGE], ctx[b] % PAGE
+        k_pool[pg, :, slot, :] = k[b]; v_pool[pg, :, :, slot] = v[b]; ks_pool[pg, :, slot] = ks[b]; vs_pool[pg, :, slot] = vs[b]
+    assert_same(to_np(kd), k_pool, "K pool"); assert_same(to_np(vd), v_pool, "V pool")
+    assert_same(to_np(ksd), ks_pool, "K scales"); assert_same(to_np(vsd), vs_pool, "V scales")
+    k0 = cache.pools(0)[0]
+    assert int(k0.abs().max()) == 0          # the other layer was not touched
+    cache.close()

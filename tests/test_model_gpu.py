@@ -162,3 +162,30 @@ def test_model_distance_to_the_c_library_exp(F, layers):
     assert e_h < 1e-3
     assert np.abs(d).max() <= 1 and n_bad <= d.size // 100
     assert np.array_equal(out, libm["tokens"])
+
+
+@pytest.mark.parametrize("S,max_prefill", [(320, 128), (256, 128), (400, 256)])
+def test_model_chunked_prefill(F, S, max_prefill):
+    """A prompt longer than max_prefill goes through the layers in chunks of max_prefill tokens, each chunk's attention
+    reading the earlier chunks' keys and values from the paged cache (ragged last chunk included): same tokens, same logits,
+    same residual stream as the oracle's one-pass prefill."""
+    from flexllm_b200 import synthetic
+    layers, hidden, hq, hkv, vocab, B, n_new, seed = 2, 512, 8, 2, 1000, 2, 4, 65
+    W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, S + n_new, seed=seed)
+    tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
+    m = F.Model(layers, hidden, hq, hkv, 8192, vocab, max_batch=B, max_prefill=max_prefill, max_ctx=S + n_new)
+    synthetic.load_numpy_weights(m, W)
+    out = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=True)
+    logits_last = to_np(m.buffer(1, (B, vocab), torch.float32))
+    ref = oracle.model_generate(W, tokens, n_new, want_hidden=True, want_logits=True)
+    assert np.array_equal(out.numpy(), ref["tokens"])
+    assert np.array_equal(logits_last.view(np.uint32), ref["logits_last"].view(np.uint32))
+    # the residual stream of the LAST chunk is what the runner's buffer holds after a prefill
+    m.prefill(torch.from_numpy(tokens).cuda()); torch.cuda.synchronize()
+    c0 = (S - 1) // max_prefill * max_prefill
+    Sc = S - c0
+    got = to_np(m.buffer(0, (B * Sc, hidden), torch.float32)).reshape(B, Sc, hidden)
+    want = ref["hidden"].reshape(B, S, hidden)[:, c0:]
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(to_np(m.buffer(1, (B, vocab), torch.float32)).view(np.uint32), ref["logits_prefill"].view(np.uint32))
+    m.close()
