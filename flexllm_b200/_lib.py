@@ -5,7 +5,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflexllm_b200.so")
 
-OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM, ETOOBIG, EDEVDATA = 0, -1, -2, -3, -4, -5, -6, -7
+OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM, ETOOBIG, EDEVDATA, EIO = 0, -1, -2, -3, -4, -5, -6, -7, -8
 
 # name -> argument types, in the order of include/flexllm_b200.h (return type is int unless noted)
 _P, _I, _L, _F, _SZ = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_size_t
@@ -21,6 +21,14 @@ SIGNATURES = {
     "flexllm_linear_decode_i8_noalloc": [_P, _P, _P, _P, _I, _I, _I, _P, _P],
     "flexllm_quant_per_token": [_P, _I, _I, _P, _P, _P],
     "flexllm_dequant": [_P, _P, _P, _I, _I, _P, _P],
+    "flexllm_quant_per_token_asym": [_P, _I, _I, _I, _P, _P, _P, _P],
+    "flexllm_dequant_asym": [_P, _P, _P, _P, _P, _I, _I, _P, _P],
+    "flexllm_linear_prefill_asym": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_linear_decode_asym": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "flexllm_ckpt_read_bin": [C.c_char_p, _SZ, _SZ, _P],
+    "flexllm_ckpt_read_c_array_f32": [C.c_char_p, C.c_char_p, _L, _L, _P],
+    "flexllm_ckpt_load_layer": [C.c_char_p, _I, _I, _I, _I, _I, _P],
+    "flexllm_ckpt_load_head": [C.c_char_p, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "flexllm_static_quant": [_P, _L, _I, _P, _I, _F, _I, _P, _P],
     "flexllm_fht": [_P, _L, _I, _F, _P, _P],
     "flexllm_rope": [_P, _P, _P, _P, _L, _I, _P, _P],
@@ -71,6 +79,11 @@ SIGNATURES = {
 class ModelConfig(C.Structure):
     _fields_ = [("layers", _I), ("hidden", _I), ("heads_q", _I), ("heads_kv", _I), ("ffn", _I), ("vocab", _I),
                 ("eps", _F), ("fht_scale", _F), ("max_batch", _I), ("max_prefill", _I), ("max_ctx", _I)]
+
+
+class CkptLayerBuffers(C.Structure):
+    _fields_ = ([(n, _P) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")] + [(n, _P) for n in ("sq", "sk", "sv", "so", "sg", "su", "sd")] +
+                [(n, _P) for n in ("sumq", "sumk", "sumv", "sumo", "sumg", "sumu", "sumd")] + [(n, _P) for n in ("gamma0", "gamma1", "a_s")])
 
 
 class LayerWeights(C.Structure):

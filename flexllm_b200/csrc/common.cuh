@@ -63,6 +63,12 @@ inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
         if (_st != FLEXLLM_OK) return _st;                         \
     } while (0)
 
+#define TRY_RC(expr)                          \
+    do {                                      \
+        int _rc = (expr);                     \
+        if (_rc != FLEXLLM_OK) return _rc;    \
+    } while (0)
+
 #define FLEXLLM_REQUIRE(cond)                 \
     do {                                      \
         if (!(cond)) return FLEXLLM_EINVAL;   \

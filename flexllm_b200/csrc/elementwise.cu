@@ -51,6 +51,58 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const float* __res
 }
 
 // ---------------------------------------------------------------------------------------------
+// Asymmetric per-token quantisation (Modules/quant.h:53-81): s = (max - min) / (2^bits - 1) (0 -> 1), zero point
+// b = min, q = (unsigned) round((x - b) / s). Same structure as the symmetric kernel above.
+// ---------------------------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(256) quant_per_token_asym_kernel(const float* __restrict__ x, int K, float base, unsigned mask,
+                                                                   uint8_t* __restrict__ q, float* __restrict__ s, float* __restrict__ b) {
+    __shared__ float red[64];
+    const long row = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * K);
+    const int nv = K >> 2;
+    float4 v[VPT];
+    float mx = -1e32f, mn = 1e32f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        int c = threadIdx.x + i * 256;
+        if (c < nv) {
+            v[i] = xr[c];
+            mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            mn = fminf(mn, fminf(fminf(v[i].x, v[i].y), fminf(v[i].z, v[i].w)));
+        }
+    }
+    block_max_min(mx, mn, red);
+    float sc = (mx - mn) / base;
+    if (sc == 0.0f) sc = 1.0f;
+    if (threadIdx.x == 0) { s[row] = sc; b[row] = mn; }
+    uchar4* qr = reinterpret_cast<uchar4*>(q + row * K);
+    auto qz = [&](float t) { return (unsigned char)((unsigned)(long long)roundf((t - mn) / sc) & mask); };
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        int c = threadIdx.x + i * 256;
+        if (c < nv) qr[c] = make_uchar4(qz(v[i].x), qz(v[i].y), qz(v[i].z), qz(v[i].w));
+    }
+}
+
+// y = ((float)acc * s_tok[m]) * s_ch[n] + b_tok[m] * wsum[n]     (Modules/quant.h:146-148; every operation rounded on its own)
+__global__ void dequant_asym_kernel(const int32_t* __restrict__ acc, const float* __restrict__ s_tok, const float* __restrict__ b_tok,
+                                    const float* __restrict__ s_ch, const float* __restrict__ wsum, int M, int N, float* __restrict__ y) {
+    const long nv = (long)M * (N >> 2);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+        const int m = (int)(i / (N >> 2)), c = (int)(i % (N >> 2));
+        const int4 a = reinterpret_cast<const int4*>(acc)[i];
+        const float4 w = reinterpret_cast<const float4*>(s_ch)[c];
+        const float4 z = reinterpret_cast<const float4*>(wsum)[c];
+        const float st = s_tok[m], bt = b_tok[m];
+        float4 o;
+        o.x = ((float)a.x * st) * w.x + bt * z.x; o.y = ((float)a.y * st) * w.y + bt * z.y;
+        o.z = ((float)a.z * st) * w.z + bt * z.z; o.w = ((float)a.w * st) * w.w + bt * z.w;
+        reinterpret_cast<float4*>(y)[i] = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Dequant (Modules/quant.h:151): y = ((float)acc * s_tok[m]) * s_ch[n]
 // ---------------------------------------------------------------------------------------------
 __global__ void dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ s_tok,
@@ -342,6 +394,7 @@ extern "C" const char* flexllm_status_string(int st) {
         case FLEXLLM_ENOMEM: return "out of memory";
         case FLEXLLM_ETOOBIG: return "problem exceeds a fixed built-in buffer";
         case FLEXLLM_EDEVDATA: return "token id or context length in device memory out of range (clamped)";
+        case FLEXLLM_EIO: return "parameter file missing or too short";
         default: return "unknown status";
     }
 }
@@ -361,6 +414,46 @@ extern "C" int flexllm_quant_per_token(const float* x, int M, int K, int8_t* q, 
     else if (nv <= 1024) launch_k(quant_per_token_kernel<4>, dim3(M), dim3(256), 0, st, x, K, q, s);
     else launch_k(quant_per_token_kernel<8>, dim3(M), dim3(256), 0, st, x, K, q, s);
     return launch_status();
+}
+
+extern "C" int flexllm_quant_per_token_asym(const float* x, int M, int K, int bits, uint8_t* q, float* s, float* b, void* stream) {
+    FLEXLLM_REQUIRE(M >= 0 && K > 0 && (K % 4) == 0 && K <= 8192);
+    if (bits < 2 || bits > 7) return FLEXLLM_ENOTSUP;
+    if (M == 0) return FLEXLLM_OK;
+    FLEXLLM_REQUIRE(x && q && s && b && aligned(x, 16) && aligned(q, 4));
+    cudaStream_t st = (cudaStream_t)stream;
+    const float base = (float)((1 << bits) - 1);
+    const unsigned mask = (1u << bits) - 1u;
+    const int nv = K / 4;
+    if (nv <= 256) quant_per_token_asym_kernel<1><<<M, 256, 0, st>>>(x, K, base, mask, q, s, b);
+    else if (nv <= 512) quant_per_token_asym_kernel<2><<<M, 256, 0, st>>>(x, K, base, mask, q, s, b);
+    else if (nv <= 1024) quant_per_token_asym_kernel<4><<<M, 256, 0, st>>>(x, K, base, mask, q, s, b);
+    else quant_per_token_asym_kernel<8><<<M, 256, 0, st>>>(x, K, base, mask, q, s, b);
+    return launch_status();
+}
+
+extern "C" int flexllm_dequant_asym(const int32_t* acc, const float* s_tok, const float* b_tok, const float* s_ch, const float* wsum,
+                                    int M, int N, float* y, void* stream) {
+    FLEXLLM_REQUIRE(acc && s_tok && b_tok && s_ch && wsum && y && M >= 0 && N > 0 && (N % 4) == 0);
+    FLEXLLM_REQUIRE(aligned(acc, 16) && aligned(s_ch, 16) && aligned(wsum, 16) && aligned(y, 16));
+    if (M == 0) return FLEXLLM_OK;
+    dequant_asym_kernel<<<grid_for((long)M * N / 4, 256), 256, 0, (cudaStream_t)stream>>>(acc, s_tok, b_tok, s_ch, wsum, M, N, y);
+    return launch_status();
+}
+
+// The integer product of the asymmetric layers runs on the int8 GEMMs (activation values of up to 7 bits are non-negative
+// int8); the zero point enters in the dequantiser.
+extern "C" int flexllm_linear_prefill_asym(const uint8_t* a, const float* s_tok, const float* b_tok, const int8_t* w, const float* s_ch,
+                                           const float* wsum, int M, int N, int K, int32_t* acc, float* y, void* stream) {
+    FLEXLLM_REQUIRE(acc && y);
+    TRY_RC(flexllm_linear_prefill_i8(reinterpret_cast<const int8_t*>(a), nullptr, w, nullptr, M, N, K, acc, nullptr, stream));
+    return flexllm_dequant_asym(acc, s_tok, b_tok, s_ch, wsum, M, N, y, stream);
+}
+extern "C" int flexllm_linear_decode_asym(const uint8_t* a, const float* s_tok, const float* b_tok, const int8_t* w, const float* s_ch,
+                                          const float* wsum, int M, int N, int K, int32_t* acc, float* y, void* stream) {
+    FLEXLLM_REQUIRE(acc && y);
+    TRY_RC(flexllm_linear_decode_i8(reinterpret_cast<const int8_t*>(a), nullptr, w, nullptr, M, N, K, acc, nullptr, stream));
+    return flexllm_dequant_asym(acc, s_tok, b_tok, s_ch, wsum, M, N, y, stream);
 }
 
 extern "C" int flexllm_dequant(const int32_t* acc, const float* s_tok, const float* s_ch, int M, int N, float* y,

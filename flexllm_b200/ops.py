@@ -88,6 +88,40 @@ def pref_quant_layer_fp32_qint(x):
 dec_quant_layer_fp32_qint = pref_quant_layer_fp32_qint
 
 
+def pref_quant_layer_fp32_qint_asym(x, bits=4):
+    """Asymmetric per-token quantiser of the reference's shipped configuration (quant.h:53-81, is_act_asym = true).
+    Returns (q uint8 [M,K] in [0, 2^bits-1], scale [M], zero point [M])."""
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    b = torch.empty((M,), dtype=torch.float32, device=x.device)
+    _call("flexllm_quant_per_token_asym", _ptr(x), M, K, bits, _ptr(q), _ptr(s), _ptr(b))
+    return q, s, b
+
+
+def pref_dequant_layer_qint_fp32_asym(acc, s_tok, b_tok, s_ch, wsum):
+    """y = ((float)acc * s_tok) * s_ch + b_tok * wsum (quant.h:146-148)."""
+    M, N = acc.shape
+    y = torch.empty((M, N), dtype=torch.float32, device=acc.device)
+    _call("flexllm_dequant_asym", _ptr(acc), _ptr(s_tok), _ptr(b_tok), _ptr(s_ch), _ptr(wsum), M, N, _ptr(y))
+    return y
+
+
+def pref_Linear_Layer_i4xi4(a, s_tok, b_tok, w, s_ch, wsum, decode=False):
+    """The reference's asymmetric-activation linear layer (pref_/dec_Linear_Layer_i4xi4 with is_uint_input + the asymmetric
+    dequantiser): a uint8 [M,K] from the asymmetric quantiser, w int8 [N,K]. Returns (acc int32, y fp32)."""
+    M, K = a.shape; N = w.shape[0]
+    acc = torch.empty((M, N), dtype=torch.int32, device=a.device)
+    y = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _call("flexllm_linear_decode_asym" if decode else "flexllm_linear_prefill_asym", _ptr(a), _ptr(s_tok), _ptr(b_tok), _ptr(w),
+          _ptr(s_ch), _ptr(wsum), M, N, K, _ptr(acc), _ptr(y))
+    return acc, y
+
+
+def dec_Linear_Layer_i4xi4(a, s_tok, b_tok, w, s_ch, wsum):
+    return pref_Linear_Layer_i4xi4(a, s_tok, b_tok, w, s_ch, wsum, decode=True)
+
+
 def pref_dequant_layer_qint_fp32(acc, s_tok, s_ch):
     M, N = acc.shape
     y = torch.empty((M, N), dtype=torch.float32, device=acc.device)
@@ -302,6 +336,37 @@ def MHA_i8xi8_Decoding(cache, layer, q, qs, k, ks, v, vs, cos_t, sin_t, a_s, pag
         cache._h, layer, _ptr(q), _ptr(qs), _ptr(k), _ptr(ks), _ptr(v), _ptr(vs), _ptr(cos_t), _ptr(sin_t), _ptr(a_s),
         _ptr(page_table), page_table.shape[1], _ptr(ctx), max_ctx, B, HQ, _ptr(out), _ptr(oacc), _ptr(ws), nbytes, _stream()))
     return out, oacc
+
+
+def read_reference_layer(directory, layer, hidden, kv_hidden, ffn, heads_q):
+    """One decoder layer of a checkpoint in the reference's on-disk format (its demo's parameters/ directory) as CPU
+    tensors: keys wq wk wv wo wg wu wd (int8 [out,in]), sq.. sd (scales), sumq.. sumd (row sums of the asymmetric
+    dequantiser), gamma0 gamma1 a_s. The first 17 are what Model.load_layer takes."""
+    dims = dict(q=(hidden, hidden), k=(kv_hidden, hidden), v=(kv_hidden, hidden), o=(hidden, hidden), g=(ffn, hidden), u=(ffn, hidden),
+                d=(hidden, ffn))
+    out = {}
+    for k, (n, kk) in dims.items():
+        out["w" + k] = torch.empty((n, kk), dtype=torch.int8)
+        out["s" + k] = torch.empty((n,), dtype=torch.float32)
+        out["sum" + k] = torch.empty((n,), dtype=torch.float32)
+    out["gamma0"] = torch.empty((hidden,), dtype=torch.float32); out["gamma1"] = torch.empty((hidden,), dtype=torch.float32)
+    out["a_s"] = torch.empty((heads_q,), dtype=torch.float32)
+    b = _lib.CkptLayerBuffers(*[C.c_void_p(out[n].data_ptr()) for n, _ in _lib.CkptLayerBuffers._fields_])
+    _check("flexllm_ckpt_load_layer", lib().flexllm_ckpt_load_layer(str(directory).encode(), layer, hidden, kv_hidden, ffn, heads_q, C.byref(b)))
+    return out
+
+
+def read_reference_head(directory, layers, hidden, vocab, table_len, want_embed=False):
+    """lm_head (int8 + scales + row sums), final RMSNorm weight, RoPE tables and optionally the fp32 embedding table."""
+    out = dict(lm_w=torch.empty((vocab, hidden), dtype=torch.int8), lm_s=torch.empty((vocab,), dtype=torch.float32),
+               lm_sum=torch.empty((vocab,), dtype=torch.float32), gamma_final=torch.empty((hidden,), dtype=torch.float32),
+               cos_t=torch.empty((table_len, 32), dtype=torch.float32), sin_t=torch.empty((table_len, 32), dtype=torch.float32))
+    if want_embed:
+        out["embed"] = torch.empty((vocab, hidden), dtype=torch.float32)
+    p = lambda n: C.c_void_p(out[n].data_ptr()) if n in out else None
+    _check("flexllm_ckpt_load_head", lib().flexllm_ckpt_load_head(str(directory).encode(), layers, hidden, vocab, table_len, p("lm_w"), p("lm_s"),
+                                                                  p("lm_sum"), p("gamma_final"), p("cos_t"), p("sin_t"), p("embed")))
+    return out
 
 
 def tp_unique_id():

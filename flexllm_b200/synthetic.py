@@ -85,3 +85,48 @@ def load_random_weights(model, layers, hidden, heads_q, heads_kv, ffn, vocab, ma
                          a_s=torch.full((heads_q,), a_s, device=device))
     cos_t, sin_t = rope_table(max_ctx + 1)
     model.load_head(w8(vocab, D), sc(vocab), gam(), torch.from_numpy(cos_t).to(device), torch.from_numpy(sin_t).to(device))
+
+
+def write_reference_format(directory, W, embed=False):
+    """Writes the weights W (as made by numpy_weights) in the on-disk format of the reference's demo (its parameters/
+    directory): <proj>_L%02d.bin int8 [out][in], C headers with the scale / row-sum / norm / A_s / RoPE arrays,
+    lm_head_L00.bin, optionally model_embed_tokens_fp32.bin. Row sums are accumulated in fp32 in index order, as the
+    reference's test bench does (Linear_Layer_Prefilling_tb.cpp:222-237)."""
+    import os
+    os.makedirs(directory, exist_ok=True)
+    L = len(W["wq"])
+    names = dict(q="q_proj", k="k_proj", v="v_proj", o="o_proj", g="gate_proj", u="up_proj", d="down_proj")
+
+    def rowsum(w, s):
+        acc = np.zeros(w.shape[0], np.float32)
+        ws = w.astype(np.float32) * s[:, None].astype(np.float32)
+        for j in range(w.shape[1]):
+            acc = (acc + ws[:, j]).astype(np.float32)
+        return acc
+
+    def c_array(name, a):
+        a = np.asarray(a, np.float32)
+        dims = "".join(f"[{d}]" for d in a.shape)
+        flat = a.reshape(-1)
+        body = ",\n".join(", ".join(f"{float(v):.9e}f" for v in flat[i:i + 8]) for i in range(0, flat.size, 8))
+        return f"static const float {name}{dims} = {{\n{body}\n}};\n"
+
+    sums = {}
+    for k, nm in names.items():
+        for l in range(L):
+            W["w" + k][l].astype(np.int8).tofile(os.path.join(directory, f"{nm}_L{l:02d}.bin"))
+        sc = np.stack([W["s" + k][l] for l in range(L)])
+        sm = np.stack([rowsum(W["w" + k][l], W["s" + k][l]) for l in range(L)])
+        sums[k] = sm
+        with open(os.path.join(directory, f"w_{nm}_s_sum.h"), "w") as f:
+            f.write(f"// per-channel scales and row sums of {nm}\n" + c_array(f"w_{nm}_s", sc) + c_array(f"w_{nm}_sum", sm))
+    norm = np.stack([W["g0"][l // 2] if l % 2 == 0 else W["g1"][l // 2] for l in range(2 * L)] + [W["g_final"]])
+    open(os.path.join(directory, "w_rmsnorm.h"), "w").write(c_array("RMSNorm_weight", norm))
+    open(os.path.join(directory, "A_s.h"), "w").write(c_array("A_s", np.stack(W["a_s"])))
+    open(os.path.join(directory, "RoPE_sin_cos.h"), "w").write(c_array("PE_sin", W["sin_t"]) + "/* cosines */\n" + c_array("PE_cos", W["cos_t"]))
+    W["lm_w"].astype(np.int8).tofile(os.path.join(directory, "lm_head_L00.bin"))
+    open(os.path.join(directory, "w_lm_head_lm_head.h"), "w").write(
+        c_array("w_lm_head_lm_head_s", W["lm_s"]) + c_array("w_lm_head_lm_head_sum", rowsum(W["lm_w"], W["lm_s"])))
+    if embed:
+        (W["lm_w"].astype(np.float32) * W["lm_s"][:, None]).astype(np.float32).tofile(os.path.join(directory, "model_embed_tokens_fp32.bin"))
+    return sums

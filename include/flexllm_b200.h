@@ -40,6 +40,7 @@ extern "C" {
 #define FLEXLLM_ENOMEM (-5)
 #define FLEXLLM_ETOOBIG (-6)   /* problem larger than a fixed built-in buffer */
 #define FLEXLLM_EDEVDATA (-7)  /* a token id or context length in DEVICE memory was out of range (clamped) */
+#define FLEXLLM_EIO (-8)       /* a parameter file could not be opened, or holds fewer values than asked for */
 
 /* RMSNorm summation orders (Modules/LayerNorm.h:82-130 prefill, :263-321 decode). */
 #define FLEXLLM_NORM_PREFILL 0 /* 4 interleaved partial sums over the whole row          */
@@ -292,6 +293,49 @@ FLEXLLM_API int flexllm_model_set_sampling(flexllm_model* m, int lanes, int top_
  * a [M][K] x [N][K] problem with an epilogue that reads the accumulators and stores nothing. Its rate is
  * the int8 tensor-core ceiling this library's main loop reaches on the device (N > 128). */
 FLEXLLM_API int flexllm_gemm_i8_mainloop_probe(const int8_t* a, const int8_t* w, int M, int N, int K, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The reference's on-disk model (its demo's parameters/ directory; host code, HOST buffers):
+ *   <proj>_L%02d.bin int8 [out][in]; w_<proj>_s_sum.h with w_<proj>_s / w_<proj>_sum [layers][out]; w_rmsnorm.h with
+ *   RMSNorm_weight[2*layers+1][hidden]; A_s.h; RoPE_sin_cos.h (PE_cos, PE_sin [pos][32]); lm_head_L00.bin,
+ *   w_lm_head_lm_head.h; model_embed_tokens_fp32.bin  (readers of the demo:
+ *   SpinQuant_Llama_32_1B_Ins/SpinQuant_Prefilling_Decoding_mem_opt_demo.cpp:21-74, :132-175, :437-490).
+ * NULL members / arguments are skipped. The buffers a layer fills are exactly what flexllm_model_load_layer takes
+ * (host pointers are accepted there), so a checkpoint directory can be loaded layer by layer.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+    int8_t *wq, *wk, *wv, *wo, *wg, *wu, *wd;             /* [out][in] */
+    float *sq, *sk, *sv, *so, *sg, *su, *sd;              /* per-channel scales  w_<proj>_s[layer]   */
+    float *sumq, *sumk, *sumv, *sumo, *sumg, *sumu, *sumd; /* row sums            w_<proj>_sum[layer] */
+    float *gamma0, *gamma1, *a_s;
+} flexllm_ckpt_layer_buffers;
+FLEXLLM_API int flexllm_ckpt_read_bin(const char* path, size_t offset_bytes, size_t bytes, void* out_host);
+/* `count` numbers of the C array `name` defined in the header file `path`, starting at flat index `skip` */
+FLEXLLM_API int flexllm_ckpt_read_c_array_f32(const char* path, const char* name, long skip, long count, float* out_host);
+FLEXLLM_API int flexllm_ckpt_load_layer(const char* dir, int layer, int hidden, int kv_hidden, int ffn, int heads_q,
+                                        const flexllm_ckpt_layer_buffers* buffers);
+FLEXLLM_API int flexllm_ckpt_load_head(const char* dir, int layers, int hidden, int vocab, int table_len, int8_t* lm_w,
+                                       float* lm_s, float* lm_sum, float* gamma_final, float* cos_t, float* sin_t,
+                                       float* embed);
+
+/* ---------------------------------------------------------------------------------------------
+ * The reference's shipped precision for the linear layers: asymmetric activations of `bits` bits per token
+ * (pref_quant_layer_fp32_qint<4, true, ...>, Modules/quant.h:53-81) against symmetric per-channel weights, with the
+ * zero point folded into the dequantiser (quant.h:146-148):
+ *     s = (max - min) / (2^bits - 1) (0 -> 1),  b = min,  q = round((x - b) / s)  in [0, 2^bits - 1]
+ *     y[m][n] = ((float)acc * s[m]) * s_ch[n] + b[m] * wsum[n],   wsum[n] = sum_k w[n][k] * s_ch[n]
+ * q is stored one value per byte; the integer product runs on the same int8 tensor-core GEMM (values of up to 7 bits
+ * are non-negative int8), so 2 <= bits <= 7. The linear entries need `acc` (int32 [M][N], also an output).
+ * ------------------------------------------------------------------------------------------- */
+FLEXLLM_API int flexllm_quant_per_token_asym(const float* x, int M, int K, int bits, uint8_t* q, float* s, float* b, void* stream);
+FLEXLLM_API int flexllm_dequant_asym(const int32_t* acc, const float* s_tok, const float* b_tok, const float* s_ch,
+                                     const float* wsum, int M, int N, float* y, void* stream);
+FLEXLLM_API int flexllm_linear_prefill_asym(const uint8_t* a, const float* s_tok, const float* b_tok, const int8_t* w,
+                                            const float* s_ch, const float* wsum, int M, int N, int K, int32_t* acc, float* y,
+                                            void* stream);
+FLEXLLM_API int flexllm_linear_decode_asym(const uint8_t* a, const float* s_tok, const float* b_tok, const int8_t* w,
+                                           const float* s_ch, const float* wsum, int M, int N, int K, int32_t* acc, float* y,
+                                           void* stream);
 
 /* Test aids for the failure path of the persistent decode-step kernel (no counterpart in the reference).
  * which = 0: bound, in nanoseconds, of that kernel's grid-barrier and flag waits (0 restores the default

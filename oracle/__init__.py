@@ -104,6 +104,21 @@ def quant_per_token(x):
     return q, s
 
 
+def quant_per_token_asym(x, bits=4):
+    """Asymmetric per-token quantiser (quant.h:53-81). Returns (q uint8 in [0, 2^bits-1], scale, zero point)."""
+    x = _f32(x); M, K = x.shape
+    q = np.empty((M, K), np.uint8); s = np.empty(M, np.float32); b = np.empty(M, np.float32)
+    _lib.orc_quant_per_token_asym(_p(x), C.c_int(M), C.c_int(K), C.c_int(bits), _p(q), _p(s), _p(b))
+    return q, s, b
+
+
+def dequant_asym(acc, s_tok, b_tok, s_ch, wsum):
+    """y = ((float)acc * s_tok) * s_ch + b_tok * wsum (quant.h:146-148)."""
+    acc = _i32(acc); M, N = acc.shape; y = np.empty((M, N), np.float32)
+    _lib.orc_dequant_asym(_p(acc), _p(_f32(s_tok)), _p(_f32(b_tok)), _p(_f32(s_ch)), _p(_f32(wsum)), C.c_int(M), C.c_int(N), _p(y))
+    return y
+
+
 def gemm_s8s8(a, w):
     a = _i8(a); w = _i8(w); M, K = a.shape; N = w.shape[0]
     acc = np.empty((M, N), np.int32)
@@ -334,6 +349,22 @@ class _Ref:
         fn = self.lib.ref_dec_quant_per_token if decode else self.lib.ref_quant_per_token
         fn(_p(x), C.c_int(M), C.c_int(K), _p(q), _p(s))
         return q, s
+
+    def quant_per_token_asym4(self, x):
+        x = _f32(x); M, K = x.shape
+        q = np.empty((M, K), np.uint8); s = np.empty(M, np.float32); b = np.empty(M, np.float32)
+        self.lib.ref_quant_per_token_asym4(_p(x), C.c_int(M), C.c_int(K), _p(q), _p(s), _p(b))
+        return q, s, b
+
+    def dequant_asym(self, acc, s_tok, b_tok, s_ch, wsum):
+        acc = _i32(acc); M, N = acc.shape; y = np.empty((M, N), np.float32)
+        self.lib.ref_dequant_asym(_p(acc), _p(_f32(s_tok)), _p(_f32(b_tok)), _p(_f32(s_ch)), _p(_f32(wsum)), C.c_int(M), C.c_int(N), _p(y))
+        return y
+
+    def gemm_u4s4(self, a, w):
+        a = np.ascontiguousarray(a, dtype=np.uint8); w = _i8(w); M, K = a.shape; N = w.shape[0]; acc = np.empty((M, N), np.int32)
+        self.lib.ref_gemm_u4s4(_p(a), _p(w), C.c_int(M), C.c_int(N), C.c_int(K), _p(acc))
+        return acc
 
     def dequant(self, acc, s_tok, s_ch):
         acc = _i32(acc); M, N = acc.shape; y = np.empty((M, N), np.float32)

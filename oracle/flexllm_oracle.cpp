@@ -104,6 +104,41 @@ ORC_API void orc_quant_per_token(const float* x, int M, int K, int8_t* q, float*
     }
 }
 
+// Asymmetric per-token quantiser, `bits` bits (the reference's shipped configuration: 4-bit asymmetric activations in
+// front of every linear layer; quant.h:53-81): s = (max - min) / (2^bits - 1) (0 -> 1), zero point b = min,
+// q = (unsigned) round((x - b) / s), in [0, 2^bits - 1] by construction.
+ORC_API void orc_quant_per_token_asym(const float* x, int M, int K, int bits, uint8_t* q, float* s, float* b) {
+    const float base = (float)((1 << bits) - 1);
+    const long long mask = (1ll << bits) - 1;
+#pragma omp parallel for
+    for (int m = 0; m < M; m++) {
+        const float* xr = x + (long)m * K;
+        float mx = -1e32f, mn = 1e32f;
+        for (int k = 0; k < K; k++) { if (xr[k] > mx) mx = xr[k]; if (xr[k] < mn) mn = xr[k]; }
+        float sc = (mx - mn) / base;
+        if (sc == 0) sc = 1;
+        s[m] = sc; b[m] = mn;
+        for (int k = 0; k < K; k++) {
+            const float t = (xr[k] - mn) / sc;
+            q[(long)m * K + k] = (uint8_t)((long long)std::round(t) & mask);
+        }
+    }
+}
+
+// Dequant with the zero point (quant.h:146-148): y = ((float)acc * s_tok) * s_ch + b_tok * wsum, where
+// wsum[n] = sum_k w[n][k] * s_ch[n] comes with the checkpoint (Linear_Layer_Prefilling_tb.cpp:222-237).
+ORC_API void orc_dequant_asym(const int32_t* acc, const float* s_tok, const float* b_tok, const float* s_ch, const float* wsum, int M,
+                              int N, float* y) {
+#pragma omp parallel for
+    for (int m = 0; m < M; m++)
+        for (int n = 0; n < N; n++) {
+            float t = (float)acc[(long)m * N + n] * s_tok[m];
+            t = t * s_ch[n];
+            const float z = b_tok[m] * wsum[n];
+            y[(long)m * N + n] = t + z;
+        }
+}
+
 // ----------------------------------------------------------------------------------------------
 // A.2  exact integer matmul  acc[m][n] = sum_k a[m][k]*w[n][k]   (PE.h:526-583, MHA.h:113-187)
 // ----------------------------------------------------------------------------------------------

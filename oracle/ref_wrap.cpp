@@ -109,6 +109,73 @@ REF_API void ref_dequant(const int32_t* acc, const float* s_tok, const float* s_
     }
 }
 
+// ---- quant.h:6 pref_quant_layer_fp32_qint<4,true,...>: the shipped model's activation quantiser (4-bit asymmetric) ----
+REF_API void ref_quant_per_token_asym4(const float* x, int M, int K, uint8_t* q, float* s, float* b) {
+    constexpr int P = 8;
+    for (int m0 = 0; m0 < M; m0 += P) {
+        tapa::stream<hls::vector<float, P>> in;
+        tapa::stream<hls::vector<float, 2>> sb;
+        tapa::stream<hls::vector<ap_int<4>, P>> out;
+        for (int k = 0; k < K; k++) {
+            hls::vector<float, P> v;
+            for (int m = 0; m < P; m++) v[m] = (m0 + m < M) ? x[(long)(m0 + m) * K + k] : 0.0f;
+            in.write(v);
+        }
+        pref_quant_layer_fp32_qint<4, true, P, 8192, P>(in, sb, out, P, K);
+        for (int m = 0; m < P; m++) { auto t = sb.read(); if (m0 + m < M) { s[m0 + m] = t[0]; b[m0 + m] = t[1]; } }
+        for (int k = 0; k < K; k++) {
+            auto v = out.read();
+            for (int m = 0; m < P; m++) if (m0 + m < M) q[(long)(m0 + m) * K + k] = (uint8_t)((long long)v[m] & 15);   // the 4 bits, read as unsigned
+        }
+    }
+}
+
+// ---- quant.h:116 pref_dequant_layer_qint_fp32<.., true, ..>: acc * s * ws + b * wsum ---------------------------------
+REF_API void ref_dequant_asym(const int32_t* acc, const float* s_tok, const float* b_tok, const float* s_ch, const float* wsum, int M,
+                              int N, float* y) {
+    constexpr int P = 1;
+    for (int m = 0; m < M; m++) {
+        tapa::stream<hls::vector<ap_int<32>, P>> in;
+        tapa::stream<hls::vector<float, 2>> sb, ws;
+        tapa::stream<hls::vector<float, P>> out;
+        hls::vector<float, 2> t; t[0] = s_tok[m]; t[1] = b_tok[m];
+        sb.write(t);
+        for (int n = 0; n < N; n++) {
+            hls::vector<ap_int<32>, P> v; v[0] = ap_int<32>(acc[(long)m * N + n]);
+            in.write(v);
+            hls::vector<float, 2> u; u[0] = s_ch[n]; u[1] = wsum[n];
+            ws.write(u);
+        }
+        pref_dequant_layer_qint_fp32<32, true, P, 8192, 1>(in, sb, ws, out, 1, N);
+        for (int n = 0; n < N; n++) y[(long)m * N + n] = out.read()[0];
+    }
+}
+
+// ---- Linear_Layer.h:9 systolic_array_i4xi4_pack_2x2_2D<.., is_uint_A = true>: unsigned 4-bit activations x signed 4-bit weights ----
+REF_API void ref_gemm_u4s4(const uint8_t* a, const int8_t* w, int M, int N, int K, int32_t* acc) {
+    constexpr int BA = 8, BB = 16, LOG2K = 13;
+    for (int m0 = 0; m0 < M; m0 += BA)
+        for (int n0 = 0; n0 < N; n0 += BB) {
+            hls::stream<hls::vector<ap_int<4>, BA>> A;
+            hls::stream<hls::vector<ap_int<4>, BB>> B;
+            hls::stream<hls::vector<ap_int<LOG2K + 8>, BA>> C;
+            for (int k = 0; k < K; k++) {
+                hls::vector<ap_int<4>, BA> va;
+                hls::vector<ap_int<4>, BB> vb;
+                for (int i = 0; i < BA; i++) va[i] = ap_int<4>((int)((m0 + i < M) ? a[(long)(m0 + i) * K + k] : 0));
+                for (int j = 0; j < BB; j++) vb[j] = ap_int<4>((int)((n0 + j < N) ? w[(long)(n0 + j) * K + k] : 0));
+                A.write(va);
+                B.write(vb);
+            }
+            systolic_array_i4xi4_pack_2x2_2D<BA, BB, LOG2K, true>(A, B, C, K);
+            for (int j = 0; j < BB; j++) {
+                auto c = C.read();
+                for (int i = 0; i < BA; i++)
+                    if (m0 + i < M && n0 + j < N) acc[(long)(m0 + i) * N + n0 + j] = (int32_t)(long long)c[i];
+            }
+        }
+}
+
 // ---- MHA.h:114 systolic_array_i8xi8_pack_2x2 (s8 x s8 and u8 x s8), tiled 8 x 16 ---------------
 template <bool is_uint_A>
 static void ref_gemm(const int8_t* a, const int8_t* w, int M, int N, int K, int32_t* acc) {

@@ -340,3 +340,22 @@ def test_topk_sampling(F, lanes, V):
         assert np.array_equal(to_np(gi), wi), (rnd_value, to_np(gi)[:3], wi[:3])
         assert np.array_equal(to_np(gv).view(np.uint32), wv.view(np.uint32))
         assert np.array_equal(to_np(got), want), (rnd_value, to_np(got), want)
+
+
+@pytest.mark.parametrize("M,N,K,decode", [(128, 2048, 2048, False), (37, 520, 400, False), (1, 2048, 2048, True), (40, 2048, 8192, True)])
+def test_asymmetric_4bit_linear(F, M, N, K, decode):
+    """The reference's shipped W4A4 configuration (asymmetric 4-bit activations, zero point in the dequantiser; quant.h:53-81,
+    :146-148): quantiser, integer sums and dequantised output bit for bit against the oracle, whose functions are pinned
+    against the reference templates. Inputs U(-1, 1) as in the reference's bench (Linear_Layer_Prefilling_tb.cpp:172-200)."""
+    g = np.random.default_rng(42 + M)
+    x = g.uniform(-1, 1, (M, K)).astype(np.float32)
+    w = g.integers(-8, 8, (N, K), dtype=np.int8)
+    sc = g.uniform(0.001, 0.01, N).astype(np.float32)
+    wsum = (w.astype(np.float64) * sc[:, None]).sum(axis=1).astype(np.float32)
+    q, s, b = F.pref_quant_layer_fp32_qint_asym(dev(x), 4)
+    qo, so, bo = oracle.quant_per_token_asym(x, 4)
+    assert_same(to_np(q), qo, "asymmetric quantiser"); assert_same(to_np(s), so, "scales"); assert_same(to_np(b), bo, "zero points")
+    acc, y = F.pref_Linear_Layer_i4xi4(q, s, b, dev(w), dev(sc), dev(wsum), decode=decode)
+    acco = oracle.gemm_s8s8(qo.astype(np.int8), w)
+    assert_same(to_np(acc), acco, "integer sums")
+    assert_same(to_np(y), oracle.dequant_asym(acco, so, bo, sc, wsum), "dequantised output")

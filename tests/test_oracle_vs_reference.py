@@ -217,3 +217,32 @@ def test_topk_sample_restatement_vs_reference(lanes):
             got = oracle.topk_sample(logits, rnd, lanes=lanes)
         want = oracle.ref.topk_sample(logits, rnd, lanes=lanes)
         assert np.array_equal(got, want), (rnd_value, got, want)
+
+
+def test_asymmetric_4bit_linear_path_matches_reference_templates():
+    """The reference's shipped precision: 4-bit asymmetric activations (pref_quant_layer_fp32_qint<4, true>, quant.h:53-81),
+    unsigned x signed 4-bit systolic array (Linear_Layer.h:9, is_uint_A), dequantiser with zero point (quant.h:146-148).
+    Inputs as in the reference's own test bench: U(-1, 1) (Linear_Layer_Prefilling_tb.cpp:172-200)."""
+    R = oracle.ref
+    if R is None:
+        pytest.skip("reference templates not built")
+    g = np.random.default_rng(42)
+    x = g.uniform(-1, 1, (24, 512)).astype(np.float32)
+    x[5] = 0.25                                               # constant row: scale 0 -> 1
+    q, s, b = oracle.quant_per_token_asym(x, 4)
+    q2, s2, b2 = R.quant_per_token_asym4(x)
+    assert np.array_equal(q, q2) and np.array_equal(s.view(np.uint32), s2.view(np.uint32)) and np.array_equal(b.view(np.uint32), b2.view(np.uint32))
+    assert q.min() == 0 and q.max() == 15
+    w = g.integers(-8, 8, (48, 512), dtype=np.int8)
+    acc = oracle.gemm_s8s8(q.astype(np.int8), w)
+    assert np.array_equal(acc, R.gemm_u4s4(q, w))
+    sc = g.uniform(0.001, 0.01, 48).astype(np.float32)
+    wsum = np.zeros(48, np.float32)
+    ws = w.astype(np.float32) * sc[:, None]
+    for j in range(512):
+        wsum = (wsum + ws[:, j]).astype(np.float32)
+    y = oracle.dequant_asym(acc, s, b, sc, wsum)
+    assert np.array_equal(y.view(np.uint32), R.dequant_asym(acc, s, b, sc, wsum).view(np.uint32))
+    # the reference bench's own tolerance check against the fake-quant product (rel 1e-2, Linear_Layer_Prefilling_tb.cpp:281)
+    fq = (q.astype(np.float32) * s[:, None] + b[:, None]) @ ws.T
+    assert np.abs(y - fq).max() <= 1e-2 * np.abs(fq).max()
