@@ -66,11 +66,17 @@ SIGNATURES = {
     "flexllm_model_load_layer": [_P, _I, _P, _P],
     "flexllm_model_load_head": [_P, _P, _P, _P, _P, _P, _I, _P],
     "flexllm_model_prefill": [_P, _P, _I, _I, _P, _P],
+    "flexllm_model_prefill_embeds": [_P, _P, _I, _I, _I, _P, _P],
+    "flexllm_model_embed_tokens": [_P, _P, _I, _P, _P],
+    "flexllm_hmt_create": [_P, _P, _P, _I, _P, _P, _P],
+    "flexllm_hmt_destroy": [_P],
+    "flexllm_hmt_prefill": [_P, _P, _I, _P, _P, _P],
     "flexllm_model_begin": [_P, _I, _P],
     "flexllm_model_decode": [_P, _I, _I, _P],
     "flexllm_model_generate_host": [_P, _P, _I, _I, _I, _P, _I, _P],
     "flexllm_model_set_sampling": [_P, _I, _I, _P],
     "flexllm_model_buffer": [_P, _I, _P],
+    "flexllm_model_limits": [_P, _P, _P, _P],
     "flexllm_debug_hook": [_I, C.c_longlong],
     "flexllm_gemm_i8_mainloop_probe": [_P, _P, _I, _I, _I, _P],
 }
@@ -84,6 +90,10 @@ class ModelConfig(C.Structure):
 class CkptLayerBuffers(C.Structure):
     _fields_ = ([(n, _P) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")] + [(n, _P) for n in ("sq", "sk", "sv", "so", "sg", "su", "sd")] +
                 [(n, _P) for n in ("sumq", "sumk", "sumv", "sumo", "sumg", "sumu", "sumd")] + [(n, _P) for n in ("gamma0", "gamma1", "a_s")])
+
+
+class HmtConfig(C.Structure):
+    _fields_ = [("seg_len", _I), ("sum_len", _I), ("rec_len", _I), ("mem_num", _I)]
 
 
 class LayerWeights(C.Structure):

@@ -76,10 +76,10 @@ __global__ void embed_kernel(const int32_t* __restrict__ tok, const int8_t* __re
     }
 }
 
-// rows (b*S + S-1) of x -> y[b]
-__global__ void gather_last_kernel(const float* __restrict__ x, int S, int D, float* __restrict__ y) {
+// rows (b*S + n - 1) of x -> y[b]   (n: valid rows per sequence, the rest is padding)
+__global__ void gather_last_kernel(const float* __restrict__ x, int S, int n, int D, float* __restrict__ y) {
     const int b = blockIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(x + ((long)b * S + S - 1) * D);
+    const float4* src = reinterpret_cast<const float4*>(x + ((long)b * S + n - 1) * D);
     float4* dst = reinterpret_cast<float4*>(y + (long)b * D);
     for (int i = threadIdx.x; i < D / 4; i += blockDim.x) dst[i] = src[i];
 }
@@ -433,7 +433,7 @@ static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, i
             TRY(kv_regroup(m->kvs_stage, n_pg, g, HKV, 256, dst->vs + ds, st));
         }
     }
-    gather_last_kernel<<<Bl, 256, 0, st>>>(m->x, Sc, D, dm->xlast);          // the last chunk's rows are in x
+    gather_last_kernel<<<Bl, 256, 0, st>>>(m->x, Sc, Sc, D, dm->xlast);      // the last chunk's rows are in x
     note_launches(1);
     TRY(run_head(dm, dm->xlast, Bl, FLEXLLM_NORM_PREFILL, st));
     fill_ctx_kernel<<<1, 64, 0, st>>>(dm->ctx, Bl, S);
@@ -447,13 +447,18 @@ static int prefill_rows(flexllm_model* m, const int32_t* tokens, int B, int S, i
 
 // One chunk of the prompt (positions c0 .. c0 + Sc - 1 of every sequence) through all layers: single GPU, or the
 // all-gather partition of the tensor-parallel model.
-static int prefill_chunk(flexllm_model* m, const int32_t* tokens, int B, int S, int c0, int Sc, cudaStream_t st) {
+static int prefill_chunk(flexllm_model* m, const int32_t* tokens, const float* embeds, int B, int S, int c0, int Sc, cudaStream_t st) {
     const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl, F = m->cfg.ffn;
     const int QKV = (HQ + 2 * HKV) * 64;
     const int M = B * Sc;
     const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl;
-    embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag(), S, c0, Sc, 0L);
-    note_launches(1);
+    if (embeds) {       // rows given as vectors (not token ids): sequence b's chunk is contiguous in embeds [B][S][D]
+        for (int b = 0; b < B; b++)
+            TRY(copy_any(m->x + (size_t)b * Sc * D, embeds + ((size_t)b * S + c0) * D, (size_t)Sc * D * 4, st));
+    } else {
+        embed_kernel<<<M, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag(), S, c0, Sc, 0L);
+        note_launches(1);
+    }
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
         TRY(flexllm_rmsnorm_quant(m->x, L.g0, M, D, m->cfg.eps, FLEXLLM_NORM_PREFILL, nullptr, m->xq, m->xs, st));
@@ -493,27 +498,55 @@ static int prefill_chunk(flexllm_model* m, const int32_t* tokens, int B, int S, 
 // before it from the paged KV cache. The reference's host program has one fixed prefill length and repacks the cache
 // between its two launches (SpinQuant_Prefilling_Decoding_mem_opt_demo.cpp:947-970); here prefill and decode share one
 // paged cache, so there is nothing to repack and no limit but max_ctx.
+static int prefill_any(flexllm_model* m, const int32_t* tokens, const float* embeds, int B, int S, int n_valid, int32_t* next_out,
+                       cudaStream_t st) {
+    m->rows_mode = false;
+    const int D = m->cfg.hidden;
+    int Sc = S, c_last = 0;
+    for (int c0 = 0; c0 < S; c0 += m->cfg.max_prefill) {
+        Sc = S - c0 < m->cfg.max_prefill ? S - c0 : m->cfg.max_prefill;
+        c_last = c0;
+        TRY(prefill_chunk(m, tokens, embeds, B, S, c0, Sc, st));
+    }
+    // the last chunk's rows are in x; the token comes from the last VALID position (rows after it are padding)
+    gather_last_kernel<<<B, 256, 0, st>>>(m->x, Sc, n_valid - c_last, D, m->xlast);
+    note_launches(1);
+    TRY(run_head(m, m->xlast, B, FLEXLLM_NORM_PREFILL, st));
+    fill_ctx_kernel<<<1, 64, 0, st>>>(m->ctx, B, n_valid);
+    TRY(launch_status());
+    if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
+    m->B = B; m->S = n_valid; m->pos = n_valid; m->last_chunk = Sc;
+    return FLEXLLM_OK;
+}
+
 extern "C" int flexllm_model_prefill(flexllm_model* m, const int32_t* tokens, int B, int S, int32_t* next_out, void* stream) {
     FLEXLLM_REQUIRE(m && tokens && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_ctx);
     if (S % 16 != 0) return FLEXLLM_ENOTSUP;
     if (S > m->cfg.max_prefill && m->cfg.max_prefill % 128 != 0) return FLEXLLM_ENOTSUP;     // chunks start at multiples of 128
     cudaStream_t st = (cudaStream_t)stream;
     if (m->dm && B % m->g == 0) return prefill_rows(m, tokens, B, S, next_out, st);
-    m->rows_mode = false;
-    const int D = m->cfg.hidden;
-    int Sc = S;
-    for (int c0 = 0; c0 < S; c0 += m->cfg.max_prefill) {
-        Sc = S - c0 < m->cfg.max_prefill ? S - c0 : m->cfg.max_prefill;
-        TRY(prefill_chunk(m, tokens, B, S, c0, Sc, st));
-    }
-    gather_last_kernel<<<B, 256, 0, st>>>(m->x, Sc, D, m->xlast);             // the last chunk's rows are in x
-    note_launches(1);
-    TRY(run_head(m, m->xlast, B, FLEXLLM_NORM_PREFILL, st));
-    fill_ctx_kernel<<<1, 64, 0, st>>>(m->ctx, B, S);
-    TRY(launch_status());
-    if (next_out) TRY(copy_any(next_out, m->next, (size_t)B * 4, st));
-    m->B = B; m->S = S; m->pos = S; m->last_chunk = Sc;
-    return FLEXLLM_OK;
+    return prefill_any(m, tokens, nullptr, B, S, S, next_out, st);
+}
+
+// Prefill from EMBEDDING VECTORS embeds [B][S][hidden] fp32 (device) instead of token ids -- what the HMT plug-in feeds the
+// prefill graph (summary / memory vectors are not rows of the embedding table, Modules/HMT.h:48-170). Rows n_valid .. S-1
+// of every sequence are padding up to a multiple of 16 (causal attention: they change nothing before them); the first
+// token is chosen at position n_valid - 1 and decoding continues from context length n_valid. Single GPU.
+extern "C" int flexllm_model_prefill_embeds(flexllm_model* m, const float* embeds, int B, int S, int n_valid, int32_t* next_out,
+                                            void* stream) {
+    FLEXLLM_REQUIRE(m && embeds && B > 0 && B <= m->cfg.max_batch && S > 0 && S <= m->cfg.max_ctx && n_valid > 0 && n_valid <= S);
+    if (m->g != 1 || S % 16 != 0) return FLEXLLM_ENOTSUP;
+    if (S > m->cfg.max_prefill && m->cfg.max_prefill % 128 != 0) return FLEXLLM_ENOTSUP;
+    FLEXLLM_REQUIRE(S - n_valid < (S > m->cfg.max_prefill ? S - (S - 1) / m->cfg.max_prefill * m->cfg.max_prefill : S));   // the last valid row lies in the last chunk
+    return prefill_any(m, nullptr, embeds, B, S, n_valid, next_out, (cudaStream_t)stream);
+}
+
+// Embedding rows of n token ids (tied embeddings: row t = (float)lm_head_q[t] * lm_head_s[t]): tokens [n] -> out [n][hidden].
+extern "C" int flexllm_model_embed_tokens(flexllm_model* m, const int32_t* tokens, int n, float* out, void* stream) {
+    FLEXLLM_REQUIRE(m && tokens && out && n >= 0);
+    if (n == 0) return FLEXLLM_OK;
+    embed_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(tokens, m->lm_w, m->lm_s, m->cfg.hidden, m->cfg.vocab, out, device_error_flag(), 1, 0, 1, 0L);
+    return launch_status();
 }
 
 // One decode step for the B sequences of the last prefill: consumes m->next, leaves the new
@@ -691,6 +724,14 @@ extern "C" int flexllm_model_set_sampling(flexllm_model* m, int lanes, int top_k
     m->sample_lanes = top_k > 0 ? lanes : 0; m->sample_k = top_k; m->sample_rnd = top_k > 0 ? rnd : nullptr;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }      // the captured step holds the old choice
     if (m->mega) mega_set_sampling(m->mega, m->sample_lanes, m->sample_k, m->sample_rnd);
+    return FLEXLLM_OK;
+}
+
+extern "C" int flexllm_model_limits(const flexllm_model* m, int* max_batch, int* max_prefill, int* max_ctx) {
+    FLEXLLM_REQUIRE(m);
+    if (max_batch) *max_batch = m->cfg.max_batch;
+    if (max_prefill) *max_prefill = m->cfg.max_prefill;
+    if (max_ctx) *max_ctx = m->cfg.max_ctx;
     return FLEXLLM_OK;
 }
 

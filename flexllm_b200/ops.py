@@ -369,6 +369,31 @@ def read_reference_head(directory, layers, hidden, vocab, table_len, want_embed=
     return out
 
 
+class HMT:
+    """HMT long-context plug-in (Modules/HMT.h) on a Model: segment recurrence with a ring of memory vectors."""
+
+    def __init__(self, model, hidden, wq, wk, t_embed, seg_len=990, sum_len=495, rec_len=32, mem_num=64):
+        self.model, self.hidden = model, hidden
+        self.cfg = _lib.HmtConfig(seg_len, sum_len, rec_len, mem_num)
+        self._h = C.c_void_p()
+        p = lambda t: C.c_void_p(t.contiguous().data_ptr())
+        _check("flexllm_hmt_create", lib().flexllm_hmt_create(C.byref(self._h), model._h, C.byref(self.cfg), hidden, p(wq), p(wk), p(t_embed)))
+
+    def close(self):
+        if self._h:
+            lib().flexllm_hmt_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def prefill(self, embeds, want_trace=False):
+        """embeds [T,hidden] fp32 CUDA. Returns (first token [1], trace [segments,4,hidden] | None)."""
+        T = embeds.shape[0]
+        nseg = (T + self.cfg.seg_len - 1) // self.cfg.seg_len
+        nxt = torch.empty((1,), dtype=torch.int32, device=embeds.device)
+        tr = torch.zeros((nseg, 4, self.hidden), dtype=torch.float32, device=embeds.device) if want_trace else None
+        _check("flexllm_hmt_prefill", lib().flexllm_hmt_prefill(self._h, _ptr(embeds), T, _ptr(nxt), _ptr(tr), _stream()))
+        return nxt, tr
+
+
 def tp_unique_id():
     """128-byte NCCL id made on one rank; hand it to the others (e.g. torch.distributed broadcast)."""
     from . import build
@@ -447,6 +472,19 @@ class Model:
         nxt = torch.empty((B,), dtype=torch.int32, device=tokens.device)
         _check("flexllm_model_prefill", lib().flexllm_model_prefill(self._h, _ptr(tokens), B, S, _ptr(nxt), _stream()))
         return nxt
+
+    def prefill_embeds(self, embeds, n_valid=None):
+        """embeds [B,S,hidden] fp32 CUDA; rows n_valid.. are padding. Returns the first tokens [B]."""
+        B, S, _ = embeds.shape
+        nxt = torch.empty((B,), dtype=torch.int32, device=embeds.device)
+        _check("flexllm_model_prefill_embeds", lib().flexllm_model_prefill_embeds(self._h, _ptr(embeds), B, S, S if n_valid is None else n_valid,
+                                                                                  _ptr(nxt), _stream()))
+        return nxt
+
+    def embed_tokens(self, tokens, hidden):
+        out = torch.empty((tokens.numel(), hidden), dtype=torch.float32, device=tokens.device)
+        _check("flexllm_model_embed_tokens", lib().flexllm_model_embed_tokens(self._h, _ptr(tokens), tokens.numel(), _ptr(out), _stream()))
+        return out
 
     def begin(self, n_new):
         _check("flexllm_model_begin", lib().flexllm_model_begin(self._h, n_new, _stream()))

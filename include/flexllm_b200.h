@@ -283,6 +283,35 @@ FLEXLLM_API int flexllm_model_decode(flexllm_model* m, int n_steps, int use_grap
 /* Whole request through HOST buffers: tokens_host [B][S] -> out_host [B][n_new]; synchronises. */
 FLEXLLM_API int flexllm_model_generate_host(flexllm_model* m, const int32_t* tokens_host, int B, int S, int n_new,
                                 int32_t* out_host, int use_graph, void* stream);
+/* Prefill from embedding vectors embeds [B][S][hidden] fp32 (device) instead of token ids: rows n_valid .. S-1 of every
+ * sequence are padding up to a multiple of 16; the first token is chosen at position n_valid - 1 and decoding continues
+ * from context length n_valid (what the HMT plug-in needs: its summary and memory vectors are not rows of the embedding
+ * table, Modules/HMT.h:48-170). Single GPU. */
+FLEXLLM_API int flexllm_model_prefill_embeds(flexllm_model* m, const float* embeds, int B, int S, int n_valid, int32_t* next_out,
+                                             void* stream);
+/* Embedding rows (tied embeddings) of n token ids: tokens [n] (device) -> out [n][hidden] fp32 (device). */
+FLEXLLM_API int flexllm_model_embed_tokens(flexllm_model* m, const int32_t* tokens, int n, float* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * HMT long-context plug-in (Modules/HMT.h; HMT_SpinQuant_Llama_32_1B/): the prompt is processed in segments of seg_len
+ * tokens through the same prefill path; per segment a summary pass over [T, first sum_len tokens, T] queries a ring of
+ * mem_num memory vectors by fp32 cross-attention (Q = Wq S, keys Wk M, dec_Softmax with scale sqrt(hidden)) for the
+ * prompt vector P, and the main pass over [P, rec_len tokens of the previous segment, the segment, P] yields the new
+ * memory vector (hmt_segment_loader_sync_template HMT.h:8-195, cross-attention :278-355, memory caches :357-470).
+ * The reference's sizes: seg_len 990, sum_len 495, rec_len 32, mem_num 64. The model must have
+ * max_prefill >= 1 + rec_len + seg_len + 1 rounded up to 16, max_batch >= 1. One sequence per call.
+ * wq, wk [hidden][hidden] fp32 and t_embed [hidden] (host or device) are copied. After flexllm_hmt_prefill the model
+ * holds the last segment's KV cache and first token: continue with flexllm_model_begin / flexllm_model_decode.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct { int seg_len, sum_len, rec_len, mem_num; } flexllm_hmt_config;
+typedef struct flexllm_hmt flexllm_hmt;
+FLEXLLM_API int flexllm_hmt_create(flexllm_hmt** out, flexllm_model* model, const flexllm_hmt_config* cfg, int hidden,
+                                   const float* wq, const float* wk, const float* t_embed);
+FLEXLLM_API int flexllm_hmt_destroy(flexllm_hmt* h);
+/* embeds [T][hidden] fp32 (device); next_out [1] (device, optional); trace (device, optional) [segments][4][hidden]
+ * receives S_n, P_n, M_n, K_n of each segment that produces them. */
+FLEXLLM_API int flexllm_hmt_prefill(flexllm_hmt* h, const float* embeds, int T, int32_t* next_out, float* trace, void* stream);
+
 /* Token choice of the following prefill / decode calls. top_k == 0: greedy argmax (default). Otherwise the reference's
  * top-k sampling (flexllm_topk_sample) with `lanes` lanes and uniform numbers rnd [n_new][B] in DEVICE memory, row c for
  * output column c -- the reference's rand_seeds_mmap, one number per decode step (SpinQuant_Decoding_mem_opt.h:934-937).
@@ -344,6 +373,9 @@ FLEXLLM_API int flexllm_linear_decode_asym(const uint8_t* a, const float* s_tok,
  * flexllm_device_status() reports FLEXLLM_ETIMEDOUT (one-shot). A generation that timed out is void: start
  * again from flexllm_model_prefill / flexllm_model_begin, which also re-arm the barrier counter. */
 FLEXLLM_API int flexllm_debug_hook(int which, long long value);
+
+/* The sizes the model was created with. */
+FLEXLLM_API int flexllm_model_limits(const flexllm_model* m, int* max_batch, int* max_prefill, int* max_ctx);
 
 /* Device pointers of internal buffers (tests): 0 residual stream, 1 logits, 2 token table, 3 ctx. */
 FLEXLLM_API int flexllm_model_buffer(flexllm_model* m, int which, void** ptr);

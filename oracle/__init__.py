@@ -290,6 +290,23 @@ def attn_row(q, qs, k, ks, v, vs, a_s):
     return r
 
 
+def linear_fp32_chain4(x, w):
+    """y = W x in fp32 with the reference's accumulation order (dec_Linear_Layer_fp32xfp32, PE.h:655-756): four
+    interleaved chains over k mod 4, combined (p0 + p1) + (p2 + p3). x [K], w [N,K] -> y [N]."""
+    x = _f32(x); w = _f32(w); N, K = w.shape
+    y = np.empty(N, np.float32)
+    _lib.orc_linear_fp32_chain4(_p(x), _p(w), C.c_int(N), C.c_int(K), _p(y))
+    return y
+
+
+def softmax_dec(x, lanes=4, scale=1.0):
+    """dec_Softmax with enable_scale and enable_sub_max (Softmax.h:261-363): p = softmax((x - max) / scale) with `lanes`
+    block-partitioned lanes of four interleaved partial sums each."""
+    x = _f32(x); p = np.empty_like(x)
+    _lib.orc_softmax_dec(_p(x), C.c_int(x.size), C.c_int(lanes), C.c_float(scale), _p(p))
+    return p
+
+
 class _OrcModel(C.Structure):
     _PP = C.POINTER(C.c_void_p)
     _fields_ = ([("L", C.c_int), ("D", C.c_int), ("HQ", C.c_int), ("HKV", C.c_int), ("F", C.c_int), ("V", C.c_int),
@@ -299,12 +316,8 @@ class _OrcModel(C.Structure):
                 [("g_final", C.c_void_p), ("lm_w", C.c_void_p), ("lm_s", C.c_void_p), ("cos_t", C.c_void_p), ("sin_t", C.c_void_p)])
 
 
-def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False, sampling=None):
-    """Full-model greedy generation on the CPU. `weights`: dict with per-layer lists under the keys
-    wq wk wv wo wg wu wd (int8 [N,K]), sq sk sv so sg su sd g0 g1 a_s (fp32) and g_final, lm_w, lm_s,
-    cos_t, sin_t, plus ints HQ, HKV. tokens [B,S] int32. sampling: None (greedy) or (lanes, top_k, rnd [n_new,B])
-    for the reference's top-k sampling. Returns dict(tokens [B,n_new], hidden, logits_prefill, logits_last)."""
-    tokens = _i32(tokens); B, S = tokens.shape
+def _orc_model(weights):
+    """(struct, keep-alive list) for the C model functions."""
     L = len(weights["wq"]); D = weights["wq"][0].shape[1]; F = weights["wg"][0].shape[0]; V = weights["lm_w"].shape[0]
     keep = []
     m = _OrcModel()
@@ -321,6 +334,17 @@ def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False,
     for name, conv in (("g_final", _f32), ("lm_w", _i8), ("lm_s", _f32), ("cos_t", _f32), ("sin_t", _f32)):
         a = conv(weights[name]); keep.append(a)
         setattr(m, name, a.ctypes.data)
+    return m, keep
+
+
+def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False, sampling=None):
+    """Full-model greedy generation on the CPU. `weights`: dict with per-layer lists under the keys
+    wq wk wv wo wg wu wd (int8 [N,K]), sq sk sv so sg su sd g0 g1 a_s (fp32) and g_final, lm_w, lm_s,
+    cos_t, sin_t, plus ints HQ, HKV. tokens [B,S] int32. sampling: None (greedy) or (lanes, top_k, rnd [n_new,B])
+    for the reference's top-k sampling. Returns dict(tokens [B,n_new], hidden, logits_prefill, logits_last)."""
+    tokens = _i32(tokens); B, S = tokens.shape
+    m, keep = _orc_model(weights)
+    D, V = m.D, m.V
     out = np.zeros((B, max(n_new, 1)), np.int32)
     hidden = np.empty((B * S, D), np.float32) if want_hidden else None
     lp = np.empty((B, V), np.float32) if want_logits else None
@@ -334,6 +358,66 @@ def model_generate(weights, tokens, n_new, want_hidden=False, want_logits=False,
     finally:
         _lib.orc_set_sampling(C.c_int(0), C.c_int(0), None)
     return dict(tokens=out[:, :n_new], hidden=hidden, logits_prefill=lp, logits_last=ll)
+
+
+def model_forward_embeds(weights, embeds, n_valid, n_new=0):
+    """One sequence from embeddings [S,D] (rows from n_valid on are padding): returns (residual stream [S,D], tokens [n_new])."""
+    embeds = _f32(embeds); S, D = embeds.shape
+    m, keep = _orc_model(weights)
+    hidden = np.empty((S, D), np.float32)
+    out = np.zeros(max(n_new, 1), np.int32)
+    _lib.orc_model_forward_embeds(C.byref(m), _p(embeds), C.c_int(S), C.c_int(n_valid), C.c_int(n_new), _p(hidden), _p(out))
+    return hidden, out[:n_new]
+
+
+def hmt_prefill(weights, embeds, t_embed, wq, wk, seg_len, sum_len, rec_len, mem_num, n_new=0, pad=16):
+    """The HMT segment recurrence (Modules/HMT.h:8-195 segment loop, :278-355 cross-attention, :357-470 memory caches)
+    for one long sequence given as embeddings [T,D]: per segment, stage 0 = prefill of [T_tok, first sum_len tokens, T_tok]
+    whose last row S_n queries the memory (Q = Wq S_n, scores against the cached keys, dec_Softmax with scale sqrt(D),
+    P_n = sum_s A_s M_s); stage 1 = prefill of [P_n, rec_len tail tokens of the previous segment, the segment, P_n] whose
+    last row M_n and its key Wk M_n go into slot seg % mem_num. Returns dict(P, M, K per segment, hidden of the last
+    stage-1 run, n_valid of that run, tokens)."""
+    embeds = _f32(embeds); T, D = embeds.shape
+    seg_num = (T + seg_len - 1) // seg_len
+    mem = np.zeros((mem_num, D), np.float32); kmem = np.zeros((mem_num, D), np.float32)
+    Pn = np.zeros(D, np.float32)
+    scale = np.float32(np.sqrt(np.float32(D)))
+    rec = dict(P=[], M=[], K=[], S=[])
+    padded = lambda n: (n + pad - 1) // pad * pad
+    hidden = None; tokens = None; n1 = 0
+    for seg in range(seg_num):
+        cur = seg_len if seg < seg_num - 1 else T - seg * seg_len
+        sl = min(cur, sum_len); off = seg * seg_len
+        if seg > 0:
+            n0 = 1 + sl + 1
+            x0 = np.zeros((padded(n0), D), np.float32)
+            x0[0] = t_embed; x0[1:1 + sl] = embeds[off:off + sl]; x0[1 + sl] = t_embed
+            h0, _ = model_forward_embeds(weights, x0, n0)
+            Sn = h0[1 + sl]
+            Qn = linear_fp32_chain4(Sn, wq)
+            A = linear_fp32_chain4(Qn, kmem)
+            Pa = softmax_dec(A, 4, scale)
+            Pn = linear_fp32_chain4(Pa, np.ascontiguousarray(mem.T))
+            rec["S"].append(Sn); rec["P"].append(Pn)
+        last = seg == seg_num - 1
+        n1 = 1 + rec_len + cur + (0 if last else 1)
+        x1 = np.zeros((padded(n1), D), np.float32)
+        x1[0] = Pn
+        for i in range(rec_len):
+            j = off - rec_len + i
+            if j >= 0:
+                x1[1 + i] = embeds[j]
+        x1[1 + rec_len:1 + rec_len + cur] = embeds[off:off + cur]
+        if not last:
+            x1[1 + rec_len + cur] = Pn
+        hidden, tokens = model_forward_embeds(weights, x1, n1, n_new if last else 0)
+        if not last:
+            Mn = hidden[1 + rec_len + cur].copy()
+            Kn = linear_fp32_chain4(Mn, wk)
+            mem[seg % mem_num] = Mn; kmem[seg % mem_num] = Kn
+            rec["M"].append(Mn); rec["K"].append(Kn)
+    rec.update(hidden=hidden, n_valid=n1, tokens=tokens)
+    return rec
 
 
 # ------------------------------------------------------------------ Tier A (reference templates)
@@ -365,6 +449,18 @@ class _Ref:
         a = np.ascontiguousarray(a, dtype=np.uint8); w = _i8(w); M, K = a.shape; N = w.shape[0]; acc = np.empty((M, N), np.int32)
         self.lib.ref_gemm_u4s4(_p(a), _p(w), C.c_int(M), C.c_int(N), C.c_int(K), _p(acc))
         return acc
+
+    def linear_fp32(self, x, w):
+        x = _f32(x); w = _f32(w); N, K = w.shape; y = np.empty(N, np.float32)
+        rc = self.lib.ref_linear_fp32(_p(x), _p(w), C.c_int(N), C.c_int(K), _p(y))
+        assert rc == 0
+        return y
+
+    def softmax_dec4_64(self, x, scale):
+        x = _f32(x); assert x.size == 64
+        p = np.empty_like(x)
+        self.lib.ref_softmax_dec4_64(_p(x), C.c_float(scale), _p(p))
+        return p
 
     def dequant(self, acc, s_tok, s_ch):
         acc = _i32(acc); M, N = acc.shape; y = np.empty((M, N), np.float32)

@@ -775,3 +775,75 @@ ORC_API void orc_model_generate(const OrcModel* mp, const int32_t* tokens, int B
         for (int b = 0; b < B; b++) out_tokens[(size_t)b * n_new + step] = next[b];
     }
 }
+
+// ----------------------------------------------------------------------------------------------
+// HMT (hierarchical memory transformer) plug-in, Modules/HMT.h: the two fp32 primitives of its memory cross-attention.
+//
+// dec_Linear_Layer_fp32xfp32 (Linear_Layer.h:1040-1101) over PE_fp32xfp32_pack_1x2_1D (PE.h:655-756, the non-versal
+// path): y[n] = (p0 + p1) + (p2 + p3), p[c] = sum over k = c, c+4, ... of a[k] * w[n][k], each product and each add
+// rounded on its own, k increasing.
+// ----------------------------------------------------------------------------------------------
+ORC_API void orc_linear_fp32_chain4(const float* a, const float* w, int N, int K, float* y) {
+#pragma omp parallel for
+    for (int n = 0; n < N; n++) {
+        const float* wr = w + (long)n * K;
+        float p[4] = {0, 0, 0, 0};
+        for (int k = 0; k < K; k++) { const float t = a[k] * wr[k]; p[k & 3] = p[k & 3] + t; }
+        const float t0 = p[0] + p[1], t1 = p[2] + p[3];
+        y[n] = t0 + t1;
+    }
+}
+
+// dec_Softmax<float, lanes, dim, enable_scale = true, enable_sub_max = true> (Softmax.h:261-363, non-versal path) as
+// hmt_attn_softmax instantiates it (HMT_SpinQuant_Unit.h:97-105): lane i holds elements i * (dim / lanes) + k;
+// e = exp((x - max) / scale); per lane four chains over k mod 4, lane total (s0 + s1) + (s2 + s3); lane totals added
+// from 0 in lane order; p = e * (1 / total).
+ORC_API void orc_softmax_dec(const float* x, int dim, int lanes, float scale, float* pr) {
+    const int per = dim / lanes;
+    float mx = -1e32f;
+    for (int i = 0; i < dim; i++) mx = x[i] > mx ? x[i] : mx;
+    float total = 0;
+    for (int i = 0; i < lanes; i++) {
+        float s[4] = {0, 0, 0, 0};
+        for (int k = 0; k < per; k++) {
+            const float e = ref_exp((x[i * per + k] - mx) / scale);
+            pr[i * per + k] = e;
+            s[k & 3] += e;
+        }
+        total += (s[0] + s[1]) + (s[2] + s[3]);
+    }
+    const float r = 1.0f / total;
+    for (int i = 0; i < dim; i++) pr[i] = pr[i] * r;
+}
+
+// One sequence from EMBEDDINGS (HMT feeds the prefill graph vectors that are not rows of the embedding table): prefill of
+// S rows (positions 0 .. S-1; rows from n_valid on are padding), residual stream out [S][D]; then greedy generation of n_new
+// tokens continuing after position n_valid - 1.
+ORC_API void orc_model_forward_embeds(const OrcModel* mp, const float* embeds, int S, int n_valid, int n_new, float* hidden_out,
+                                      int32_t* out_tokens) {
+    const OrcModel& m = *mp;
+    OrcCache c;
+    c.B = 1; c.T = S + (n_new > 0 ? n_new : 0);
+    size_t rows = (size_t)m.L * c.T * m.HKV;
+    c.k.assign(rows * 64, 0); c.v.assign(rows * 64, 0); c.ks.assign(rows, 0); c.vs.assign(rows, 0);
+    std::vector<int> seq(S, 0), pos(S);
+    for (int i = 0; i < S; i++) pos[i] = i;
+    std::vector<float> x(embeds, embeds + (size_t)S * m.D);
+    for (int l = 0; l < m.L; l++) model_layer(m, l, x, S, seq.data(), pos.data(), c, 0);
+    if (hidden_out) std::memcpy(hidden_out, x.data(), sizeof(float) * x.size());
+    if (n_new <= 0) return;
+    std::vector<float> last(&x[(size_t)(n_valid - 1) * m.D], &x[(size_t)n_valid * m.D]);
+    int32_t next = 0;
+    g_sample_step = 0;
+    model_head(m, last.data(), 1, 0, nullptr, &next);
+    out_tokens[0] = next;
+    for (int step = 1; step < n_new; step++) {
+        int dseq = 0, dpos = n_valid + step - 1;
+        model_embed(m, &next, 1, x);
+        for (int l = 0; l < m.L; l++) model_layer(m, l, x, 1, &dseq, &dpos, c, 8);
+        g_sample_step = step;
+        model_head(m, x.data(), 1, 8, nullptr, &next);
+        out_tokens[step] = next;
+    }
+}
+

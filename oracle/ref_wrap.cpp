@@ -531,3 +531,57 @@ REF_API int ref_topk_sample(const float* logits, int V, int lanes, float rnd, in
     if (lanes == 32) return ref_topk_sample_p<32>(logits, V, rnd, idx);
     return -1;
 }
+
+// ---- Linear_Layer.h:1040 dec_Linear_Layer_fp32xfp32<4, 8, ...> (the HMT cross-attention's linear unit) -------------------
+// One input vector x [K] against W [N][K]. Lanes are block-partitioned: lane i carries inputs i * K/4 + k and produces the
+// outputs i * N/4 + ...; each lane's weight stream delivers, for its output block, 8 rows at a time, column by column in the
+// order the layer replays the input (lane blocks 0..3, k inside the block).
+REF_API int ref_linear_fp32(const float* x, const float* w, int N, int K, float* y) {
+    constexpr int BP = 4, WP = 8, MAXD = 2048;
+    if (K % (BP * 4) || N % (BP * WP) || K > MAXD || N > MAXD) return -1;
+    tapa::stream<hls::vector<float, BP>> in, out;
+    tapa::stream<hls::vector<float, WP>> wls[BP];
+    tapa::istreams<hls::vector<float, WP>, BP> wl;
+    for (int i = 0; i < BP; i++) wl.s[i] = &wls[i];
+    // dec_Linear_Layer_fp32xfp32 stores A[i * MAXD/BP + k] = pack[i] and replays A[Kb * MAXD/BP + k]: feed K == MAXD-shaped input
+    // by placing element i * (K/BP) + k in lane i at position k only when K == MAXD; for smaller K the same holds because the
+    // replay uses the same (lane block, k) addressing.
+    for (int k = 0; k < K / BP; k++) {
+        hls::vector<float, BP> v;
+        for (int i = 0; i < BP; i++) v[i] = x[i * (K / BP) + k];
+        in.write(v);
+    }
+    for (int Nb = 0; Nb < N / (BP * WP); Nb++)
+        for (int Kb = 0; Kb < BP; Kb++)
+            for (int k = 0; k < K / BP; k++)
+                for (int i = 0; i < BP; i++) {
+                    hls::vector<float, WP> wv;
+                    for (int n = 0; n < WP; n++) wv[n] = w[(long)(i * (N / BP) + Nb * WP + n) * K + Kb * (K / BP) + k];
+                    wls[i].write(wv);
+                }
+    dec_Linear_Layer_fp32xfp32<BP, WP, MAXD, MAXD>(in, wl, out, K, N);
+    for (int Nb = 0; Nb < N / (BP * WP); Nb++)
+        for (int n = 0; n < WP; n++) {
+            auto v = out.read();
+            for (int i = 0; i < BP; i++) y[i * (N / BP) + Nb * WP + n] = v[i];
+        }
+    return 0;
+}
+
+// ---- Softmax.h:261 dec_Softmax<float, 4, 64, true, true> as hmt_attn_softmax instantiates it -------------------------------
+REF_API int ref_softmax_dec4_64(const float* x, float scale, float* p) {
+    constexpr int BP = 4, DIM = 64;
+    tapa::stream<hls::vector<float, BP>> in, out;
+    for (int k = 0; k < DIM / BP; k++) {
+        hls::vector<float, BP> v;
+        for (int i = 0; i < BP; i++) v[i] = x[i * (DIM / BP) + k];
+        in.write(v);
+    }
+    dec_Softmax<float, BP, DIM, true, true>(in, out, DIM, scale);
+    for (int k = 0; k < DIM / BP; k++) {
+        auto v = out.read();
+        for (int i = 0; i < BP; i++) p[i * (DIM / BP) + k] = v[i];
+    }
+    return 0;
+}
+

@@ -246,3 +246,21 @@ def test_asymmetric_4bit_linear_path_matches_reference_templates():
     # the reference bench's own tolerance check against the fake-quant product (rel 1e-2, Linear_Layer_Prefilling_tb.cpp:281)
     fq = (q.astype(np.float32) * s[:, None] + b[:, None]) @ ws.T
     assert np.abs(y - fq).max() <= 1e-2 * np.abs(fq).max()
+
+
+def test_hmt_fp32_primitives_match_reference_templates():
+    """The HMT cross-attention's linear unit (dec_Linear_Layer_fp32xfp32, Linear_Layer.h:1040; four interleaved chains,
+    PE.h:655-756) and its softmax (dec_Softmax<float, 4, 64, scale, sub-max>, Softmax.h:261) against the restatement."""
+    R = oracle.ref
+    if R is None:
+        pytest.skip("reference templates not built")
+    g = np.random.default_rng(7)
+    for N, K in [(2048, 2048), (64, 2048), (2048, 64)]:
+        x = g.standard_normal(K).astype(np.float32); w = g.standard_normal((N, K)).astype(np.float32)
+        assert np.array_equal(oracle.linear_fp32_chain4(x, w).view(np.uint32), R.linear_fp32(x, w).view(np.uint32))
+    for trial in range(4):
+        x = (g.standard_normal(64) * 40).astype(np.float32)
+        x[16 * trial:] = 0                                      # empty memory slots score exactly 0
+        with oracle.exp_mode(oracle.EXP_LIBM):                  # the template calls the C library's expf
+            p = oracle.softmax_dec(x, 4, 45.2548339959)
+        assert np.array_equal(p.view(np.uint32), R.softmax_dec4_64(x, 45.2548339959).view(np.uint32))
