@@ -12,6 +12,18 @@ inline int dec_Linear_Layer_i8xi8(const int8_t* a, const float* input_s, const i
                                   float* y, int tokens, int output_dim, int input_dim, stream_t st = nullptr) {
     return flexllm_linear_decode_i8(a, input_s, w, weight_s, tokens, output_dim, input_dim, acc, y, st);
 }
+// pref_Linear_Layer_i4xi4<.., is_uint_input = true> (Linear_Layer.h:294) / dec_Linear_Layer_i4xi4 (:863) with the asymmetric
+// dequantiser: a [tokens][K] unsigned (from the asymmetric quantiser), w [N][K] s8; acc is required (int32 [tokens][N])
+inline int pref_Linear_Layer_i4xi4(const uint8_t* a, const float* input_s, const float* input_b, const int8_t* w, const float* weight_s,
+                                   const float* weight_sum, int32_t* acc, float* y, int seq_len, int output_dim, int input_dim,
+                                   stream_t st = nullptr) {
+    return flexllm_linear_prefill_asym(a, input_s, input_b, w, weight_s, weight_sum, seq_len, output_dim, input_dim, acc, y, st);
+}
+inline int dec_Linear_Layer_i4xi4(const uint8_t* a, const float* input_s, const float* input_b, const int8_t* w, const float* weight_s,
+                                  const float* weight_sum, int32_t* acc, float* y, int tokens, int output_dim, int input_dim,
+                                  stream_t st = nullptr) {
+    return flexllm_linear_decode_asym(a, input_s, input_b, w, weight_s, weight_sum, tokens, output_dim, input_dim, acc, y, st);
+}
 // pref_Gate_Layer_fp32xfp32 (Linear_Layer.h:613) / dec_Gate_Layer_fp32xfp32 (:1104)
 inline int pref_Gate_Layer_fp32xfp32(const float* input, const float* gate, float* y, long n, stream_t st = nullptr) {
     return flexllm_gate(input, gate, n, y, st);

@@ -24,6 +24,11 @@ class SpinQuantModel {
         int rc = flexllm_model_begin(h_, n_new, st);
         return rc ? rc : flexllm_model_decode(h_, n_steps, use_graph ? 1 : 0, st);
     }
+    // the same graph fed with embedding vectors [B][S][hidden] (rows from n_valid on are padding)
+    int Prefilling_embeds(const float* embeds, int B, int S, int n_valid, int32_t* next = nullptr, stream_t st = nullptr) {
+        return flexllm_model_prefill_embeds(h_, embeds, B, S, n_valid, next, st);
+    }
+    flexllm_model* handle() const { return h_; }
     // demo flow: host ids in, host ids out
     int generate(const int32_t* tokens_host, int B, int S, int n_new, int32_t* out_host, bool use_graph = true, stream_t st = nullptr) {
         return flexllm_model_generate_host(h_, tokens_host, B, S, n_new, out_host, use_graph ? 1 : 0, st);

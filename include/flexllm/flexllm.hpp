@@ -1,6 +1,7 @@
 // Umbrella header: #include <flexllm/flexllm.hpp>
 #pragma once
 #include "FHT.hpp"
+#include "HMT.hpp"
 #include "LayerNorm.hpp"
 #include "Linear_Layer.hpp"
 #include "Logits.hpp"

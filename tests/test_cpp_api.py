@@ -17,6 +17,10 @@ int main() {
     if (pref_Linear_Layer_i8xi8(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 8, 64, 64) != FLEXLLM_EINVAL) return 3;
     if (dec_Layer_Norm(nullptr, nullptr, nullptr, nullptr, nullptr, 1, 2048) != FLEXLLM_EINVAL) return 4;
     if (MHA_i8xi8_Prefilling_workspace(4, 1024, 32, 8) == 0) return 5;
+    if (pref_quant_layer_fp32_qint_asym(nullptr, nullptr, nullptr, nullptr, 8, 64) != FLEXLLM_EINVAL) return 6;
+    if (pref_Linear_Layer_i4xi4(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 8, 64, 64) != FLEXLLM_EINVAL) return 7;
+    HMT hmt; SpinQuantModel model;
+    if (hmt.Prefilling(nullptr, 16) != FLEXLLM_EINVAL) return 8;
     std::printf("%s\n", status_string(FLEXLLM_EINVAL));
     return 0;
 }
