@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 5): 16 layers, hidden 2048, 32/8 heads, FFN 8192, vocab 128256, tied
+Workload: the full Llama-3.2-1B W8A8 model, 16 layers, hidden 2048, 32/8 heads, FFN 8192, vocab 128256, tied
 embeddings; random-init int8 weights with per-channel scales, synthetic token ids; batch 32,
 prefill 1024 tokens, greedy decode of 256 tokens. One "step" = one such request batch.
 
@@ -11,8 +11,10 @@ prefill 1024 tokens, greedy decode of 256 tokens. One "step" = one such request 
   e2e   : the same request through flexllm_model_generate_host: prompt ids in pinned HOST memory,
           host->device copy, prefill, decode, device->host copy of the generated ids inside the
           timed region
-  N > 1 : one process per GPU, every rank serves its own batch of 32 sequences (batch-parallel
-          request streams, no data-path collective): weak scaling; time = max over ranks.
+  N > 1 : one process per GPU. Default (--parallel tp): ONE batch of 32 sequences on all N GPUs, prefill
+          tensor-parallel, decode batch-parallel after the KV cache has been regrouped by sequence (strong
+          scaling; rank 0 also checks the tokens against a single-GPU run: "tp_tokens_match"). --parallel dp:
+          every rank serves its own batch of 32 (independent replicas, weak scaling). Time = max over ranks.
 
 --impl reference times the reference's own operator templates (oracle/_ref, built from the FlexLLM
 sources through the header shim) on the host cores, on a bounded sample of the same workload.
@@ -193,7 +195,9 @@ def workload_config(world=1, parallel="dp"):
                         ", prefill 1024 + greedy decode 256",
             "global_batch": BATCH if tp else BATCH * world, "prefill_len": PREFILL, "decode_len": NEW, "layers": CFG["layers"],
             "l2": "weights (1.24 GB) and activations exceed the 126 MB L2; no flush needed",
-            "parallelism": (f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + NCCL int32 all-reduce, vocab-parallel lm_head"
+            "parallelism": (f"tp{world}: prefill tensor-parallel (column-parallel q/k/v/gate/up by heads / FFN channels, row-parallel o/down with an "
+                            f"NCCL int32 reduce-scatter of the partial sums, token rows owned per rank in between), then the KV cache regrouped "
+                            f"by sequence and {BATCH // world} sequences decoded per rank (batch-parallel decode streams)"
                             if tp else ("single GPU" if world == 1 else f"dp{world}: batch-parallel replicas, no data-path collective"))}
 
 
@@ -509,6 +513,37 @@ def micro(args):
         def fn():
             it[0] += 1
             return F.dec_Linear_Layer_i8xi8(a, st, ws[it[0] % 5], sc)
+    elif name == "gemv_b1":             # decode linear layer for ONE token (dp4a weight streaming), gate projection, 8 weight sets > L2
+        N, K, B = 8192, 2048, 1
+        ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(8)]
+        a = torch.randint(-127, 128, (B, K), dtype=torch.int8, device=dev); st = torch.rand(B, device=dev); sc = torch.rand(N, device=dev)
+        it = [0]
+        def fn():
+            it[0] += 1
+            return F.dec_Linear_Layer_i8xi8(a, st, ws[it[0] % 8], sc)
+    elif name == "decode_attention":    # one layer of paged decode attention, batch 64, contexts ~ U{512..8192} (about 300 MB of KV pages)
+        import numpy as np
+        B, HQ, HKV, PAGE = 64, 32, 8, 64
+        rng = np.random.default_rng(4)
+        ctx = rng.integers(512, 8193, B).astype(np.int32)
+        pages = (ctx + 1 + PAGE - 1) // PAGE
+        n_pages, max_pages = int(pages.sum()) + 3, int(pages.max())
+        perm = rng.permutation(n_pages).astype(np.int32)
+        pt = np.zeros((B, max_pages), np.int32); o = 0
+        for b in range(B):
+            pt[b, :pages[b]] = perm[o:o + pages[b]]; o += pages[b]
+        cache = F.KVCache(1, n_pages, HKV)
+        kd, ksd, vd, vsd = cache.pools(0)
+        kd.copy_(torch.randint(-127, 128, kd.shape, dtype=torch.int8, device=dev)); vd.copy_(torch.randint(-127, 128, vd.shape, dtype=torch.int8, device=dev))
+        ksd.copy_(torch.rand(ksd.shape, device=dev) * 0.045 + 0.005); vsd.copy_(torch.rand(vsd.shape, device=dev) * 0.045 + 0.005)
+        max_ctx = int(ctx.max()) + 1
+        c, s_ = synthetic.rope_table(max_ctx + 1); c = torch.from_numpy(c).to(dev); s_ = torch.from_numpy(s_).to(dev)
+        q = torch.randint(-127, 128, (B, HQ, 64), dtype=torch.int8, device=dev); k = torch.randint(-127, 128, (B, HKV, 64), dtype=torch.int8, device=dev)
+        v = torch.randint(-127, 128, (B, HKV, 64), dtype=torch.int8, device=dev)
+        qs = torch.rand((B, HQ), device=dev) * 0.045 + 0.005; ks = torch.rand((B, HKV), device=dev) * 0.045 + 0.005; vs = ks.clone()
+        a_s = torch.full((HQ,), 1.0 / 255, device=dev)
+        ptd, ctxd = torch.from_numpy(pt).to(dev), torch.from_numpy(ctx).to(dev)
+        fn = lambda: F.MHA_i8xi8_Decoding(cache, 0, q, qs, k, ks, v, vs, c, s_, a_s, ptd, ctxd, max_ctx)
     elif name == "swiglu_fht":
         gg = torch.randn((4096, 8192), device=dev); uu = torch.randn((4096, 8192), device=dev)
         fn = lambda: F.swiglu_fht_quant(gg, uu)
@@ -648,9 +683,9 @@ def gpu_arm(args):
                 "decode_tokens_per_s": round(nb * (NEW - 1) / r["t_dec"] * 1e3, 1),
                 "decode_hbm_frac_of_measured": round(dec_bytes / (r["t_dec"] / (NEW - 1) / 1e3) / 1e9 / (peaks.get("hbm_gbs") or 6650.0), 4)}
 
-    # N > 1: the headline partition is --parallel (replicas by default: for a 1.2 GB model every
-    # collective only adds latency, so independent batch-parallel replicas are the faster use of N
-    # GPUs); the other partition is measured in the same run and reported beside it
+    # N > 1: the headline partition is --parallel (tensor parallel by default: the partition the workload names;
+    # strong scaling on a fixed batch of 32); the other partition (independent replicas, weak scaling) is measured
+    # in the same run and reported beside it
     use_tp = multi and args.parallel == "tp"
     main_r = measure(use_tp, args.steps)
     other = None
@@ -722,13 +757,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     # profiling aids (the headline workload is the default): shorter decode / skip the side measurements
-    ap.add_argument("--parallel", default="dp", choices=["tp", "dp"],
-                    help="N > 1: headline partition - independent batch-parallel replicas (default) or tensor parallel over "
-                         "the N GPUs with a fixed total batch; the other one is reported under other_partition")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "dp"],
+                    help="N > 1: headline partition - tensor parallel over the N GPUs with a fixed total batch of 32 (default: the "
+                         "partition the workload names), or independent batch-parallel replicas; the other one is reported under "
+                         "other_partition")
     ap.add_argument("--decode-len", type=int, default=NEW)
     ap.add_argument("--no-extras", action="store_true", help="skip roofline kernel timing and the CPU baseline")
     ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, gemm_prefill, "
-                                                  "gemm_prefill_k8192, decode_linear, swiglu_fht, decode_step)")
+                                                  "gemm_prefill_k8192, decode_linear, gemv_b1, decode_attention, swiglu_fht, decode_step)")
     args = ap.parse_args()
     globals()["NEW"] = args.decode_len
     args.warmup = max(args.warmup, 0)

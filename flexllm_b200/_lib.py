@@ -3,7 +3,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libflexllm_b200.so")
+LIB_PATH = os.environ.get("FLEXLLM_B200_LIB") or os.path.join(_HERE, "libflexllm_b200.so")   # the override is a development aid
 
 OK, EINVAL, ECUDA, ETIMEDOUT, ENOTSUP, ENOMEM, ETOOBIG, EDEVDATA, EIO = 0, -1, -2, -3, -4, -5, -6, -7, -8
 

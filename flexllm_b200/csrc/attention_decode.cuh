@@ -423,10 +423,11 @@ __device__ __forceinline__ void mma_s8u8(int (&d)[4], const int (&a)[4], const i
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// round to nearest, halves away from zero (std::round), for the u8 quantiser: t >= 0 in every legitimate call
-// (probabilities, scales and a_s are positive), where floor(t + 0.5) with the sum rounded DOWN is exact
+// round to nearest, halves away from zero (std::round), without a branch: floor(|t| + 0.5) with the sum rounded DOWN is
+// exact (an integer is never crossed upwards), the truncating conversion saturates, and the sign is put back
 __device__ __forceinline__ int round_half_away_to_int(float t) {
-    return t >= 0.0f ? __float2int_rz(__fadd_rd(t, 0.5f)) : (int)roundf(t);
+    const int r = __float2int_rz(__fadd_rd(fabsf(t), 0.5f));
+    return t < 0.0f ? -r : r;
 }
 
 // Returns false when a bounded wait ran out (the same verdict for all NT threads).

@@ -289,9 +289,11 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
                 }
                 tmem_ld_wait();
                 if (sweep == 0) {
+                    // the row maximum is tracked WITHOUT the factor 0.125 (scaling by a power of two is exact and keeps
+                    // the order, so max(x * 0.125) == max(x) * 0.125: applied once after the sweep)
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
-                        float x = (((float)(int)v[i] * qscale) * ksv[i]) * 0.125f;
+                        float x = ((float)(int)v[i] * qscale) * ksv[i];
                         x = (kc + i <= qlim) ? x : -1e32f;                       // causal mask (MHA.h:262-267)
                         mx = x > mx ? x : mx;
                     }
@@ -314,6 +316,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sempty);
+            if (it == n_kt - 1) mx = mx * 0.125f;             // end of sweep 0: the maximum of the scaled scores
         }
         // ---- sweep 2: U = min(round((e * r * vs) / a_s), 255) from the cached e, into shared memory
         const float rinv = 1.0f / ((ps0 + ps1) + (ps2 + ps3));
@@ -347,8 +350,7 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const float p = ee[i] * rinv;
-                        const float t = div_for_rounding(p * vv[i], d_as);
-                        int r = (int)roundf(t);
+                        int r = round_half_away_to_int(div_for_rounding(p * vv[i], d_as));
                         r = r > 255 ? 255 : r;
                         w |= ((uint32_t)r & 0xffu) << (8 * i);
                     }
