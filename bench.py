@@ -491,7 +491,7 @@ def micro(args):
     F.lib()
     name = args.micro
     dev = "cuda"
-    if name == "attn_prefill":          # BASELINE config 3: B=4, S=1024, 32/8 heads
+    if name == "attn_prefill":          # the prefill-attention workload: B=4, S=1024, 32/8 heads
         B, S, HQ, HKV = 4, 1024, 32, 8
         g = torch.Generator(device=dev).manual_seed(0)
         r8 = lambda *sh: torch.randint(-127, 128, sh, dtype=torch.int8, device=dev, generator=g)

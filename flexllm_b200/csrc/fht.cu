@@ -32,23 +32,34 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
     const long row = blockIdx.x;
     const float4* xr = reinterpret_cast<const float4*>(x + row * ld_in);   // ld_in: input row stride in floats
     const float4* ur = FUSED ? reinterpret_cast<const float4*>(u + row * ld_in) : nullptr;
+    // two batches of four 16-byte vectors per operand: all loads of a batch are issued before the first value is used
+    // (SiLU's exponential is long enough to keep the next loads from being hoisted over it otherwise)
 #pragma unroll
-    for (int it = 0; it < N / 1024; it++) {
-        const int c = it * 256 + tid;
-        float4 v;
-        if (FUSED == 2) {
-            const int segw = N / win.g, e = c * 4, seg = e / segw;
-            v = *reinterpret_cast<const float4*>(x + ((long)seg * win.rows + row) * segw + (e - seg * segw));
-        } else {
-            v = xr[c];
+    for (int half = 0; half < N / 1024; half += 4) {
+        float4 vv[4], ww[4];
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int c = (half + it) * 256 + tid;
+            if (FUSED == 2) {
+                const int segw = N / win.g, e = c * 4, seg = e / segw;
+                vv[it] = *reinterpret_cast<const float4*>(x + ((long)seg * win.rows + row) * segw + (e - seg * segw));
+            } else {
+                vv[it] = xr[c];
+            }
+            if (FUSED == 1) ww[it] = ur[c];
         }
-        if (FUSED == 1) {
-            float4 w = ur[c];
-            v.x = silu_f(v.x) * w.x; v.y = silu_f(v.y) * w.y; v.z = silu_f(v.z) * w.z; v.w = silu_f(v.w) * w.w;
-            if (act) reinterpret_cast<float4*>(act + row * N)[c] = v;
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int c = (half + it) * 256 + tid;
+            float4 v = vv[it];
+            if (FUSED == 1) {
+                const float4 w = ww[it];
+                v.x = silu_f(v.x) * w.x; v.y = silu_f(v.y) * w.y; v.z = silu_f(v.z) * w.z; v.w = silu_f(v.w) * w.w;
+                if (act) reinterpret_cast<float4*>(act + row * N)[c] = v;
+            }
+            const int p = pad32(c * 4);
+            buf[p] = v.x; buf[p + 1] = v.y; buf[p + 2] = v.z; buf[p + 3] = v.w;
         }
-        const int p = pad32(c * 4);
-        buf[p] = v.x; buf[p + 1] = v.y; buf[p + 2] = v.z; buf[p + 3] = v.w;
     }
     float r[32];
     fht8192_passes<0>(buf, tid, r);

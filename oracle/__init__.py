@@ -1,6 +1,6 @@
 """ctypes bindings for the CPU oracle.
 
-TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke()`` and by the CPU
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the repository's smoke check and by the CPU
 baseline / reference arm of ``bench.py``. The product package (``flexllm_b200``) never imports it.
 
 Two libraries:

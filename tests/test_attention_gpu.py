@@ -1,4 +1,4 @@
-"""GPU parity of the int8 attention kernels against the CPU oracle (BASELINE configs 3 and 4 at
+"""GPU parity of the int8 attention kernels against the CPU oracle (the prefill-attention and paged decode-attention workloads at
 sizes the oracle finishes in seconds, plus edge cases)."""
 import numpy as np
 import pytest
@@ -68,7 +68,7 @@ def test_prefill_small(F, B, S, HQ, HKV):
 
 
 def test_prefill_config3_slice(F):
-    """BASELINE config 3 shapes (S=1024, 32/8 heads) on one batch element."""
+    """The prefill-attention workload's shapes (S=1024, 32/8 heads) on one batch element."""
     check_prefill(F, 1, 1024, 32, 8, 31)
 
 
@@ -147,7 +147,7 @@ def test_decode_page_boundaries(F):
 
 
 def test_decode_config4_slice(F):
-    """BASELINE config 4 shapes: contexts drawn uniformly from [512, 8192], one layer, 8 sequences."""
+    """The decode-attention workload's shapes: contexts drawn uniformly from [512, 8192], one layer, 8 sequences."""
     g = np.random.default_rng(42)
     decode_case(F, 8, g.integers(512, 8193, 8), seed=42)
 

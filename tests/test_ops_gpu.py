@@ -241,7 +241,7 @@ def test_linear_decode_gemv(F, M, N, K):
     assert_same(to_np(acc), acc_o, "acc"); assert_same(to_np(y), y_o, "y")
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 2048, 2048),      # BASELINE config 1
+@pytest.mark.parametrize("M,N,K", [(128, 2048, 2048),      # the single prefill linear layer of the reference's own bench
                                    (128, 256, 128), (256, 512, 256), (100, 264, 144), (1, 16, 16), (300, 2048, 8192),
                                    (130, 128, 2048), (64, 64, 512), (17, 40, 1040)])
 def test_linear_prefill_tcgen05(F, M, N, K):

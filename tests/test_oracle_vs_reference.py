@@ -173,7 +173,7 @@ def test_argmax_ties():
 
 
 def test_attention_row_composition():
-    """The build-specific composition (per-token scales folded as described in DESIGN.md) is made of
+    """The build-specific composition (per-token value scales folded into P before its quantisation) is made of
     reference operators only: check each stage of one row against them."""
     g = rng(13)
     nk = 37
