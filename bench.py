@@ -455,9 +455,9 @@ def unit_configs(F, torch, peaks, with_cpu=True):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch: ncu capture at context 131..136
-# (1.358 GB read + 0.107 GB written, profiles/decode_mega_kernel_batch32_ctx131.md) plus the KV pages the
+# (1.358 GB read + 0.117 GB written, profiles/decode_mega_kernel_batch32_ctx131.md) plus the KV pages the
 # bench's mean context of 1152 adds (16 layers x 1088 B x 32 sequences x 1019 tokens; KV traffic is proportional)
-DRAM_TRAFFIC_PER_LAUNCH = int(1.358e9 + 0.107e9 + 16 * 1088 * 32 * 1019)
+DRAM_TRAFFIC_PER_LAUNCH = int(1.358e9 + 0.117e9 + 16 * 1088 * 32 * 1019)
 
 
 def prefill_ops(nb):
@@ -471,15 +471,16 @@ def prefill_ops(nb):
     return lin + att + 2.0 * nb * V * D
 
 
-def decode_step_bytes():
+def decode_step_bytes(batch=None):
     """Algorithmic bytes one decode step has to read: every int8 weight once (layers + lm_head), the
     scales, and the int8 KV pages of all layers for the step's context lengths (K and V rows of 64
-    bytes per KV head plus two fp32 scales per head: 1088 bytes per cached token and layer)."""
+    bytes per KV head plus two fp32 scales per head: 1088 bytes per cached token and layer).
+    batch: sequences the launch decodes (default: the whole batch)."""
     D, F, V, L = CFG["hidden"], CFG["ffn"], CFG["vocab"], CFG["layers"]
     qkv = (CFG["heads_q"] + 2 * CFG["heads_kv"]) * 64
     weights = L * (qkv * D + D * D + 2 * F * D + D * F) + V * D
     scales = 4 * (L * (qkv + D + 2 * F + D + 2 * D) + V + D)
-    kv = L * 1088 * BATCH * (PREFILL + NEW / 2)
+    kv = L * 1088 * (BATCH if batch is None else batch) * (PREFILL + NEW / 2)
     return weights + scales + kv
 
 
@@ -676,7 +677,7 @@ def gpu_arm(args):
         return r
 
     def phases(r, nb):
-        dec_bytes = decode_step_bytes()
+        dec_bytes = decode_step_bytes(nb // world if nb % world == 0 else None)      # one rank's sequences against one GPU's bandwidth
         return {"prefill_ms": round(r["t_pre"], 3), "prefill_tokens_per_s": round(nb * PREFILL / r["t_pre"] * 1e3, 1),
                 "prefill_tops": round(prefill_ops(nb) / r["t_pre"] / 1e9, 1),
                 "decode_ms_per_step": round(r["t_dec"] / (NEW - 1), 4),
@@ -687,7 +688,21 @@ def gpu_arm(args):
     # strong scaling on a fixed batch of 32); the other partition (independent replicas, weak scaling) is measured
     # in the same run and reported beside it
     use_tp = multi and args.parallel == "tp"
-    main_r = measure(use_tp, args.steps)
+    tp_error = None
+    if use_tp:
+        # if the partitioned run fails on any rank, all ranks fall back to independent replicas (and the line says so)
+        try:
+            main_r = measure(True, args.steps)
+        except Exception as e:
+            main_r, tp_error = None, f"{type(e).__name__}: {e}"
+        ok = torch.tensor([0.0 if main_r is None else 1.0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() != 1.0:
+            use_tp = False
+            tp_error = tp_error or "failed on another rank"
+            main_r = measure(False, args.steps)
+    else:
+        main_r = measure(False, args.steps)
     other = None
     if multi and not args.no_extras:
         other = {"parallelism": workload_config(world, "dp" if use_tp else "tp")["parallelism"],
@@ -708,10 +723,21 @@ def gpu_arm(args):
         # time); its duration is the CUDA-event time of the decode loop / launches, measured above
         hbm_peak = peaks.get("hbm_gbs") or 6650.0
         step_ms = main_r["t_dec"] / (NEW - 1)
-        nbytes = decode_step_bytes()
-        roof = {"bound": "hbm", "kernel": "decode_mega_kernel (whole decode step, batch 32, context 1024..1279)" if not use_tp
-                else "decode step (tensor-parallel kernel sequence)", "achieved": round(nbytes / step_ms / 1e6, 1), "peak": hbm_peak, "unit": "GB/s",
-                "frac": round(nbytes / step_ms / 1e6 / hbm_peak, 4), "traffic": DRAM_TRAFFIC_PER_LAUNCH,
+        rows_mode = use_tp and BATCH % world == 0 and os.environ.get("FLEXLLM_TP_MODE", "") != "allgather"
+        if not use_tp:
+            kname = "decode_mega_kernel (whole decode step, batch 32, context 1024..1279)"
+            nbytes, traffic = decode_step_bytes(), DRAM_TRAFFIC_PER_LAUNCH
+        elif rows_mode:
+            # after the tensor-parallel prefill every rank decodes its own BATCH / N sequences with the full (replicated)
+            # weights: one persistent launch per rank and step; bytes, time and peak are ONE GPU's
+            kname = f"decode_mega_kernel (one rank's launch: {BATCH // world} of the 32 sequences, replicated weights, context 1024..1279)"
+            nbytes = decode_step_bytes(BATCH // world)
+            traffic = int(1.358e9 + 0.117e9 + 16 * 1088 * (BATCH // world) * 1019)
+        else:
+            kname = "decode step (tensor-parallel kernel sequence; bytes of the whole step over all ranks / N)"
+            nbytes, traffic = decode_step_bytes() / world, None
+        roof = {"bound": "hbm", "kernel": kname, "achieved": round(nbytes / step_ms / 1e6, 1), "peak": hbm_peak, "unit": "GB/s",
+                "frac": round(nbytes / step_ms / 1e6 / hbm_peak, 4), "traffic": traffic,
                 "algorithmic_bytes_per_launch": int(nbytes), "us_per_launch": round(step_ms * 1e3, 1),
                 "peak_source": "measured (MEASURED_PEAKS.json)" if peaks.get("hbm_gbs") else "fallback"}
         units = None
@@ -731,13 +757,15 @@ def gpu_arm(args):
         line = {"metric": METRIC, "value": round(r["value"], 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(r["ms_dev"] / args.steps, 3), "higher_is_better": True,
                 "scaling": "strong" if use_tp else "weak",
-                "vs_baseline": None, "dtype": "s8", "data": "synthetic", "config": workload_config(world, args.parallel),
+                "vs_baseline": None, "dtype": "s8", "data": "synthetic", "config": workload_config(world, "tp" if use_tp else "dp"),
                 "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": BATCH * PREFILL * 4,
                         "d2h_bytes_per_step": BATCH * NEW * 4, "ms_per_step": round(r["ms_e2e"] / args.steps, 3)},
                 "gpu_launches": int(r["launches"]), "clocks": r["clocks"], "roofline": roof, "cpu_baseline": cpu,
                 "phases": phases(r, nb)}
         if "tp_tokens_match" in r:
             line["tp_tokens_match"] = r["tp_tokens_match"]
+        if tp_error is not None:
+            line["tensor_parallel_failed"] = tp_error
         if other is not None:
             line["other_partition"] = other
         if units is not None:

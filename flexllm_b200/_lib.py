@@ -52,6 +52,8 @@ SIGNATURES = {
     "flexllm_mha_i8xi8_decode": [_P, _I] + [_P] * 10 + [_I, _P, _I, _I, _I, _P, _P, _P, _SZ, _P],
     "flexllm_tp_unique_id": [_P, C.c_char_p],
     "flexllm_tp_init": [_P, _I, _I, _P, C.c_char_p],
+    "flexllm_tp_init_local": [_P, _I],
+    "flexllm_tp_is_local": [_P],
     "flexllm_tp_destroy": [_P],
     "flexllm_tp_rank": [_P],
     "flexllm_tp_size": [_P],

@@ -751,7 +751,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             stg.cap_pages = half_bytes / 4096 < 20 ? half_bytes / 4096 : 20;
             stg.abort_flag = abort_flag;
             if (is_tma) prefetch_weights_l2(mega_job(a, l, 1));
-            for (int idx = 2 * cta + half; idx < a.B * a.HKV; idx += 2 * G) {
+            // items spread over the CTAs first (item i on CTA i mod G): with fewer items than CTAs every item has an SM to itself
+            for (int idx = cta + half * G; idx < a.B * a.HKV; idx += 2 * G) {
                 const int b = idx / a.HKV;
                 const int pos = dec_guarded_pos(a.ctx, b, a.max_ctx, a.error_flag);
                 if (pos / PAGE + 1 <= stg.cap_pages) {

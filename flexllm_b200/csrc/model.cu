@@ -663,6 +663,7 @@ extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph
     FLEXLLM_REQUIRE(n_steps == 0 || (long)m->pos + n_steps - 1 <= (long)m->cfg.max_ctx);
     m->pos += n_steps;
     cudaStream_t st = (cudaStream_t)stream;
+    if (flexllm_tp_is_local(m->tp)) use_graph = 0;      // ranks sharing a device: the collectives need their host-side rendezvous
     int done = 0;
     if (use_graph && n_steps > 0 && (!m->graph || m->graph_B != m->B)) {
         // the first step runs eagerly so that every lazily created resource (function attributes,

@@ -412,6 +412,19 @@ class TensorParallel:
         idbuf = (C.c_ubyte * 128).from_buffer_copy(unique_id)
         _check("flexllm_tp_init", lib().flexllm_tp_init(C.byref(self._h), rank, size, idbuf, build.nccl_library().encode()))
 
+    @classmethod
+    def local_group(cls, size):
+        """`size` communicators whose ranks share the current GPU (one host thread per rank, one stream): the
+        partitioned model of any rank count on a single device, for checking its arithmetic."""
+        hs = (C.c_void_p * size)()
+        _check("flexllm_tp_init_local", lib().flexllm_tp_init_local(hs, size))
+        group = []
+        for r in range(size):
+            t = cls.__new__(cls)
+            t.rank, t.size, t._h = r, size, C.c_void_p(hs[r])
+            group.append(t)
+        return group
+
     def close(self):
         if self._h:
             lib().flexllm_tp_destroy(self._h)

@@ -234,6 +234,13 @@ FLEXLLM_API int flexllm_mha_i8xi8_decode(flexllm_kv_cache* c, int layer, const i
 typedef struct flexllm_tp flexllm_tp;
 FLEXLLM_API int flexllm_tp_unique_id(unsigned char* id128, const char* nccl_lib_path);   /* rank 0; share the 128 bytes */
 FLEXLLM_API int flexllm_tp_init(flexllm_tp** out, int rank, int size, const unsigned char* id128, const char* nccl_lib_path);
+/* `size` (<= 8) communicators whose ranks SHARE the current device: each is driven by its own host thread of this
+ * process, all ranks issue their work to one stream, and a collective is a rendezvous of those threads around device
+ * copies in that stream (no NCCL). It runs the partitioned model of any rank count on a single GPU, for checking the
+ * partition's arithmetic where fewer GPUs than ranks are at hand; it is not a way to go faster. Its collectives cannot
+ * be captured into a CUDA graph (FLEXLLM_ENOTSUP); the model runner ignores use_graph on such a group. out[size]. */
+FLEXLLM_API int flexllm_tp_init_local(flexllm_tp** out, int size);
+FLEXLLM_API int flexllm_tp_is_local(const flexllm_tp* t);      /* 1 for a communicator made by flexllm_tp_init_local */
 FLEXLLM_API int flexllm_tp_destroy(flexllm_tp* t);
 FLEXLLM_API int flexllm_tp_rank(const flexllm_tp* t);
 FLEXLLM_API int flexllm_tp_size(const flexllm_tp* t);

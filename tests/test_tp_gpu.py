@@ -72,3 +72,60 @@ def test_tp_matches_oracle(world, cfg, mode):
         assert ret[f"status{rank}"] == 0
         assert np.array_equal(ret[f"tokens{rank}"], ref["tokens"]), f"rank {rank}: tokens differ"
     assert np.array_equal(ret["hidden"].view(np.uint32), ref["hidden"].view(np.uint32))
+
+
+def _shared_device_rank(tp, cfg, W, tokens, ret):
+    import flexllm_b200 as F
+    from flexllm_b200 import synthetic
+    layers, hidden, hq, hkv, vocab, B, S, n_new, seed = cfg
+    try:
+        torch.cuda.set_device(0)
+        m = F.Model(layers, hidden, hq, hkv, 8192, vocab, max_batch=B, max_prefill=S, max_ctx=S + n_new, tp=tp)
+        synthetic.load_numpy_weights(m, W)
+        ret[f"tokens{tp.rank}"] = m.generate_host(torch.from_numpy(tokens), n_new, use_graph=True).numpy().copy()
+        m.prefill(torch.from_numpy(tokens).cuda())
+        hidden_gpu = m.buffer(0, (B * S, hidden), torch.float32).cpu().numpy()      # a collective on the token-row partition
+        if tp.rank == 0:
+            ret["hidden"] = hidden_gpu
+        m.close()
+    except Exception as e:       # reported by the parent; the other ranks' rendezvous give up by themselves
+        ret[f"error{tp.rank}"] = repr(e)
+
+
+@pytest.mark.parametrize("world,cfg,mode", [
+    (2, (2, 1024, 16, 4, 2000, 12, 48, 4, 61), None),
+    (4, (2, 1024, 16, 4, 2016, 8, 32, 4, 64), None),
+    (8, (1, 2048, 32, 8, 2048, 8, 32, 3, 63), None),            # one KV head, four query heads, 1024 FFN channels, one sequence per rank
+    (8, (2, 2048, 32, 8, 2048, 16, 64, 3, 65), None),           # two sequences per rank, two layers
+    (8, (1, 2048, 32, 8, 2048, 8, 32, 3, 63), "allgather"),
+])
+def test_tp_ranks_sharing_one_gpu_match_oracle(world, cfg, mode, monkeypatch):
+    """The same partitioned dataflow with all ranks on ONE GPU (a host thread per rank, collectives as device copies in
+    one stream): every rank count up to 8 is checked on any box."""
+    import threading
+    import oracle
+    import flexllm_b200 as F
+    from flexllm_b200 import synthetic
+    if mode:
+        monkeypatch.setenv("FLEXLLM_TP_MODE", mode)
+    else:
+        monkeypatch.delenv("FLEXLLM_TP_MODE", raising=False)
+    layers, hidden, hq, hkv, vocab, B, S, n_new, seed = cfg
+    W = synthetic.numpy_weights(layers, hidden, hq, hkv, 8192, vocab, S + n_new, seed=seed)
+    tokens = np.random.default_rng(seed + 1).integers(0, vocab, (B, S)).astype(np.int32)
+    group = F.TensorParallel.local_group(world)
+    ret = {}
+    threads = [threading.Thread(target=_shared_device_rank, args=(tp, cfg, W, tokens, ret)) for tp in group]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for tp in group:
+        tp.close()
+    assert not [k for k in ret if k.startswith("error")], {k: v for k, v in ret.items() if k.startswith("error")}
+    assert F.lib().flexllm_device_status() == 0
+    with oracle.exp_mode(oracle.EXP_CORRECTLY_ROUNDED):
+        ref = oracle.model_generate(W, tokens, n_new, want_hidden=True)
+    for rank in range(world):
+        assert np.array_equal(ret[f"tokens{rank}"], ref["tokens"]), f"rank {rank}: tokens differ"
+    assert np.array_equal(ret["hidden"].view(np.uint32), ref["hidden"].view(np.uint32))
