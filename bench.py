@@ -492,7 +492,7 @@ def micro(args):
     F.lib()
     name = args.micro
     dev = "cuda"
-    if name == "attn_prefill":          # the prefill-attention workload: B=4, S=1024, 32/8 heads
+    if name in ("attn_prefill", "attn_prefill_online"):          # the prefill-attention workload: B=4, S=1024, 32/8 heads
         B, S, HQ, HKV = 4, 1024, 32, 8
         g = torch.Generator(device=dev).manual_seed(0)
         r8 = lambda *sh: torch.randint(-127, 128, sh, dtype=torch.int8, device=dev, generator=g)
@@ -500,7 +500,8 @@ def micro(args):
         q, k, v, qs, ks, vs = r8(B, S, HQ, 64), r8(B, S, HKV, 64), r8(B, S, HKV, 64), rs(B, S, HQ), rs(B, S, HKV), rs(B, S, HKV)
         c, s_ = synthetic.rope_table(S); c = torch.from_numpy(c).to(dev); s_ = torch.from_numpy(s_).to(dev)
         a_s = torch.full((HQ,), 0.05 / 255, device=dev)
-        fn = lambda: F.MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, c, s_, a_s)
+        fn = (lambda: F.MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, c, s_, a_s)) if name == "attn_prefill" else \
+             (lambda: F.MHA_i8xi8_Prefilling_online(q, qs, k, ks, v, vs, c, s_))      # single-sweep variant, not bit-exact
     elif name in ("gemm_prefill", "gemm_prefill_k8192"):
         M, N, K = (8192, 8192, 2048) if name == "gemm_prefill" else (8192, 2048, 8192)
         a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev); w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
@@ -791,7 +792,7 @@ def main():
                          "other_partition")
     ap.add_argument("--decode-len", type=int, default=NEW)
     ap.add_argument("--no-extras", action="store_true", help="skip roofline kernel timing and the CPU baseline")
-    ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, gemm_prefill, "
+    ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, attn_prefill_online, gemm_prefill, "
                                                   "gemm_prefill_k8192, decode_linear, gemv_b1, decode_attention, swiglu_fht, decode_step)")
     args = ap.parse_args()
     globals()["NEW"] = args.decode_len

@@ -43,6 +43,7 @@ SIGNATURES = {
     "flexllm_qk_prepare": [_P, _P, _P, _P, _P, _L, _I, _P, _P, _P],
     "flexllm_mha_prefill_workspace": [_I, _I, _I, _I],
     "flexllm_mha_i8xi8_prefill": [_P] * 9 + [_I, _I, _I, _I, _P, _P, _P, _SZ, _P],
+    "flexllm_mha_i8xi8_prefill_online": [_P] * 8 + [_I, _I, _I, _I, _P, _P, _SZ, _P],
     "flexllm_kv_cache_create": [_P, _I, _I, _I, _I],
     "flexllm_kv_cache_destroy": [_P],
     "flexllm_kv_cache_reset": [_P, _P],

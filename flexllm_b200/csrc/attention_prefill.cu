@@ -23,6 +23,8 @@
 // order. One CTA = 128 queries of one (batch, query head) against 64-key tiles; 4 softmax warps +
 // TMA warp + MMA warp; TMEM: S (64 columns) + O (64 columns) = 128 columns, so four CTAs share an SM
 // and their 16 softmax warps hide each other's latencies.
+#include <cstdlib>
+
 #include "attention_decode.cuh"     // layout of the paged KV cache
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -403,6 +405,305 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
     if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, ATT_TMEM_COLS); }
 }
 
+
+// ------------------------------------------------------------------ single-sweep variant (not bit-exact)
+// The same attention with a flash-style online softmax: ONE sweep over the key tiles, a running row maximum and
+// denominator, fast exponentials (ex2.approx), P quantised per key tile to u8 against that tile's largest value scale,
+// P.V on the tensor core per tile, and the running output rescaled in fp32 registers. It does NOT reproduce the
+// reference's arithmetic (which quantises the final normalised P against a static scale and accumulates a whole row in
+// int32): it exists to measure what that exactness costs, is off by default, and is checked to fp32 tolerance only.
+//   per tile j:  x = S * (qs * 0.125 * log2 e) * ks[k];  m' = max(m, max_k x);  alpha = 2^(m - m')
+//                c_j = 255 / max_k vs[k];  pc = 2^(x - m') * c_j;  U = rint(pc * vs[k]) (<= 255);  l = l * alpha + sum(pc) / c_j
+//                O_j = U . V (tensor core, int32);  o = o * alpha + O_j / c_j
+//   out = o / l
+// TMEM: S and O double-buffered (4 x 64 columns): the MMA warp runs one key tile ahead of the softmax warps.
+constexpr int ATO_TMEM_COLS = 256;
+constexpr int ATO_SLOTS = 6;
+constexpr int ATO_SMEM = ATT_Q_BYTES + ATO_SLOTS * ATT_TILE_BYTES + 2 * ATT_P_BYTES + 1024 + 256;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(192, 2) attn_prefill_online_kernel(const __grid_constant__ CUtensorMap tmapQ,
+                                                                     const __grid_constant__ CUtensorMap tmapK,
+                                                                     const __grid_constant__ CUtensorMap tmapV,
+                                                                     const AttnArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t sQ = base;
+    const uint32_t sT = sQ + ATT_Q_BYTES;
+    const uint32_t sP = sT + ATO_SLOTS * ATT_TILE_BYTES;
+    uint8_t* sP_ptr = base_ptr + ATT_Q_BYTES + ATO_SLOTS * ATT_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP_ptr + 2 * ATT_P_BYTES);
+    // barriers: q_full, t_full[6], t_empty[6], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2]
+    const uint32_t bar_qfull = smem_u32(bars);
+    const uint32_t bar_tfull = bar_qfull + 8;
+    const uint32_t bar_tempty = bar_tfull + 8 * ATO_SLOTS;
+    const uint32_t bar_sfull = bar_tempty + 8 * ATO_SLOTS;
+    const uint32_t bar_sempty = bar_sfull + 16;
+    const uint32_t bar_pfull = bar_sempty + 16;
+    const uint32_t bar_pempty = bar_pfull + 16;
+    const uint32_t bar_ofull = bar_pempty + 16;
+    const uint32_t bar_oempty = bar_ofull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 2 * ATO_SLOTS + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = args.q_off + args.Sq;
+    const int n_qt = (args.Sq + 127) >> 7;
+    const int qt_l = n_qt - 1 - (int)(blockIdx.x % n_qt);
+    const int qt0 = args.q_off >> 7, qt = qt0 + qt_l;
+    const int hq = (int)((blockIdx.x / n_qt) % args.HQ);
+    const int b = (int)(blockIdx.x / ((long)n_qt * args.HQ));
+    const int hkv = hq / (args.HQ / args.HKV);
+    const int n_kt_all = (S + ATT_KT - 1) / ATT_KT;
+    const int n_kt = 2 * (qt + 1) < n_kt_all ? 2 * (qt + 1) : n_kt_all;
+    const bool paged = args.page_table != nullptr;
+    const int32_t* pt = paged ? args.page_table + (long)b * args.max_pages : nullptr;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_qfull, 1);
+        for (int i = 0; i < ATO_SLOTS; i++) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 1); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(bar_sfull + 8 * i, 1); mbar_init(bar_sempty + 8 * i, 4);
+            mbar_init(bar_pfull + 8 * i, 4); mbar_init(bar_pempty + 8 * i, 1);
+            mbar_init(bar_ofull + 8 * i, 1); mbar_init(bar_oempty + 8 * i, 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 5) { tmem_alloc(smem_u32(tmem_slot), ATO_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer: K_0, then K_{j+1}, V_j for every tile j
+        if (lane == 0) {
+            tma_prefetch_desc(&tmapQ); tma_prefetch_desc(&tmapK); tma_prefetch_desc(&tmapV);
+            mbar_expect_tx(bar_qfull, ATT_Q_BYTES);
+            tma_load_2d(sQ, &tmapQ, bar_qfull, 0, ((b * args.HQ + hq) * args.Sq) + qt_l * 128);
+            int slot = 0; uint32_t phase = 0;
+            auto load = [&](bool is_k, int j) {
+                if (!mbar_wait(bar_tempty + 8 * slot, phase ^ 1u, abort_flag)) return false;
+                const uint32_t full = bar_tfull + 8 * slot;
+                const uint32_t dst = sT + slot * ATT_TILE_BYTES;
+                mbar_expect_tx(full, ATT_TILE_BYTES);
+                if (paged) tma_load_2d(dst, is_k ? &tmapK : &tmapV, full, 0, (__ldg(pt + j) * args.HKV + hkv) * 64);
+                else if (is_k) tma_load_2d(dst, &tmapK, full, 0, ((b * args.HKV + hkv) * args.Sk) + j * ATT_KT);
+                else tma_load_2d(dst, &tmapV, full, j * ATT_KT, (b * args.HKV + hkv) * 64);
+                if (++slot == ATO_SLOTS) { slot = 0; phase ^= 1u; }
+                return true;
+            };
+            bool ok = load(true, 0);
+            for (int j = 0; ok && j < n_kt; j++) {
+                if (j + 1 < n_kt) ok = load(true, j + 1);
+                if (ok) ok = load(false, j);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer: Q.K^T one tile ahead of U.V
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_i8(128, ATT_KT, 1, 1);
+            constexpr uint32_t idesc_pv = umma_idesc_i8(128, 64, 0, 1);
+            bool ok = mbar_wait(bar_qfull, 0, abort_flag);
+            const uint64_t qdesc = umma_desc_k_sw64(sQ);
+            int slot = 0; uint32_t tphase = 0;
+            auto next_tile = [&](uint32_t& sTile) {       // waits for the next ring slot in load order
+                if (!mbar_wait(bar_tfull + 8 * slot, tphase, abort_flag)) return false;
+                sTile = sT + slot * ATT_TILE_BYTES;
+                return true;
+            };
+            auto release_tile = [&]() {
+                umma_commit(bar_tempty + 8 * slot);
+                if (++slot == ATO_SLOTS) { slot = 0; tphase ^= 1u; }
+            };
+            auto issue_qk = [&](int j) {
+                uint32_t sTile;
+                const int sb = j & 1;
+                if (!next_tile(sTile)) return false;
+                if (!mbar_wait(bar_sempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag)) return false;
+                tc_fence_after();
+                const uint64_t kdesc = umma_desc_k_sw64(sTile);
+                umma_i8(tmem_base + sb * 64, qdesc, kdesc, idesc_qk, 0u);
+                umma_i8(tmem_base + sb * 64, qdesc + 2, kdesc + 2, idesc_qk, 1u);
+                umma_commit(bar_sfull + 8 * sb);
+                release_tile();
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; ok && j < n_kt; j++) {
+                if (j + 1 < n_kt && !issue_qk(j + 1)) { ok = false; break; }
+                const int pb = j & 1;
+                uint32_t sTile;
+                if (!next_tile(sTile)) { ok = false; break; }
+                if (!mbar_wait(bar_pfull + 8 * pb, (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar_oempty + 8 * pb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t pdesc = umma_desc_k_sw64(sP + pb * ATT_P_BYTES);
+                const uint64_t vdesc = umma_desc_k_sw64(sTile);
+                umma_i8(tmem_base + 128 + pb * 64, pdesc, vdesc, idesc_pv, 0u);
+                umma_i8(tmem_base + 128 + pb * 64, pdesc + 2, vdesc + 2, idesc_pv, 1u);
+                umma_commit(bar_ofull + 8 * pb);
+                umma_commit(bar_pempty + 8 * pb);
+                release_tile();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps 0..3: one query row per thread
+        const int row_in_tile = warp * 32 + lane;
+        const int qpos = qt * 128 + row_in_tile;
+        const bool q_ok = qpos < S;
+        const int qlim = q_ok ? qpos : -1;
+        const float qsl = q_ok ? args.qs[((long)b * args.HQ + hq) * args.Sq + (qpos - args.q_off)] * (0.125f * 1.4426950408889634f) : 0.0f;
+        const float* ksp = args.ks + ((long)b * args.HKV + hkv) * args.Sk;
+        const float* vsp = args.vs + ((long)b * args.HKV + hkv) * args.Sk;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        float m = -1e30f, l = 0.0f;
+        float o[64];
+#pragma unroll
+        for (int i = 0; i < 64; i++) o[i] = 0.0f;
+        float alpha_prev = 1.0f, f_prev = 0.0f;
+        bool ok = true;
+        auto wait_bar = [&](uint32_t bar, uint32_t parity) {
+            int got = (lane == 0) ? (mbar_wait(bar, parity, abort_flag) ? 1 : 0) : 1;
+            return __shfl_sync(0xffffffffu, got, 0) != 0;
+        };
+        auto fold_o = [&](int jj) {        // o = o * alpha + O_jj * f, O_jj from its TMEM buffer
+            const int ob = jj & 1;
+            if (!wait_bar(bar_ofull + 8 * ob, (uint32_t)((jj >> 1) & 1))) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[16];
+                tmem_ld_32x16(tmem_base + 128 + ob * 64 + lane_addr + c * 16, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; i++) o[c * 16 + i] = __fmaf_rn(o[c * 16 + i], alpha_prev, (float)(int)v[i] * f_prev);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_oempty + 8 * ob);
+            return true;
+        };
+        for (int j = 0; ok && j < n_kt; j++) {
+            const int sb = j & 1;
+            const int k0 = j * ATT_KT;
+            const float* kst = paged ? args.ks + ((long)__ldg(pt + j) * args.HKV + hkv) * 64 : ksp + k0;
+            const float* vst = paged ? args.vs + ((long)__ldg(pt + j) * args.HKV + hkv) * 64 : vsp + k0;
+            // this tile's largest value scale (keys beyond the sequence count as 0)
+            float vmax = fmaxf(k0 + lane < S ? vst[lane] : 0.0f, k0 + 32 + lane < S ? vst[32 + lane] : 0.0f);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+            vmax = fmaxf(vmax, 1e-30f);
+            const float cj = 255.0f / vmax, lcj = lg2_approx(cj), fj = vmax * (1.0f / 255.0f);
+            const bool diag = k0 + ATT_KT - 1 > qt * 128;          // tile may hold keys beyond some row's own position
+            if (!wait_bar(bar_sfull + 8 * sb, (uint32_t)((j >> 1) & 1))) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tS = tmem_base + sb * 64 + lane_addr;
+            // pass 1: the tile's row maximum
+            float tmax = -1e30f;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[16];
+                tmem_ld_32x16(tS + c * 16, v);
+                float ksv[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    const float4 t = (k0 + c * 16 + i < S) ? *reinterpret_cast<const float4*>(kst + c * 16 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    ksv[i] = t.x; ksv[i + 1] = t.y; ksv[i + 2] = t.z; ksv[i + 3] = t.w;
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    float x = ((float)(int)v[i] * qsl) * ksv[i];
+                    if (diag) x = (k0 + c * 16 + i <= qlim) ? x : -1e30f;
+                    tmax = fmaxf(tmax, x);
+                }
+            }
+            const float m_new = fmaxf(m, tmax);
+            const float alpha = ex2_approx(m - m_new);
+            const float mref = m_new - lcj;                        // 2^(x - mref) = 2^(x - m_new) * c_j
+            if (!wait_bar(bar_pempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u)) { ok = false; break; }
+            // pass 2: pc, its sum, U into shared memory
+            uint8_t* prow = sP_ptr + sb * ATT_P_BYTES + row_in_tile * 64;
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[16];
+                tmem_ld_32x16(tS + c * 16, v);
+                float ksv[16], vsv[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    const bool in = k0 + c * 16 + i < S;
+                    const float4 t = in ? *reinterpret_cast<const float4*>(kst + c * 16 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 u = in ? *reinterpret_cast<const float4*>(vst + c * 16 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    ksv[i] = t.x; ksv[i + 1] = t.y; ksv[i + 2] = t.z; ksv[i + 3] = t.w;
+                    vsv[i] = u.x; vsv[i + 1] = u.y; vsv[i + 2] = u.z; vsv[i + 3] = u.w;
+                }
+                tmem_ld_wait();
+                uint32_t packed[4];
+#pragma unroll
+                for (int i4 = 0; i4 < 4; i4++) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int ii = i4 * 4 + i;
+                        const float x = ((float)(int)v[ii] * qsl) * ksv[ii];
+                        float pc = ex2_approx(x - mref);
+                        if (diag) pc = (k0 + c * 16 + ii <= qlim) ? pc : 0.0f;
+                        sum += pc;
+                        uint32_t r = __float2uint_rn(pc * vsv[ii]);
+                        r = r > 255u ? 255u : r;
+                        w |= r << (8 * i);
+                    }
+                    packed[i4] = w;
+                }
+                const int chunk = c ^ ((row_in_tile >> 1) & 3);
+                *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(bar_pfull + 8 * sb); mbar_arrive(bar_sempty + 8 * sb); }
+            l = __fmaf_rn(l, alpha, sum * fj);
+            m = m_new;
+            // the previous tile's U.V has had this tile's softmax to finish: fold it in now
+            if (j > 0 && !fold_o(j - 1)) { ok = false; break; }
+            alpha_prev = alpha; f_prev = fj;
+        }
+        if (ok) ok = fold_o(n_kt - 1);
+        if (ok && q_ok) {
+            const float rl = 1.0f / l;
+            const long ob = (((long)b * args.Sq + (qpos - args.q_off)) * args.HQ + hq) * 64;
+#pragma unroll
+            for (int i = 0; i < 64; i += 4)
+                *reinterpret_cast<float4*>(args.out + ob + i) = make_float4(o[i] * rl, o[i + 1] * rl, o[i + 2] * rl, o[i + 3] * rl);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+        if (threadIdx.x == 0 && args.error_flag) atomicOr(args.error_flag, 1);
+        __syncthreads();
+    }
+    if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, ATO_TMEM_COLS); }
+}
+
 int* device_error_flag();
 
 // fp32 front end used by the model: qkv [B*Sq][(HQ+2*HKV)*64] fp32 as the fused q/k/v projection writes it, tokens at
@@ -533,7 +834,7 @@ struct PagedWs {
 // a: everything but the error flag filled in. k_rows / v_rows: rows of the [rows][64 B] (K; paged V^T) or
 // [rows][v_row_bytes] (contiguous V^T) matrices the tensor maps describe.
 static int mha_prefill_core(AttnArgs a, const int8_t* q2, const int8_t* kmat, uint64_t k_rows, const int8_t* vmat, uint64_t v_rows,
-                            uint64_t v_row_bytes, cudaStream_t st) {
+                            uint64_t v_row_bytes, cudaStream_t st, bool online = false) {
     CUtensorMap tq, tk, tv;
     int rc = make_tmap_2d_u8_box(&tq, q2, (uint64_t)a.B * a.HQ * a.Sq, 64, 64, 128, 64);
     if (rc != FLEXLLM_OK) return rc;
@@ -551,6 +852,15 @@ static int mha_prefill_core(AttnArgs a, const int8_t* q2, const int8_t* kmat, ui
     }
     const int n_qt = (a.Sq + 127) / 128;
     const long grid = (long)a.B * a.HQ * n_qt;
+    if (online) {
+        static std::atomic<bool> attr_set_online[kMaxDevices];
+        if (!attr_set_online[dev].load(std::memory_order_acquire)) {
+            FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_online_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATO_SMEM));
+            attr_set_online[dev].store(true, std::memory_order_release);
+        }
+        attn_prefill_online_kernel<<<(unsigned)grid, 192, ATO_SMEM, st>>>(tq, tk, tv, a);
+        return launch_status();
+    }
     attn_prefill_kernel<<<(unsigned)grid, 192, ATT_SMEM, st>>>(tq, tk, tv, a);
     return launch_status();
 }
@@ -594,7 +904,9 @@ int mha_prefill_paged(const float* qkv, const float* cos_t, const float* sin_t, 
     a.qs = ws.qs2; a.ks = ks_pool; a.vs = vs_pool; a.page_table = page_table; a.max_pages = max_pages;
     a.a_s = a_s; a.out = out; a.oacc = nullptr; a.ecache = ws.ecache;
     const uint64_t rows = (uint64_t)c->n_pages * HKV * 64;
-    return mha_prefill_core(a, ws.q2, k_pool, rows, v_pool, rows, 64, st);
+    // FLEXLLM_ATTN_ONLINE=1: the single-sweep variant (not bit-exact) in the model's prefill, for measuring what exactness costs
+    static const bool online = [] { const char* e = getenv("FLEXLLM_ATTN_ONLINE"); return e && e[0] == '1'; }();
+    return mha_prefill_core(a, ws.q2, k_pool, rows, v_pool, rows, 64, st, online);
 }
 
 }  // namespace flexllm
@@ -606,7 +918,7 @@ extern "C" size_t flexllm_mha_prefill_workspace(int B, int S, int HQ, int HKV) {
     return PrefillWs::bytes(B, S, HQ, HKV);
 }
 
-extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+static int mha_prefill_contiguous(bool online, const int8_t* q, const float* qs, const int8_t* k, const float* ks,
                                          const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
                                          const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
                                          void* workspace, size_t workspace_bytes, void* stream) {
@@ -629,5 +941,21 @@ extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const
     a.B = B; a.HQ = HQ; a.HKV = HKV; a.Sq = S; a.q_off = 0; a.Sk = S;
     a.qs = ws.qs2; a.ks = ws.ks2; a.vs = ws.vsT; a.page_table = nullptr; a.max_pages = 0;
     a.a_s = a_s; a.out = out; a.oacc = oacc; a.ecache = ws.ecache;
-    return mha_prefill_core(a, ws.q2, ws.k2, (uint64_t)B * HKV * S, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, st);
+    return mha_prefill_core(a, ws.q2, ws.k2, (uint64_t)B * HKV * S, ws.vT, (uint64_t)B * HKV * 64, (uint64_t)S, st, online);
+}
+
+extern "C" int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                                         const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
+                                         const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
+                                         void* workspace, size_t workspace_bytes, void* stream) {
+    return mha_prefill_contiguous(false, q, qs, k, ks, v, vs, cos_t, sin_t, a_s, B, S, HQ, HKV, out, oacc, workspace, workspace_bytes, stream);
+}
+
+extern "C" int flexllm_mha_i8xi8_prefill_online(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                                                const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
+                                                int B, int S, int HQ, int HKV, float* out, void* workspace, size_t workspace_bytes,
+                                                void* stream) {
+    static const float unused_scale[1] = {1.0f};
+    return mha_prefill_contiguous(true, q, qs, k, ks, v, vs, cos_t, sin_t, unused_scale, B, S, HQ, HKV, out, nullptr, workspace, workspace_bytes,
+                                  stream);
 }

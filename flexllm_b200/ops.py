@@ -267,6 +267,20 @@ def MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, cos_t, sin_t, a_s, want_oacc=False
     return out, oacc
 
 
+def MHA_i8xi8_Prefilling_online(q, qs, k, ks, v, vs, cos_t, sin_t):
+    """Prefill GQA attention in one sweep with an online softmax: close to, not bit-identical with,
+    MHA_i8xi8_Prefilling (no static P scale). Returns out fp32 [B,S,HQ*64]."""
+    B, S, HQ, D = q.shape
+    HKV = k.shape[2]
+    assert D == 64
+    nbytes = lib().flexllm_mha_prefill_workspace(B, S, HQ, HKV)
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+    out = torch.empty((B, S, HQ * 64), dtype=torch.float32, device=q.device)
+    _call("flexllm_mha_i8xi8_prefill_online", _ptr(q), _ptr(qs), _ptr(k), _ptr(ks), _ptr(v), _ptr(vs), _ptr(cos_t),
+          _ptr(sin_t), B, S, HQ, HKV, _ptr(out), _ptr(ws), nbytes)
+    return out
+
+
 class KVCache:
     """Paged int8 KV cache (library-owned device memory). Pools of one layer are exposed as torch
     views: k [n_pages,HKV,64,64] (token-major rows), v [n_pages,HKV,64 dims,64 tokens] (transposed

@@ -191,6 +191,14 @@ FLEXLLM_API int flexllm_mha_i8xi8_prefill(const int8_t* q, const float* qs, cons
                               const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
                               const float* a_s, int B, int S, int HQ, int HKV, float* out, int32_t* oacc,
                               void* workspace, size_t workspace_bytes, void* stream);
+/* The same attention in ONE sweep over the keys with a flash-style online softmax (running maximum and denominator,
+ * fast exponentials, P quantised per 64-key tile against the tile's largest value scale, output rescaled in fp32).
+ * NOT bit-exact with the reference arithmetic above and not used unless asked for: it exists so that the cost of the
+ * exact three-sweep kernel is a measured number. Agreement with flexllm_mha_i8xi8_prefill: a few times 1e-3 of the
+ * output's largest magnitude. No a_s (P's scale is chosen per tile), no oacc. Same workspace. */
+FLEXLLM_API int flexllm_mha_i8xi8_prefill_online(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                              const int8_t* v, const float* vs, const float* cos_t, const float* sin_t,
+                              int B, int S, int HQ, int HKV, float* out, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Paged int8 KV cache (replaces dec_K_cache_manager / dec_V_cache_manager and their scale caches,

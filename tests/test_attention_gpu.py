@@ -93,6 +93,46 @@ def test_prefill_rows_sum_property(F):
     assert (o[:, 0] == 255).all()
 
 
+def _float_attention(ref, v, vs):
+    """Attention of the prepared int8 Q / K (after RoPE, FHT-64 and re-quantisation) and the int8 V in float64, with no
+    quantisation of P: what both kernels approximate with their 8-bit P."""
+    q2, qs2, k2, ks2 = ref["q2"], ref["qs2"], ref["k2"], ref["ks2"]
+    B, S, HQ, _ = q2.shape; HKV = k2.shape[2]; G = HQ // HKV
+    out = np.empty((B, S, HQ * 64))
+    mask = np.tril(np.ones((S, S), bool))
+    for b in range(B):
+        for h in range(HQ):
+            kv = h // G
+            x = (q2[b, :, h].astype(np.float64) @ k2[b, :, kv].astype(np.float64).T) * qs2[b, :, h, None] * ks2[b, None, :, kv] * 0.125
+            x = np.where(mask, x, -np.inf)
+            p = np.exp(x - x.max(axis=1, keepdims=True)); p /= p.sum(axis=1, keepdims=True)
+            out[b, :, h * 64:(h + 1) * 64] = p @ (v[b, :, kv].astype(np.float64) * vs[b, :, kv, None])
+    return out
+
+
+@pytest.mark.parametrize("B,S,HQ,HKV", [(1, 128, 4, 1), (2, 256, 8, 2), (1, 144, 4, 1), (1, 400, 8, 2), (1, 1024, 32, 8)])
+def test_prefill_online_softmax_variant_is_close(F, B, S, HQ, HKV):
+    """The single-sweep online-softmax variant is NOT bit-exact (it quantises P per key tile against a dynamic scale and
+    uses fast exponentials). Both it and the exact kernel approximate the unquantised-P attention with an 8-bit P; the
+    variant's distance to that float64 attention must stay within 3 % of the largest output (worst element) and 0.3 %
+    (mean) -- the fp32-level tolerance an 8-bit P allows -- and is printed beside the exact kernel's own distance."""
+    q, qs, k, ks, v, vs, a_s = attn_inputs(B, S, HQ, HKV, 33)
+    cos_t, sin_t = oracle.rope_table(max(S, 16))
+    args = [dev(q), dev(qs), dev(k), dev(ks), dev(v), dev(vs), dev(cos_t), dev(sin_t)]
+    exact, _ = F.MHA_i8xi8_Prefilling(*args, dev(a_s))
+    online = F.MHA_i8xi8_Prefilling_online(*args)
+    torch.cuda.synchronize()
+    assert F.lib().flexllm_device_status() == 0
+    exact = to_np(exact); online = to_np(online)
+    assert np.isfinite(online).all()
+    ref = _float_attention(oracle.mha_prefill(q, qs, k, ks, v, vs, cos_t, sin_t, a_s), v, vs)
+    scale = np.abs(ref).max()
+    d_on = np.abs(online - ref) / scale; d_ex = np.abs(exact - ref) / scale
+    print(f"online softmax B={B} S={S}: distance to float64 attention, of the largest output: online max {d_on.max():.2e} mean "
+          f"{d_on.mean():.2e}; exact kernel max {d_ex.max():.2e} mean {d_ex.mean():.2e}")
+    assert d_on.max() < 3e-2 and d_on.mean() < 3e-3
+
+
 # ------------------------------------------------------------------------------ decode (config 4)
 def decode_case(F, B, ctx, HQ=32, HKV=8, seed=40, steps=1):
     g = np.random.default_rng(seed)

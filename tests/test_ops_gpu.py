@@ -233,7 +233,11 @@ def lin_inputs(M, N, K, seed):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (1, 8192, 2048), (1, 2048, 8192), (3, 512, 2048), (8, 64, 128),
-                                   (5, 24, 64)])
+                                   (5, 24, 64),
+                                   # every token-count variant on wide and narrow matrices (whole-K warps and the K split over
+                                   # the four warps of a CTA)
+                                   (2, 16384, 2048), (4, 8192, 2048), (8, 2048, 8192), (7, 3072, 2048), (1, 4104, 1024), (3, 1032, 2048),
+                                   (2, 9000, 640), (8, 16384, 2048), (1, 304, 8192), (6, 2056, 1152)])
 def test_linear_decode_gemv(F, M, N, K):
     a, st, w, sc = lin_inputs(M, N, K, 20)
     acc, y = F.dec_Linear_Layer_i8xi8(dev(a), dev(st), dev(w), dev(sc), want_acc=True)
