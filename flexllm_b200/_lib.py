@@ -42,6 +42,8 @@ SIGNATURES = {
     "flexllm_topk_sample": [_P, _I, _L, _I, _I, _P, _P, _P, _P, _P],
     "flexllm_qk_prepare": [_P, _P, _P, _P, _P, _L, _I, _P, _P, _P],
     "flexllm_mha_prefill_workspace": [_I, _I, _I, _I],
+    "flexllm_mlp_block_workspace": [_I, _I, _I],
+    "flexllm_mlp_block_decode": [_P] * 6 + [_I, _I, _I, _F, _I, _F, _P, _P, _SZ, _P],
     "flexllm_mha_i8xi8_prefill": [_P] * 9 + [_I, _I, _I, _I, _P, _P, _P, _SZ, _P],
     "flexllm_mha_i8xi8_prefill_online": [_P] * 8 + [_I, _I, _I, _I, _P, _P, _SZ, _P],
     "flexllm_kv_cache_create": [_P, _I, _I, _I, _I],
@@ -104,7 +106,7 @@ class LayerWeights(C.Structure):
                                   "gamma0", "gamma1", "a_s")]
 
 RESTYPES = {"flexllm_status_string": C.c_char_p, "flexllm_launch_count": C.c_ulonglong, "flexllm_mha_prefill_workspace": C.c_size_t,
-            "flexllm_mha_decode_workspace": C.c_size_t}
+            "flexllm_mha_decode_workspace": C.c_size_t, "flexllm_mlp_block_workspace": C.c_size_t}
 
 
 def load():

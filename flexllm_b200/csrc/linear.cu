@@ -116,3 +116,41 @@ extern "C" int flexllm_linear_decode_i8_residual(const int8_t* a, const float* s
     FLEXLLM_REQUIRE(residual);
     return linear_decode(a, s_tok, w, s_ch, M, N, K, nullptr, y, residual, stream);
 }
+
+// ---- decode MLP block as one call -----------------------------------------------------------------------------------
+namespace flexllm {
+int swiglu_fht_quant_strided(const float* g, const float* u, long ld, int M, float scale, int8_t* q, float* s, cudaStream_t st);
+static size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
+}  // namespace flexllm
+extern "C" int flexllm_rmsnorm_quant(const float* x, const float* gamma, int M, int D, float eps, int order, float* y, int8_t* q,
+                                     float* s, void* stream);
+
+extern "C" size_t flexllm_mlp_block_workspace(int M, int D, int F) {
+    if (M <= 0 || D <= 0 || F <= 0) return 0;
+    return up256((size_t)M * D) + 2 * up256((size_t)M * 4) + up256((size_t)M * 2 * F * 4) + up256((size_t)M * F) + 256;
+}
+
+// RMSNorm + quant -> fused gate|up projection -> SiLU(gate) * up, FHT-8192, quant -> down projection + residual: the four
+// launches follow one another with programmatic dependent launch, so each kernel's launch and (for the weight-streaming
+// GEMV) first weight loads overlap the tail of the one before.
+extern "C" int flexllm_mlp_block_decode(const float* x, const float* gamma, const int8_t* w_gu, const float* s_gu, const int8_t* w_d,
+                                        const float* s_d, int M, int D, int F, float eps, int order, float fht_scale, float* y,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+    FLEXLLM_REQUIRE(x && gamma && w_gu && s_gu && w_d && s_d && y && M >= 0 && D > 0);
+    if (F != 8192) return FLEXLLM_ENOTSUP;
+    if (M == 0) return FLEXLLM_OK;
+    if (M > 64) return FLEXLLM_ENOTSUP;
+    FLEXLLM_REQUIRE(workspace && workspace_bytes >= flexllm_mlp_block_workspace(M, D, F));
+    uint8_t* w = (uint8_t*)(((uintptr_t)workspace + 255) & ~(uintptr_t)255);
+    int8_t* xq = (int8_t*)w; w += up256((size_t)M * D);
+    float* xs = (float*)w; w += up256((size_t)M * 4);
+    float* hs = (float*)w; w += up256((size_t)M * 4);
+    float* gu = (float*)w; w += up256((size_t)M * 2 * F * 4);
+    int8_t* hq = (int8_t*)w;
+    cudaStream_t st = (cudaStream_t)stream;
+    struct PdlScope { PdlScope() { g_pdl = 1; } ~PdlScope() { g_pdl = 0; } } pdl;
+    TRY_RC(flexllm_rmsnorm_quant(x, gamma, M, D, eps, order, nullptr, xq, xs, st));
+    TRY_RC(linear_decode(xq, xs, w_gu, s_gu, M, 2 * F, D, nullptr, gu, nullptr, st));
+    TRY_RC(swiglu_fht_quant_strided(gu, gu + F, 2L * F, M, fht_scale, hq, hs, st));
+    return linear_decode(hq, hs, w_d, s_d, M, D, F, nullptr, y, x, st);
+}

@@ -267,6 +267,19 @@ def MHA_i8xi8_Prefilling(q, qs, k, ks, v, vs, cos_t, sin_t, a_s, want_oacc=False
     return out, oacc
 
 
+def dec_MLP_block(x, gamma, w_gu, s_gu, w_d, s_d, eps=1e-5, order=8, fht_scale=90.50966799, out=None, workspace=None):
+    """Decode MLP block in one call: RMSNorm + quant -> gate|up -> SiLU * up -> FHT-8192 -> quant -> down + residual.
+    x [M,D] fp32; w_gu [2F,D] int8 (gate rows, then up rows); w_d [D,F]. Returns y [M,D] fp32."""
+    M, D = x.shape
+    Fd = w_d.shape[1]
+    nbytes = lib().flexllm_mlp_block_workspace(M, D, Fd)
+    ws = workspace if workspace is not None else torch.empty((nbytes,), dtype=torch.uint8, device=x.device)
+    y = out if out is not None else torch.empty_like(x)
+    _call("flexllm_mlp_block_decode", _ptr(x), _ptr(gamma), _ptr(w_gu), _ptr(s_gu), _ptr(w_d), _ptr(s_d), M, D, Fd, eps, order,
+          fht_scale, _ptr(y), _ptr(ws), ws.numel())
+    return y
+
+
 def MHA_i8xi8_Prefilling_online(q, qs, k, ks, v, vs, cos_t, sin_t):
     """Prefill GQA attention in one sweep with an online softmax: close to, not bit-identical with,
     MHA_i8xi8_Prefilling (no static P scale). Returns out fp32 [B,S,HQ*64]."""

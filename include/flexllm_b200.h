@@ -177,6 +177,17 @@ FLEXLLM_API int flexllm_topk_sample(const float* logits, int B, long V, int lane
 FLEXLLM_API int flexllm_qk_prepare(const int8_t* q, const float* s, const int32_t* pos, const float* cos_t,
                        const float* sin_t, long T, int H, int8_t* q_out, float* s_out, void* stream);
 
+/* The decode MLP block as one call: the operator sequence of the reference's decode graph for one layer's second half
+ * (SpinQuant_Decoding_mem_opt.h:1090-1126: dec_Layer_Norm + quantiser -> gate and up linear layers + dequantisers ->
+ * Swish and gate -> FHT-8192 -> quantiser -> down linear layer + dequantiser -> residual), for M <= 64 tokens.
+ * x, y [M][D] fp32 (y may alias x); gamma [D]; w_gu [2F][D] int8 = gate rows then up rows, s_gu [2F]; w_d [D][F],
+ * s_d [D]; order = FLEXLLM_NORM_*; F must be 8192. Results are bit-identical to calling the five operators one by one.
+ * workspace: flexllm_mlp_block_workspace(M, D, F) bytes. */
+FLEXLLM_API size_t flexllm_mlp_block_workspace(int M, int D, int F);
+FLEXLLM_API int flexllm_mlp_block_decode(const float* x, const float* gamma, const int8_t* w_gu, const float* s_gu,
+                              const int8_t* w_d, const float* s_d, int M, int D, int F, float eps, int order, float fht_scale,
+                              float* y, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Prefill GQA attention, int8 x int8 (replaces the graph MHA_i8xi8_Prefilling_tb,
  * SpinQuant_Llama_32_1B/MHA_i8xi8.h:369-427, with per-head-per-token scales).

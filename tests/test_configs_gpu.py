@@ -57,6 +57,14 @@ def test_decode_mlp_block(F, B):
     assert_same(to_np(acc), ref["down_acc"], "down projection int32 sums")
     _, out = F.dec_Linear_Layer_i8xi8(hq, hs, dev(wd), dev(sd), residual=hd)
     assert_same(to_np(out), ref["out"], "block output")
+    # the same block as ONE call (fused gate|up weights, dependent launches), twice in a row and in place the second time
+    w_gu = dev(np.concatenate([wg, wu])); s_gu = dev(np.concatenate([sg, su]))
+    y = F.dec_MLP_block(hd, dev(gamma), w_gu, s_gu, dev(wd), dev(sd), order=8)
+    assert_same(to_np(y), ref["out"], "block output, one call")
+    x2 = hd.clone()
+    F.dec_MLP_block(x2, dev(gamma), w_gu, s_gu, dev(wd), dev(sd), order=8, out=x2)
+    assert_same(to_np(x2), ref["out"], "block output, one call, in place")
+    assert F.lib().flexllm_device_status() == 0
 
 
 def test_decode_attention_batch64(F):
