@@ -177,9 +177,11 @@ FLEXLLM_API int flexllm_topk_sample(const float* logits, int B, long V, int lane
 FLEXLLM_API int flexllm_qk_prepare(const int8_t* q, const float* s, const int32_t* pos, const float* cos_t,
                        const float* sin_t, long T, int H, int8_t* q_out, float* s_out, void* stream);
 
-/* The decode MLP block as one call: the operator sequence of the reference's decode graph for one layer's second half
- * (SpinQuant_Decoding_mem_opt.h:1090-1126: dec_Layer_Norm + quantiser -> gate and up linear layers + dequantisers ->
- * Swish and gate -> FHT-8192 -> quantiser -> down linear layer + dequantiser -> residual), for M <= 64 tokens.
+/* The decode MLP block as one call: the FFN passes of the reference's decode graph (SpinQuant_Decoding_mem_opt.h: the
+ * shared dec_Layer_Norm_012 :1061, dec_quant_layer_qkvo_FFN :1066, dec_Linear_Layer_i4xi4_qkvo_FFN_half :1078-1079 and
+ * dec_dequant_layer_qkvo_FFN :1082 on their gate / up / down turns, dec_Swish_Layer_FFN, dec_Gate_layer_FFN and dec_FHT_R4
+ * :1115-1117, dec_residual_layer :1111): RMSNorm + quantiser -> gate and up linear layers + dequantisers -> Swish and
+ * gate -> FHT-8192 -> quantiser -> down linear layer + dequantiser -> residual, for M <= 64 tokens.
  * x, y [M][D] fp32 (y may alias x); gamma [D]; w_gu [2F][D] int8 = gate rows then up rows, s_gu [2F]; w_d [D][F],
  * s_d [D]; order = FLEXLLM_NORM_*; F must be 8192. Results are bit-identical to calling the five operators one by one.
  * workspace: flexllm_mlp_block_workspace(M, D, F) bytes. */
