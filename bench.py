@@ -562,6 +562,15 @@ def micro(args):
     elif name == "swiglu_fht":
         gg = torch.randn((4096, 8192), device=dev); uu = torch.randn((4096, 8192), device=dev)
         fn = lambda: F.swiglu_fht_quant(gg, uu)
+    elif name == "rmsnorm_prefill":     # RMSNorm (prefill summation order) + per-token quantiser on 32768 x 2048 fp32 rows (268 MB)
+        x = torch.randn((32768, 2048), device=dev); gam = torch.ones(2048, device=dev)
+        fn = lambda: F.pref_Layer_Norm(x, gam, quant=True, want_y=False)
+    elif name == "prefill_small":       # a 2-layer model's prefill of 8 x 1024 tokens: every prefill kernel at its model shapes, < 2 GB
+        cfg2 = dict(CFG); cfg2["layers"] = 2
+        m = F.Model(max_batch=8, max_prefill=1024, max_ctx=1040, **cfg2)
+        synthetic.load_random_weights(m, max_ctx=1040, seed=0, **cfg2)
+        tok = torch.randint(0, CFG["vocab"], (8, 1024), dtype=torch.int32).cuda()
+        fn = lambda: m.prefill(tok)
     elif name == "decode_step":         # whole-model decode steps (one persistent kernel each) at a short context: small enough for ncu
         S, n = 128, 6
         m = F.Model(max_batch=BATCH, max_prefill=S, max_ctx=S + 16, **CFG)
@@ -755,7 +764,7 @@ def gpu_arm(args):
                 "algorithmic_bytes_per_launch": int(nbytes), "us_per_launch": round(step_ms * 1e3, 1),
                 "peak_source": "measured (MEASURED_PEAKS.json)" if peaks.get("hbm_gbs") else "fallback"}
         units = None
-        if not args.no_extras:
+        if not args.no_extras and not multi:      # the operator-level configurations and the CPU baseline belong to the one-GPU line
             roof["standalone_linear"] = kernel_roofline(F, torch, peaks)
             try:
                 units = unit_configs(F, torch, peaks)
@@ -806,7 +815,7 @@ def main():
     ap.add_argument("--decode-len", type=int, default=NEW)
     ap.add_argument("--no-extras", action="store_true", help="skip roofline kernel timing and the CPU baseline")
     ap.add_argument("--micro", default=None, help="run one kernel on a small case and exit (attn_prefill, attn_prefill_online, gemm_prefill, "
-                                                  "gemm_prefill_k8192, decode_linear, gemv_b1, decode_attention, swiglu_fht, decode_step)")
+                                                  "gemm_prefill_k8192, decode_linear, gemv_b1, decode_attention, swiglu_fht, rmsnorm_prefill, prefill_small, decode_step)")
     args = ap.parse_args()
     globals()["NEW"] = args.decode_len
     args.warmup = max(args.warmup, 0)
