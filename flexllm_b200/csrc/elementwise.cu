@@ -1,6 +1,8 @@
 // Row-wise and elementwise operators of the quantized Llama path: per-token quantisation, dequant,
 // static quantisation, RMSNorm(+quant), SiLU, gate, residual, RoPE, softmax, greedy argmax.
 // All are HBM-bound: one pass over the data with 128-bit accesses where the layout allows.
+#include <atomic>
+
 #include "common.cuh"
 #include "rmsnorm_core.cuh"
 
@@ -144,8 +146,8 @@ __global__ void static_quant_kernel(const float* __restrict__ x, long rows, int 
 //                                  added from 0 in chunk order.
 // A chain is a strictly sequential fp32 accumulation, so one thread owns it. To keep all 32 lanes
 // busy a warp runs 32 chains at once: in the prefill order the 4 chains of 8 different rows, in the
-// decode order the (up to) 32 chains of one row. Rows are staged through shared memory in 128-float
-// pieces with coalesced 128-bit loads; the output pass re-reads the row (an L1/L2 hit).
+// decode order the (up to) 32 chains of one row. The rows sit in shared memory (prefill) or in
+// registers (decode) between the sum and the output pass: each is read from global memory once.
 // ---------------------------------------------------------------------------------------------
 constexpr int RMS_WARPS = 4;
 constexpr int RMS_PIECE = 128;           // floats per row per staging step
@@ -187,49 +189,76 @@ __device__ __forceinline__ void rmsnorm_output_row(const float* __restrict__ xr,
     }
 }
 
-// Prefill order: each warp takes 8 consecutive rows. Requires D % 128 == 0.
-template <int MAXV>
-__global__ void __launch_bounds__(RMS_WARPS * 32) rmsnorm_prefill_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+// Prefill order: a CTA of 8 warps takes 8 consecutive rows. All threads bring the rows into shared memory (coalesced
+// 128-bit loads, all in flight at once); warp 0 then runs the 32 chains (4 per row) over them; afterwards every warp
+// normalises and quantises one row straight from shared memory -- each row is read from global memory once. Row stride
+// D + 4 floats: the 32 chains' reads (row rr, element 4k + j) fall into 32 different banks. Requires D % 128 == 0.
+constexpr int RMSP_ROWS = 8;
+__global__ void __launch_bounds__(RMSP_ROWS * 32) rmsnorm_prefill_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                          int M, int D, float eps, float* __restrict__ y,
                                                                          int8_t* __restrict__ q, float* __restrict__ s) {
-    __shared__ __align__(16) float stage[RMS_WARPS][8][RMS_PSTRIDE];
+    extern __shared__ __align__(16) float rows_sm[];          // [8][D + 4], then rinv[8]
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long row0 = ((long)blockIdx.x * RMS_WARPS + w) * 8;
-    if (row0 >= M) return;
-    const int rr = lane >> 2, j = lane & 3;      // chain (row rr of the group, residue j)
-    float ss = 0.0f;
-    // the next piece's loads are in flight while the chains run over the current one
-    float4 nxt[8];
-    auto fetch = [&](int p) {
-#pragma unroll
-        for (int r = 0; r < 8; r++) {
-            nxt[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row0 + r < M) nxt[r] = *reinterpret_cast<const float4*>(x + (row0 + r) * D + p + lane * 4);
-        }
-    };
-    fetch(0);
-    for (int p = 0; p < D; p += RMS_PIECE) {
-#pragma unroll
-        for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(&stage[w][r][lane * 4]) = nxt[r];
-        __syncwarp();
-        if (p + RMS_PIECE < D) fetch(p + RMS_PIECE);
-#pragma unroll
-        for (int k = 0; k < RMS_PIECE / 4; k++) { const float v = stage[w][rr][4 * k + j]; ss += v * v; }
-        __syncwarp();
+    const int ld = D + 4, nv = D >> 2;
+    const long row0 = (long)blockIdx.x * RMSP_ROWS;
+    float* rinv_sm = rows_sm + RMSP_ROWS * ld;
+    {   // warp w brings in row w
+        const bool in = row0 + w < M;
+        const float4* src = reinterpret_cast<const float4*>(x + (row0 + w) * D);
+        float4* dst = reinterpret_cast<float4*>(rows_sm + w * ld);
+        for (int c = lane; c < nv; c += 32) dst[c] = in ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // (p0+p1)+(p2+p3) inside each group of four lanes
-    const int base = lane & ~3;
-    const float p0 = __shfl_sync(0xffffffffu, ss, base), p1 = __shfl_sync(0xffffffffu, ss, base + 1);
-    const float p2 = __shfl_sync(0xffffffffu, ss, base + 2), p3 = __shfl_sync(0xffffffffu, ss, base + 3);
-    const float tot = (p0 + p1) + (p2 + p3);
-    const float rinv = 1.0f / sqrtf(tot / (float)D + eps);
-#pragma unroll 1
-    for (int r = 0; r < 8; r++) {
-        const float rr_inv = __shfl_sync(0xffffffffu, rinv, r * 4);
-        const long row = row0 + r;
-        if (row < M)
-            rmsnorm_output_row<MAXV>(x + row * D, gamma, D, rr_inv, y ? y + row * D : nullptr, q ? q + row * D : nullptr,
-                                     s ? s + row : nullptr, lane);
+    __syncthreads();
+    if (w == 0) {
+        const int rr = lane >> 2, j = lane & 3;      // chain (row rr, residue j)
+        const float* src = rows_sm + rr * ld + j;
+        float ss = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < nv; k++) { const float v = src[4 * k]; ss += v * v; }
+        // (p0+p1)+(p2+p3) inside each group of four lanes
+        const int base = lane & ~3;
+        const float p0 = __shfl_sync(0xffffffffu, ss, base), p1 = __shfl_sync(0xffffffffu, ss, base + 1);
+        const float p2 = __shfl_sync(0xffffffffu, ss, base + 2), p3 = __shfl_sync(0xffffffffu, ss, base + 3);
+        const float tot = (p0 + p1) + (p2 + p3);
+        if (j == 0) rinv_sm[rr] = 1.0f / sqrtf(tot / (float)D + eps);
+    }
+    __syncthreads();
+    const long row = row0 + w;
+    if (row >= M) return;
+    const float r = rinv_sm[w];
+    const float4* xr = reinterpret_cast<const float4*>(rows_sm + w * ld);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    float4* yr = y ? reinterpret_cast<float4*>(y + row * D) : nullptr;
+    // first pass: the normalised row's largest magnitude (max(|max|, |min|) of the row = max of |.|), fp32 output if asked for;
+    // second pass: the same products again (same bits) and the quantiser -- nothing of the row is held in registers
+    float amax = 0.0f;
+#pragma unroll 4
+    for (int c = lane; c < nv; c += 32) {
+        const float4 v = xr[c], g = g4[c];
+        float4 o;
+        o.x = (v.x * r) * g.x; o.y = (v.y * r) * g.y; o.z = (v.z * r) * g.z; o.w = (v.w * r) * g.w;
+        if (yr) yr[c] = o;
+        amax = fmaxf(fmaxf(amax, fabsf(o.x)), fmaxf(fabsf(o.y), fmaxf(fabsf(o.z), fabsf(o.w))));
+    }
+    if (q) {
+        amax = warp_max(amax);
+        float sc = amax / 127.0f;
+        if (sc == 0.0f) sc = 1.0f;
+        const DivBy dsc = div_by(sc);       // one reciprocal per row: every element is then quantised without a full division
+        if (lane == 0) s[row] = sc;
+        char4* qr = reinterpret_cast<char4*>(q + row * D);
+        auto q8 = [&](float t) {            // round half away from zero of the correctly rounded quotient; |quotient| <= 127
+            const float qt = div_for_rounding(t, dsc);
+            const int m = __float2int_rz(__fadd_rd(fabsf(qt), 0.5f));
+            return (int8_t)(qt < 0.0f ? -m : m);
+        };
+#pragma unroll 4
+        for (int c = lane; c < nv; c += 32) {
+            const float4 v = xr[c], g = g4[c];
+            char4 v4;
+            v4.x = q8((v.x * r) * g.x); v4.y = q8((v.y * r) * g.y); v4.z = q8((v.z * r) * g.z); v4.w = q8((v.w * r) * g.w);
+            qr[c] = v4;
+        }
     }
 }
 
@@ -483,9 +512,19 @@ extern "C" int flexllm_rmsnorm_quant(const float* x, const float* gamma, int M, 
     cudaStream_t st = (cudaStream_t)stream;
     if (order == 0) {
         if (D % RMS_PIECE != 0) return FLEXLLM_ENOTSUP;
-        const int grid = (M + RMS_WARPS * 8 - 1) / (RMS_WARPS * 8);
-        if (D <= 2048) rmsnorm_prefill_kernel<16><<<grid, RMS_WARPS * 32, 0, st>>>(x, gamma, M, D, eps, y, q, s);
-        else rmsnorm_prefill_kernel<32><<<grid, RMS_WARPS * 32, 0, st>>>(x, gamma, M, D, eps, y, q, s);
+        const int grid = (M + RMSP_ROWS - 1) / RMSP_ROWS;
+        const size_t smem = ((size_t)RMSP_ROWS * (D + 4) + RMSP_ROWS) * sizeof(float);
+        static std::atomic<int> attr_done[kMaxDevices];
+        const int dev = current_device();
+        if (dev < 0) return FLEXLLM_ECUDA;
+        if (!attr_done[dev].load(std::memory_order_acquire)) {
+            FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    (int)(((size_t)RMSP_ROWS * (4096 + 4) + RMSP_ROWS) * sizeof(float))));
+            // three 66 KB CTAs per SM need the largest shared-memory carve-out
+            FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm_prefill_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+            attr_done[dev].store(1, std::memory_order_release);
+        }
+        rmsnorm_prefill_kernel<<<grid, RMSP_ROWS * 32, smem, st>>>(x, gamma, M, D, eps, y, q, s);
     } else {
         const int grid = (M + RMS_WARPS - 1) / RMS_WARPS;
         const size_t smem = (size_t)RMS_WARPS * (D + 4 * order) * sizeof(float);
