@@ -481,7 +481,7 @@ __device__ __forceinline__ bool dec_attn_staged_body(const DecAttnIn& in, const 
     }
     for (int i = tid; i < npages; i += NT) pt_sm[i] = page_table[(long)b * max_pages + i];
     // K scales of this thread's keys (tid + u * NT) into registers; the new token's own scale comes from its preparation
-    constexpr int UK = 5;                                             // 5 * 256 keys = the staging capacity
+    constexpr int UK = 5;                                             // 5 * NT keys >= the staging capacity (20 / 32 pages)
     float ks_pre[UK];
 #pragma unroll
     for (int u = 0; u < UK; u++) {
@@ -705,13 +705,14 @@ __device__ __forceinline__ bool dec_attn_staged_body(const DecAttnIn& in, const 
     if (!sm.last) return false;
     ATT_TS(7);
     // ---- G. P.V on the tensor cores: A = 16 dims x 32 keys of the V^T page, B = 32 keys x the 4 heads' u8 probabilities.
-    //         Warp w: dims 16 (w & 3) .. +15, pages (w >> 2), (w >> 2) + 2, ...; the two partial sums per dim block are
+    //         Warp w: dims 16 (w & 3) .. +15, pages (w >> 2), (w >> 2) + NT / 128, ...; the partial sums per dim block are
     //         added through shared memory (integers: exact)
     {
-        static_assert(NT == 256, "eight warps: four dim blocks x two page sets");
+        constexpr int NPS = NT / 128;                     // page sets: 2 (eight warps) or 4 (sixteen warps)
+        static_assert(NT == 256 || NT == 512, "four dim blocks x NT / 128 page sets");
         const int dblk = w & 3, pset = w >> 2;
         int d[4] = {0, 0, 0, 0};
-        for (int p = pset; p < npages; p += 2) {
+        for (int p = pset; p < npages; p += NPS) {
             const uint8_t* rows = st.kv + (size_t)p * 4096 + (size_t)(dblk * 16 + gi) * PAGE + ti * 4;
             const uint8_t* ucol = u_sm + (gi & 3) * cs + p * PAGE + ti * 4;
 #pragma unroll
@@ -727,18 +728,23 @@ __device__ __forceinline__ bool dec_attn_staged_body(const DecAttnIn& in, const 
             }
         }
         ATT_TS(8);
-        int* pv_sm = reinterpret_cast<int*>(sc);          // the exponentials are no longer needed: [G][64] sums of page set 1
+        // the exponentials and the u8 rows are no longer needed: [NPS - 1][G][64] sums of page sets 1 .. NPS - 1 (at most
+        // 3 KB of the item's scratch, which holds at least 4 KB)
+        int* pv_sm = reinterpret_cast<int*>(dsm);
         named_sync_id<NT>(bar);
-        if (pset == 1 && ti < 2) {
-            pv_sm[(2 * ti) * 64 + dblk * 16 + gi] = d[0]; pv_sm[(2 * ti + 1) * 64 + dblk * 16 + gi] = d[1];
-            pv_sm[(2 * ti) * 64 + dblk * 16 + gi + 8] = d[2]; pv_sm[(2 * ti + 1) * 64 + dblk * 16 + gi + 8] = d[3];
+        if (pset > 0 && ti < 2) {
+            int* dst = pv_sm + (pset - 1) * (G * 64);
+            dst[(2 * ti) * 64 + dblk * 16 + gi] = d[0]; dst[(2 * ti + 1) * 64 + dblk * 16 + gi] = d[1];
+            dst[(2 * ti) * 64 + dblk * 16 + gi + 8] = d[2]; dst[(2 * ti + 1) * 64 + dblk * 16 + gi + 8] = d[3];
         }
         named_sync_id<NT>(bar);
         if (pset == 0 && ti < 2) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int hd = 2 * ti + (i & 1), dim = dblk * 16 + gi + (i >> 1) * 8;
-                const int tot = d[i] + pv_sm[hd * 64 + dim];
+                int tot = d[i];
+#pragma unroll
+                for (int ps = 0; ps < NPS - 1; ps++) tot += pv_sm[ps * (G * 64) + hd * 64 + dim];
                 const int hq = hkv * G + hd;
                 out[((long)b * HQ + hq) * 64 + dim] = (float)tot * a_s[hq];
             }

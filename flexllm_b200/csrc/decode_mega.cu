@@ -751,7 +751,35 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             stg.cap_pages = half_bytes / 4096 < 20 ? half_bytes / 4096 : 20;
             stg.abort_flag = abort_flag;
             if (is_tma) prefetch_weights_l2(mega_job(a, l, 1));
-            // items spread over the CTAs first (item i on CTA i mod G): with fewer items than CTAs every item has an SM to itself
+            if (a.B * a.HKV <= G) {
+                // no more items than CTAs: one item per CTA, worked on by all 512 threads (an item is a chain of dependent
+                // stages; twice the threads shorten the stages that scale -- scores, exponentials, quantiser, P.V)
+                if (cta < a.B * a.HKV) {
+                    const int b = cta / a.HKV;
+                    const int pos = dec_guarded_pos(a.ctx, b, a.max_ctx, a.error_flag);
+                    uint8_t* dsm1 = scratch;
+                    DecAttnSmem& sm1 = *reinterpret_cast<DecAttnSmem*>(dsm1 + a.attn_bytes - sizeof(DecAttnSmem));
+                    DecAttnStage st1;
+                    st1.kv = ring_ptr; st1.bar_k = bar_att; st1.bar_v = bar_att + 8;
+                    const int ring_pages = (STAGES * STAGE_BYTES) / 4096;
+                    st1.cap_pages = ring_pages < 40 ? ring_pages : 40;
+                    st1.abort_flag = abort_flag;
+                    bool ok1 = true;
+                    if (pos / PAGE + 1 <= st1.cap_pages) {
+                        st1.parity = att_uses & 1u;
+                        att_uses++;
+                        ok1 = dec_attn_staged_body<512>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.HQ, a.HKV, a.cs, a.att,
+                                                        cta % a.HKV, b, pos, dsm1, sm1, st1, tid, MG_BAR_WORK);
+                    } else
+                        dec_attn_fused_body<2, 512>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
+                                                    a.att, nullptr, cta % a.HKV, b, dsm1, sm1, tid, MG_BAR_WORK);
+                    if (ok1) {
+                        named_sync<MG_BAR_WORK, MG_WORKERS>();
+                        if (tid < 256) mega_att_row_quant(a, b, sm1, tid, MG_BAR_HALF0);
+                    }
+                }
+            } else
+            // items spread over the CTAs first (item i on CTA i mod G)
             for (int idx = cta + half * G; idx < a.B * a.HKV; idx += 2 * G) {
                 const int b = idx / a.HKV;
                 const int pos = dec_guarded_pos(a.ctx, b, a.max_ctx, a.error_flag);
