@@ -717,48 +717,56 @@ __global__ void __launch_bounds__(256) attn_qkv_prepare_f32_kernel(const float* 
                                                                    int8_t* __restrict__ k_pool, float* __restrict__ ks_pool,
                                                                    const int32_t* __restrict__ page_table, int max_pages,
                                                                    int8_t* __restrict__ v2, float* __restrict__ vs2) {
-    const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
+    // one CTA per token, its eight warps share the token's heads: the token's indices, rotation factors and cache row
+    // are worked out once, not per head
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = HQ + 2 * HKV;
-    if (w >= (long)B * Sq * heads) return;
-    const int h = (int)(w % heads);
-    const long bt = w / heads;
+    const long bt = blockIdx.x;
     const int t = (int)(bt % Sq);
     const int b = (int)(bt / Sq);
     const int pos = q_off + t;
-    const float* src = qkv + bt * (long)heads * 64 + (long)h * 64;
-    const float x0 = src[lane], x1 = src[lane + 32];
-    float a, bb;
-    const bool rotate = h < HQ + HKV;
-    if (rotate) {
-        const float c = cos_t[(long)pos * 32 + lane], sn = sin_t[(long)pos * 32 + lane];
-        a = x0 * c - x1 * sn;
-        bb = x0 * sn + x1 * c;
-        auto lane_stage = [&](int bit) {
-            float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
-            float pb = __shfl_xor_sync(0xffffffffu, bb, 1 << bit);
-            if (lane & (1 << bit)) { a = pa - a; bb = pb - bb; }
-            else { a = a + pa; bb = bb + pb; }
+    const float c = cos_t[(long)pos * 32 + lane], sn = sin_t[(long)pos * 32 + lane];
+    const long krow = (long)page_table[(long)b * max_pages + pos / 64] * HKV * 64 + (pos & 63);
+    for (int h = warp; h < heads; h += 8) {
+        const float* src = qkv + bt * (long)heads * 64 + (long)h * 64;
+        const float x0 = src[lane], x1 = src[lane + 32];
+        float a, bb;
+        if (h < HQ + HKV) {
+            a = x0 * c - x1 * sn;
+            bb = x0 * sn + x1 * c;
+            auto lane_stage = [&](int bit) {
+                float pa = __shfl_xor_sync(0xffffffffu, a, 1 << bit);
+                float pb = __shfl_xor_sync(0xffffffffu, bb, 1 << bit);
+                if (lane & (1 << bit)) { a = pa - a; bb = pb - bb; }
+                else { a = a + pa; bb = bb + pb; }
+            };
+            lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
+            { float lo = a, hi = bb; a = lo + hi; bb = lo - hi; }
+            lane_stage(0);
+            a = a / 8.0f;
+            bb = bb / 8.0f;
+        } else {
+            a = x0; bb = x1;
+        }
+        // scale = max(|max|, |min|) / 127 = the largest magnitude / 127; one reciprocal per head, then every value is
+        // divided by the short exact sequence and rounded half away from zero (|quotient| <= 127)
+        const float amax = warp_max(fmaxf(fabsf(a), fabsf(bb)));
+        float sc = amax / 127.0f;
+        if (sc == 0.0f) sc = 1.0f;
+        const DivBy dsc = div_by(sc);
+        auto q8 = [&](float v) {
+            const float qt = div_for_rounding(v, dsc);
+            const int m = __float2int_rz(__fadd_rd(fabsf(qt), 0.5f));
+            return (int8_t)(qt < 0.0f ? -m : m);
         };
-        lane_stage(1); lane_stage(2); lane_stage(3); lane_stage(4);
-        { float lo = a, hi = bb; a = lo + hi; bb = lo - hi; }
-        lane_stage(0);
-        a = a / 8.0f;
-        bb = bb / 8.0f;
-    } else {
-        a = x0; bb = x1;
+        int8_t* dst; float* sdst;
+        if (h < HQ) { const long o = ((long)b * HQ + h) * Sq + t; dst = q2 + o * 64; sdst = qs2 + o; }
+        else if (h < HQ + HKV) { const long row = krow + (long)(h - HQ) * 64; dst = k_pool + row * 64; sdst = ks_pool + row; }
+        else { const long o = bt * HKV + (h - HQ - HKV); dst = v2 + o * 64; sdst = vs2 + o; }
+        if (lane == 0) *sdst = sc;
+        dst[lane] = q8(a);
+        dst[lane + 32] = q8(bb);
     }
-    const float mx = warp_max(fmaxf(a, bb)), mn = warp_min(fminf(a, bb));
-    const float sc = sym_scale_from(mx, mn);
-    int8_t* dst; float* sdst;
-    if (h < HQ) { const long o = ((long)b * HQ + h) * Sq + t; dst = q2 + o * 64; sdst = qs2 + o; }
-    else if (h < HQ + HKV) {
-        const long row = ((long)page_table[(long)b * max_pages + pos / 64] * HKV + (h - HQ)) * 64 + (pos & 63);
-        dst = k_pool + row * 64; sdst = ks_pool + row;
-    } else { const long o = ((long)b * Sq + t) * HKV + (h - HQ - HKV); dst = v2 + o * 64; sdst = vs2 + o; }
-    if (lane == 0) *sdst = sc;
-    dst[lane] = quant_s8(a, sc);
-    dst[lane + 32] = quant_s8(bb, sc);
 }
 
 // V [B][Sq][HKV][64] (token-major scratch) -> the cache's V^T pages [page][HKV][64 dims][64 tokens] and scale pages,
@@ -892,8 +900,7 @@ int mha_prefill_paged(const float* qkv, const float* cos_t, const float* sin_t, 
     PagedWs ws(workspace, B, max_prefill, HQ, HKV);
     int8_t* k_pool = c->k + (size_t)layer * c->page_bytes; int8_t* v_pool = c->v + (size_t)layer * c->page_bytes;
     float* ks_pool = c->ks + (size_t)layer * (c->scale_bytes / 4); float* vs_pool = c->vs + (size_t)layer * (c->scale_bytes / 4);
-    const long warps = (long)B * Sq * (HQ + 2 * HKV);
-    attn_qkv_prepare_f32_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(qkv, cos_t, sin_t, B, Sq, q_off, HQ, HKV, ws.q2, ws.qs2, k_pool,
+    attn_qkv_prepare_f32_kernel<<<(unsigned)((long)B * Sq), 256, 0, st>>>(qkv, cos_t, sin_t, B, Sq, q_off, HQ, HKV, ws.q2, ws.qs2, k_pool,
                                                                             ks_pool, page_table, max_pages, ws.v2, ws.vs2);
     dim3 g((Sq + 63) / 64, HKV, B);
     attn_v_to_pages_kernel<<<g, 256, 0, st>>>(ws.v2, ws.vs2, Sq, q_off, HKV, page_table, max_pages, v_pool, vs_pool);
