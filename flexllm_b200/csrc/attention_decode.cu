@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(64 * G) dec_pv_kernel(KvLayer cache, const int
         if (key < k_end) {
             const float p = e[key] * r;
             const float tt = (p * cache.vs[prow + t]) / as;
-            int q = (int)roundf(tt);
+            int q = round_half_away_to_int(tt);
             q = q > 255 ? 255 : q;
             u = (uint8_t)q;
         }

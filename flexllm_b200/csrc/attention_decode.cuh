@@ -319,7 +319,7 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
                 if (key < nk) {
                     const float p = sc[g * cs + key] * rinv_g[g];
                     const float tt = div_for_rounding(p * vsc, as_g[g]);
-                    int r = (int)roundf(tt);
+                    int r = round_half_away_to_int(tt);
                     r = r > 255 ? 255 : r;
                     uq = (uint8_t)r;
                 }
@@ -421,13 +421,6 @@ __device__ __forceinline__ void mma_s8u8(int (&d)[4], const int (&a)[4], const i
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-
-// round to nearest, halves away from zero (std::round), without a branch: floor(|t| + 0.5) with the sum rounded DOWN is
-// exact (an integer is never crossed upwards), the truncating conversion saturates, and the sign is put back
-__device__ __forceinline__ int round_half_away_to_int(float t) {
-    const int r = __float2int_rz(__fadd_rd(fabsf(t), 0.5f));
-    return t < 0.0f ? -r : r;
 }
 
 // Returns false when a bounded wait ran out (the same verdict for all NT threads).

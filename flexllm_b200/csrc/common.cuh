@@ -138,7 +138,14 @@ __device__ __forceinline__ float sym_scale_from(float mx, float mn) {
     return s;
 }
 
-__device__ __forceinline__ int8_t quant_s8(float x, float s) { return (int8_t)(int)roundf(x / s); }
+// round to nearest, halves away from zero (std::round), without a branch: floor(|t| + 0.5) with the sum rounded DOWN is
+// exact (an integer is never crossed upwards), the truncating conversion saturates, and the sign is put back
+__device__ __forceinline__ int round_half_away_to_int(float t) {
+    const int r = __float2int_rz(__fadd_rd(fabsf(t), 0.5f));
+    return t < 0.0f ? -r : r;
+}
+
+__device__ __forceinline__ int8_t quant_s8(float x, float s) { return (int8_t)round_half_away_to_int(x / s); }
 
 // Correctly rounded x / s for MANY x and ONE s, without the full division each time. With
 // y = RN(1/s): q0 = RN(x*y) is within two ulps of x/s; a residual step r = x - q*s (exact in one

@@ -362,7 +362,7 @@ __device__ __forceinline__ void mega_row_fht(const MegaArgs& a, const MegaLayer&
     for (int hi = 0; hi < 4; hi++) {
         union { int8_t b[8]; int2 v; } o;
 #pragma unroll
-        for (int c = 0; c < 8; c++) o.b[c] = (int8_t)(int)roundf(div_for_rounding(r[hi * 8 + c], dsc));
+        for (int c = 0; c < 8; c++) o.b[c] = (int8_t)round_half_away_to_int(div_for_rounding(r[hi * 8 + c], dsc));
         *reinterpret_cast<int2*>(a.hq + (long)row * N + hi * 2048 + tid * 8) = o.v;
     }
     asm volatile("fence.proxy.async.global;" ::: "memory");   // hq is read by other CTAs' TMA (async proxy)
@@ -454,8 +454,8 @@ __device__ __forceinline__ void mega_row_fht4(const MegaArgs& a, const MegaLayer
     const DivBy dsc = div_by(sc);
     if (part == 0 && tid == 0) a.xs[row] = sc;
     char4 o;
-    o.x = (int8_t)(int)roundf(div_for_rounding(x[0], dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(x[1], dsc));
-    o.z = (int8_t)(int)roundf(div_for_rounding(x[2], dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(x[3], dsc));
+    o.x = (int8_t)round_half_away_to_int(div_for_rounding(x[0], dsc)); o.y = (int8_t)round_half_away_to_int(div_for_rounding(x[1], dsc));
+    o.z = (int8_t)round_half_away_to_int(div_for_rounding(x[2], dsc)); o.w = (int8_t)round_half_away_to_int(div_for_rounding(x[3], dsc));
     reinterpret_cast<char4*>(a.hq + (long)row * N + part * NP)[tid] = o;
     asm volatile("fence.proxy.async.global;" ::: "memory");   // hq is read by other CTAs' TMA (async proxy)
 }

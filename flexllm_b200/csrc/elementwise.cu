@@ -45,8 +45,8 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const float* __res
         int c = threadIdx.x + i * 256;
         if (c < nv) {
             char4 o;
-            o.x = (int8_t)(int)roundf(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v[i].y, dsc));
-            o.z = (int8_t)(int)roundf(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v[i].w, dsc));
+            o.x = (int8_t)round_half_away_to_int(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)round_half_away_to_int(div_for_rounding(v[i].y, dsc));
+            o.z = (int8_t)round_half_away_to_int(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)round_half_away_to_int(div_for_rounding(v[i].w, dsc));
             qr[c] = o;
         }
     }
@@ -182,7 +182,7 @@ __device__ __forceinline__ void rmsnorm_output_row(const float* __restrict__ xr,
             int c = lane + i * 32;
             if (c < nv) {
                 char4 w;
-                w.x = (int8_t)(int)roundf(div_for_rounding(o[i].x, dsc)); w.y = (int8_t)(int)roundf(div_for_rounding(o[i].y, dsc)); w.z = (int8_t)(int)roundf(div_for_rounding(o[i].z, dsc)); w.w = (int8_t)(int)roundf(div_for_rounding(o[i].w, dsc));
+                w.x = (int8_t)round_half_away_to_int(div_for_rounding(o[i].x, dsc)); w.y = (int8_t)round_half_away_to_int(div_for_rounding(o[i].y, dsc)); w.z = (int8_t)round_half_away_to_int(div_for_rounding(o[i].z, dsc)); w.w = (int8_t)round_half_away_to_int(div_for_rounding(o[i].w, dsc));
                 qr[c] = w;
             }
         }

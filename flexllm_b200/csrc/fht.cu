@@ -63,13 +63,12 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
     }
     float r[32];
     fht8192_passes<0>(buf, tid, r);
-    float mx = -1e32f, mn = 1e32f;
     div_rn_array(r, div_by(scale));
+    // the quantiser's scale is max(|max|, |min|) / 127: the largest magnitude alone carries it
+    float mx = 0.0f;
 #pragma unroll
-    for (int v = 0; v < 32; v++) {
-        mx = fmaxf(mx, r[v]);
-        mn = fminf(mn, r[v]);
-    }
+    for (int v = 0; v < 32; v++) mx = fmaxf(mx, fabsf(r[v]));
+    float mn = -mx;
     if (!FUSED) {
 #pragma unroll
         for (int hi = 0; hi < 4; hi++) {
@@ -86,7 +85,7 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
         for (int hi = 0; hi < 4; hi++) {
             union { int8_t b[8]; int2 v; } o;
 #pragma unroll
-            for (int c = 0; c < 8; c++) o.b[c] = (int8_t)(int)roundf(div_for_rounding(r[hi * 8 + c], dsc));
+            for (int c = 0; c < 8; c++) o.b[c] = (int8_t)round_half_away_to_int(div_for_rounding(r[hi * 8 + c], dsc));
             const int idx0 = hi * 2048 + tid * 8;
             if (FUSED == 2) {
                 if (idx0 >= win.col0 && idx0 < win.col0 + win.cols)

@@ -62,7 +62,7 @@ __device__ __forceinline__ void rmsnorm_decode_row(float4 (&v)[MAXV], float4 (&g
             const int c = lane + i * 32;
             if (c < nv) {
                 char4 o;
-                o.x = (int8_t)(int)roundf(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v[i].y, dsc)); o.z = (int8_t)(int)roundf(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v[i].w, dsc));
+                o.x = (int8_t)round_half_away_to_int(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)round_half_away_to_int(div_for_rounding(v[i].y, dsc)); o.z = (int8_t)round_half_away_to_int(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)round_half_away_to_int(div_for_rounding(v[i].w, dsc));
                 qr[c] = o;
             }
         }

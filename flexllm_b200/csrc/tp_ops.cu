@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) quant_gathered_kernel(const float* __rest
         const int c = threadIdx.x + i * 256;
         if (c < nv && c / wv == r) {
             char4 o;
-            o.x = (int8_t)(int)roundf(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v[i].y, dsc)); o.z = (int8_t)(int)roundf(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v[i].w, dsc));
+            o.x = (int8_t)round_half_away_to_int(div_for_rounding(v[i].x, dsc)); o.y = (int8_t)round_half_away_to_int(div_for_rounding(v[i].y, dsc)); o.z = (int8_t)round_half_away_to_int(div_for_rounding(v[i].z, dsc)); o.w = (int8_t)round_half_away_to_int(div_for_rounding(v[i].w, dsc));
             qr[c - r * wv] = o;
         }
     }
@@ -166,8 +166,8 @@ __global__ void __launch_bounds__(256) quant_given_amax_kernel(const float* __re
     for (int c = threadIdx.x; c < (W >> 2); c += 256) {
         const float4 v = xr[c];
         char4 o;
-        o.x = (int8_t)(int)roundf(div_for_rounding(v.x, dsc)); o.y = (int8_t)(int)roundf(div_for_rounding(v.y, dsc));
-        o.z = (int8_t)(int)roundf(div_for_rounding(v.z, dsc)); o.w = (int8_t)(int)roundf(div_for_rounding(v.w, dsc));
+        o.x = (int8_t)round_half_away_to_int(div_for_rounding(v.x, dsc)); o.y = (int8_t)round_half_away_to_int(div_for_rounding(v.y, dsc));
+        o.z = (int8_t)round_half_away_to_int(div_for_rounding(v.z, dsc)); o.w = (int8_t)round_half_away_to_int(div_for_rounding(v.w, dsc));
         qr[c] = o;
     }
 }
