@@ -14,6 +14,12 @@ inline int MHA_i8xi8_Prefilling(const int8_t* q, const float* qs, const int8_t* 
                                 int32_t* oacc, void* workspace, size_t workspace_bytes, stream_t st = nullptr) {
     return flexllm_mha_i8xi8_prefill(q, qs, k, ks, v, vs, PE_cos, PE_sin, a_s, B, S, HQ, HKV, out, oacc, workspace, workspace_bytes, st);
 }
+// the same graph in one sweep with an online softmax: close to, not bit-identical with, the call above (no static P scale)
+inline int MHA_i8xi8_Prefilling_online(const int8_t* q, const float* qs, const int8_t* k, const float* ks, const int8_t* v, const float* vs,
+                                       const float* PE_cos, const float* PE_sin, int B, int S, int HQ, int HKV, float* out,
+                                       void* workspace, size_t workspace_bytes, stream_t st = nullptr) {
+    return flexllm_mha_i8xi8_prefill_online(q, qs, k, ks, v, vs, PE_cos, PE_sin, B, S, HQ, HKV, out, workspace, workspace_bytes, st);
+}
 // dec_K_cache_manager / dec_V_cache_manager (MHA.h:485, :774) as a paged pool
 class KVCache {
   public:
