@@ -148,7 +148,7 @@ extern "C" int flexllm_mlp_block_decode(const float* x, const float* gamma, cons
     float* gu = (float*)w; w += up256((size_t)M * 2 * F * 4);
     int8_t* hq = (int8_t*)w;
     cudaStream_t st = (cudaStream_t)stream;
-    struct PdlScope { PdlScope() { g_pdl = 1; } ~PdlScope() { g_pdl = 0; } } pdl;
+    struct PdlScope { int before; PdlScope() : before(g_pdl) { g_pdl = 1; } ~PdlScope() { g_pdl = before; } } pdl;
     TRY_RC(flexllm_rmsnorm_quant(x, gamma, M, D, eps, order, nullptr, xq, xs, st));
     TRY_RC(linear_decode(xq, xs, w_gu, s_gu, M, 2 * F, D, nullptr, gu, nullptr, st));
     TRY_RC(swiglu_fht_quant_strided(gu, gu + F, 2L * F, M, fht_scale, hq, hs, st));
