@@ -195,8 +195,9 @@ def workload_config(world=1, parallel="dp"):
                         ", prefill 1024 + greedy decode 256",
             "global_batch": BATCH if tp else BATCH * world, "prefill_len": PREFILL, "decode_len": NEW, "layers": CFG["layers"],
             "l2": "weights (1.24 GB) and activations exceed the 126 MB L2; no flush needed",
-            "parallelism": (f"tp{world}: prefill tensor-parallel (column-parallel q/k/v/gate/up by heads / FFN channels, row-parallel o/down with an "
-                            f"NCCL int32 reduce-scatter of the partial sums, token rows owned per rank in between), then the KV cache regrouped "
+            "parallelism": (f"tp{world}: prefill tensor-parallel (column-parallel q/k/v/gate/up by heads / FFN channels; token rows owned per "
+                            f"rank in between: int8 attention columns and fp32 gated activations go to the rows' owners by all-to-all, which run "
+                            f"the o and down projections for their rows with the full weights), then the KV cache regrouped "
                             f"by sequence and {BATCH // world} sequences decoded per rank (batch-parallel decode streams)"
                             if tp else ("single GPU" if world == 1 else f"dp{world}: batch-parallel replicas, no data-path collective"))}
 

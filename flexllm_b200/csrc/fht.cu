@@ -168,6 +168,14 @@ int fht_quant_gathered(const float* h, int M, int g, int r, float scale, int8_t*
     return launch_status();
 }
 
+// The same input layout, whole rows out: h [g][M][8192/g] -> FHT-8192/scale -> per-token int8 [M][8192].
+int fht_quant_gathered_rows(const float* h, int M, int g, float scale, int8_t* q, float* s, cudaStream_t st) {
+    if (M == 0) return FLEXLLM_OK;
+    launch_k(fht8192_kernel<2>, dim3(M), dim3(256), 0, st, h, (const float*)nullptr, 0L, scale, (float*)nullptr, q, s, (float*)nullptr,
+             FhtWindow{g, (long)M, 0, 8192});
+    return launch_status();
+}
+
 }  // namespace flexllm
 
 using namespace flexllm;

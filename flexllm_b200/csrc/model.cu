@@ -44,10 +44,9 @@ int dequant_residual(const int32_t* acc, const float* s_tok, const float* s_ch, 
 int argmax_pair(const float* logits, int B, long V, int offset, void* pairs, cudaStream_t st);
 int argmax_select(const void* pairs, int g, int B, int32_t* idx, cudaStream_t st);
 int fht_quant_gathered(const float* h, int M, int g, int r, float scale, int8_t* q, float* s, cudaStream_t st);
+int fht_quant_gathered_rows(const float* h, int M, int g, float scale, int8_t* q, float* s, cudaStream_t st);
 int row_absmax(const float* x, long M, int W, float* amax, cudaStream_t st);
 int quant_given_amax(const float* x, long M, int W, const float* amax, int8_t* q, float* s_out, cudaStream_t st);
-int swiglu_fht_local(const float* gu, long M, int Fl, int g, float* send, cudaStream_t st);
-int fht_cross(const float* recv, long M, int W, int g, float scale, float* hf, float* amax, cudaStream_t st);
 int kv_regroup(const void* stage, int n_pages, int g, int hl, int elem_bytes, void* dst, cudaStream_t st);
 int topk_sample(const float* logits, int B, long V, int lanes, int top_k, const float* rnd, const int32_t* col, int32_t* idx,
                 int32_t* top_idx, float* top_val, cudaStream_t st);
@@ -109,7 +108,6 @@ using namespace flexllm;
 
 struct LayerW {
     int8_t *wqkv, *wo, *wgu, *wd;
-    int8_t* wd_x = nullptr;     // token-row partition: this rank's down_proj columns in the order the FHT exchange leaves them
     float *sqkv, *so, *sgu, *sd, *g0, *g1, *a_s;
 };
 
@@ -235,8 +233,6 @@ extern "C" int flexllm_model_create_tp(flexllm_model** out, const flexllm_model_
             dc.max_batch = c->max_batch / g;
             dc.max_prefill = 16;                    // the decode model never prefills; its row buffers serve the head
             if ((rc = flexllm_model_create(&m->dm, &dc))) return fail(rc);
-            for (int l = 0; l < NL; l++)
-                if ((rc = dmalloc(m, &m->L[l].wd_x, (size_t)D * m->Fl))) return fail(rc);
             const size_t pages_l = (size_t)dc.max_batch * m->max_pages;
             if ((rc = dmalloc(m, &m->amax, Mmax)) || (rc = dmalloc(m, &m->xs2, Mmax)) || (rc = dmalloc(m, &m->aq, Mmax * m->Dl)) ||
                 (rc = dmalloc(m, &m->kv_stage, pages_l * c->heads_kv * 4096)) || (rc = dmalloc(m, &m->kvs_stage, pages_l * c->heads_kv * 256)))
@@ -299,12 +295,7 @@ extern "C" int flexllm_model_load_layer(flexllm_model* m, int layer, const flexl
     TRY(copy_any(L.g0, w->gamma0, (size_t)D * 4, st));
     TRY(copy_any(L.g1, w->gamma1, (size_t)D * 4, st));
     TRY(copy_any(L.a_s, w->a_s + r * m->HQl, (size_t)m->HQl * 4, st));
-    if (m->dm) {
-        // K order of the token-row partition's down_proj: after the FHT exchange rank r holds, from every rank s,
-        // the window [r * W, (r + 1) * W) of s's Fl channels, i.e. original columns s * Fl + r * W + j at position s * W + j
-        const size_t W = Fl / m->g;
-        for (int s = 0; s < m->g; s++)
-            FLEXLLM_CHECK_CUDA(cudaMemcpy2DAsync(L.wd_x + s * W, Fl, w->wd + s * Fl + r * W, F, W, D, cudaMemcpyDefault, st));
+    if (m->dm) {      // the decode model keeps the full weights (also used by the token-row prefill's o and down projections)
         TRY(flexllm_model_load_layer(m->dm, layer, w, stream));
     }
     return FLEXLLM_OK;
@@ -350,25 +341,27 @@ static int run_head(flexllm_model* m, const float* xin, int B, int order, cudaSt
 // Between the projections every rank owns a block of M / g token rows (= B / g whole sequences) of the residual
 // stream: RMSNorm and the residual adds run on those rows only. Around them, per layer:
 //   all-gather   int8 rows + scales of the normalised input          -> column-parallel q|k|v (local heads), gate|up
-//   all-reduce   max over the ranks of the per-token largest magnitude of the attention output / FHT output, so that
-//                each rank quantises ITS columns with the whole row's scale (no row ever leaves the rank in fp32)
-//   reduce-scatter  int32 partial sums of the row-parallel o / down projections (exact, order-free) -> dequant +
-//                residual on the rank's rows
-//   all-to-all   between the local stages (index bits 1 .. log2(Fl)-1) and the cross-rank stages + bit 0 of the
-//                8192-point Hadamard transform: the reference's stage order, hence the single-GPU bits
-// Every exchanged quantity is either an integer sum or a maximum, or moves values unchanged, so the results equal the
-// single-GPU model's bit for bit. Afterwards the KV cache (sharded by KV head during the prefill) is regrouped by
+//   all-reduce   max over the ranks of the per-token largest magnitude of the attention output, so that each rank
+//                quantises ITS columns with the whole row's scale
+//   all-to-all   (int8) those columns to the rows' owners, which run the o projection for their rows with the full
+//                weight matrix (every rank holds the full weights for decode anyway): the integer sums over the whole
+//                K are formed on one rank, the residual add is the GEMM's epilogue
+//   all-to-all   (fp32) silu(gate) * up of the rank's FFN channels to the rows' owners, which then hold whole rows:
+//                8192-point Hadamard transform, quantiser and down projection are the single-GPU kernels on M / g rows
+// Every exchanged quantity is a maximum or moves values unchanged, and every sum is formed on one rank in the
+// single-GPU order, so the results equal the single-GPU model's bit for bit. Afterwards the KV cache (sharded by KV head during the prefill) is regrouped by
 // sequence, and each rank decodes its B / g sequences with the full (replicated, 1.2 GB) weights on the persistent
 // decode kernel: independent batch-parallel decode streams, no collective inside a decode step.
 // One chunk of the prompt (tokens at positions c0 .. c0 + Sc - 1 of every sequence) through all layers.
 static int prefill_rows_chunk(flexllm_model* m, const int32_t* tokens, int B, int S, int c0, int Sc, cudaStream_t st) {
     const int D = m->cfg.hidden, HQ = m->HQl, HKV = m->HKVl;
     const int QKV = (HQ + 2 * HKV) * 64;
-    const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl, W = Fl / g;
+    const int g = m->g, r = m->r, Dl = m->Dl, Fl = m->Fl, F = m->cfg.ffn;
     const long M = (long)B * Sc, Mr = M / g;
     int8_t* xq_mine = m->xq + (size_t)r * Mr * D;
     float* xs_mine = m->xs + (size_t)r * Mr;
-    int32_t* acc_mine = m->acc32 + (size_t)r * Mr * D;
+    int8_t* a_recv = reinterpret_cast<int8_t*>(m->acc32);           // the o projection's input columns as received
+    int8_t* a_rows = a_recv + (size_t)Mr * D;                         // ... and as rows [Mr][D]
     embed_kernel<<<(unsigned)Mr, 256, 0, st>>>(tokens, m->lm_w, m->lm_s, D, m->cfg.vocab, m->x, device_error_flag(), S, c0, Sc, (long)r * Mr);
     note_launches(1);
     auto norm_and_gather = [&](const float* gamma) {
@@ -379,28 +372,31 @@ static int prefill_rows_chunk(flexllm_model* m, const int32_t* tokens, int B, in
     };
     for (int l = 0; l < m->cfg.layers; l++) {
         const LayerW& L = m->L[l];
+        const LayerW& DL = m->dm->L[l];             // the decode model's copy: full (unsliced) o and down weights
         TRY(norm_and_gather(L.g0));
         TRY(gemm_i8_prefill(m->xq, m->xs, L.wqkv, L.sqkv, (int)M, QKV, D, nullptr, m->qkv, st, nullptr));
         TRY(mha_prefill_paged(m->qkv, m->cos_t, m->sin_t, L.a_s, B, Sc, c0, HQ, HKV, m->cfg.max_prefill, m->cache, l, m->page_table,
                               m->max_pages, m->att, m->attn_ws, st));
-        // o projection, row-parallel over this rank's heads
+        // o projection: every rank quantises its heads' columns of ALL rows with the rows' common scale (all-reduce of
+        // the per-token largest magnitude), the int8 columns go to the rows' owners (all-to-all), and each owner runs the
+        // whole projection for its rows with the full weight matrix (held for decode anyway) -- the integer sums over the
+        // full K are formed on one rank, the residual add is the GEMM's epilogue
         TRY(row_absmax(m->att, M, Dl, m->amax, st));
         TRY(flexllm_tp_allreduce_max_f32(m->tp, m->amax, (size_t)M, st));
         TRY(quant_given_amax(m->att, M, Dl, m->amax, m->aq, m->xs2, st));
-        TRY(gemm_i8_prefill(m->aq, nullptr, L.wo, nullptr, (int)M, D, Dl, m->acc32, nullptr, st, nullptr));
-        TRY(flexllm_tp_reduce_scatter_s32(m->tp, m->acc32, acc_mine, (size_t)Mr * D, st));
-        TRY(dequant_residual(acc_mine, m->xs2 + (size_t)r * Mr, L.so, Mr, D, m->x, m->x, st));
+        TRY(flexllm_tp_alltoall(m->tp, m->aq, a_recv, (size_t)Mr * Dl, st));                 // [g][Mr][Dl]
+        TRY(kv_regroup(a_recv, (int)Mr, g, 1, Dl, a_rows, st));                              // -> [Mr][D]
+        TRY(gemm_i8_prefill(a_rows, m->xs2 + (size_t)r * Mr, DL.wo, DL.so, (int)Mr, D, D, nullptr, m->x, st, m->x));
         // MLP
         TRY(norm_and_gather(L.g1));
         TRY(gemm_i8_prefill(m->xq, m->xs, L.wgu, L.sgu, (int)M, 2 * Fl, D, nullptr, m->gu, st, nullptr));
-        TRY(swiglu_fht_local(m->gu, M, Fl, g, m->hloc, st));
-        TRY(flexllm_tp_alltoall(m->tp, m->hloc, m->gath, (size_t)M * W * 4, st));
-        TRY(fht_cross(m->gath, M, W, g, m->cfg.fht_scale, m->hloc, m->amax, st));
-        TRY(flexllm_tp_allreduce_max_f32(m->tp, m->amax, (size_t)M, st));
-        TRY(quant_given_amax(m->hloc, M, Fl, m->amax, m->hq, m->xs2, st));
-        TRY(gemm_i8_prefill(m->hq, nullptr, L.wd_x, nullptr, (int)M, D, Fl, m->acc32, nullptr, st, nullptr));
-        TRY(flexllm_tp_reduce_scatter_s32(m->tp, m->acc32, acc_mine, (size_t)Mr * D, st));
-        TRY(dequant_residual(acc_mine, m->xs2 + (size_t)r * Mr, L.sd, Mr, D, m->x, m->x, st));
+        // silu(gate) * up of this rank's channels goes to the rows' owners (all-to-all, fp32: the only exchange that is not
+        // int8); the owner then has whole rows: the 8192-point transform, the quantiser and the down projection with the
+        // full weight matrix are the single-GPU kernels on Mr rows
+        TRY(swiglu_slice(m->gu, M, Fl, m->hloc, st));
+        TRY(flexllm_tp_alltoall(m->tp, m->hloc, m->gath, (size_t)Mr * Fl * 4, st));          // [g][Mr][Fl]
+        TRY(fht_quant_gathered_rows(m->gath, (int)Mr, g, m->cfg.fht_scale, m->hq, m->xs2, st));
+        TRY(gemm_i8_prefill(m->hq, m->xs2, DL.wd, DL.sd, (int)Mr, D, F, nullptr, m->x, st, m->x));
     }
     return FLEXLLM_OK;
 }

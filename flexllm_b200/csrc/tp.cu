@@ -3,15 +3,16 @@
 //   all-reduce (sum, int32)  partial accumulators of the row-parallel o_proj / down_proj --
 //                            integer addition is exact and order-free, so every rank ends up
 //                            with the bits a single GPU would have computed
-//   reduce-scatter (sum, int32)  the same partial sums when every rank keeps only its block of token rows
+//   reduce-scatter (sum, int32)  the same partial sums when a caller keeps only one block of rows per rank (offered;
+//                            the model runner's token-row partition needs no sum across ranks)
 //   all-reduce (max, fp32)   per-token largest magnitudes, so that each rank can quantise its own column
 //                            slice of a row with the scale of the whole row
 //   all-gather (bytes)       int8 rows + scales of the token-row blocks, fp32 activations of the
 //                            column-parallel stages in the all-gather partition, and the (value, index)
 //                            pairs of the vocab-parallel argmax
-//   all-to-all (bytes)       the exchange between the local and the cross-rank stages of the 8192-point
-//                            Hadamard transform, and the hand-over of the KV cache from the head-sharded
-//                            prefill to the sequence-sharded decode
+//   all-to-all (bytes)       column slices of all rows to the rows' owners (int8 attention output, fp32 gated
+//                            activations), and the hand-over of the KV cache from the head-sharded prefill to the
+//                            sequence-sharded decode
 // NCCL is loaded at run time from the library the process already uses (torch's bundled
 // libnccl.so.2), so libflexllm_b200.so itself carries no link-time dependency on it.
 #include <dlfcn.h>

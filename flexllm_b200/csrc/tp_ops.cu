@@ -132,8 +132,7 @@ __global__ void argmax_select_kernel(const ArgPair* __restrict__ pairs, int g, i
 
 // ---------------------------------------------------------------------------------------------
 // Token-row partition ("each rank owns a block of rows between the projections"): kernels that let a rank
-// quantise ITS column slice of a row with the scale of the WHOLE row, and the two halves of the 8192-point
-// Hadamard transform around its one exchange.
+// quantise ITS column slice of a row with the scale of the WHOLE row, and the regrouping of exchanged blocks.
 // ---------------------------------------------------------------------------------------------
 
 // amax[m] = max_k |x[m][k]| over this rank's W columns (the per-token quantiser's max(|max|, |min|),
@@ -172,90 +171,6 @@ __global__ void __launch_bounds__(256) quant_given_amax_kernel(const float* __re
     }
 }
 
-// First half of the FHT-8192 on a rank that holds Fl = 2^LB consecutive elements of each row (its gate/up
-// channels): h = silu(gate) * up, then the butterflies on index bits 1 .. LB-1 (the reference's stage order is
-// bits 1, 2, ..., 12, then 0; bits LB .. 12 pair elements of different ranks and bit 0 comes after them). The
-// result is written in all-to-all order: out[dest][m][j] = element dest * W + j, W = Fl / g, so that rank `dest`
-// receives, from every rank, the same W-wide window of the local index. One CTA of Fl / 8 threads per row.
-template <int LB>
-__global__ void __launch_bounds__((1 << LB) / 8) swiglu_fht_local_kernel(const float* __restrict__ gu, long M, int g, float* __restrict__ out) {
-    constexpr int Fl = 1 << LB, NT = Fl / 8;
-    __shared__ float buf[Fl + Fl / 32];
-    const int tid = threadIdx.x;
-    const long m = blockIdx.x;
-    const float4* gr = reinterpret_cast<const float4*>(gu + m * 2 * Fl);
-    const float4* ur = gr + Fl / 4;
-#pragma unroll
-    for (int it = 0; it < 2; it++) {
-        const int c = it * NT + tid;
-        const float4 a = gr[c], u = ur[c];
-        const int p = pad32(c * 4);
-        buf[p] = silu_f(a.x) * u.x; buf[p + 1] = silu_f(a.y) * u.y; buf[p + 2] = silu_f(a.z) * u.z; buf[p + 3] = silu_f(a.w) * u.w;
-    }
-    __syncthreads();
-    float r[8];
-    // one pass = the group of index bits b0, b0+1, b0+2 held in registers; SKIP low bits of the group were done by the pass before
-    auto pass = [&](const int b0, const int skip) {
-        const int base = (tid & ((1 << b0) - 1)) | ((tid >> b0) << (b0 + 3));
-#pragma unroll
-        for (int v = 0; v < 8; v++) r[v] = buf[pad32(base | (v << b0))];
-        if (skip < 1) reg_butterfly<0>(r);
-        if (skip < 2) reg_butterfly<1>(r);
-        reg_butterfly<2>(r);
-#pragma unroll
-        for (int v = 0; v < 8; v++) buf[pad32(base | (v << b0))] = r[v];
-        __syncthreads();
-    };
-    constexpr int NB = LB - 1;                  // bits 1 .. LB-1
-    constexpr int FULL = NB / 3, REM = NB - 3 * FULL;
-#pragma unroll
-    for (int k = 0; k < FULL; k++) pass(1 + 3 * k, 0);
-    if (REM) pass(LB - 3, 3 - REM);
-    const int W = Fl / g;
-#pragma unroll
-    for (int it = 0; it < 2; it++) {
-        const int c = it * NT + tid, e = c * 4, p = pad32(e);
-        const int dest = e / W, j = e - dest * W;
-        *reinterpret_cast<float4*>(out + ((long)dest * M + m) * W + j) = make_float4(buf[p], buf[p + 1], buf[p + 2], buf[p + 3]);
-    }
-}
-
-// Second half, on the rank that received window W of every rank: in[src][m][j] is element src * Fl + r * W + j of the
-// row after the local stages. Butterflies over the rank index (index bits LB, LB+1, ... in that order), then the stage
-// on bit 0 (neighbouring j), then / scale. Output hf[m][src * W + j] (this order is the K order of the rank's down_proj
-// slice) and the row's largest magnitude, merged over the CTA's threads with an integer max on the float bits
-// (non-negative floats order like their bit patterns). amax must be zero on entry. 4 consecutive j per thread.
-template <int G>
-__global__ void __launch_bounds__(256) fht_cross_kernel(const float* __restrict__ in, long M, int W, float scale, float* __restrict__ hf,
-                                                        unsigned* __restrict__ amax_bits) {
-    const int tpr = W >> 2;                                   // threads per row
-    const long idx = (long)blockIdx.x * 256 + threadIdx.x;
-    const long m = idx / tpr;
-    const int j4 = (int)(idx - m * tpr);
-    if (m >= M) return;
-    float4 w[G];
-#pragma unroll
-    for (int s = 0; s < G; s++) w[s] = reinterpret_cast<const float4*>(in + ((long)s * M + m) * W)[j4];
-    auto bf = [](float& lo, float& hi) { const float a = lo + hi, d = lo - hi; lo = a; hi = d; };
-#pragma unroll
-    for (int bit = 1; bit < G; bit <<= 1)
-#pragma unroll
-        for (int s = 0; s < G; s++)
-            if (!(s & bit)) { bf(w[s].x, w[s | bit].x); bf(w[s].y, w[s | bit].y); bf(w[s].z, w[s | bit].z); bf(w[s].w, w[s | bit].w); }
-    const DivBy d = div_by(scale);
-    float mx = 0.0f;
-#pragma unroll
-    for (int s = 0; s < G; s++) {
-        float x[4] = {w[s].x + w[s].y, w[s].x - w[s].y, w[s].z + w[s].w, w[s].z - w[s].w};      // bit 0
-        div_rn_array(x, d);
-        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))));
-        reinterpret_cast<float4*>(hf + m * (long)(G * W) + (long)s * W)[j4] = make_float4(x[0], x[1], x[2], x[3]);
-    }
-    // threads of a warp belong to one row (W / 4 is a multiple of 32)
-    mx = warp_max(mx);
-    if ((threadIdx.x & 31) == 0) atomicMax(amax_bits + m, __float_as_uint(mx));
-}
-
 // KV-cache hand-over from the head-sharded prefill to the sequence-sharded decode: `stage` holds, for every source
 // rank s, the pages of this rank's sequences with s's KV heads, [s][n_pages][hl][elems]; they are interleaved into
 // the decode cache's pages [n_pages][g * hl][elems] (head s * hl + h). elems = 4096 bytes (K, V pages) or 64 floats.
@@ -283,27 +198,6 @@ int quant_given_amax(const float* x, long M, int W, const float* amax, int8_t* q
     return launch_status();
 }
 // gu [M][2 * Fl] -> send [g][M][Fl / g]
-int swiglu_fht_local(const float* gu, long M, int Fl, int g, float* send, cudaStream_t st) {
-    if (M == 0) return FLEXLLM_OK;
-    if (Fl == 4096) swiglu_fht_local_kernel<12><<<(unsigned)M, 512, 0, st>>>(gu, M, g, send);
-    else if (Fl == 2048) swiglu_fht_local_kernel<11><<<(unsigned)M, 256, 0, st>>>(gu, M, g, send);
-    else if (Fl == 1024) swiglu_fht_local_kernel<10><<<(unsigned)M, 128, 0, st>>>(gu, M, g, send);
-    else return FLEXLLM_ENOTSUP;
-    return launch_status();
-}
-// recv [g][M][W] -> hf [M][g * W], amax [M] (zeroed here)
-int fht_cross(const float* recv, long M, int W, int g, float scale, float* hf, float* amax, cudaStream_t st) {
-    if (M == 0) return FLEXLLM_OK;
-    if (W % 128) return FLEXLLM_ENOTSUP;
-    FLEXLLM_CHECK_CUDA(cudaMemsetAsync(amax, 0, (size_t)M * sizeof(float), st));
-    const long threads = M * (W / 4);
-    const unsigned grid = (unsigned)((threads + 255) / 256);
-    if (g == 2) fht_cross_kernel<2><<<grid, 256, 0, st>>>(recv, M, W, scale, hf, (unsigned*)amax);
-    else if (g == 4) fht_cross_kernel<4><<<grid, 256, 0, st>>>(recv, M, W, scale, hf, (unsigned*)amax);
-    else if (g == 8) fht_cross_kernel<8><<<grid, 256, 0, st>>>(recv, M, W, scale, hf, (unsigned*)amax);
-    else return FLEXLLM_ENOTSUP;
-    return launch_status();
-}
 int kv_regroup(const void* stage, int n_pages, int g, int hl, int elem_bytes, void* dst, cudaStream_t st) {
     const long total = (long)g * n_pages * hl * (elem_bytes / 16);
     if (total == 0) return FLEXLLM_OK;

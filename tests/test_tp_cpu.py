@@ -107,25 +107,13 @@ def _rank(rank, world, port, ret):
     dist.barrier(); dist.destroy_process_group()
 
 
-def _fht_bits(x, bits):
-    """In-place-equivalent Walsh-Hadamard butterflies (lo, hi) <- (lo + hi, lo - hi) on the given index bits of the
-    last axis, in the given order, in fp32 (the reference's stage order is bits 1, 2, ..., log2(N)-1, then 0;
-    Modules/FHT.h:31-53)."""
-    x = np.array(x, dtype=np.float32, copy=True)
-    n = x.shape[-1]
-    idx = np.arange(n)
-    for b in bits:
-        lo = idx[(idx >> b) & 1 == 0]; hi = lo | (1 << b)
-        a, c = x[..., lo].copy(), x[..., hi].copy()
-        x[..., lo] = a + c; x[..., hi] = a - c
-    return x
-
-
 def _rank_rows(rank, world, port, ret):
     """The token-row partition of the GPU runner's tensor-parallel prefill: each rank owns T / g rows of the residual
-    stream; int8 rows are all-gathered for the column-parallel projections; the row-parallel projections quantise
-    their input slice with the all-reduced (max) row magnitude and reduce-scatter their int32 partial sums; the
-    8192-point FHT runs its local stages, one all-to-all, then the cross-rank stages and bit 0."""
+    stream; int8 rows are all-gathered for the column-parallel projections (q|k|v by heads, gate|up by FFN channels);
+    the attention output is quantised per column slice with the all-reduced (max) row magnitude and its int8 columns
+    go to the rows' owners (all-to-all), which run the o projection for their rows with the full weights; silu(gate) *
+    up goes to the rows' owners in fp32 (all-to-all), which then run the 8192-point FHT, the quantiser and the down
+    projection on whole rows."""
     CFG.clear(); CFG.update(CFGS_ROWS[world])
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -133,9 +121,7 @@ def _rank_rows(rank, world, port, ret):
     oracle.set_exp_mode(oracle.EXP_CORRECTLY_ROUNDED)
     c = CFG; W, x_all = _layer_inputs(); T, D, F = c["T"], c["hidden"], c["ffn"]
     g, r = world, rank
-    HQl, HKVl, Dl, Fl, Tr = c["hq"] // g, c["hkv"] // g, D // g, F // g, T // g
-    Wn = Fl // g
-    lb = Fl.bit_length() - 1
+    HQl, HKVl, Fl, Tr = c["hq"] // g, c["hkv"] // g, F // g, T // g
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
     rows = lambda w, n: w[r * n:(r + 1) * n]
 
@@ -147,9 +133,6 @@ def _rank_rows(rank, world, port, ret):
     def allreduce_max(a):
         v = t(a); dist.all_reduce(v, op=dist.ReduceOp.MAX); return v.numpy()
 
-    def reduce_scatter(acc):               # int32 [T][D] partial sums -> this rank's rows of the total
-        v = t(acc); dist.all_reduce(v); return v.numpy()[r * Tr:(r + 1) * Tr]
-
     def alltoall(blocks):                   # blocks[p] goes to rank p; returns the list received (index = source)
         every = [None] * g                  # gloo has no all_to_all: gather everything, pick what is addressed to this rank
         dist.all_gather_object(every, [np.ascontiguousarray(b) for b in blocks])
@@ -159,31 +142,25 @@ def _rank_rows(rank, world, port, ret):
         s = (amax / np.float32(127.0)).astype(np.float32); s[s == 0] = 1
         return _round_half_away(v / s[:, None]).astype(np.int8), s
 
-    x = x_all[r * Tr:(r + 1) * Tr]          # this rank's rows
+    own = slice(r * Tr, (r + 1) * Tr)
+    x = x_all[own]                          # this rank's rows
     xq_l, xs_l = oracle.quant_per_token(oracle.rmsnorm(x, W["g0"][0]))
     xq, xs = allgather_rows(xq_l), allgather_rows(xs_l)
     lin = lambda w, s, n: oracle.linear_i8(xq, xs, rows(w, n), rows(s, n))[1]
     att_l = _attention(oracle, W, lin(W["wq"][0], W["sq"][0], HQl * 64), lin(W["wk"][0], W["sk"][0], HKVl * 64),
                        lin(W["wv"][0], W["sv"][0], HKVl * 64), HQl, HKVl, W["a_s"][0][r * HQl:(r + 1) * HQl], T)
     amax = allreduce_max(np.abs(att_l).max(axis=1).astype(np.float32))
-    aq, as_ = quant_with(amax, att_l)
-    acc = reduce_scatter(oracle.gemm_s8s8(aq, np.ascontiguousarray(W["wo"][0][:, r * Dl:(r + 1) * Dl])))
-    x1 = oracle.residual(x, oracle.dequant(acc, as_[r * Tr:(r + 1) * Tr], W["so"][0]))
+    aq_l, as_ = quant_with(amax, att_l)                                          # this rank's columns of ALL rows
+    aq = np.concatenate(alltoall([aq_l[p * Tr:(p + 1) * Tr] for p in range(g)]), axis=1)     # all columns of this rank's rows
+    x1 = oracle.residual(x, oracle.linear_i8(aq, as_[own], W["wo"][0], W["so"][0])[1])
     xq_l, xs_l = oracle.quant_per_token(oracle.rmsnorm(x1, W["g1"][0]))
     xq, xs = allgather_rows(xq_l), allgather_rows(xs_l)
     gt = oracle.linear_i8(xq, xs, rows(W["wg"][0], Fl), rows(W["sg"][0], Fl))[1]
     up = oracle.linear_i8(xq, xs, rows(W["wu"][0], Fl), rows(W["su"][0], Fl))[1]
-    h = _fht_bits(oracle.silu_mul(gt, up), range(1, lb))                          # local stages: bits 1 .. lb-1
-    got = alltoall([h[:, p * Wn:(p + 1) * Wn] for p in range(g)])                # window r of every rank
-    z = np.stack(got, axis=1)                                                    # [T][src][Wn]
-    z = _fht_bits(z.transpose(0, 2, 1), range(0, g.bit_length() - 1)).transpose(0, 2, 1)   # rank-index bits = index bits lb, lb+1, ...
-    z = _fht_bits(z, [0])                                                        # bit 0 inside the window
-    hf = (z.reshape(T, g * Wn) / np.float32(np.sqrt(8192))).astype(np.float32)
-    amax = allreduce_max(np.abs(hf).max(axis=1).astype(np.float32))
-    hq, hs = quant_with(amax, hf)
-    cols = np.concatenate([np.arange(s_ * Fl + r * Wn, s_ * Fl + (r + 1) * Wn) for s_ in range(g)])     # K order of this rank's slice
-    acc = reduce_scatter(oracle.gemm_s8s8(hq, np.ascontiguousarray(W["wd"][0][:, cols])))
-    out_l = oracle.residual(x1, oracle.dequant(acc, hs[r * Tr:(r + 1) * Tr], W["sd"][0]))
+    h_l = oracle.silu_mul(gt, up)                                                # this rank's FFN channels of ALL rows
+    h = np.concatenate(alltoall([h_l[p * Tr:(p + 1) * Tr] for p in range(g)]), axis=1)       # whole rows of this rank
+    hq, hs = oracle.quant_per_token(oracle.fht(h, float(np.float32(np.sqrt(8192)))))
+    out_l = oracle.residual(x1, oracle.linear_i8(hq, hs, W["wd"][0], W["sd"][0])[1])
     ret[rank] = (allgather_rows(out_l), None)
     dist.barrier(); dist.destroy_process_group()
 
