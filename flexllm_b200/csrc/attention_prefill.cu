@@ -302,9 +302,16 @@ __global__ void __launch_bounds__(192, 4) attn_prefill_kernel(const __grid_const
                 } else {
                     float e[16];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const float x = (((float)(int)v[i] * qscale) * ksv[i]) * 0.125f;
-                        e[i] = (kc + i <= qlim) ? ref_expf(x - mx) : 0.0f;      // exp(-1e32 - max) is exactly 0
+                    for (int i4 = 0; i4 < 16; i4 += 4) {          // four exponentials at a time (their chains interleave)
+                        float xx[4], ee[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float x = (((float)(int)v[i4 + i] * qscale) * ksv[i4 + i]) * 0.125f;
+                            xx[i] = (kc + i4 + i <= qlim) ? x - mx : -1e32f;    // masked: exp(-1e32) is exactly 0
+                        }
+                        ref_expf_x4<true>(xx, ee);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) e[i4 + i] = ee[i];
                     }
                     // ordered chains: key mod 4 == i mod 4 because kc is a multiple of 16; adding the
                     // exact zeros of masked keys leaves the sums unchanged, as in the reference

@@ -239,6 +239,57 @@ __device__ __forceinline__ float ref_expf(float x) {
     return __double2float_rn(__hiloint2double(hi, lo));
 }
 
+// Four evaluations at once: the same arithmetic per value, written so that the four dependency chains interleave
+// (one test and one rare branch for the group instead of one per value).
+// EARLY: first test whether all four lie below -104 (masked keys, the tail of a peaked softmax) and return zeros.
+template <bool EARLY = false>
+__device__ __forceinline__ void ref_expf_x4(const float (&x)[4], float (&e)[4]) {
+    if (EARLY && x[0] < -104.0f && x[1] < -104.0f && x[2] < -104.0f && x[3] < -104.0f) {
+        e[0] = e[1] = e[2] = e[3] = 0.0f;
+        return;
+    }
+    const double shift = 0x1.8p52;
+    unsigned hard = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const double xd = (double)x[i];
+        const double t = __fma_rn(xd, FLEXLLM_EXP_INV_LN2_32, shift);
+        const int k = __double2loint(t);
+        const double kd = t - shift;
+        double r = __fma_rn(kd, -FLEXLLM_EXP_LN2_32_HI, xd);
+        r = __fma_rn(kd, -FLEXLLM_EXP_LN2_32_LO, r);
+        double p = __fma_rn(r, 1.0 / 120.0, 1.0 / 24.0);
+        p = __fma_rn(p, r, 1.0 / 6.0);
+        p = __fma_rn(p, r, 0.5);
+        p = __fma_rn(p, r, 1.0);
+        p = __fma_rn(p, r, 1.0);
+        const double res = __ldg(&g_exp2_table[k & 31]) * p;
+        const int hi = __double2hiint(res) + ((k >> 5) << 20);
+        const int lo = __double2loint(res);
+        const unsigned low29 = (unsigned)lo & 0x1fffffffu;
+        const unsigned dist = low29 > 0x10000000u ? low29 - 0x10000000u : 0x10000000u - low29;
+        const bool zero = x[i] < -104.0f;                               // exp(x) < 2^-150 rounds to +0
+        const bool rare = !zero && (dist < 256u || !(fabsf(x[i]) < 80.0f));
+        e[i] = zero ? 0.0f : __double2float_rn(__hiloint2double(hi, lo));
+        hard |= rare ? (1u << i) : 0u;
+    }
+    if (hard) {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (hard & (1u << i)) e[i] = ref_expf_accurate(x[i]);
+    }
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + ref_expf(-g)); }
+// silu(g) * u on four values (same arithmetic per value)
+__device__ __forceinline__ float4 silu_mul_x4(const float4 g, const float4 u) {
+    const float x[4] = {-g.x, -g.y, -g.z, -g.w};
+    float e[4];
+    ref_expf_x4(x, e);
+    float4 o;
+    o.x = (g.x / (1.0f + e[0])) * u.x; o.y = (g.y / (1.0f + e[1])) * u.y;
+    o.z = (g.z / (1.0f + e[2])) * u.z; o.w = (g.w / (1.0f + e[3])) * u.w;
+    return o;
+}
 
 }  // namespace flexllm

@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256) fht8192_kernel(const float* __restrict__ 
             float4 v = vv[it];
             if (FUSED == 1) {
                 const float4 w = ww[it];
-                v.x = silu_f(v.x) * w.x; v.y = silu_f(v.y) * w.y; v.z = silu_f(v.z) * w.z; v.w = silu_f(v.w) * w.w;
+                v = silu_mul_x4(v, w);
                 if (act) reinterpret_cast<float4*>(act + row * N)[c] = v;
             }
             const int p = pad32(c * 4);

@@ -53,7 +53,7 @@ __global__ void swiglu_slice_kernel(const float* __restrict__ gu, long M, int W,
         const float4 g = reinterpret_cast<const float4*>(gu + m * 2 * W)[c];
         const float4 u = reinterpret_cast<const float4*>(gu + m * 2 * W + W)[c];
         float4 o;
-        o.x = silu_f(g.x) * u.x; o.y = silu_f(g.y) * u.y; o.z = silu_f(g.z) * u.z; o.w = silu_f(g.w) * u.w;
+        o = silu_mul_x4(g, u);
         reinterpret_cast<float4*>(h)[i] = o;
     }
 }
