@@ -510,7 +510,14 @@ __device__ __noinline__ void mega_row_sample(const MegaArgs& a, int row, int col
 }
 
 // ---- the kernel -----------------------------------------------------------------------------------
-template <int BN>
+// ATT selects which attention bodies are compiled in. The whole kernel is several hundred KB of instructions and a
+// latency-bound step pays for every instruction-cache miss, so the host launches the leanest variant that covers the
+// launch (measured: 5 % off the step against the variant that holds every body):
+//   0  every body: both item layouts, the staged copies and the per-thread-load body for contexts beyond the staging area
+//   1  two items per CTA, staged copies only (more items than CTAs, every context fits half of the operand ring)
+//   2  one item per CTA on all 512 threads, staged copies only (no more items than CTAs, every context fits the ring)
+// A variant that meets a context it was not built for raises the device-data error bit and skips the item.
+template <int BN, int ATT>
 __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid_constant__ MegaArgs a) {
     constexpr int STAGE_BYTES = MG_A_TILE + BN * 128;
     constexpr int TMEM_COLS = 2 * BN;
@@ -751,7 +758,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             stg.cap_pages = half_bytes / 4096 < 20 ? half_bytes / 4096 : 20;
             stg.abort_flag = abort_flag;
             if (is_tma) prefetch_weights_l2(mega_job(a, l, 1));
-            if (a.B * a.HKV <= G) {
+            if (ATT != 1 && (ATT == 2 || a.B * a.HKV <= G)) {
                 // no more items than CTAs: one item per CTA, worked on by all 512 threads (an item is a chain of dependent
                 // stages; twice the threads shorten the stages that scale -- scores, exponentials, quantiser, P.V)
                 if (cta < a.B * a.HKV) {
@@ -770,39 +777,48 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                         att_uses++;
                         ok1 = dec_attn_staged_body<512>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.HQ, a.HKV, a.cs, a.att,
                                                         cta % a.HKV, b, pos, dsm1, sm1, st1, tid, MG_BAR_WORK);
-                    } else
+                    } else if (ATT == 0) {
                         dec_attn_fused_body<2, 512>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
                                                     a.att, nullptr, cta % a.HKV, b, dsm1, sm1, tid, MG_BAR_WORK);
+                    } else if (tid == 0) {
+                        atomicOr(a.error_flag, 2);
+                    }
                     if (ok1) {
                         named_sync<MG_BAR_WORK, MG_WORKERS>();
                         if (tid < 256) mega_att_row_quant(a, b, sm1, tid, MG_BAR_HALF0);
                     }
                 }
-            } else
-            // items spread over the CTAs first (item i on CTA i mod G)
-            for (int idx = cta + half * G; idx < a.B * a.HKV; idx += 2 * G) {
-                const int b = idx / a.HKV;
-                const int pos = dec_guarded_pos(a.ctx, b, a.max_ctx, a.error_flag);
-                if (pos / PAGE + 1 <= stg.cap_pages) {
-                    stg.parity = att_uses & 1u;
-                    att_uses++;
-                    if (!dec_attn_staged_body<256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.HQ, a.HKV, a.cs, a.att,
-                                                   idx % a.HKV, b, pos, dsm, sm, stg, tid & 255, MG_BAR_HALF0 + half))
-                        break;
-                } else     // contexts beyond the staging area: per-thread global loads
-                dec_attn_fused_body<2, 256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
-                                            a.att, nullptr, idx % a.HKV, b, dsm, sm, tid & 255, MG_BAR_HALF0 + half);
-                // the item that completes its sequence's attention row (the last of its HKV items to arrive)
-                // quantises the row for the o projection -- no separate phase, no extra grid barrier
-                mega_att_row_quant(a, b, sm, tid & 255, MG_BAR_HALF0 + half);
+            } else if (ATT != 2) {
+                // items spread over the CTAs first (item i on CTA i mod G)
+                for (int idx = cta + half * G; idx < a.B * a.HKV; idx += 2 * G) {
+                    const int b = idx / a.HKV;
+                    const int pos = dec_guarded_pos(a.ctx, b, a.max_ctx, a.error_flag);
+                    if (pos / PAGE + 1 <= stg.cap_pages) {
+                        stg.parity = att_uses & 1u;
+                        att_uses++;
+                        if (!dec_attn_staged_body<256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.HQ, a.HKV, a.cs, a.att,
+                                                       idx % a.HKV, b, pos, dsm, sm, stg, tid & 255, MG_BAR_HALF0 + half))
+                            break;
+                    } else if (ATT == 0) {     // contexts beyond the staging area: per-thread global loads
+                        dec_attn_fused_body<2, 256>(in, a.cos_t, a.sin_t, ly.a_s, ly.kv, a.page_table, a.max_pages, a.ctx, a.HQ, a.HKV, a.cs,
+                                                    a.att, nullptr, idx % a.HKV, b, dsm, sm, tid & 255, MG_BAR_HALF0 + half);
+                    } else if ((tid & 255) == 0) {
+                        atomicOr(a.error_flag, 2);
+                    }
+                    // the item that completes its sequence's attention row (the last of its HKV items to arrive)
+                    // quantises the row for the o projection -- no separate phase, no extra grid barrier
+                    mega_att_row_quant(a, b, sm, tid & 255, MG_BAR_HALF0 + half);
+                }
             }
             // both halves are done with the ring (each thread has fenced its accesses): the o projection's weights may come in
             named_sync<MG_BAR_WORK, MG_WORKERS>();
             if (is_tma && !*abort_flag) prefetch_weights(mega_job(a, l, 1));
         } else if (k == PH_D) {
-            const int parts = 4 * a.B <= G ? 4 : 1;         // CTAs per row
+            // CTAs per row: four when the grid has them (always so for up to 32 sequences: the host refuses smaller grids,
+            // and the one-CTA-per-row code is then not even compiled in), else one
+            const int parts = (BN <= 32 || 4 * a.B <= G) ? 4 : 1;
             if (cta < parts * a.B) {
-                if (parts == 4) mega_row_fht4(a, ly, cta >> 2, cta & 3, rowbuf, rowred, tid, abort_flag);
+                if (BN <= 32 || parts == 4) mega_row_fht4(a, ly, cta >> 2, cta & 3, rowbuf, rowred, tid, abort_flag);
                 else mega_row_fht(a, ly, cta, rowbuf, rowred, tid);
             }
         } else if (k == PH_TOKEN) {
@@ -857,6 +873,7 @@ struct MegaPlan {
     size_t work_bytes = 0;
     int grid = 0, bn = 0;
     size_t smem = 0;
+    int cap_pair = 0, cap_single = 0;       // pages of KV the staging areas of the two attention item layouts hold
 };
 
 void mega_destroy(MegaPlan* p) {
@@ -889,7 +906,11 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     const int G = gemm_sm_count();
     if (v.max_batch > G) return FLEXLLM_ENOTSUP;
     const int bn = v.max_batch <= 32 ? 32 : 64;
-    const void* kern = bn == 32 ? (const void*)decode_mega_kernel<32> : (const void*)decode_mega_kernel<64>;
+    if (bn == 32 && G < 4 * 32) return FLEXLLM_ENOTSUP;     // the 32-sequence kernel always splits an FFN row over four CTAs
+    const void* kerns[3];
+    if (bn == 32) { kerns[0] = (const void*)decode_mega_kernel<32, 0>; kerns[1] = (const void*)decode_mega_kernel<32, 1>; kerns[2] = (const void*)decode_mega_kernel<32, 2>; }
+    else { kerns[0] = (const void*)decode_mega_kernel<64, 0>; kerns[1] = (const void*)decode_mega_kernel<64, 1>; kerns[2] = (const void*)decode_mega_kernel<64, 2>; }
+    const void* kern = kerns[0];
     cudaFuncAttributes fa;
     FLEXLLM_CHECK_CUDA(cudaFuncGetAttributes(&fa, kern));
     const int stage_bytes = MG_A_TILE + bn * 128;
@@ -904,14 +925,21 @@ int mega_create(const MegaModelView& v, MegaPlan** out) {
     if (stages > MG_MAX_STAGES) stages = MG_MAX_STAGES;
     if (stages < 3) return FLEXLLM_ENOTSUP;      // long contexts: the per-operator kernels take over
     const size_t smem = 1024 + (size_t)stages * stage_bytes + scratch + 256;
-    FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int per_sm = 0;
-    FLEXLLM_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MG_THREADS, smem));
-    if (per_sm < 1) return FLEXLLM_ENOTSUP;
+    for (int i = 0; i < 3; i++) {
+        FLEXLLM_CHECK_CUDA(cudaFuncSetAttribute(kerns[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int per_sm = 0;
+        FLEXLLM_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kerns[i], MG_THREADS, smem));
+        if (per_sm < 1) return FLEXLLM_ENOTSUP;
+    }
 
     MegaPlan* p = new (std::nothrow) MegaPlan();
     if (!p) return FLEXLLM_ENOMEM;
     p->grid = G; p->bn = bn; p->smem = smem;
+    {
+        const int ring = stages * stage_bytes, half = (ring >> 1) & ~127;
+        p->cap_pair = half / 4096 < 20 ? half / 4096 : 20;
+        p->cap_single = ring / 4096 < 40 ? ring / 4096 : 40;
+    }
     const int n_maps = 2 + 4 * v.layers + 1;
     std::vector<CUtensorMap> maps(n_maps);
     std::vector<MegaLayer> layers(v.layers);
@@ -997,8 +1025,17 @@ int mega_reset(MegaPlan* p, cudaStream_t st) {
 static std::atomic<long long> g_hook_wait_limit_ns{0};
 static std::atomic<int> g_hook_barrier_extra{0};
 
-int mega_launch(MegaPlan* p, int B, cudaStream_t st) {
-    if (B < 1 || B > p->bn) return FLEXLLM_EINVAL;
+// The leanest kernel variant that covers a launch of B sequences whose positions stay <= max_pos.
+int mega_variant(const MegaPlan* p, int B, int max_pos) {
+    const int pages = max_pos / PAGE + 1;
+    if (B * p->args.HKV <= p->grid) return pages <= p->cap_single ? 2 : 0;
+    return pages <= p->cap_pair ? 1 : 0;
+}
+
+int mega_launch(MegaPlan* p, int B, int variant, cudaStream_t st) {
+    if (B < 1 || B > p->bn || variant < 0 || variant > 2) return FLEXLLM_EINVAL;
+    if (variant == 2 && B * p->args.HKV > p->grid) return FLEXLLM_EINVAL;
+    if (variant == 1 && B * p->args.HKV <= p->grid) return FLEXLLM_EINVAL;
     p->args.B = B;
     const long long lim = g_hook_wait_limit_ns.load();
     p->args.wait_limit_ns = lim > 0 ? (unsigned long long)lim : kWaitLimitNs;
@@ -1009,8 +1046,15 @@ int mega_launch(MegaPlan* p, int B, cudaStream_t st) {
     at[0].id = cudaLaunchAttributeCooperative;     // all CTAs co-resident: the grid barrier cannot starve
     at[0].val.cooperative = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    if (p->bn == 32) cudaLaunchKernelEx(&cfg, decode_mega_kernel<32>, p->args);
-    else cudaLaunchKernelEx(&cfg, decode_mega_kernel<64>, p->args);
+    if (p->bn == 32) {
+        if (variant == 0) cudaLaunchKernelEx(&cfg, decode_mega_kernel<32, 0>, p->args);
+        else if (variant == 1) cudaLaunchKernelEx(&cfg, decode_mega_kernel<32, 1>, p->args);
+        else cudaLaunchKernelEx(&cfg, decode_mega_kernel<32, 2>, p->args);
+    } else {
+        if (variant == 0) cudaLaunchKernelEx(&cfg, decode_mega_kernel<64, 0>, p->args);
+        else if (variant == 1) cudaLaunchKernelEx(&cfg, decode_mega_kernel<64, 1>, p->args);
+        else cudaLaunchKernelEx(&cfg, decode_mega_kernel<64, 2>, p->args);
+    }
     return launch_status();
 }
 

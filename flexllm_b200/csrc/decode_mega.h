@@ -35,7 +35,10 @@ void mega_destroy(MegaPlan* p);
 int mega_reset(MegaPlan* p, cudaStream_t st);
 // Token choice of the following steps: top_k == 0 greedy, else top-k sampling with rnd [n_new][B] (device).
 void mega_set_sampling(MegaPlan* p, int lanes, int top_k, const float* rnd);
-// One decode step for B sequences (one kernel launch).
-int mega_launch(MegaPlan* p, int B, cudaStream_t st);
+// The kernel is built in three variants that differ in the attention code they carry; mega_variant names the leanest one
+// that covers B sequences at positions <= max_pos (0 = the general one, valid for every launch).
+int mega_variant(const MegaPlan* p, int B, int max_pos);
+// One decode step for B sequences (one kernel launch) with the given variant.
+int mega_launch(MegaPlan* p, int B, int variant, cudaStream_t st);
 
 }  // namespace flexllm

@@ -131,6 +131,7 @@ struct flexllm_model {
     int n_new = 0;                              // columns of the token table of the running generation
     int pos = 0;                                // context length of the batch = position the next decode step writes
     cudaGraphExec_t graph = nullptr; int graph_B = 0; int graph_kernels = 0;
+    int mega_variant = 0, graph_variant = 0;   // attention variant of the persistent kernel for the current decode call / in the captured step
     std::vector<void*> owned;
     // tensor parallelism: g ranks, this one is r; *l = local (per-rank) sizes
     flexllm_tp* tp = nullptr;
@@ -574,7 +575,7 @@ static int mega_prepare(flexllm_model* m) {
 static int decode_step_body(flexllm_model* m, cudaStream_t st);
 static int decode_step(flexllm_model* m, cudaStream_t st) {
     TRY(mega_prepare(m));
-    if (m->mega_state == 1) return mega_launch(m->mega, m->B, st);
+    if (m->mega_state == 1) return mega_launch(m->mega, m->B, m->mega_variant, st);
     static int use_pdl = -1;
     if (use_pdl < 0) { const char* e = getenv("FLEXLLM_PDL"); use_pdl = e ? atoi(e) : 1; }
     g_pdl = use_pdl;
@@ -647,7 +648,7 @@ static int build_graph(flexllm_model* m) {
     cudaStreamDestroy(cap);
     if (rc != FLEXLLM_OK) return rc;
     FLEXLLM_CHECK_CUDA(e);
-    m->graph_B = m->B;
+    m->graph_B = m->B; m->graph_variant = m->mega_variant;
     return FLEXLLM_OK;
 }
 
@@ -661,7 +662,9 @@ extern "C" int flexllm_model_decode(flexllm_model* m, int n_steps, int use_graph
     cudaStream_t st = (cudaStream_t)stream;
     if (flexllm_tp_is_local(m->tp)) use_graph = 0;      // ranks sharing a device: the collectives need their host-side rendezvous
     int done = 0;
-    if (use_graph && n_steps > 0 && (!m->graph || m->graph_B != m->B)) {
+    TRY(mega_prepare(m));
+    m->mega_variant = m->mega_state == 1 ? mega_variant(m->mega, m->B, m->pos) : 0;      // every position of this call is < m->pos
+    if (use_graph && n_steps > 0 && (!m->graph || m->graph_B != m->B || m->graph_variant != m->mega_variant)) {
         // the first step runs eagerly so that every lazily created resource (function attributes,
         // tensor maps, split-K scratch) exists before capture
         TRY(decode_step(m, st));
