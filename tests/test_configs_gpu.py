@@ -74,13 +74,22 @@ def test_decode_attention_batch64(F):
     decode_case(F, 64, g.integers(512, 8193, 64), seed=44)
 
 
-def test_full_model_two_decode_paths(F, monkeypatch):
-    """16 layers, hidden 2048, 32/8 heads, FFN 8192, vocab 128256, batch 32, prompt 1024, 8 generated tokens:
-    the persistent decode-step kernel and the kernel-per-operator decode path (FLEXLLM_MEGA=0) produce the
+# which attention variant of the persistent kernel the decode steps of a case take (it is chosen per launch from the
+# number of (sequence, KV head) items against the number of SMs and from the longest context against the staging areas)
+@pytest.mark.parametrize("layers,B,S,n_new,what", [
+    (16, 32, 1024, 8, "the full-model workload: two items per CTA, staged copies"),
+    (2, 20, 1296, 3, "two items per CTA, contexts beyond half of the operand ring (per-thread loads)"),
+    (2, 16, 1040, 3, "one item per CTA on all 512 threads, staged copies"),
+    (2, 4, 2112, 3, "one item per CTA, contexts beyond the operand ring (per-thread loads)"),
+])
+def test_full_model_two_decode_paths(F, monkeypatch, layers, B, S, n_new, what):
+    """Hidden 2048, 32/8 heads, FFN 8192, vocab 128256 -- 16 layers at batch 32, prompt 1024, 8 generated tokens, and
+    2-layer stacks at the batch sizes and context lengths that select the persistent kernel's other attention
+    variants: the persistent decode-step kernel and the kernel-per-operator decode path (FLEXLLM_MEGA=0) produce the
     same tokens, the same residual stream of the last step and the same logits."""
     from flexllm_b200 import synthetic
     cfg = dict(synthetic.LLAMA32_1B)
-    B, S, n_new = 32, 1024, 8
+    cfg["layers"] = layers
     tok = torch.randint(0, cfg["vocab"], (B, S), dtype=torch.int32, generator=torch.Generator().manual_seed(77))
     res = {}
     for mega in ("1", "0"):
@@ -94,8 +103,8 @@ def test_full_model_two_decode_paths(F, monkeypatch):
         m.close()
         del m
         torch.cuda.empty_cache()
-    assert np.array_equal(res["1"][0], res["0"][0]), "tokens differ between the two decode paths"
+    assert np.array_equal(res["1"][0], res["0"][0]), f"tokens differ between the two decode paths ({what})"
     assert_same(res["1"][1], res["0"][1], "residual stream of the last decode step")
     assert_same(res["1"][2], res["0"][2], "logits of the last decode step")
     # not a degenerate run: the sequences do not all emit one token
-    assert len(np.unique(res["1"][0])) > B
+    assert len(np.unique(res["1"][0])) > min(B, 8)
