@@ -285,10 +285,14 @@ __device__ __forceinline__ void dec_attn_fused_body(const DecAttnIn& in, const f
         }
     }
     ATT_TS(4);
-    // ---- D. e = exp(x - max), in place
-    for (int g = 0; g < G; g++) {
-        const float m = row_max[g];
-        for (int key = tid; key < nk; key += NT) sc[g * cs + key] = ref_expf(sc[g * cs + key] - m);
+    // ---- D. e = exp(x - max), in place: the four heads of a key together (four independent evaluations in flight)
+    {
+        const float m0 = row_max[0], m1 = row_max[1], m2 = row_max[2], m3 = row_max[3];
+        for (int key = tid; key < nk; key += NT) {
+            const float x0 = sc[key] - m0, x1 = sc[cs + key] - m1, x2 = sc[2 * cs + key] - m2, x3 = sc[3 * cs + key] - m3;
+            const float e0 = ref_expf(x0), e1 = ref_expf(x1), e2 = ref_expf(x2), e3 = ref_expf(x3);
+            sc[key] = e0; sc[cs + key] = e1; sc[2 * cs + key] = e2; sc[3 * cs + key] = e3;
+        }
     }
     named_sync_id<NT>(bar);
     ATT_TS(5);
