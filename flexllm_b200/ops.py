@@ -466,6 +466,22 @@ class TensorParallel:
         _check("flexllm_tp_allgather", lib().flexllm_tp_allgather(self._h, _ptr(t), _ptr(out), t.numel() * t.element_size(), _stream()))
         return out
 
+    def reduce_scatter_s32(self, t):
+        """t int32 [size, n]: returns block `rank` of the sum over the ranks, [n]."""
+        out = torch.empty(t.shape[1:], dtype=torch.int32, device=t.device)
+        _check("flexllm_tp_reduce_scatter_s32", lib().flexllm_tp_reduce_scatter_s32(self._h, _ptr(t), _ptr(out), out.numel(), _stream()))
+        return out
+
+    def allreduce_max_f32(self, t):
+        _check("flexllm_tp_allreduce_max_f32", lib().flexllm_tp_allreduce_max_f32(self._h, _ptr(t), t.numel(), _stream()))
+        return t
+
+    def alltoall(self, t):
+        """t [size, ...]: block p goes to rank p; returns the blocks received, indexed by source rank."""
+        out = torch.empty_like(t)
+        _check("flexllm_tp_alltoall", lib().flexllm_tp_alltoall(self._h, _ptr(t), _ptr(out), t[0].numel() * t.element_size(), _stream()))
+        return out
+
 
 class Model:
     """Whole-model runner (SpinQuant_Prefilling + SpinQuant_Decoding graphs). Weights are given as

@@ -129,3 +129,47 @@ def test_tp_ranks_sharing_one_gpu_match_oracle(world, cfg, mode, monkeypatch):
     for rank in range(world):
         assert np.array_equal(ret[f"tokens{rank}"], ref["tokens"]), f"rank {rank}: tokens differ"
     assert np.array_equal(ret["hidden"].view(np.uint32), ref["hidden"].view(np.uint32))
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_collectives_of_ranks_sharing_one_gpu(world):
+    """Every collective of the device-sharing group against numpy: all-reduce (sum, max), reduce-scatter, all-gather,
+    all-to-all, several in a row on one stream (the second rendezvous keeps a rank's next collective from overwriting
+    buffers its peers still have to read)."""
+    import threading
+    import flexllm_b200 as F
+    group = F.TensorParallel.local_group(world)
+    rng = np.random.default_rng(90)
+    n = 3000
+    a = rng.integers(-1000, 1000, (world, world, n)).astype(np.int32)         # [rank][block][n]
+    f = rng.standard_normal((world, n)).astype(np.float32)
+    ret = {}
+
+    def run(tp):
+        try:
+            torch.cuda.set_device(0)
+            r = tp.rank
+            mine = torch.from_numpy(a[r]).cuda()
+            ret[("rs", r)] = tp.reduce_scatter_s32(mine).cpu().numpy()
+            ret[("ar", r)] = tp.allreduce_s32(mine.clone()).cpu().numpy()
+            ret[("mx", r)] = tp.allreduce_max_f32(torch.from_numpy(f[r]).cuda()).cpu().numpy()
+            ret[("ag", r)] = tp.allgather(mine[0].contiguous()).cpu().numpy()
+            ret[("aa", r)] = tp.alltoall(mine).cpu().numpy()
+        except Exception as e:
+            ret[("error", tp.rank)] = repr(e)
+
+    threads = [threading.Thread(target=run, args=(tp,)) for tp in group]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for tp in group:
+        tp.close()
+    assert not [k for k in ret if k[0] == "error"], {k: v for k, v in ret.items() if k[0] == "error"}
+    total = a.sum(axis=0)
+    for r in range(world):
+        assert np.array_equal(ret[("rs", r)], total[r])
+        assert np.array_equal(ret[("ar", r)], total)
+        assert np.array_equal(ret[("mx", r)], f.max(axis=0))
+        assert np.array_equal(ret[("ag", r)], a[:, 0])
+        assert np.array_equal(ret[("aa", r)], a[:, r])
