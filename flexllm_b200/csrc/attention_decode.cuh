@@ -79,6 +79,29 @@ __device__ __forceinline__ void dec_attn_prefetch_l2(const KvLayer& cache, const
     }
 }
 
+// The same hint issued by a group of 128 threads (index `t`) with ONE dependent load per thread: thread t takes the lines
+// t % 6, t % 6 + 6, ... of page t / 6 (+ 21, + 42, ...), so that its page-table entry is read once and the prefetches
+// follow without further waits. Several groups of a CTA can serve different items side by side.
+__device__ __forceinline__ void dec_attn_prefetch_l2_g128(const KvLayer& cache, const int32_t* __restrict__ page_table, int max_pages,
+                                                          const int32_t* __restrict__ ctx, int HKV, int hkv, int b, int t) {
+    int npages = (ctx[b] + 1 + PAGE - 1) / PAGE;
+    npages = npages < 0 ? 0 : (npages > max_pages ? max_pages : npages);
+    const int sub = t % 6;
+    for (int p = t / 6; p < npages; p += 21) {
+        if (t >= 126) break;                                   // threads 126, 127 have no page in this layout
+        const long pg = page_table[(long)b * max_pages + p];
+        const long base = pg * HKV + hkv;
+        for (int j = sub; j < 68; j += 6) {
+            const void* line;
+            if (j < 32) line = cache.k + base * (long)(64 * PAGE) + (long)j * 128;
+            else if (j < 64) line = cache.v + base * (long)(64 * PAGE) + (long)(j - 32) * 128;
+            else if (j < 66) line = cache.ks + base * PAGE + (j - 64) * 32;
+            else line = cache.vs + base * PAGE + (j - 66) * 32;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+        }
+    }
+}
+
 // Small per-call shared-memory state of dec_attn_fused_body (one per group of threads that runs it).
 struct DecAttnSmem {
     __align__(16) int8_t q_sm[4][64];

@@ -735,8 +735,16 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 // idle CTAs of the FHT phase, or from all CTAs at its start -- the page-table look-ups are a chain of
                 // latencies that then sits on that phase's critical path.)
                 const MegaLayer& nx = a.layers[p == 0 ? 0 : l + 1];
-                for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
-                    dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
+                if (ATT == 2 || (ATT == 0 && a.B * a.HKV <= G)) {
+                    // few items (at most one per CTA): groups of 128 threads with one dependent load per thread
+                    // (measured: 1.5 % off the step at 16 sequences; at 32 sequences the plain form below was 0.7 % faster)
+                    const int grp = tid >> 7, stride = G - a.B;
+                    for (int idx = cta - a.B + grp * stride; idx < a.B * a.HKV; idx += 4 * stride)
+                        dec_attn_prefetch_l2_g128(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid & 127);
+                } else {
+                    for (int idx = cta - a.B; idx < a.B * a.HKV; idx += G - a.B)
+                        dec_attn_prefetch_l2(nx.kv, a.page_table, a.max_pages, a.ctx, a.HKV, idx % a.HKV, idx / a.HKV, tid, MG_WORKERS);
+                }
             }
         } else if (k == PH_ATT) {
             DecAttnIn in;
