@@ -81,11 +81,16 @@ class ClockSampler:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
 
+    def mark(self):
+        """Start of the timed region: earlier samples are dropped."""
+        self._first = len(self.samples)
+        self.reasons.clear()
+
     def stop(self):
         self._stop.set()
         if self._thread:
             self._thread.join()
-        s = sorted(self.samples)
+        s = sorted(self.samples[getattr(self, "_first", 0):])
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
@@ -651,8 +656,11 @@ def gpu_arm(args):
         def timed(fn):
             for _ in range(args.warmup):
                 fn()
-            barrier()
+            # the sampler (NVML initialisation, thread start) comes up BEFORE the barrier: ranks that finish it at different
+            # times would otherwise charge their skew to the timed region of the first collective
             sampler = ClockSampler(local); sampler.start()
+            barrier()
+            sampler.mark()              # only samples taken from here on count
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
             l0 = lib.flexllm_launch_count()
             e0.record()
